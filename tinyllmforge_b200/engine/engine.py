@@ -1,0 +1,250 @@
+"""The engine: request intake, the schedule -> run -> postprocess loop, rank management.
+
+Parity: tinyvllm/engine/llm_engine.py:15-101 (``LLMEngine``): ``add_request``, ``step``,
+``is_finished``, ``generate`` (outputs sorted by request id as ``{"text", "token_ids"}`` dicts), ``exit``.
+
+Two ways to get tensor-parallel ranks:
+  * spawn mode (the reference's): ``LLM(..., tensor_parallel_size=N)`` in one process starts N-1
+    follower processes;
+  * launcher mode: when the process was started by ``torchrun`` (``WORLD_SIZE == tensor_parallel_size``)
+    every rank constructs ``LLM`` itself; rank 0 schedules, the others execute the published steps inside
+    their own ``generate`` call and return an empty list.
+
+A follower that dies or reports an error surfaces on rank 0 as ``EngineDeadError`` at the next step
+(the reference hangs in its next collective).
+"""
+from __future__ import annotations
+
+import atexit
+import json
+import os
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from ..config import Config
+from ..parallel.comm import TPGroup, find_free_port
+from ..sampling_params import SamplingParams
+from . import rpc
+from .request import Request
+from .scheduler import Scheduler
+from .stats import EngineStats
+from .step_batch import build_decode, build_prefill
+from .worker import Worker, follower_loop, follower_main
+
+
+class EngineDeadError(RuntimeError):
+    pass
+
+
+def _load_tokenizer(config: Config):
+    if config.skip_tokenizer_init:
+        return None
+    if not any(os.path.exists(os.path.join(config.model, f)) for f in ("tokenizer.json", "tokenizer.model", "vocab.json")):
+        return None
+    from transformers import AutoTokenizer
+    return AutoTokenizer.from_pretrained(config.model, use_fast=True)
+
+
+class LLMEngine:
+    def __init__(self, model: str, **kwargs):
+        self.config = config = Config.from_kwargs(model, **kwargs)
+        tp_size = config.tensor_parallel_size
+        self.procs: list = []
+        self.chan: rpc.ShmChannel | None = None
+        self.worker: Worker | None = None
+        self._closed = False
+        self.step_index = 0
+        self.stats = EngineStats()
+        self._trace = open(config.trace_path, "a") if config.trace_path else None
+
+        env_world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.launcher_mode = tp_size > 1 and env_world == tp_size and "RANK" in os.environ
+        self.rank = int(os.environ["RANK"]) if self.launcher_mode else 0
+        try:
+            if config.device == "cuda":
+                local = int(os.environ.get("LOCAL_RANK", self.rank)) if self.launcher_mode else 0
+                torch.cuda.set_device(local)
+            if tp_size == 1:
+                tp = TPGroup()
+            elif self.launcher_mode:
+                tp = TPGroup.init(self.rank, tp_size, config.device, "env://", config.rpc_timeout_s)
+                name = [rpc.unique_name()] if self.rank == 0 else [None]
+                if self.rank == 0:
+                    self.chan = rpc.ShmChannel(name[0], tp_size, 0, create=True, timeout_s=config.rpc_timeout_s)
+                dist.broadcast_object_list(name, src=0)
+                if self.rank != 0:
+                    self.chan = rpc.ShmChannel(name[0], tp_size, self.rank, create=False, timeout_s=config.rpc_timeout_s)
+            else:
+                name = rpc.unique_name()
+                self.chan = rpc.ShmChannel(name, tp_size, 0, create=True, timeout_s=config.rpc_timeout_s)
+                init_method = f"tcp://127.0.0.1:{find_free_port()}"
+                ctx = mp.get_context("spawn")
+                for r in range(1, tp_size):
+                    p = ctx.Process(target=follower_main, args=(config, r, name, init_method), daemon=True)
+                    p.start()
+                    self.procs.append(p)
+                self.chan.liveness = self._check_followers_alive
+                self.chan.wait_hello()
+                tp = TPGroup.init(0, tp_size, config.device, init_method, config.rpc_timeout_s)
+            self.tp = tp
+            self.worker = Worker(config, self.rank, tp)
+            tp.barrier()
+        except BaseException:
+            self.exit()
+            raise
+        self.tokenizer = _load_tokenizer(config) if self.rank == 0 else None
+        if self.tokenizer is not None and self.tokenizer.eos_token_id is not None:
+            config.eos = self.tokenizer.eos_token_id
+        self.scheduler = Scheduler(config) if self.rank == 0 else None
+        atexit.register(self.exit)
+
+    # ------------------------------------------------------------------ liveness
+    def _check_followers_alive(self) -> None:
+        for r, p in enumerate(self.procs, start=1):
+            if not p.is_alive():
+                msg = self.chan.read_error() if self.chan is not None else ""
+                raise EngineDeadError(f"tensor-parallel rank {r} exited with code {p.exitcode}. {msg}")
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, prompt: str | list[int], sampling_params: SamplingParams = SamplingParams()) -> int:
+        if isinstance(prompt, str):
+            if self.tokenizer is None:
+                raise ValueError("string prompts need tokenizer files in the model directory; pass token ids instead")
+            prompt = self.tokenizer.encode(prompt)
+        room = self.config.max_model_len - len(prompt)
+        if room < 1:
+            raise ValueError(f"prompt of {len(prompt)} tokens leaves no room under max_model_len={self.config.max_model_len}")
+        req = Request(prompt, sampling_params)
+        req.max_tokens = min(req.max_tokens, room)
+        self.scheduler.add(req)
+        return req.req_id
+
+    def is_finished(self) -> bool:
+        return self.scheduler.is_finished()
+
+    # ------------------------------------------------------------------ one step
+    def step(self):
+        """schedule -> build -> (publish) -> run -> postprocess.  Returns (finished, signed token count):
+        finished = [(req_id, completion_token_ids)], count > 0: prefill tokens, < 0: decode sequences."""
+        st = self.stats
+        t0 = time.perf_counter()
+        reqs, is_prefill = self.scheduler.schedule()
+        t1 = time.perf_counter()
+        bs = self.config.kvcache_block_size
+        if is_prefill:
+            sb = build_prefill(reqs, bs, self.step_index, self.config.seed)
+        else:
+            pad, width = self.worker.decode_padding(len(reqs))
+            sb = build_decode(reqs, bs, self.step_index, self.config.seed, pad_to=pad, table_width=width)
+        t2 = time.perf_counter()
+        try:
+            if self.chan is not None:
+                self.chan.publish(rpc.KIND_STEP, sb.buf[:sb.num_words])
+            token_ids = self.worker.run(sb)
+        except (rpc.PeerFailed, rpc.ChannelTimeout) as e:
+            raise EngineDeadError(str(e)) from e
+        t3 = time.perf_counter()
+        self.step_index += 1
+        finished = self.scheduler.postprocess(reqs, token_ids)
+        t4 = time.perf_counter()
+
+        st.schedule_s += t1 - t0
+        st.build_s += t2 - t1
+        st.run_s += t3 - t2
+        st.postprocess_s += t4 - t3
+        if is_prefill:
+            st.prefill_steps += 1
+            st.prefill_tokens += sb.num_tokens
+            st.prefix_cached_tokens += sum(r.num_cached_tokens for r in reqs)
+            count = sb.num_tokens
+        else:
+            st.decode_steps += 1
+            st.decode_tokens += len(reqs)
+            st.decode_batch_hist[len(reqs)] += 1
+            count = -len(reqs)
+        st.preemptions = self.scheduler.num_preemptions
+        st.finished_requests += len(finished)
+        if self._trace is not None:
+            self._trace.write(json.dumps({"step": self.step_index - 1, "prefill": is_prefill, "seqs": len(reqs),
+                                          "tokens": sb.num_tokens, "schedule_ms": (t1 - t0) * 1e3,
+                                          "build_ms": (t2 - t1) * 1e3, "run_ms": (t3 - t2) * 1e3,
+                                          "post_ms": (t4 - t3) * 1e3}) + "\n")
+        return [(r.req_id, r.completion_token_ids) for r in finished], count
+
+    # ------------------------------------------------------------------ generate
+    def generate(self, prompts: list[str] | list[list[int]], sampling_params: SamplingParams | list[SamplingParams],
+                 use_tqdm: bool = True) -> list[dict]:
+        if self.rank != 0:          # launcher mode: execute rank 0's steps until it marks the end of this call
+            kind = follower_loop(self.worker, self.chan)
+            if kind == rpc.KIND_EXIT:
+                self.exit()
+            return []
+        if not isinstance(sampling_params, list):
+            sampling_params = [sampling_params] * len(prompts)
+        if len(sampling_params) != len(prompts):
+            raise ValueError("need one SamplingParams per prompt")
+        pbar = None
+        if use_tqdm:
+            from tqdm.auto import tqdm
+            pbar = tqdm(total=len(prompts), desc="Generating", dynamic_ncols=True)
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, sampling_params)]
+        outputs: dict[int, list[int]] = {}
+        prefill_tps = decode_tps = 0.0
+        try:
+            while not self.is_finished():
+                t = time.perf_counter()
+                finished, count = self.step()
+                if pbar is not None:
+                    dt = time.perf_counter() - t
+                    if count > 0:
+                        prefill_tps = count / dt
+                    else:
+                        decode_tps = -count / dt
+                    pbar.set_postfix({"Prefill": f"{int(prefill_tps)}tok/s", "Decode": f"{int(decode_tps)}tok/s"})
+                    pbar.update(len(finished))
+                for req_id, toks in finished:
+                    outputs[req_id] = toks
+        finally:
+            if pbar is not None:
+                pbar.close()
+            if self.launcher_mode and self.chan is not None and not self._closed:
+                self.chan.publish(rpc.KIND_PING)
+        result = []
+        for req_id in ids:
+            toks = outputs[req_id]
+            text = self.tokenizer.decode(toks) if self.tokenizer is not None else ""
+            result.append({"text": text, "token_ids": toks})
+        return result
+
+    # ------------------------------------------------------------------ teardown
+    def exit(self) -> None:
+        if self._closed:
+            return
+        self._closed = True
+        try:
+            if self.chan is not None and self.rank == 0:
+                try:
+                    self.chan.publish(rpc.KIND_EXIT)
+                    self.chan.drain(timeout_s=10.0)
+                except Exception:
+                    pass
+            if self.worker is not None:
+                self.worker.close()
+                self.worker = None
+            for p in self.procs:
+                p.join(timeout=15.0)
+                if p.is_alive():
+                    p.terminate()
+            if getattr(self, "tp", None) is not None:
+                self.tp.close()
+        finally:
+            if self.chan is not None:
+                self.chan.close()
+                self.chan = None
+            if self._trace is not None:
+                self._trace.close()
+                self._trace = None

@@ -1,0 +1,141 @@
+"""Qwen3 dense decoder: owns the (sharded) weights and calls the op set in order.
+
+Parity: tinyvllm/models/qwen3.py:14-234.
+  * pre-norm decoder with the fused-residual convention: every norm after the first is
+    add + RMSNorm and also emits the updated residual stream (qwen3.py:164-172,194);
+  * attention = fused QKV projection -> per-head q/k RMSNorm over head_dim -> NeoX RoPE ->
+    paged causal GQA attention -> output projection (qwen3.py:74-96);
+  * MLP = fused gate/up projection -> SiLU(gate) * up -> down projection (qwen3.py:123-130);
+  * tied input/output embeddings share one tensor (qwen3.py:215-216);
+  * ``packed_modules_mapping`` names the Hugging Face tensors that are packed into one local
+    matrix (qwen3.py:200-206).
+
+The model is a thin object, not an ``nn.Module`` tree: the per-step attention metadata arrives as an
+explicit ``DeviceBatch`` argument (the reference passes it through a module-level global,
+tinyvllm/utils/context.py), and each block issues a handful of fused ops:
+
+    add_rms_norm -> qkv GEMM -> [q/k norm + RoPE + KV store] -> attention -> o GEMM (+ all-reduce)
+    add_rms_norm -> gate_up GEMM with SiLU*mul epilogue -> down GEMM (+ all-reduce)
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config import ModelConfig
+from ..ops import ref as ref_ops
+from ..parallel.comm import TPGroup
+from ..parallel.tp_layers import (MergedColumnParallelLinear, ParallelLMHead, QKVParallelLinear,
+                                  RowParallelLinear, VocabParallelEmbedding)
+
+
+class Qwen3DecoderLayer:
+    def __init__(self, cfg: ModelConfig, tp: TPGroup, dtype, device):
+        H, d = cfg.hidden_size, cfg.head_dim
+        self.qkv_proj = QKVParallelLinear(H, d, cfg.num_attention_heads, cfg.num_key_value_heads, tp, dtype, device,
+                                          bias=cfg.attention_bias)
+        self.o_proj = RowParallelLinear(cfg.num_attention_heads * d, H, tp, dtype, device)
+        self.gate_up_proj = MergedColumnParallelLinear(H, [cfg.intermediate_size] * 2, tp, dtype, device)
+        self.down_proj = RowParallelLinear(cfg.intermediate_size, H, tp, dtype, device)
+        self.input_layernorm = torch.ones(H, dtype=dtype, device=device)
+        self.post_attention_layernorm = torch.ones(H, dtype=dtype, device=device)
+        self.q_norm = torch.ones(d, dtype=dtype, device=device)
+        self.k_norm = torch.ones(d, dtype=dtype, device=device)
+
+
+class Qwen3ForCausalLM:
+    # Hugging Face tensor-name fragment -> (local packed module, shard id)
+    packed_modules_mapping = {
+        "q_proj": ("qkv_proj", "q"),
+        "k_proj": ("qkv_proj", "k"),
+        "v_proj": ("qkv_proj", "v"),
+        "gate_proj": ("gate_up_proj", 0),
+        "up_proj": ("gate_up_proj", 1),
+    }
+
+    def __init__(self, cfg: ModelConfig, tp: TPGroup | None = None, dtype=None, device="cpu", ops=None,
+                 max_positions: int | None = None):
+        self.cfg = cfg
+        self.tp = tp or TPGroup()
+        self.dtype = dtype or cfg.dtype
+        self.device = torch.device(device)
+        self.ops = ops or ref_ops.RefOps
+        tp_size = self.tp.size
+        self.num_heads = cfg.num_attention_heads // tp_size
+        self.num_kv_heads = cfg.num_key_value_heads // tp_size
+        self.head_dim = cfg.head_dim
+        self.scale = cfg.head_dim ** -0.5
+        self.eps = cfg.rms_norm_eps
+        self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, self.tp, self.dtype, self.device)
+        self.layers = [Qwen3DecoderLayer(cfg, self.tp, self.dtype, self.device) for _ in range(cfg.num_hidden_layers)]
+        self.norm = torch.ones(cfg.hidden_size, dtype=self.dtype, device=self.device)
+        self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, self.tp, self.dtype, self.device)
+        if cfg.tie_word_embeddings:
+            self.lm_head.weight = self.embed_tokens.weight
+        self.rope = ref_ops.rope_table(max_positions or cfg.max_position_embeddings, cfg.head_dim, cfg.rope_theta,
+                                       self.device)
+        self.kv_cache: torch.Tensor | None = None      # [L, 2, blocks, kv_heads, block_size, d]
+
+    # ------------------------------------------------------------------ parameters by Hugging Face name
+    def named_parameters(self):
+        yield "model.embed_tokens.weight", self.embed_tokens.weight, self.embed_tokens, None
+        for i, l in enumerate(self.layers):
+            p = f"model.layers.{i}."
+            for hf, (mod, sid) in self.packed_modules_mapping.items():
+                kind = "self_attn" if mod == "qkv_proj" else "mlp"
+                m = getattr(l, mod)
+                yield f"{p}{kind}.{hf}.weight", m.weight, m, sid
+                if m.bias is not None:
+                    yield f"{p}{kind}.{hf}.bias", m.bias, m, sid
+            yield p + "self_attn.o_proj.weight", l.o_proj.weight, l.o_proj, None
+            yield p + "mlp.down_proj.weight", l.down_proj.weight, l.down_proj, None
+            yield p + "self_attn.q_norm.weight", l.q_norm, None, None
+            yield p + "self_attn.k_norm.weight", l.k_norm, None, None
+            yield p + "input_layernorm.weight", l.input_layernorm, None, None
+            yield p + "post_attention_layernorm.weight", l.post_attention_layernorm, None, None
+        yield "model.norm.weight", self.norm, None, None
+        if not self.cfg.tie_word_embeddings:
+            yield "lm_head.weight", self.lm_head.weight, self.lm_head, None
+
+    def num_parameter_bytes(self) -> int:
+        seen, total = set(), 0
+        for _, t, _, _ in self.named_parameters():
+            if t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+        return total
+
+    def bind_kv_cache(self, kv_cache: torch.Tensor) -> None:
+        assert kv_cache.shape[0] == len(self.layers) and kv_cache.shape[1] == 2
+        self.kv_cache = kv_cache
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, batch) -> torch.Tensor:
+        """Hidden states ``[tokens, hidden]`` after the final norm."""
+        ops = self.ops
+        h = self.embed_tokens.forward(ops, batch.input_ids)
+        residual = None
+        for i, l in enumerate(self.layers):
+            x, residual = ops.add_rms_norm(h, residual, l.input_layernorm, self.eps)
+            qkv = l.qkv_proj.forward(ops, x)
+            kc, vc = self.kv_cache[i, 0], self.kv_cache[i, 1]
+            q = ops.qk_norm_rope_store(qkv, l.q_norm, l.k_norm, self.eps, self.rope, batch.positions,
+                                       batch.slot_mapping, kc, vc, self.num_heads, self.num_kv_heads, self.head_dim)
+            a = ops.attention(q, kc, vc, batch, self.scale)
+            h = l.o_proj.forward(ops, a)
+            x, residual = ops.add_rms_norm(h, residual, l.post_attention_layernorm, self.eps)
+            x = l.gate_up_proj.forward_silu_mul(ops, x)
+            h = l.down_proj.forward(ops, x)
+        x, _ = ops.add_rms_norm(h, residual, self.norm, self.eps)
+        return x
+
+    def compute_logits(self, hidden: torch.Tensor, batch) -> torch.Tensor:
+        """This rank's logits shard for the last token of every sequence: ``[seqs, vocab / tp]``."""
+        last = self.ops.select_rows(hidden, batch.last_index)
+        return self.lm_head.forward(self.ops, last)
+
+    def sample(self, logits: torch.Tensor, batch) -> torch.Tensor:
+        return self.ops.sample(logits, batch, self.lm_head.vocab_start, self.tp)
+
+    def step(self, batch) -> torch.Tensor:
+        """forward + logits + sampling: token ids for the first ``batch.num_seqs`` rows."""
+        return self.sample(self.compute_logits(self.forward(batch), batch), batch)
