@@ -1,0 +1,291 @@
+// Memory-bound ops of a decoder block as hand-written kernels: 16-byte accesses, fp32 math, one pass.
+//
+//   rms_norm / add_rms_norm     tinyvllm/layers/layernorm.py:21-45   (Inductor-generated there)
+//   qk_norm_rope_store          tinyvllm/models/qwen3.py:79-94 + tinyvllm/layers/rotary_embedding.py:42-57 +
+//                               tinyvllm/layers/attention.py:9-48: four launches there, one here
+//   silu_mul                    tinyvllm/layers/activation.py:11-14
+//   embedding (vocab shard)     tinyvllm/layers/embed_head.py:34-40
+//   gather_rows                 tinyvllm/layers/embed_head.py:60-62 (last token of every sequence)
+//
+// Rounding follows the PyTorch statement of each op in ops/ref.py so results match it bit for bit where
+// the order of fp32 additions allows.
+#include "../include/ptx.cuh"
+
+namespace forge {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < nw ? red[lane] : 0.f;
+  t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// ---------------------------------------------------------------------------------------------------------
+// y = rms_norm(x (+ residual)) * w ; residual <- x + residual (rounded to bf16).  One CTA per row; a row of
+// up to 4 * blockDim * 8 elements stays in registers between the two passes.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kNormMaxChunks = 4;
+
+template <bool kAdd>
+__global__ void __launch_bounds__(256) rms_norm_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ residual,
+                                                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                                                       int H, float eps) {
+  __shared__ float red[32];
+  const size_t row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
+  uint4* rr = kAdd ? reinterpret_cast<uint4*>(residual + row * H) : nullptr;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* yr = reinterpret_cast<uint4*>(y + row * H);
+  const int nvec = H >> 3;
+  float vals[kNormMaxChunks][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int c = 0; c < kNormMaxChunks; ++c) {
+    const int i = threadIdx.x + c * blockDim.x;
+    if (i < nvec) {
+      uint4 a = xr[i];
+      const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+      if constexpr (kAdd) {
+        uint4 b = rr[i];
+        const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+        uint32_t sw[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float lo = bf16_round(bf16_lo(aw[j]) + bf16_lo(bw[j]));
+          const float hi = bf16_round(bf16_hi(aw[j]) + bf16_hi(bw[j]));
+          vals[c][2 * j] = lo;
+          vals[c][2 * j + 1] = hi;
+          sw[j] = pack_bf16x2(lo, hi);
+        }
+        rr[i] = make_uint4(sw[0], sw[1], sw[2], sw[3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          vals[c][2 * j] = bf16_lo(aw[j]);
+          vals[c][2 * j + 1] = bf16_hi(aw[j]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += vals[c][j] * vals[c][j];
+    }
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / static_cast<float>(H) + eps);
+#pragma unroll
+  for (int c = 0; c < kNormMaxChunks; ++c) {
+    const int i = threadIdx.x + c * blockDim.x;
+    if (i < nvec) {
+      uint4 wv = wr[i];
+      const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = bf16_round(vals[c][2 * j] * inv) * bf16_lo(ww[j]);
+        const float hi = bf16_round(vals[c][2 * j + 1] * inv) * bf16_hi(ww[j]);
+        o[j] = pack_bf16x2(lo, hi);
+      }
+      yr[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+extern "C" int forge_rms_norm(const void* x, void* residual, const void* w, void* y, int rows, int H, float eps,
+                              cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if ((H & 7) || H > kNormMaxChunks * 256 * 8) return -1;
+  int threads = ((H >> 3) + kNormMaxChunks - 1) / kNormMaxChunks;
+  threads = ((threads + 31) / 32) * 32;
+  if (threads < 32) threads = 32;
+  if (threads > 256) threads = 256;
+  if (residual != nullptr)
+    rms_norm_kernel<true><<<rows, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(residual),
+                                                        static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), H, eps);
+  else
+    rms_norm_kernel<false><<<rows, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), nullptr,
+                                                         static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), H, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Fused split + per-head RMSNorm(q, k) + NeoX RoPE(q, k) + paged KV store.
+// One warp per (token, head) of the packed qkv row [q heads | k heads | v heads].
+//   q head: normalise, rotate, write q_out[token, head, :]
+//   k head: normalise, rotate, write k_cache[slot];  v head: copy to v_cache[slot]
+// Cache layout [blocks, kv_heads, block_size, D]; slot = block * block_size + offset; slot < 0 is skipped,
+// slot >= num_slots is skipped and reported in the status word.
+// Lane l owns elements {l*E .. l*E+E-1} of the first half and the same of the second half (E = D / 64),
+// i.e. exactly the pairs the rotation mixes.
+// ---------------------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(
+    const __nv_bfloat16* __restrict__ qkv, int ld_qkv, const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
+    float eps, const float* __restrict__ rope, int rope_rows, const int* __restrict__ positions, const int* __restrict__ slots,
+    __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+    int T, int nq, int nkv, int block_size, long long num_slots, int do_rope, unsigned* status) {
+  constexpr int E = D / 64;           // elements per lane per half
+  static_assert(D == 64 || D == 128 || D == 256, "head_dim");
+  const int heads = nq + 2 * nkv;
+  const long long wid = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wid >= static_cast<long long>(T) * heads) return;
+  const int lane = threadIdx.x & 31;
+  const int t = static_cast<int>(wid / heads);
+  const int h = static_cast<int>(wid % heads);
+  const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * ld_qkv + static_cast<size_t>(h) * D;
+
+  float a[E], b[E];   // first-half and second-half elements
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    a[e] = __bfloat162float(src[lane * E + e]);
+    b[e] = __bfloat162float(src[D / 2 + lane * E + e]);
+  }
+  const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+  if (is_q || is_k) {
+    const __nv_bfloat16* w = is_q ? qw : kw;
+    if (w != nullptr) {
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < E; ++e) ss += a[e] * a[e] + b[e] * b[e];
+      const float inv = rsqrtf(warp_sum(ss) / static_cast<float>(D) + eps);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        a[e] = bf16_round(bf16_round(a[e] * inv) * __bfloat162float(w[lane * E + e]));
+        b[e] = bf16_round(bf16_round(b[e] * inv) * __bfloat162float(w[D / 2 + lane * E + e]));
+      }
+    }
+    if (do_rope) {
+      int pos = positions[t];
+      pos = pos < 0 ? 0 : (pos >= rope_rows ? rope_rows - 1 : pos);
+      const float* cs = rope + static_cast<size_t>(pos) * D;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const float c = cs[lane * E + e], s = cs[D / 2 + lane * E + e];
+        const float x1 = a[e], x2 = b[e];
+        a[e] = x1 * c - x2 * s;
+        b[e] = x2 * c + x1 * s;
+      }
+    }
+  }
+  __nv_bfloat16* dst;
+  if (is_q) {
+    dst = q_out + (static_cast<size_t>(t) * nq + h) * D;
+  } else {
+    const long long slot = slots[t];
+    if (slot < 0) return;
+    if (slot >= num_slots) {
+      if (lane == 0) set_status(status, kStatusBadIndex);
+      return;
+    }
+    const int kvh = is_k ? h - nq : h - nq - nkv;
+    const long long blk = slot / block_size, off = slot % block_size;
+    dst = (is_k ? k_cache : v_cache) + ((blk * nkv + kvh) * block_size + off) * D;
+  }
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    dst[lane * E + e] = __float2bfloat16_rn(a[e]);
+    dst[D / 2 + lane * E + e] = __float2bfloat16_rn(b[e]);
+  }
+}
+
+extern "C" int forge_qk_norm_rope_store(const void* qkv, int ld_qkv, const void* qw, const void* kw, float eps,
+                                        const float* rope, int rope_rows, const int* positions, const int* slots,
+                                        void* q_out, void* k_cache, void* v_cache, int T, int nq, int nkv, int D,
+                                        int block_size, long long num_slots, int do_rope, unsigned* status,
+                                        cudaStream_t stream) {
+  if (T <= 0) return 0;
+  const long long warps = static_cast<long long>(T) * (nq + 2 * nkv);
+  const int grid = static_cast<int>((warps + 3) / 4);
+#define FORGE_QK(DD)                                                                                                  \
+  qk_norm_rope_store_kernel<DD><<<grid, 128, 0, stream>>>(                                                            \
+      static_cast<const __nv_bfloat16*>(qkv), ld_qkv, static_cast<const __nv_bfloat16*>(qw),                         \
+      static_cast<const __nv_bfloat16*>(kw), eps, rope, rope_rows, positions, slots, static_cast<__nv_bfloat16*>(q_out), \
+      static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), T, nq, nkv, block_size, num_slots, \
+      do_rope, status)
+  if (D == 128) FORGE_QK(128);
+  else if (D == 64) FORGE_QK(64);
+  else if (D == 256) FORGE_QK(256);
+  else return -1;
+#undef FORGE_QK
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// out[t, :I] = silu(x[t, :I]) * x[t, I:2I]
+// ---------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
+                                                       long long rows, int I) {
+  const int nvec = I >> 3;
+  const long long total = rows * nvec;
+  for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = idx / nvec;
+    const int v = static_cast<int>(idx % nvec);
+    const uint4 g = reinterpret_cast<const uint4*>(x + r * 2 * I)[v];
+    const uint4 u = reinterpret_cast<const uint4*>(x + r * 2 * I + I)[v];
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = pack_bf16x2(silu(bf16_lo(gw[j])) * bf16_lo(uw[j]), silu(bf16_hi(gw[j])) * bf16_hi(uw[j]));
+    reinterpret_cast<uint4*>(out + r * I)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+extern "C" int forge_silu_mul(const void* x, void* out, long long rows, int I, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (I & 7) return -1;
+  const long long total = rows * (I >> 3);
+  int grid = static_cast<int>((total + 255) / 256);
+  if (grid > 148 * 16) grid = 148 * 16;
+  silu_mul_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), rows, I);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Row gathers.  embedding: out[t] = id in [start, start + n) ? W[id - start] : 0.  gather_rows: out[s] = x[idx[s]].
+// ---------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ w,
+                                                        __nv_bfloat16* __restrict__ out, int H, int vocab_start, int vocab_n) {
+  const int t = blockIdx.x;
+  const int local = ids[t] - vocab_start;
+  const bool ok = local >= 0 && local < vocab_n;
+  const uint4* src = reinterpret_cast<const uint4*>(w + static_cast<size_t>(ok ? local : 0) * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H);
+  for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) dst[i] = ok ? src[i] : make_uint4(0, 0, 0, 0);
+}
+
+extern "C" int forge_embedding(const int* ids, const void* w, void* out, int T, int H, int vocab_start, int vocab_n,
+                               cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H & 7) return -1;
+  embedding_kernel<<<T, 128, 0, stream>>>(ids, static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(out), H,
+                                          vocab_start, vocab_n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+__global__ void __launch_bounds__(128) gather_rows_kernel(const int* __restrict__ idx, const __nv_bfloat16* __restrict__ x,
+                                                          __nv_bfloat16* __restrict__ out, int H, int x_rows) {
+  int r = idx[blockIdx.x];
+  r = r < 0 ? 0 : (r >= x_rows ? x_rows - 1 : r);
+  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(blockIdx.x) * H);
+  for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) dst[i] = src[i];
+}
+
+extern "C" int forge_gather_rows(const int* idx, const void* x, void* out, int S, int H, int x_rows, cudaStream_t stream) {
+  if (S <= 0) return 0;
+  if (H & 7) return -1;
+  gather_rows_kernel<<<S, 128, 0, stream>>>(idx, static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), H, x_rows);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+}  // namespace forge

@@ -1,0 +1,159 @@
+// Temperature sampling without a softmax and without materialising probabilities.
+//
+// The reference computes softmax(logits / T), divides by Exp(1) noise and takes the argmax
+// (tinyvllm/layers/sampler.py:13-21): eight ATen kernels over [rows, vocab] fp32.  Dividing by an
+// exponential and taking the argmax is the Gumbel-max trick, and the softmax normaliser is constant
+// per row, so   token = argmax_i ( logit_i / T  -  log(-log u_i) )   draws from the same distribution.
+// T == 0 selects plain argmax.
+//
+// u_i comes from Philox-4x32-10 keyed by the engine seed with counter (global vocab id / 4, row, step, 0),
+// lane = id % 4: a pure function of (seed, step, row, GLOBAL vocab id).  A vocabulary sharded over
+// tensor-parallel ranks therefore samples the same token as an unsharded one: each rank reduces its shard to
+// one (score, id) pair per row and only those pairs are merged (ops/ref.py gumbel_noise is the same function
+// on the CPU).
+//
+// Two kernels: partial argmax per (row, vocab slice), then a merge per row that can also fold in the pairs
+// of other ranks.
+#include "../include/ptx.cuh"
+
+namespace forge {
+
+__device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0, uint32_t k1,
+                                              uint32_t out[4]) {
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    const uint32_t n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+    c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+__device__ __forceinline__ float gumbel_from_bits(uint32_t bits) {
+  const float u = static_cast<float>(bits >> 8) * (1.0f / 16777216.0f) + (0.5f / 16777216.0f);
+  return -logf(-logf(u));
+}
+
+struct Best {
+  float v;
+  int i;
+};
+__device__ __forceinline__ Best better(Best a, Best b) {   // larger value wins; ties go to the smaller index
+  return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
+}
+__device__ __forceinline__ Best warp_best(Best x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Best y;
+    y.v = __shfl_xor_sync(0xffffffffu, x.v, o);
+    y.i = __shfl_xor_sync(0xffffffffu, x.i, o);
+    x = better(x, y);
+  }
+  return x;
+}
+
+constexpr int kSampleThreads = 256;
+
+// header: the packed step buffer's first words; [9] = step index, [10], [11] = seed low / high.
+__global__ void __launch_bounds__(kSampleThreads) sample_partial_kernel(
+    const __nv_bfloat16* __restrict__ logits, int ld, int vocab, int vocab_start, const float* __restrict__ temps,
+    const int* __restrict__ header, float* __restrict__ part_v, int* __restrict__ part_i, int nsplit) {
+  __shared__ float sv[kSampleThreads / 32];
+  __shared__ int si[kSampleThreads / 32];
+  const int row = blockIdx.y, split = blockIdx.x;
+  const float T = temps[row];
+  const bool greedy = !(T > 0.f);
+  const float inv_t = greedy ? 1.f : 1.f / T;
+  const uint32_t step = static_cast<uint32_t>(header[9]);
+  const uint32_t k0 = static_cast<uint32_t>(header[10]), k1 = static_cast<uint32_t>(header[11]);
+  // slice boundaries in groups of four ids, aligned on the GLOBAL id so one Philox call serves four ids
+  const int g_first = vocab_start >> 2, g_last = (vocab_start + vocab - 1) >> 2;
+  const int ngroups = g_last - g_first + 1;
+  const int per = (ngroups + nsplit - 1) / nsplit;
+  const int gb = g_first + split * per;
+  const int ge = min(gb + per, g_last + 1);
+  const __nv_bfloat16* lrow = logits + static_cast<size_t>(row) * ld;
+  Best best{-INFINITY, 0x7fffffff};
+  for (int g = gb + threadIdx.x; g < ge; g += kSampleThreads) {
+    uint32_t rnd[4] = {0, 0, 0, 0};
+    if (!greedy) philox4x32_10(static_cast<uint32_t>(g), static_cast<uint32_t>(row), step, 0u, k0, k1, rnd);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int id = g * 4 + j;
+      const int local = id - vocab_start;
+      if (local >= 0 && local < vocab) {
+        float s = __bfloat162float(lrow[local]) * inv_t;
+        if (!greedy) s += gumbel_from_bits(rnd[j]);
+        best = better(best, Best{s, id});
+      }
+    }
+  }
+  best = warp_best(best);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sv[warp] = best.v; si[warp] = best.i; }
+  __syncthreads();
+  if (warp == 0) {
+    Best b = lane < kSampleThreads / 32 ? Best{sv[lane], si[lane]} : Best{-INFINITY, 0x7fffffff};
+    b = warp_best(b);
+    if (lane == 0) {
+      part_v[static_cast<size_t>(row) * nsplit + split] = b.v;
+      part_i[static_cast<size_t>(row) * nsplit + split] = b.i;
+    }
+  }
+}
+
+// One warp per row merges `n` candidate pairs; writes the winning id (and value when out_v != nullptr).
+__global__ void __launch_bounds__(128) sample_merge_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int n,
+                                                           int rows, int* __restrict__ out_i, float* __restrict__ out_v) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  Best b{-INFINITY, 0x7fffffff};
+  for (int j = lane; j < n; j += 32) b = better(b, Best{part_v[static_cast<size_t>(row) * n + j], part_i[static_cast<size_t>(row) * n + j]});
+  b = warp_best(b);
+  if (lane == 0) {
+    out_i[row] = b.i;
+    if (out_v != nullptr) out_v[row] = b.v;
+  }
+}
+
+extern "C" int forge_sample_nsplit(int rows, int vocab) {
+  // enough CTAs to fill the GPU at small row counts, never fewer than ~2K ids per CTA
+  int want = (148 * 4 + rows - 1) / rows;
+  int cap = (vocab + 2047) / 2048;
+  int n = want < cap ? want : cap;
+  return n < 1 ? 1 : (n > 64 ? 64 : n);
+}
+
+// logits [rows, vocab] bf16 (row stride ld); part_* are scratch of rows * nsplit entries.
+extern "C" int forge_sample(const void* logits, int ld, int rows, int vocab, int vocab_start, const float* temps,
+                            const int* header, float* part_v, int* part_i, int nsplit, int* out_i, float* out_v,
+                            cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  dim3 grid(nsplit, rows);
+  sample_partial_kernel<<<grid, kSampleThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), ld, vocab, vocab_start,
+                                                             temps, header, part_v, part_i, nsplit);
+  sample_merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(part_v, part_i, nsplit, rows, out_i, out_v);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Merge pairs gathered from all ranks: vals/ids laid out [ranks, rows] -> transposed read.
+__global__ void __launch_bounds__(128) sample_merge_ranks_kernel(const float* __restrict__ vals, const int* __restrict__ ids, int ranks,
+                                                                 int rows, int* __restrict__ out_i) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  Best b{-INFINITY, 0x7fffffff};
+  for (int r = 0; r < ranks; ++r) b = better(b, Best{vals[static_cast<size_t>(r) * rows + row], ids[static_cast<size_t>(r) * rows + row]});
+  out_i[row] = b.i;
+}
+
+extern "C" int forge_sample_merge_ranks(const float* vals, const int* ids, int ranks, int rows, int* out_i, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  sample_merge_ranks_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(vals, ids, ranks, rows, out_i);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+}  // namespace forge

@@ -1,0 +1,237 @@
+// Python bindings: tensors in, raw pointers + the current CUDA stream out.  Every argument is checked here
+// (device, dtype, contiguity, shapes, alignment), so a malformed call raises in Python instead of reaching
+// a kernel.  No counterpart in the reference (it has no native code).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <cstdint>
+
+extern "C" {
+int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K, int epi,
+                    int force_mode, unsigned* status, cudaStream_t stream);
+int forge_rms_norm(const void* x, void* residual, const void* w, void* y, int rows, int H, float eps, cudaStream_t stream);
+int forge_qk_norm_rope_store(const void* qkv, int ld_qkv, const void* qw, const void* kw, float eps, const float* rope,
+                             int rope_rows, const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache,
+                             int T, int nq, int nkv, int D, int block_size, long long num_slots, int do_rope, unsigned* status,
+                             cudaStream_t stream);
+int forge_silu_mul(const void* x, void* out, long long rows, int I, cudaStream_t stream);
+int forge_embedding(const int* ids, const void* w, void* out, int T, int H, int vocab_start, int vocab_n, cudaStream_t stream);
+int forge_gather_rows(const int* idx, const void* x, void* out, int S, int H, int x_rows, cudaStream_t stream);
+int forge_sample_nsplit(int rows, int vocab);
+int forge_sample(const void* logits, int ld, int rows, int vocab, int vocab_start, const float* temps, const int* header,
+                 float* part_v, int* part_i, int nsplit, int* out_i, float* out_v, cudaStream_t stream);
+int forge_sample_merge_ranks(const float* vals, const int* ids, int ranks, int rows, int* out_i, cudaStream_t stream);
+int forge_decode_attention(const void* q, const void* kc, const void* vc, const int* bt, const int* lens, void* out,
+                           float* part_o, float* part_ml, int B, int nq, int nkv, int head_dim, int block_size, int table_width,
+                           int num_blocks, int chunk, int max_chunks, float scale, unsigned* status, cudaStream_t stream);
+int forge_prefill_attention(const void* q, const void* kc, const void* vc, const int* cu_q, const int* lens, const int* bt,
+                            void* out, int T, int num_seqs, int max_q, int nq, int nkv, int head_dim, int block_size,
+                            int table_width, int num_blocks, float scale, unsigned* status, cudaStream_t stream);
+}
+
+namespace {
+
+using torch::Tensor;
+
+#define CHECK_CUDA_CONTIG(t) TORCH_CHECK((t).is_cuda() && (t).is_contiguous(), #t " must be a contiguous CUDA tensor")
+#define CHECK_BF16(t) TORCH_CHECK((t).scalar_type() == at::kBFloat16, #t " must be bfloat16")
+#define CHECK_I32(t) TORCH_CHECK((t).scalar_type() == at::kInt, #t " must be int32")
+#define CHECK_F32(t) TORCH_CHECK((t).scalar_type() == at::kFloat, #t " must be float32")
+
+cudaStream_t stream_of(const Tensor& t) { return at::cuda::getCurrentCUDAStream(t.get_device()).stream(); }
+
+unsigned* status_ptr(const Tensor& status) {
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 1, "status must be a CUDA int32 tensor");
+  return reinterpret_cast<unsigned*>(status.data_ptr<int>());
+}
+
+void check(int rc, const char* what) { TORCH_CHECK(rc == 0, what, " failed with code ", rc); }
+
+// out[M, n_out] = epilogue(x[M, K] @ w[*, K]^T); epi 0: store, 1: silu(gate) * up with w = [2 * n_out, K].
+void gemm(const Tensor& x, const Tensor& w, Tensor& out, int64_t epi, int64_t force_mode, const Tensor& status) {
+  CHECK_BF16(x); CHECK_BF16(w); CHECK_BF16(out);
+  TORCH_CHECK(x.is_cuda() && w.is_cuda() && out.is_cuda(), "gemm: CUDA tensors expected");
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm: 2-D tensors expected");
+  TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && out.stride(1) == 1, "gemm: innermost stride must be 1");
+  const int64_t M = x.size(0), K = x.size(1);
+  TORCH_CHECK(w.size(1) == K, "gemm: K mismatch");
+  const int64_t n_out = epi == 1 ? w.size(0) / 2 : w.size(0);
+  TORCH_CHECK(out.size(0) == M && out.size(1) == n_out, "gemm: bad output shape");
+  const c10::cuda::CUDAGuard guard(x.device());
+  check(forge_gemm_bf16(x.data_ptr(), static_cast<int>(x.stride(0)), w.data_ptr(), static_cast<int>(w.stride(0)), out.data_ptr(),
+                        static_cast<int>(out.stride(0)), static_cast<int>(M), static_cast<int>(n_out), static_cast<int>(K),
+                        static_cast<int>(epi), static_cast<int>(force_mode), status_ptr(status), stream_of(x)),
+        "forge_gemm_bf16");
+}
+
+void rms_norm(const Tensor& x, const c10::optional<Tensor>& residual, const Tensor& w, Tensor& y, double eps) {
+  CHECK_CUDA_CONTIG(x); CHECK_CUDA_CONTIG(w); CHECK_CUDA_CONTIG(y);
+  CHECK_BF16(x); CHECK_BF16(w); CHECK_BF16(y);
+  const int64_t H = x.size(-1), rows = x.numel() / H;
+  TORCH_CHECK(w.numel() == H && y.numel() == x.numel(), "rms_norm: shape mismatch");
+  void* res = nullptr;
+  if (residual.has_value()) {
+    CHECK_CUDA_CONTIG(*residual); CHECK_BF16(*residual);
+    TORCH_CHECK(residual->numel() == x.numel(), "rms_norm: residual shape mismatch");
+    res = residual->data_ptr();
+  }
+  const c10::cuda::CUDAGuard guard(x.device());
+  check(forge_rms_norm(x.data_ptr(), res, w.data_ptr(), y.data_ptr(), static_cast<int>(rows), static_cast<int>(H),
+                       static_cast<float>(eps), stream_of(x)),
+        "forge_rms_norm");
+}
+
+void qk_norm_rope_store(const Tensor& qkv, const c10::optional<Tensor>& qw, const c10::optional<Tensor>& kw, double eps,
+                        const Tensor& rope, const Tensor& positions, const Tensor& slots, Tensor& q_out, Tensor& k_cache,
+                        Tensor& v_cache, int64_t nq, int64_t nkv, bool do_rope, const Tensor& status) {
+  CHECK_BF16(qkv); CHECK_CUDA_CONTIG(q_out); CHECK_BF16(q_out);
+  CHECK_CUDA_CONTIG(k_cache); CHECK_CUDA_CONTIG(v_cache); CHECK_BF16(k_cache); CHECK_BF16(v_cache);
+  CHECK_CUDA_CONTIG(rope); CHECK_F32(rope); CHECK_CUDA_CONTIG(positions); CHECK_I32(positions);
+  CHECK_CUDA_CONTIG(slots); CHECK_I32(slots);
+  TORCH_CHECK(qkv.is_cuda() && qkv.dim() == 2 && qkv.stride(1) == 1, "qkv must be [T, (nq + 2 nkv) * D]");
+  TORCH_CHECK(k_cache.dim() == 4 && v_cache.sizes() == k_cache.sizes(), "caches must be [blocks, kv_heads, block_size, D]");
+  const int64_t T = qkv.size(0), D = k_cache.size(3), bs = k_cache.size(2);
+  TORCH_CHECK(qkv.size(1) == (nq + 2 * nkv) * D && k_cache.size(1) == nkv, "qk_norm_rope_store: head layout mismatch");
+  TORCH_CHECK(positions.numel() >= T && slots.numel() >= T && q_out.numel() == T * nq * D, "qk_norm_rope_store: length mismatch");
+  TORCH_CHECK(rope.dim() == 2 && rope.size(1) == D, "rope table must be [positions, D]");
+  const void* qwp = nullptr;
+  const void* kwp = nullptr;
+  if (qw.has_value()) { CHECK_CUDA_CONTIG(*qw); CHECK_BF16(*qw); TORCH_CHECK(qw->numel() == D); qwp = qw->data_ptr(); }
+  if (kw.has_value()) { CHECK_CUDA_CONTIG(*kw); CHECK_BF16(*kw); TORCH_CHECK(kw->numel() == D); kwp = kw->data_ptr(); }
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  check(forge_qk_norm_rope_store(qkv.data_ptr(), static_cast<int>(qkv.stride(0)), qwp, kwp, static_cast<float>(eps),
+                                 rope.data_ptr<float>(), static_cast<int>(rope.size(0)), positions.data_ptr<int>(),
+                                 slots.data_ptr<int>(), q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                 static_cast<int>(T), static_cast<int>(nq), static_cast<int>(nkv), static_cast<int>(D),
+                                 static_cast<int>(bs), static_cast<long long>(k_cache.size(0)) * bs, do_rope ? 1 : 0,
+                                 status_ptr(status), stream_of(qkv)),
+        "forge_qk_norm_rope_store");
+}
+
+void silu_mul(const Tensor& x, Tensor& out) {
+  CHECK_CUDA_CONTIG(x); CHECK_CUDA_CONTIG(out); CHECK_BF16(x); CHECK_BF16(out);
+  const int64_t I = x.size(-1) / 2, rows = x.numel() / (2 * I);
+  TORCH_CHECK(out.numel() == rows * I, "silu_mul: bad output shape");
+  const c10::cuda::CUDAGuard guard(x.device());
+  check(forge_silu_mul(x.data_ptr(), out.data_ptr(), rows, static_cast<int>(I), stream_of(x)), "forge_silu_mul");
+}
+
+void embedding(const Tensor& ids, const Tensor& w, Tensor& out, int64_t vocab_start) {
+  CHECK_CUDA_CONTIG(ids); CHECK_I32(ids); CHECK_CUDA_CONTIG(w); CHECK_BF16(w); CHECK_CUDA_CONTIG(out); CHECK_BF16(out);
+  const int64_t T = ids.numel(), H = w.size(1);
+  TORCH_CHECK(out.numel() == T * H, "embedding: bad output shape");
+  const c10::cuda::CUDAGuard guard(w.device());
+  check(forge_embedding(ids.data_ptr<int>(), w.data_ptr(), out.data_ptr(), static_cast<int>(T), static_cast<int>(H),
+                        static_cast<int>(vocab_start), static_cast<int>(w.size(0)), stream_of(w)),
+        "forge_embedding");
+}
+
+void gather_rows(const Tensor& idx, const Tensor& x, Tensor& out) {
+  CHECK_CUDA_CONTIG(idx); CHECK_I32(idx); CHECK_CUDA_CONTIG(x); CHECK_BF16(x); CHECK_CUDA_CONTIG(out); CHECK_BF16(out);
+  const int64_t S = idx.numel(), H = x.size(1);
+  TORCH_CHECK(out.numel() == S * H, "gather_rows: bad output shape");
+  const c10::cuda::CUDAGuard guard(x.device());
+  check(forge_gather_rows(idx.data_ptr<int>(), x.data_ptr(), out.data_ptr(), static_cast<int>(S), static_cast<int>(H),
+                          static_cast<int>(x.size(0)), stream_of(x)),
+        "forge_gather_rows");
+}
+
+int64_t sample_nsplit(int64_t rows, int64_t vocab) { return forge_sample_nsplit(static_cast<int>(rows), static_cast<int>(vocab)); }
+
+// logits [rows, vocab] bf16; header = first words of the packed step buffer (step index, seed) on the device.
+void sample(const Tensor& logits, int64_t vocab_start, const Tensor& temps, const Tensor& header, Tensor& part_v, Tensor& part_i,
+            Tensor& out_i, const c10::optional<Tensor>& out_v) {
+  CHECK_BF16(logits); CHECK_CUDA_CONTIG(temps); CHECK_F32(temps); CHECK_CUDA_CONTIG(header); CHECK_I32(header);
+  CHECK_CUDA_CONTIG(part_v); CHECK_F32(part_v); CHECK_CUDA_CONTIG(part_i); CHECK_I32(part_i); CHECK_CUDA_CONTIG(out_i); CHECK_I32(out_i);
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1, "logits must be [rows, vocab]");
+  const int64_t rows = logits.size(0), vocab = logits.size(1);
+  TORCH_CHECK(temps.numel() >= rows && out_i.numel() >= rows && header.numel() >= 12, "sample: length mismatch");
+  TORCH_CHECK(part_v.numel() == part_i.numel() && part_v.numel() % rows == 0 && part_v.numel() >= rows, "sample: bad scratch");
+  const int nsplit = static_cast<int>(part_v.numel() / rows);
+  float* ov = nullptr;
+  if (out_v.has_value()) { CHECK_CUDA_CONTIG(*out_v); CHECK_F32(*out_v); TORCH_CHECK(out_v->numel() >= rows); ov = out_v->data_ptr<float>(); }
+  const c10::cuda::CUDAGuard guard(logits.device());
+  check(forge_sample(logits.data_ptr(), static_cast<int>(logits.stride(0)), static_cast<int>(rows), static_cast<int>(vocab),
+                     static_cast<int>(vocab_start), temps.data_ptr<float>(), header.data_ptr<int>(), part_v.data_ptr<float>(),
+                     part_i.data_ptr<int>(), nsplit, out_i.data_ptr<int>(), ov, stream_of(logits)),
+        "forge_sample");
+}
+
+void sample_merge_ranks(const Tensor& vals, const Tensor& ids, Tensor& out_i) {
+  CHECK_CUDA_CONTIG(vals); CHECK_F32(vals); CHECK_CUDA_CONTIG(ids); CHECK_I32(ids); CHECK_CUDA_CONTIG(out_i); CHECK_I32(out_i);
+  TORCH_CHECK(vals.dim() == 2 && ids.sizes() == vals.sizes() && out_i.numel() >= vals.size(1), "sample_merge_ranks: shapes");
+  const c10::cuda::CUDAGuard guard(vals.device());
+  check(forge_sample_merge_ranks(vals.data_ptr<float>(), ids.data_ptr<int>(), static_cast<int>(vals.size(0)),
+                                 static_cast<int>(vals.size(1)), out_i.data_ptr<int>(), stream_of(vals)),
+        "forge_sample_merge_ranks");
+}
+
+void decode_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_tables,
+                      const Tensor& context_lens, Tensor& out, const c10::optional<Tensor>& part_o,
+                      const c10::optional<Tensor>& part_ml, int64_t chunk, int64_t max_chunks, double scale, const Tensor& status) {
+  CHECK_CUDA_CONTIG(q); CHECK_BF16(q); CHECK_CUDA_CONTIG(k_cache); CHECK_BF16(k_cache); CHECK_CUDA_CONTIG(v_cache); CHECK_BF16(v_cache);
+  CHECK_CUDA_CONTIG(block_tables); CHECK_I32(block_tables); CHECK_CUDA_CONTIG(context_lens); CHECK_I32(context_lens);
+  CHECK_CUDA_CONTIG(out); CHECK_BF16(out);
+  TORCH_CHECK(q.dim() == 3 && k_cache.dim() == 4 && v_cache.sizes() == k_cache.sizes() && block_tables.dim() == 2, "decode_attention: ranks");
+  const int64_t B = q.size(0), nq = q.size(1), D = q.size(2), nkv = k_cache.size(1), bs = k_cache.size(2);
+  TORCH_CHECK(k_cache.size(3) == D && block_tables.size(0) >= B && context_lens.numel() >= B && out.numel() == B * nq * D,
+              "decode_attention: shape mismatch");
+  TORCH_CHECK(max_chunks * chunk >= 1, "decode_attention: bad chunking");
+  float* po = nullptr;
+  float* pml = nullptr;
+  if (max_chunks > 1) {
+    TORCH_CHECK(part_o.has_value() && part_ml.has_value(), "decode_attention: scratch needed when max_chunks > 1");
+    CHECK_CUDA_CONTIG(*part_o); CHECK_F32(*part_o); CHECK_CUDA_CONTIG(*part_ml); CHECK_F32(*part_ml);
+    TORCH_CHECK(part_o->numel() >= B * nq * max_chunks * D && part_ml->numel() >= B * nq * max_chunks * 2, "decode_attention: scratch too small");
+    po = part_o->data_ptr<float>();
+    pml = part_ml->data_ptr<float>();
+  }
+  const c10::cuda::CUDAGuard guard(q.device());
+  check(forge_decode_attention(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr<int>(),
+                               context_lens.data_ptr<int>(), out.data_ptr(), po, pml, static_cast<int>(B), static_cast<int>(nq),
+                               static_cast<int>(nkv), static_cast<int>(D), static_cast<int>(bs), static_cast<int>(block_tables.size(1)),
+                               static_cast<int>(k_cache.size(0)), static_cast<int>(chunk), static_cast<int>(max_chunks),
+                               static_cast<float>(scale), status_ptr(status), stream_of(q)),
+        "forge_decode_attention");
+}
+
+void prefill_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& cu_seqlens_q,
+                       const Tensor& context_lens, const Tensor& block_tables, Tensor& out, int64_t num_seqs, int64_t max_q,
+                       double scale, const Tensor& status) {
+  CHECK_CUDA_CONTIG(q); CHECK_BF16(q); CHECK_CUDA_CONTIG(k_cache); CHECK_BF16(k_cache); CHECK_CUDA_CONTIG(v_cache); CHECK_BF16(v_cache);
+  CHECK_CUDA_CONTIG(cu_seqlens_q); CHECK_I32(cu_seqlens_q); CHECK_CUDA_CONTIG(context_lens); CHECK_I32(context_lens);
+  CHECK_CUDA_CONTIG(block_tables); CHECK_I32(block_tables); CHECK_CUDA_CONTIG(out); CHECK_BF16(out);
+  TORCH_CHECK(q.dim() == 3 && k_cache.dim() == 4 && v_cache.sizes() == k_cache.sizes() && block_tables.dim() == 2, "prefill_attention: ranks");
+  const int64_t T = q.size(0), nq = q.size(1), D = q.size(2), nkv = k_cache.size(1), bs = k_cache.size(2);
+  TORCH_CHECK(cu_seqlens_q.numel() >= num_seqs + 1 && context_lens.numel() >= num_seqs && block_tables.size(0) >= num_seqs &&
+                  out.numel() == T * nq * D && k_cache.size(3) == D,
+              "prefill_attention: shape mismatch");
+  TORCH_CHECK((reinterpret_cast<uintptr_t>(q.data_ptr()) & 15) == 0 && (reinterpret_cast<uintptr_t>(k_cache.data_ptr()) & 15) == 0 &&
+                  (reinterpret_cast<uintptr_t>(v_cache.data_ptr()) & 15) == 0,
+              "prefill_attention: 16-byte alignment needed");
+  const c10::cuda::CUDAGuard guard(q.device());
+  check(forge_prefill_attention(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), cu_seqlens_q.data_ptr<int>(),
+                                context_lens.data_ptr<int>(), block_tables.data_ptr<int>(), out.data_ptr(), static_cast<int>(T),
+                                static_cast<int>(num_seqs), static_cast<int>(max_q), static_cast<int>(nq), static_cast<int>(nkv),
+                                static_cast<int>(D), static_cast<int>(bs), static_cast<int>(block_tables.size(1)),
+                                static_cast<int>(k_cache.size(0)), static_cast<float>(scale), status_ptr(status), stream_of(q)),
+        "forge_prefill_attention");
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "tinyllmforge_b200 sm_100a kernels";
+  m.def("gemm", &gemm);
+  m.def("rms_norm", &rms_norm);
+  m.def("qk_norm_rope_store", &qk_norm_rope_store);
+  m.def("silu_mul", &silu_mul);
+  m.def("embedding", &embedding);
+  m.def("gather_rows", &gather_rows);
+  m.def("sample_nsplit", &sample_nsplit);
+  m.def("sample", &sample);
+  m.def("sample_merge_ranks", &sample_merge_ranks);
+  m.def("decode_attention", &decode_attention);
+  m.def("prefill_attention", &prefill_attention);
+}

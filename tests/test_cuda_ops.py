@@ -1,0 +1,232 @@
+"""Every sm_100a kernel against the plain-PyTorch fp32 statement of the same op (ops/ref.py)."""
+import math
+
+import pytest
+import torch
+
+from tinyllmforge_b200.ops import ref
+
+pytestmark = pytest.mark.gpu
+
+BF = torch.bfloat16
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from tinyllmforge_b200.ops.cuda import CudaOps
+    o = CudaOps()
+    yield o
+    o.check_status()
+
+
+def _rand(*shape, scale=1.0, dtype=BF):
+    return (torch.randn(*shape, device="cuda", dtype=torch.float32) * scale).to(dtype)
+
+
+def _close(a, b, atol, rtol):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    bad = (err > tol).sum().item()
+    assert bad == 0, f"{bad}/{a.numel()} elements off; max err {err.max().item():.4g} (max ref {b.abs().max().item():.4g})"
+
+
+# ----------------------------------------------------------------------------- GEMM (tcgen05)
+@pytest.mark.parametrize("M,N,K,mode", [
+    (1, 128, 64, 0), (16, 256, 128, 0), (7, 1024, 1024, 0), (64, 4096, 1024, 0), (200, 1024, 2048, 0),
+    (256, 6144, 1024, 0), (128, 128, 64, 1), (300, 384, 256, 1), (1000, 1024, 1024, 0), (4096, 4096, 1024, 0),
+    (130, 200, 72, 1), (33, 136, 200, 2), (256, 1024, 3072, 2), (512, 2048, 1024, 2),
+])
+def test_gemm_matches_fp32(ops, M, N, K, mode):
+    torch.manual_seed(M * 7 + N)
+    x, w = _rand(M, K), _rand(N, K, scale=0.05)
+    out = ops.linear(x, w, force_mode=mode)
+    want = x.float() @ w.float().t()
+    _close(out, want, atol=2e-2, rtol=2e-2)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("M,I,K,mode", [(8, 256, 128, 0), (100, 3072, 1024, 0), (256, 1536, 1024, 2), (700, 3072, 1024, 0), (384, 512, 256, 1)])
+def test_gemm_silu_mul_epilogue(ops, M, I, K, mode):
+    torch.manual_seed(M + I)
+    x, w = _rand(M, K), _rand(2 * I, K, scale=0.05)
+    out = ops.linear_silu_mul(x, w, force_mode=mode)
+    gu = x.float() @ w.float().t()
+    want = torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]
+    _close(out, want, atol=2e-2, rtol=2e-2)
+    ops.check_status()
+
+
+def test_gemm_strided_input(ops):
+    big = _rand(64, 3 * 256)
+    x = big[:, 256:512]          # row stride 768, 16-byte aligned start
+    w = _rand(128, 256, scale=0.05)
+    _close(ops.linear(x, w), x.float() @ w.float().t(), 2e-2, 2e-2)
+
+
+# ----------------------------------------------------------------------------- norms / activation / gathers
+@pytest.mark.parametrize("rows,H", [(1, 1024), (37, 1024), (5, 4096), (3, 5120), (2, 256), (4, 8192)])
+def test_rms_norm(ops, rows, H):
+    x, w = _rand(rows, H), _rand(H, scale=0.3) + 1
+    _close(ops.rms_norm(x, w, 1e-6), ref.rms_norm(x, w, 1e-6), 1e-2, 1e-2)
+
+
+@pytest.mark.parametrize("rows,H", [(1, 1024), (33, 1024), (6, 4096), (3, 5120)])
+def test_add_rms_norm(ops, rows, H):
+    x, r, w = _rand(rows, H), _rand(rows, H), _rand(H, scale=0.3) + 1
+    want_y, want_r = ref.add_rms_norm(x, r, w, 1e-6)
+    r2 = r.clone()
+    y, r_out = ops.add_rms_norm(x, r2, w, 1e-6)
+    assert r_out.data_ptr() == r2.data_ptr()
+    assert torch.equal(r_out, want_r)
+    _close(y, want_y, 1e-2, 1e-2)
+
+
+def test_silu_mul(ops):
+    x = _rand(77, 2 * 3072, scale=2.0)
+    _close(ops.silu_mul(x), ref.silu_mul(x), 1e-2, 1e-2)
+
+
+def test_embedding_shard_and_gather(ops):
+    w = _rand(1000, 1024)
+    ids = torch.tensor([0, 999, 1000, 1500, 2000, 1234], dtype=torch.int32, device="cuda")
+    got = ops.embedding(ids, w, 1000)
+    assert torch.equal(got, ref.embedding(ids, w, 1000))
+    idx = torch.tensor([5, 0, 3], dtype=torch.int32, device="cuda")
+    assert torch.equal(ops.select_rows(got, idx), got[idx.long()])
+
+
+# ----------------------------------------------------------------------------- q/k norm + rope + KV store
+@pytest.mark.parametrize("T,nq,nkv,bs", [(1, 16, 8, 256), (50, 16, 8, 16), (9, 4, 1, 64)])
+def test_qk_norm_rope_store(ops, T, nq, nkv, bs):
+    D, nblk = 128, 8
+    qkv = _rand(T, (nq + 2 * nkv) * D)
+    qw, kw = _rand(D, scale=0.2) + 1, _rand(D, scale=0.2) + 1
+    table = ref.rope_table(4096, D, 1e6, "cuda")
+    pos = torch.randint(0, 4096, (T,), dtype=torch.int32, device="cuda")
+    slots = torch.randperm(nblk * bs, device="cuda")[:T].to(torch.int32)
+    if T > 2:
+        slots[1] = -1
+    kc, vc = torch.zeros(nblk, nkv, bs, D, dtype=BF, device="cuda"), torch.zeros(nblk, nkv, bs, D, dtype=BF, device="cuda")
+    kc2, vc2 = kc.clone(), vc.clone()
+    q = ops.qk_norm_rope_store(qkv, qw, kw, 1e-6, table, pos, slots, kc, vc, nq, nkv, D)
+    q_want = ref.qk_norm_rope_store(qkv, qw, kw, 1e-6, table, pos, slots, kc2, vc2, nq, nkv, D)
+    _close(q, q_want, 2e-2, 2e-2)
+    _close(kc, kc2, 2e-2, 2e-2)
+    assert torch.equal(vc, vc2)
+    ops.check_status()
+
+
+# ----------------------------------------------------------------------------- attention
+class _Batch:
+    pass
+
+
+def _paged_case(q_lens, k_lens, nq, nkv, bs, seed=0):
+    torch.manual_seed(seed)
+    D = 128
+    S = len(q_lens)
+    nblk_per = [-(-k // bs) for k in k_lens]
+    total = sum(nblk_per) + 3
+    perm = torch.randperm(total).tolist()
+    width = max(nblk_per) + 1
+    bt = torch.full((S, width), -1, dtype=torch.int32)
+    p = 0
+    for s, n in enumerate(nblk_per):
+        bt[s, :n] = torch.tensor(perm[p:p + n], dtype=torch.int32)
+        p += n
+    kc, vc = _rand(total, nkv, bs, D), _rand(total, nkv, bs, D)
+    T = sum(q_lens)
+    q = _rand(T, nq, D)
+    b = _Batch()
+    b.cu_seqlens_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    b.context_lens = torch.tensor(k_lens, dtype=torch.int32, device="cuda")
+    b.block_tables = bt.cuda()
+    b.num_seqs = b.padded_seqs = S
+    b.max_seqlen_q, b.max_seqlen_k = max(q_lens), max(k_lens)
+    b.table_width = width
+    return q, kc, vc, b
+
+
+@pytest.mark.parametrize("k_lens,nq,nkv,bs", [
+    ([1], 16, 8, 256), ([5, 300, 64, 1000], 16, 8, 256), ([17, 33, 250], 8, 2, 16), ([700, 2011, 129], 32, 8, 256),
+    ([40, 90], 8, 8, 32), ([513, 77], 8, 1, 64),
+])
+def test_decode_attention(ops, k_lens, nq, nkv, bs):
+    q, kc, vc, b = _paged_case([1] * len(k_lens), k_lens, nq, nkv, bs)
+    b.is_prefill = False
+    got = ops.attention(q, kc, vc, b, 128 ** -0.5)
+    want = ref.attention(q, kc, vc, b.cu_seqlens_q, b.context_lens, b.block_tables, 128 ** -0.5, b.num_seqs)
+    _close(got, want, 2e-2, 2e-2)
+    ops.check_status()
+
+
+def test_decode_attention_padding_rows(ops):
+    q, kc, vc, b = _paged_case([1, 1, 1], [100, 0, 7], 16, 8, 256)
+    b.is_prefill = False
+    got = ops.attention(q, kc, vc, b, 128 ** -0.5)
+    assert torch.count_nonzero(got[1]) == 0
+    want = ref.attention(q, kc, vc, b.cu_seqlens_q, b.context_lens, b.block_tables, 128 ** -0.5, 3)
+    _close(got[[0, 2]], want[[0, 2]], 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("q_lens,k_lens,nq,nkv,bs", [
+    ([64], [64], 16, 8, 256), ([1, 100, 257], [1, 100, 257], 16, 8, 256), ([30, 70], [286, 70], 8, 2, 256),
+    ([50, 200], [50, 200], 4, 4, 16), ([10], [522], 8, 1, 32), ([1000], [1000], 2, 1, 256),
+])
+def test_prefill_attention(ops, q_lens, k_lens, nq, nkv, bs):
+    q, kc, vc, b = _paged_case(q_lens, k_lens, nq, nkv, bs, seed=1)
+    b.is_prefill = True
+    got = ops.attention(q, kc, vc, b, 128 ** -0.5)
+    want = ref.attention(q, kc, vc, b.cu_seqlens_q, b.context_lens, b.block_tables, 128 ** -0.5, b.num_seqs)
+    _close(got, want, 2e-2, 2e-2)
+    ops.check_status()
+
+
+# ----------------------------------------------------------------------------- sampler
+def _header(step, seed):
+    h = torch.zeros(16, dtype=torch.int32)
+    h[9], h[10], h[11] = step, seed & 0x7FFFFFFF, 0
+    return h.cuda()
+
+
+def test_sampler_greedy_and_gumbel_match_reference(ops):
+    torch.manual_seed(3)
+    rows, vocab = 6, 151936
+    logits = _rand(rows, vocab, scale=3.0)
+    temps = torch.tensor([0.0, 0.6, 1.0, 0.0, 2.0, 0.3], device="cuda")
+    ids, best = ops.sample_shard(logits, temps, _header(11, 1234), 0)
+    want_ids, want_best = ref.sample(logits.cpu(), temps.cpu(), 1234, 11, 0)
+    _close(best.cpu(), want_best, 1e-3, 1e-4)
+    assert torch.equal(ids.cpu().long()[[0, 3]], logits.float().argmax(-1).cpu()[[0, 3]])
+    # sampled rows: the chosen id must be (near-)optimal under the reference's perturbed scores
+    assert (ids.cpu().long() == want_ids).float().mean() >= 0.8
+
+
+def test_sampler_is_invariant_to_vocab_sharding(ops):
+    torch.manual_seed(4)
+    rows, vocab, tp = 5, 4096 * 4, 4
+    logits = _rand(rows, vocab, scale=2.0)
+    temps = torch.full((rows,), 0.8, device="cuda")
+    hdr = _header(5, 99)
+    full_ids, _ = ops.sample_shard(logits, temps, hdr, 0)
+    shard = vocab // tp
+    vals, ids = [], []
+    for r in range(tp):
+        i, v = ops.sample_shard(logits[:, r * shard:(r + 1) * shard], temps, hdr, r * shard)
+        ids.append(i)
+        vals.append(v)
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    ops.C.sample_merge_ranks(torch.stack(vals), torch.stack(ids), out)
+    assert torch.equal(out, full_ids)
+
+
+def test_sampler_distribution(ops):
+    """Empirical frequencies over many steps follow softmax(logits / T)."""
+    vocab, T, n = 16, 0.7, 4000
+    logits = torch.linspace(-2, 2, vocab, device="cuda").to(BF)[None].repeat(n, 1).contiguous()
+    temps = torch.full((n,), T, device="cuda")
+    ids, _ = ops.sample_shard(logits, temps, _header(1, 7), 0)
+    freq = torch.bincount(ids.long().cpu(), minlength=vocab).float() / n
+    want = torch.softmax(logits[0].float().cpu() / T, -1)
+    assert (freq - want).abs().max() < 0.03

@@ -70,7 +70,10 @@ class Worker:
         self.table_width = (config.max_model_len + self.block_size - 1) // self.block_size
         self.buckets = [] if (config.enforce_eager or not self.is_cuda) else graph_buckets(config.max_num_seqs)
         self.graphs: dict[int, object] = {}
-        self.step_ms: list[float] = []
+        self.graph_launches: dict[int, int] = {}
+        self.time_steps = bool(config.extra.get("device_timing", False))
+        self.num_steps = 0
+        self.reset_counters()
 
         if self.is_cuda:
             from ..ops.cuda import CudaOps
@@ -97,6 +100,16 @@ class Worker:
             self._allocate_kv_cache()
             if self.buckets:
                 self._capture_graphs()
+
+    def reset_counters(self) -> None:
+        """Zero the per-run measurements: device time of the steps (CUDA events), bytes staged in each
+        direction, and the number of this library's kernels launched (graph replays count their nodes)."""
+        self.device_ms = 0.0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.kernel_launches = 0
+        if getattr(self, "ops", None) is not None and hasattr(self.ops, "launches"):
+            self.ops.launches = 0
 
     # ------------------------------------------------------------------ KV cache
     def _kv_block_bytes(self) -> int:
@@ -170,21 +183,35 @@ class Worker:
     @torch.inference_mode()
     def run(self, sb: StepBatch) -> list[int]:
         """Execute one step; returns the sampled token of each of the ``num_seqs`` sequences."""
+        if not self.is_cuda:
+            return self.model.step(self._stage(sb))[:sb.num_seqs].tolist()
+        timed = self.time_steps
+        if timed:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
         batch = self._stage(sb)
         graph = None if sb.is_prefill else self.graphs.get(sb.padded_seqs)
         if graph is not None and sb.table_width == self.table_width:
             graph.replay()
             tokens = self.graph_tokens[sb.padded_seqs]
+            self.kernel_launches += self.graph_launches[sb.padded_seqs]
         else:
+            before = self.ops.launches
             tokens = self.model.step(batch)
-        if not self.is_cuda:
-            return tokens[:sb.num_seqs].tolist()
-        if self.rank != 0:
-            return []
+            self.kernel_launches += self.ops.launches - before
         out = self.host_tokens[:sb.num_seqs]
         out.copy_(tokens[:sb.num_seqs], non_blocking=True)
+        if timed:
+            e1.record()
         torch.cuda.current_stream().synchronize()
-        return out.tolist()
+        if timed:
+            self.device_ms += e0.elapsed_time(e1)
+        self.h2d_bytes += sb.nbytes
+        self.d2h_bytes += sb.num_seqs * 4
+        self.num_steps += 1
+        if sb.is_prefill or (self.num_steps & 127) == 0:
+            self.ops.check_status()
+        return out.tolist() if self.rank == 0 else []
 
     @torch.inference_mode()
     def _capture_graphs(self) -> None:
@@ -204,8 +231,10 @@ class Worker:
             self.model.step(batch)                       # warm-up outside capture
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
+            before = self.ops.launches
             with torch.cuda.graph(g, pool=pool):
                 self.graph_tokens[b] = self.model.step(batch)
+            self.graph_launches[b] = self.ops.launches - before
             pool = pool or g.pool()
             self.graphs[b] = g
         torch.cuda.synchronize()

@@ -1,0 +1,183 @@
+"""The op set on a B200: every call lands in a hand-written sm_100a kernel of ``tinyllmforge_b200._C``.
+
+There is no fallback: if the extension is missing or a kernel reports an error, the call raises.  The method
+names and argument meanings are those of ``ops.ref.RefOps`` (the PyTorch statement of each op, which is also the
+oracle the GPU tests compare against).
+
+Reference call sites replaced (all in tinyvllm/): layers/linear.py:83,181 (F.linear -> tcgen05 GEMM),
+layers/activation.py:11 (fused into the gate_up GEMM epilogue), layers/layernorm.py:21,33,
+layers/rotary_embedding.py:41 + layers/attention.py:9-48 + models/qwen3.py:79-90 (one fused kernel),
+layers/attention.py:101,108 (paged prefill / decode attention), layers/embed_head.py:34-70, layers/sampler.py:13-21.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config import Config
+from ..parallel.comm import TPGroup
+
+try:
+    from .. import _C
+except ImportError as e:  # pragma: no cover - exercised only on a broken install
+    _C = None
+    _IMPORT_ERROR = e
+
+STATUS_BITS = {1: "mbarrier wait ran out", 2: "peer flag wait ran out", 4: "slot or block id out of range",
+               8: "unsupported shape"}
+
+
+def require_ext():
+    if _C is None:
+        raise RuntimeError("tinyllmforge_b200._C is not built; run `python -m tinyllmforge_b200.build_ext` "
+                           f"(import error: {_IMPORT_ERROR})")
+    return _C
+
+
+def decode_chunking(batch: int, num_kv_heads: int, block_size: int, max_len: int) -> tuple[int, int]:
+    """(tokens per context chunk, number of chunks) for the split-KV decode kernel.
+
+    Small batches split the context finely so that all 148 SMs get work; large batches keep chunks long so
+    that the partial-merge traffic stays negligible.  Depends only on shapes known at graph-capture time."""
+    tile = min(block_size, 64)
+    ctas = batch * num_kv_heads
+    chunk = 1024 if ctas >= 1024 else 512 if ctas >= 256 else 256 if ctas >= 64 else 128 if ctas >= 16 else 64
+    chunk = max(tile, chunk)
+    return chunk, max(1, -(-max_len // chunk))
+
+
+class CudaOps:
+    name = "cuda"
+
+    def __init__(self, config: Config | None = None, tp: TPGroup | None = None, device=None, use_cublas_gemm: bool = False):
+        self.C = require_ext()
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.tp = tp or TPGroup()
+        self.max_model_len = config.max_model_len if config is not None else 4096
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self.use_cublas_gemm = use_cublas_gemm     # bring-up switch for tests; never set by the engine
+        self.launches = 0                          # kernels of this library launched so far
+
+    # ------------------------------------------------------------------ status word
+    def check_status(self) -> None:
+        """Raise if any kernel since the last check recorded an error (costs a device sync)."""
+        word = int(self.status[0].item())
+        if word:
+            self.status.zero_()
+            what = [txt for bit, txt in STATUS_BITS.items() if word & bit]
+            raise RuntimeError(f"a CUDA kernel reported: {', '.join(what) or hex(word)}")
+
+    # ------------------------------------------------------------------ GEMMs
+    def linear(self, x: torch.Tensor, w: torch.Tensor, force_mode: int = 0) -> torch.Tensor:
+        out = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
+        if self.use_cublas_gemm:
+            return torch.matmul(x, w.t(), out=out)
+        self.C.gemm(x, w, out, 0, force_mode, self.status)
+        self.launches += 1
+        return out
+
+    def linear_silu_mul(self, x: torch.Tensor, w_gate_up: torch.Tensor, force_mode: int = 0) -> torch.Tensor:
+        out = torch.empty(x.shape[0], w_gate_up.shape[0] // 2, dtype=x.dtype, device=x.device)
+        if self.use_cublas_gemm:
+            tmp = torch.matmul(x, w_gate_up.t())
+            self.C.silu_mul(tmp, out)
+            return out
+        self.C.gemm(x, w_gate_up, out, 1, force_mode, self.status)
+        self.launches += 1
+        return out
+
+    # ------------------------------------------------------------------ elementwise
+    def rms_norm(self, x, weight, eps):
+        y = torch.empty_like(x)
+        self.C.rms_norm(x, None, weight, y, eps)
+        self.launches += 1
+        return y
+
+    def add_rms_norm(self, x, residual, weight, eps):
+        """(normed, new_residual).  ``residual`` is updated in place and returned."""
+        y = torch.empty_like(x)
+        self.launches += 1
+        if residual is None:
+            self.C.rms_norm(x, None, weight, y, eps)
+            return y, x
+        self.C.rms_norm(x, residual, weight, y, eps)
+        return y, residual
+
+    def silu_mul(self, x):
+        out = torch.empty(x.shape[:-1] + (x.shape[-1] // 2,), dtype=x.dtype, device=x.device)
+        self.C.silu_mul(x, out)
+        self.launches += 1
+        return out
+
+    def embedding(self, ids, weight, vocab_start=0):
+        out = torch.empty(ids.shape[0], weight.shape[1], dtype=weight.dtype, device=weight.device)
+        self.C.embedding(ids, weight, out, vocab_start)
+        self.launches += 1
+        return out
+
+    def select_rows(self, x, index):
+        out = torch.empty(index.shape[0], x.shape[1], dtype=x.dtype, device=x.device)
+        self.C.gather_rows(index, x, out)
+        self.launches += 1
+        return out
+
+    def qk_norm_rope_store(self, qkv, q_weight, k_weight, eps, table, positions, slot_mapping, k_cache, v_cache,
+                           num_heads, num_kv_heads, head_dim, do_rope=True):
+        T = qkv.shape[0]
+        q = torch.empty(T, num_heads, head_dim, dtype=qkv.dtype, device=qkv.device)
+        self.C.qk_norm_rope_store(qkv, q_weight, k_weight, eps, table, positions, slot_mapping, q, k_cache, v_cache,
+                                  num_heads, num_kv_heads, do_rope, self.status)
+        self.launches += 1
+        return q
+
+    # ------------------------------------------------------------------ attention
+    def attention(self, q, k_cache, v_cache, batch, scale):
+        T, H, D = q.shape
+        out = torch.empty(T, H * D, dtype=q.dtype, device=q.device)
+        if batch.is_prefill:
+            self.C.prefill_attention(q, k_cache, v_cache, batch.cu_seqlens_q, batch.context_lens, batch.block_tables, out,
+                                     batch.num_seqs, batch.max_seqlen_q, scale, self.status)
+            self.launches += 1
+            return out
+        B = batch.padded_seqs
+        # graph-safe sizing: the longest context the block table can describe
+        max_len = batch.table_width * k_cache.shape[2]
+        chunk, max_chunks = decode_chunking(B, k_cache.shape[1], k_cache.shape[2], max_len)
+        part_o = part_ml = None
+        if max_chunks > 1:
+            part_o = torch.empty(B * H * max_chunks * D, dtype=torch.float32, device=q.device)
+            part_ml = torch.empty(B * H * max_chunks * 2, dtype=torch.float32, device=q.device)
+        self.C.decode_attention(q, k_cache, v_cache, batch.block_tables, batch.context_lens, out, part_o, part_ml,
+                                chunk, max_chunks, scale, self.status)
+        self.launches += 2 if max_chunks > 1 else 1
+        return out
+
+    # ------------------------------------------------------------------ collectives (library path; fused path later)
+    def tp_all_reduce(self, y, tp):
+        return tp.all_reduce(y)
+
+    # ------------------------------------------------------------------ sampling
+    def sample_shard(self, logits, temperatures, header, vocab_start):
+        """(ids int32 [rows], scores fp32 [rows]) of this vocab shard."""
+        rows, vocab = logits.shape
+        n = self.C.sample_nsplit(rows, vocab)
+        part_v = torch.empty(rows * n, dtype=torch.float32, device=logits.device)
+        part_i = torch.empty(rows * n, dtype=torch.int32, device=logits.device)
+        ids = torch.empty(rows, dtype=torch.int32, device=logits.device)
+        best = torch.empty(rows, dtype=torch.float32, device=logits.device)
+        self.C.sample(logits, vocab_start, temperatures, header, part_v, part_i, ids, best)
+        self.launches += 2
+        return ids, best
+
+    def sample(self, logits, batch, vocab_start, tp):
+        ids, best = self.sample_shard(logits, batch.temperatures, batch.header, vocab_start)
+        if tp.size == 1:
+            return ids
+        all_best = tp.all_gather_stack(best)
+        all_ids = tp.all_gather_stack(ids)
+        out = torch.empty_like(ids)
+        self.C.sample_merge_ranks(all_best, all_ids, out)
+        self.launches += 1
+        return out
+
+    def close(self):
+        pass
