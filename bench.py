@@ -189,7 +189,25 @@ def run_reference(args) -> dict:
                 "(unhashable worker args, broken Sequence unpickling, un-splatted RPC args, lm-head typo)"} if rank == 0 else None
     import torch
     sys.path.insert(0, ref_dir)
+    shims = []
     try:
+        # The reference was written against transformers 4.x, where a Qwen3 config has `rope_theta` and
+        # `rope_scaling is None`.  transformers 5.x folds both into a `rope_parameters` dict, which the
+        # reference then passes to an lru_cache'd function (unhashable) and asserts to be None.  Give the
+        # loaded config object its 4.x attribute names back; the reference's own files stay untouched.
+        import transformers
+        if int(transformers.__version__.split(".")[0]) >= 5:
+            orig_from_pretrained = transformers.AutoConfig.from_pretrained
+
+            def from_pretrained_compat(*a, **k):
+                cfg = orig_from_pretrained(*a, **k)
+                rp = getattr(cfg, "rope_parameters", None) or {}
+                theta = rp.get("rope_theta", 1000000.0)
+                cfg.rope_scaling = None
+                cfg.rope_theta = theta
+                return cfg
+            transformers.AutoConfig.from_pretrained = from_pretrained_compat
+            shims.append("transformers>=5 config: restored legacy rope_theta / rope_scaling=None attributes")
         from tinyvllm import LLM, SamplingParams
         from tinyvllm.engine.model_runner import ModelRunner
     except Exception as e:  # missing dependency of the reference
@@ -239,7 +257,7 @@ def run_reference(args) -> dict:
                    "l2": "inputs larger than L2", "timing": "value: CUDA events around ModelRunner.run, summed; e2e: wall clock of generate()"},
         "e2e": {"value": total / wall, "unit": "tok/s", "h2d_bytes_per_step": acc["h2d"] // args.steps,
                 "d2h_bytes_per_step": acc["d2h"] // args.steps, "wall_s_per_step": wall / args.steps},
-        "engine_steps_per_pass": acc["steps"] // args.steps, "clocks": clocks,
+        "engine_steps_per_pass": acc["steps"] // args.steps, "clocks": clocks, "shims": shims,
     }
 
 
