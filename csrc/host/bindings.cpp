@@ -9,7 +9,7 @@
 
 extern "C" {
 int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K, int epi,
-                    int force_mode, unsigned* status, cudaStream_t stream);
+                    int force_mode, int force_splits, unsigned* status, cudaStream_t stream);
 int forge_rms_norm(const void* x, void* residual, const void* w, void* y, int rows, int H, float eps, cudaStream_t stream);
 int forge_qk_norm_rope_store(const void* qkv, int ld_qkv, const void* qw, const void* kw, float eps, const float* rope,
                              int rope_rows, const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache,
@@ -49,7 +49,8 @@ unsigned* status_ptr(const Tensor& status) {
 void check(int rc, const char* what) { TORCH_CHECK(rc == 0, what, " failed with code ", rc); }
 
 // out[M, n_out] = epilogue(x[M, K] @ w[*, K]^T); epi 0: store, 1: silu(gate) * up with w = [2 * n_out, K].
-void gemm(const Tensor& x, const Tensor& w, Tensor& out, int64_t epi, int64_t force_mode, const Tensor& status) {
+void gemm(const Tensor& x, const Tensor& w, Tensor& out, int64_t epi, int64_t force_mode, int64_t force_splits,
+          const Tensor& status) {
   CHECK_BF16(x); CHECK_BF16(w); CHECK_BF16(out);
   TORCH_CHECK(x.is_cuda() && w.is_cuda() && out.is_cuda(), "gemm: CUDA tensors expected");
   TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && out.dim() == 2, "gemm: 2-D tensors expected");
@@ -61,7 +62,8 @@ void gemm(const Tensor& x, const Tensor& w, Tensor& out, int64_t epi, int64_t fo
   const c10::cuda::CUDAGuard guard(x.device());
   check(forge_gemm_bf16(x.data_ptr(), static_cast<int>(x.stride(0)), w.data_ptr(), static_cast<int>(w.stride(0)), out.data_ptr(),
                         static_cast<int>(out.stride(0)), static_cast<int>(M), static_cast<int>(n_out), static_cast<int>(K),
-                        static_cast<int>(epi), static_cast<int>(force_mode), status_ptr(status), stream_of(x)),
+                        static_cast<int>(epi), static_cast<int>(force_mode), static_cast<int>(force_splits), status_ptr(status),
+                        stream_of(x)),
         "forge_gemm_bf16");
 }
 

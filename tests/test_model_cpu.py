@@ -120,7 +120,7 @@ def test_loader_reports_missing_and_unexpected(ckpt, tmp_path):
     from safetensors.torch import load_file, save_file
     dst = tmp_path / "broken"
     shutil.copytree(ckpt, dst)
-    t = load_file(str(dst / "model.safetensors"))
+    t = {k: v.clone() for k, v in load_file(str(dst / "model.safetensors")).items()}   # detach from the mmap before rewriting
     t.pop("model.layers.1.mlp.down_proj.weight")
     save_file(t, str(dst / "model.safetensors"))
     m = Qwen3ForCausalLM(preset("tiny"), None, torch.float32, "cpu", max_positions=64)

@@ -143,10 +143,21 @@ class LLMEngine:
         t2 = time.perf_counter()
         try:
             if self.chan is not None:
+                if self.procs:
+                    self._check_followers_alive()       # learn of a dead rank on the host, before the next collective
                 self.chan.publish(rpc.KIND_STEP, sb.buf[:sb.num_words])
             token_ids = self.worker.run(sb)
         except (rpc.PeerFailed, rpc.ChannelTimeout) as e:
             raise EngineDeadError(str(e)) from e
+        except RuntimeError as e:
+            # a collective that lost its peer fails with a backend error: say which rank went away
+            if self.chan is not None:
+                try:
+                    self._check_followers_alive()
+                    self.chan._check_followers()
+                except (EngineDeadError, rpc.PeerFailed) as dead:
+                    raise EngineDeadError(f"{dead} (while running a step: {e})") from e
+            raise
         t3 = time.perf_counter()
         self.step_index += 1
         finished = self.scheduler.postprocess(reqs, token_ids)
