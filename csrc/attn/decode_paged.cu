@@ -15,6 +15,7 @@
 //     on the device, so the launch is CUDA-graph safe: the grid depends only on the batch bucket.
 //
 // head_dim is 128 (all Qwen3 sizes).  Scores use exp2 with the scale folded into q.
+#include "../include/launch.cuh"
 #include "../include/ptx.cuh"
 
 namespace forge {
@@ -39,6 +40,8 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kDecStages * 2 * kTileBytes);
   uint64_t* empty_bar = full_bar + kDecStages;
 
+  pdl_launch_dependents();
+  pdl_wait();                                           // q, the new K/V entries and the step buffer come from predecessors
   const int groups_per_kv = (nq / nkv) / G;             // > 1 when the GQA group is processed in slices of G
   const int kvh = blockIdx.x / groups_per_kv;
   const int qh0 = kvh * (nq / nkv) + (blockIdx.x % groups_per_kv) * G;
@@ -245,6 +248,8 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(
 __global__ void __launch_bounds__(kD) decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                             const int* __restrict__ context_lens, __nv_bfloat16* __restrict__ out,
                                                             int nq, int chunk, int max_chunks) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.y, qh = blockIdx.x, d = threadIdx.x;
   const int len = context_lens[b];
   const int n = (len + chunk - 1) / chunk;
@@ -277,15 +282,18 @@ static int launch_decode(const void* q, const void* kc, const void* vc, const in
   }
   const int groups_per_kv = (nq / nkv) / G;
   dim3 grid(nkv * groups_per_kv, B, max_chunks);
-  kern<<<grid, kDecThreads, smem, stream>>>(static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(kc),
-                                            static_cast<const __nv_bfloat16*>(vc), bt, lens, static_cast<__nv_bfloat16*>(out),
-                                            part_o, part_ml, nq, nkv, block_size, table_width, num_blocks, chunk, max_chunks,
-                                            scale_log2, status);
+  if (launch_kernel(kern, grid, dim3(kDecThreads), smem, stream, 0, static_cast<const __nv_bfloat16*>(q),
+                    static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc), bt, lens,
+                    static_cast<__nv_bfloat16*>(out), part_o, part_ml, nq, nkv, block_size, table_width, num_blocks, chunk,
+                    max_chunks, scale_log2, status) != cudaSuccess)
+    return -5;
   if (max_chunks > 1) {
     dim3 g2(nq, B);
-    decode_combine_kernel<<<g2, kD, 0, stream>>>(part_o, part_ml, lens, static_cast<__nv_bfloat16*>(out), nq, chunk, max_chunks);
+    if (launch_kernel(decode_combine_kernel, g2, dim3(kD), 0, stream, 0, static_cast<const float*>(part_o),
+                      static_cast<const float*>(part_ml), lens, static_cast<__nv_bfloat16*>(out), nq, chunk, max_chunks) != cudaSuccess)
+      return -5;
   }
-  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+  return 0;
 }
 
 // q [B, nq, 128] bf16; caches [num_blocks, nkv, block_size, 128] bf16; block_tables [B, table_width]; out [B, nq * 128].

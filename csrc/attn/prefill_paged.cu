@@ -9,6 +9,7 @@
 // TMA with the 128-byte swizzle (two boxes of 64 x 64 per tile, one per half of head_dim) through a two-stage
 // ring, so shared-memory reads by ldmatrix are conflict-free.  This version multiplies with mma.sync
 // m16n8k16 (fp32 accumulate, online softmax in registers).
+#include "../include/launch.cuh"
 #include "../include/ptx.cuh"
 
 namespace forge {
@@ -49,6 +50,8 @@ __global__ void __launch_bounds__(128) prefill_attn_kernel(
   uint64_t* bar_q = reinterpret_cast<uint64_t*>(sKV + 2 * 4 * kPHalfBytes);
   uint64_t* bar_kv = bar_q + 1;                         // [2]
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int seq = blockIdx.z, h = blockIdx.y;
   const int q_begin = cu_seqlens_q[seq], q_len = cu_seqlens_q[seq + 1] - q_begin;
   const int k_len = context_lens[seq];
@@ -247,9 +250,9 @@ extern "C" int forge_prefill_attention(const void* q, const void* kc, const void
     attr_set = true;
   }
   dim3 grid((max_q + kPM - 1) / kPM, nq, num_seqs);
-  prefill_attn_kernel<<<grid, 128, smem, stream>>>(tm_q, tm_k, tm_v, cu_q, lens, bt, static_cast<__nv_bfloat16*>(out), nq, nkv,
-                                                   block_size, table_width, num_blocks, scale * 1.4426950408889634f, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+  return launch_kernel(prefill_attn_kernel, grid, dim3(128), smem, stream, 0, tm_q, tm_k, tm_v, cu_q, lens, bt,
+                       static_cast<__nv_bfloat16*>(out), nq, nkv, block_size, table_width, num_blocks,
+                       scale * 1.4426950408889634f, status) == cudaSuccess ? 0 : -5;
 }
 
 }  // namespace forge

@@ -9,6 +9,7 @@
 //
 // Rounding follows the PyTorch statement of each op in ops/ref.py so results match it bit for bit where
 // the order of fp32 additions allows.
+#include "../include/launch.cuh"
 #include "../include/ptx.cuh"
 
 namespace forge {
@@ -43,6 +44,8 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const __nv_bfloat16* __re
                                                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                                                        int H, float eps) {
   __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t row = blockIdx.x;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
   uint4* rr = kAdd ? reinterpret_cast<uint4*>(residual + row * H) : nullptr;
@@ -108,13 +111,14 @@ extern "C" int forge_rms_norm(const void* x, void* residual, const void* w, void
   threads = ((threads + 31) / 32) * 32;
   if (threads < 32) threads = 32;
   if (threads > 256) threads = 256;
+  cudaError_t e;
   if (residual != nullptr)
-    rms_norm_kernel<true><<<rows, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(residual),
-                                                        static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), H, eps);
+    e = launch_kernel(rms_norm_kernel<true>, dim3(rows), dim3(threads), 0, stream, 0, static_cast<const __nv_bfloat16*>(x),
+                      static_cast<__nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), H, eps);
   else
-    rms_norm_kernel<false><<<rows, threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), nullptr,
-                                                         static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), H, eps);
-  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+    e = launch_kernel(rms_norm_kernel<false>, dim3(rows), dim3(threads), 0, stream, 0, static_cast<const __nv_bfloat16*>(x),
+                      static_cast<__nv_bfloat16*>(nullptr), static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), H, eps);
+  return e == cudaSuccess ? 0 : -2;
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -135,6 +139,8 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(
     int T, int nq, int nkv, int block_size, long long num_slots, int do_rope, unsigned* status) {
   constexpr int E = D / 64;           // elements per lane per half
   static_assert(D == 64 || D == 128 || D == 256, "head_dim");
+  pdl_launch_dependents();
+  pdl_wait();
   const int heads = nq + 2 * nkv;
   const long long wid = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (wid >= static_cast<long long>(T) * heads) return;
@@ -205,18 +211,19 @@ extern "C" int forge_qk_norm_rope_store(const void* qkv, int ld_qkv, const void*
   if (T <= 0) return 0;
   const long long warps = static_cast<long long>(T) * (nq + 2 * nkv);
   const int grid = static_cast<int>((warps + 3) / 4);
-#define FORGE_QK(DD)                                                                                                  \
-  qk_norm_rope_store_kernel<DD><<<grid, 128, 0, stream>>>(                                                            \
-      static_cast<const __nv_bfloat16*>(qkv), ld_qkv, static_cast<const __nv_bfloat16*>(qw),                         \
-      static_cast<const __nv_bfloat16*>(kw), eps, rope, rope_rows, positions, slots, static_cast<__nv_bfloat16*>(q_out), \
-      static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), T, nq, nkv, block_size, num_slots, \
-      do_rope, status)
+  cudaError_t e;
+#define FORGE_QK(DD)                                                                                                      \
+  e = launch_kernel(qk_norm_rope_store_kernel<DD>, dim3(grid), dim3(128), 0, stream, 0,                                   \
+                    static_cast<const __nv_bfloat16*>(qkv), ld_qkv, static_cast<const __nv_bfloat16*>(qw),               \
+                    static_cast<const __nv_bfloat16*>(kw), eps, rope, rope_rows, positions, slots,                       \
+                    static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),                            \
+                    static_cast<__nv_bfloat16*>(v_cache), T, nq, nkv, block_size, num_slots, do_rope, status)
   if (D == 128) FORGE_QK(128);
   else if (D == 64) FORGE_QK(64);
   else if (D == 256) FORGE_QK(256);
   else return -1;
 #undef FORGE_QK
-  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  return e == cudaSuccess ? 0 : -2;
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -224,6 +231,8 @@ extern "C" int forge_qk_norm_rope_store(const void* qkv, int ld_qkv, const void*
 // ---------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) silu_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
                                                        long long rows, int I) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int nvec = I >> 3;
   const long long total = rows * nvec;
   for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
@@ -246,8 +255,8 @@ extern "C" int forge_silu_mul(const void* x, void* out, long long rows, int I, c
   const long long total = rows * (I >> 3);
   int grid = static_cast<int>((total + 255) / 256);
   if (grid > 148 * 16) grid = 148 * 16;
-  silu_mul_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), rows, I);
-  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  return launch_kernel(silu_mul_kernel, dim3(grid), dim3(256), 0, stream, 0, static_cast<const __nv_bfloat16*>(x),
+                       static_cast<__nv_bfloat16*>(out), rows, I) == cudaSuccess ? 0 : -2;
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -255,6 +264,8 @@ extern "C" int forge_silu_mul(const void* x, void* out, long long rows, int I, c
 // ---------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ w,
                                                         __nv_bfloat16* __restrict__ out, int H, int vocab_start, int vocab_n) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int local = ids[t] - vocab_start;
   const bool ok = local >= 0 && local < vocab_n;
@@ -267,13 +278,14 @@ extern "C" int forge_embedding(const int* ids, const void* w, void* out, int T, 
                                cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H & 7) return -1;
-  embedding_kernel<<<T, 128, 0, stream>>>(ids, static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(out), H,
-                                          vocab_start, vocab_n);
-  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  return launch_kernel(embedding_kernel, dim3(T), dim3(128), 0, stream, 0, ids, static_cast<const __nv_bfloat16*>(w),
+                       static_cast<__nv_bfloat16*>(out), H, vocab_start, vocab_n) == cudaSuccess ? 0 : -2;
 }
 
 __global__ void __launch_bounds__(128) gather_rows_kernel(const int* __restrict__ idx, const __nv_bfloat16* __restrict__ x,
                                                           __nv_bfloat16* __restrict__ out, int H, int x_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
   int r = idx[blockIdx.x];
   r = r < 0 ? 0 : (r >= x_rows ? x_rows - 1 : r);
   const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * H);
@@ -284,8 +296,8 @@ __global__ void __launch_bounds__(128) gather_rows_kernel(const int* __restrict_
 extern "C" int forge_gather_rows(const int* idx, const void* x, void* out, int S, int H, int x_rows, cudaStream_t stream) {
   if (S <= 0) return 0;
   if (H & 7) return -1;
-  gather_rows_kernel<<<S, 128, 0, stream>>>(idx, static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), H, x_rows);
-  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  return launch_kernel(gather_rows_kernel, dim3(S), dim3(128), 0, stream, 0, idx, static_cast<const __nv_bfloat16*>(x),
+                       static_cast<__nv_bfloat16*>(out), H, x_rows) == cudaSuccess ? 0 : -2;
 }
 
 }  // namespace forge

@@ -14,6 +14,7 @@
 //
 // Two kernels: partial argmax per (row, vocab slice), then a merge per row that can also fold in the pairs
 // of other ranks.
+#include "../include/launch.cuh"
 #include "../include/ptx.cuh"
 
 namespace forge {
@@ -63,6 +64,8 @@ __global__ void __launch_bounds__(kSampleThreads) sample_partial_kernel(
     const int* __restrict__ header, float* __restrict__ part_v, int* __restrict__ part_i, int nsplit) {
   __shared__ float sv[kSampleThreads / 32];
   __shared__ int si[kSampleThreads / 32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.y, split = blockIdx.x;
   const float T = temps[row];
   const bool greedy = !(T > 0.f);
@@ -108,6 +111,8 @@ __global__ void __launch_bounds__(kSampleThreads) sample_partial_kernel(
 // One warp per row merges `n` candidate pairs; writes the winning id (and value when out_v != nullptr).
 __global__ void __launch_bounds__(128) sample_merge_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int n,
                                                            int rows, int* __restrict__ out_i, float* __restrict__ out_v) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -134,15 +139,18 @@ extern "C" int forge_sample(const void* logits, int ld, int rows, int vocab, int
                             cudaStream_t stream) {
   if (rows <= 0) return 0;
   dim3 grid(nsplit, rows);
-  sample_partial_kernel<<<grid, kSampleThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), ld, vocab, vocab_start,
-                                                             temps, header, part_v, part_i, nsplit);
-  sample_merge_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(part_v, part_i, nsplit, rows, out_i, out_v);
-  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  if (launch_kernel(sample_partial_kernel, grid, dim3(kSampleThreads), 0, stream, 0, static_cast<const __nv_bfloat16*>(logits), ld,
+                    vocab, vocab_start, temps, header, part_v, part_i, nsplit) != cudaSuccess)
+    return -2;
+  return launch_kernel(sample_merge_kernel, dim3((rows + 3) / 4), dim3(128), 0, stream, 0, static_cast<const float*>(part_v),
+                       static_cast<const int*>(part_i), nsplit, rows, out_i, out_v) == cudaSuccess ? 0 : -2;
 }
 
 // Merge pairs gathered from all ranks: vals/ids laid out [ranks, rows] -> transposed read.
 __global__ void __launch_bounds__(128) sample_merge_ranks_kernel(const float* __restrict__ vals, const int* __restrict__ ids, int ranks,
                                                                  int rows, int* __restrict__ out_i) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= rows) return;
   Best b{-INFINITY, 0x7fffffff};
@@ -152,8 +160,8 @@ __global__ void __launch_bounds__(128) sample_merge_ranks_kernel(const float* __
 
 extern "C" int forge_sample_merge_ranks(const float* vals, const int* ids, int ranks, int rows, int* out_i, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  sample_merge_ranks_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(vals, ids, ranks, rows, out_i);
-  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  return launch_kernel(sample_merge_ranks_kernel, dim3((rows + 127) / 128), dim3(128), 0, stream, 0, vals, ids, ranks, rows,
+                       out_i) == cudaSuccess ? 0 : -2;
 }
 
 }  // namespace forge

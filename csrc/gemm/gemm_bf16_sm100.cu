@@ -8,18 +8,17 @@
 //       tile of BLOCK_C output features.  One output tile per CTA.
 //
 //   gemm_weights_kernel (decode, <= 256 tokens): operands swapped.  The 128-row side is a tile of 128 weight
-//       rows, so the weight stream fills the tensor core and no rows are wasted on token padding; ALL tokens
-//       ride the N side (BLOCK_C = 16..256).  Such a GEMM has few output tiles (N / 128), so K is split over a
-//       thread-block cluster of 1..8 CTAs: each CTA accumulates its K slice in tensor memory, dumps the fp32
-//       partial tile into its shared memory, and after a cluster barrier every CTA reduces its share of the
-//       columns by reading all peers' shared memory (DSMEM) in a fixed order (deterministic) and stores bf16
-//       rows with coalesced 8-byte writes.  No global scratch, no atomics.
+//       rows, so the weight stream fills the tensor core and no rows are wasted on token padding; up to 128
+//       tokens ride the N side.  Such a GEMM has few output tiles, so K is split over a thread-block cluster of
+//       1..8 CTAs and the fp32 partial tiles are reduced through distributed shared memory with bulk copies
+//       (see the kernel's comment).
 //
 // Epilogues: plain store, or SiLU(gate) * up with two accumulators per CTA (gate rows and up rows of the
 // packed [2I, H] weight), which removes the [tokens, 2I] intermediate of tinyvllm/layers/activation.py:11-14.
 //
 // Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + UMMA issuer, warps 2..5 = epilogue
 // (TMEM lane quadrant = warp % 4).  All mbarrier waits are bounded (see ptx.cuh).
+#include "../include/launch.cuh"
 #include "../include/ptx.cuh"
 
 namespace forge {
@@ -30,6 +29,18 @@ constexpr int kUmmaK = 16;
 constexpr int kGemmThreads = 192;
 
 enum GemmEpilogue { kEpiStore = 0, kEpiSiluMul = 1 };
+
+// Optional phase timeline of the decode kernel: when set (forge_gemm_set_trace), CTA b writes %globaltimer
+// (ns) at eight points into trace[b * 8 ..].  Null in normal operation.
+__device__ unsigned long long* g_gemm_trace = nullptr;
+__device__ __forceinline__ void trace_point(int cta, int k) {
+  unsigned long long* t = g_gemm_trace;
+  if (t != nullptr) {
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    t[cta * 8 + k] = now;
+  }
+}
 
 constexpr int tmem_cols_for(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
 
@@ -81,10 +92,12 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     tmem_alloc(tmem_slot, Cfg::kTmemCols);
     tmem_relinquish();
   }
+  pdl_launch_dependents();
   tcgen05_fence_before();
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();                                   // x and out belong to predecessors; set-up above overlapped their tail
 
   if (warp == 0) {
     if (lane == 0) {
@@ -176,7 +189,7 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 }
 
 // =========================================================================================================
-// decode: R = W tile (128 features; two tiles for SiLU), C = X (all tokens), split-K over a cluster
+// decode: R = W tile (128 features; two tiles for SiLU), C = X tile (up to 128 tokens), split-K over a cluster
 // =========================================================================================================
 template <int BLOCK_C, int kEpi>
 struct WgtCfg {
@@ -184,19 +197,33 @@ struct WgtCfg {
   static constexpr int kRBytes = kBlockR * kBlockK * 2;
   static constexpr int kCBytes = BLOCK_C * kBlockK * 2;
   static constexpr int kStageBytes = kNumR * kRBytes + kCBytes;
-  static constexpr int kStagesRaw = (192 * 1024) / kStageBytes;
+  static constexpr int kTileBytes = BLOCK_C * kBlockR * 4;        // one fp32 partial tile [BLOCK_C][128]
+  static constexpr int kRecvBytes = kTileBytes;                   // [splits][cols per CTA][128]
+  // the idle ring later holds this CTA's outgoing tile and, for SiLU with several splits, the reduced gate values
+  static constexpr int kRingMin = kTileBytes + (kEpi == kEpiSiluMul ? kTileBytes / 2 : 0);
+  static constexpr int kBudget = 227 * 1024 - 1024 - 256 - kRecvBytes;
+  static constexpr int kStagesRaw = kBudget / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kPartialBytes = BLOCK_C * kBlockR * 4;     // fp32 [BLOCK_C][128], reuses the stage ring
-  static constexpr int kRingBytes = kStages * kStageBytes > kPartialBytes ? kStages * kStageBytes : kPartialBytes;
+  static constexpr int kRingBytes = kStages * kStageBytes > kRingMin ? kStages * kStageBytes : kRingMin;
   static constexpr int kTmemCols = tmem_cols_for(BLOCK_C * kNumR);
-  static constexpr int kSmemBytes = kRingBytes + 1024 + 256;
-  static_assert(BLOCK_C % 16 == 0 && BLOCK_C >= 16 && BLOCK_C <= 256, "UMMA N for M = 128");
+  static constexpr int kSmemBytes = kRingBytes + kRecvBytes + 1024 + 256;
+  static_assert(BLOCK_C % 16 == 0 && BLOCK_C >= 16 && BLOCK_C <= 128, "token tile of the decode kernel");
   static_assert(kStages >= 2, "need at least a double buffer");
-  static_assert(kEpi != kEpiSiluMul || kRingBytes >= kPartialBytes + kPartialBytes / 2, "no room for the reduced gate tile");
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
 
 // out[token, feature] (row stride ldo).  W: [n_total (or 2 * n_total) rows, K]; X: [m_total rows, K].
-// Cluster = (1, S, 1): blockIdx.x = feature tile, cluster rank = K split.
+// Grid (feature tiles, K splits, token tiles); cluster = (1, S, 1), cluster rank = K split.
+//
+// Epilogue = push-reduce over the cluster.  Columns (tokens) of the tile are dealt out to the CTAs of the
+// cluster: CTA d owns columns [d * cpc, (d + 1) * cpc).  Every CTA writes its fp32 partial tile from tensor
+// memory into its own (now idle) ring as [col][row], then ONE bulk copy per peer (cp.async.bulk shared::cta ->
+// shared::cluster, completion counted in bytes by the owner's mbarrier) moves each owner's columns into slot
+// recv[source rank] of the owner's dedicated receive buffer.  The owner waits once for all bytes, sums the S
+// slots in rank order from its own shared memory (deterministic) and stores bf16 rows with 8-byte writes.
+// No global scratch, no atomics, no remote loads.
+// SiLU: one split -> combine gate and up on the way out of tensor memory.  Several splits -> the gate sum must
+// be complete before the nonlinearity: round 0 reduces the gate tile into gate_red, round 1 the up tile.
 template <int BLOCK_C, int kEpi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
@@ -207,15 +234,22 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   // The dynamic shared window starts at the same offset in every CTA of the cluster, so equal local
   // addresses name corresponding buffers in all peers.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kRingBytes);
+  float* send = reinterpret_cast<float*>(smem);                               // [BLOCK_C][128], after the main loop
+  float* gate_red = reinterpret_cast<float*>(smem + Cfg::kTileBytes);         // [cpc][128]
+  float* recv = reinterpret_cast<float*>(smem + Cfg::kRingBytes);             // [nsplit][cpc][128]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kRingBytes + Cfg::kRecvBytes);
   uint64_t* empty_bar = full_bar + Cfg::kStages;
   uint64_t* acc_bar = empty_bar + Cfg::kStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
-  float* partial = reinterpret_cast<float*>(smem);          // [BLOCK_C][128] after the main loop
+  uint64_t* recv_bar = acc_bar + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(recv_bar + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t split = cluster_ctarank(), nsplit = cluster_nctarank();
+  const int cta_id = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+  if (threadIdx.x == 0) trace_point(cta_id, 0);                  // kernel entry
+  pdl_launch_dependents();
   const int r0 = blockIdx.x * kBlockR;
+  const int tok0 = blockIdx.z * BLOCK_C;
   const int num_kb = (K + kBlockK - 1) / kBlockK;
   const int kb0 = min(static_cast<int>(split) * kb_per_split, num_kb);
   const int my_kb = min(kb0 + kb_per_split, num_kb) - kb0;   // may be 0 for a trailing split
@@ -228,6 +262,7 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(acc_bar, 1);
+    mbar_init(recv_bar, 1);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -235,13 +270,27 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     tmem_relinquish();
   }
   tcgen05_fence_before();
-  __syncthreads();
+  __syncwarp();
+  cluster_sync();              // CTA-wide barrier too; afterwards every peer's recv_bar exists
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) trace_point(cta_id, 1);                  // prologue done
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int i = 0; i < my_kb; ++i) {
+      // Weights never depend on a predecessor kernel: start streaming them into every stage of the ring right
+      // away, and wait for the predecessor only before the first activation tile is requested.
+      const int first = min(my_kb, Cfg::kStages);
+      for (int i = 0; i < first; ++i) {
+        uint8_t* st = smem + i * Cfg::kStageBytes;
+        const int kx = (kb0 + i) * kBlockK;
+        mbar_expect_tx(&full_bar[i], Cfg::kStageBytes);
+        for (int j = 0; j < Cfg::kNumR; ++j) tma_load_2d(st + j * Cfg::kRBytes, &tm_w, &full_bar[i], kx, r0 + j * dual_off);
+      }
+      pdl_wait();
+      for (int i = 0; i < first; ++i)
+        tma_load_2d(smem + i * Cfg::kStageBytes + Cfg::kNumR * Cfg::kRBytes, &tm_x, &full_bar[i], (kb0 + i) * kBlockK, tok0);
+      for (int i = first; i < my_kb; ++i) {
         const int s = i % Cfg::kStages;
         const uint32_t ph = (i / Cfg::kStages) & 1;
         if (!mbar_wait(&empty_bar[s], ph ^ 1, status)) break;
@@ -249,16 +298,20 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const int kx = (kb0 + i) * kBlockK;
         mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
         for (int j = 0; j < Cfg::kNumR; ++j) tma_load_2d(st + j * Cfg::kRBytes, &tm_w, &full_bar[s], kx, r0 + j * dual_off);
-        tma_load_2d(st + Cfg::kNumR * Cfg::kRBytes, &tm_x, &full_bar[s], kx, 0);
+        tma_load_2d(st + Cfg::kNumR * Cfg::kRBytes, &tm_x, &full_bar[s], kx, tok0);
       }
+    } else {
+      pdl_wait();
     }
   } else if (warp == 1) {
+    pdl_wait();
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc(kBlockR, BLOCK_C, 1, 1);
       for (int i = 0; i < my_kb; ++i) {
         const int s = i % Cfg::kStages;
         const uint32_t ph = (i / Cfg::kStages) & 1;
         if (!mbar_wait(&full_bar[s], ph, status)) break;
+        if (i == 0) trace_point(cta_id, 2);                      // first stage landed
         tcgen05_fence_after();
         const uint32_t st = smem_u32(smem + s * Cfg::kStageBytes);
 #pragma unroll
@@ -276,32 +329,29 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     }
   }
 
-  // ---------------------------------------------------------------- epilogue (all threads take part in the barriers)
+  // ---------------------------------------------------------------- epilogue (warps 2..5)
   const bool is_epi = warp >= 2;
   const int quad = warp & 3;
-  const int et = is_epi ? (quad * 32 + lane) : 0;              // epilogue thread id == TMEM lane == tile row
+  const int et = quad * 32 + lane;                               // epilogue thread id == TMEM lane == tile row
+  const bool fuse = kEpi == kEpiSiluMul && nsplit == 1;
+  const int rounds = (kEpi == kEpiSiluMul && !fuse) ? 2 : 1;
+  const int cpc = BLOCK_C / static_cast<int>(nsplit);            // columns per owner
+  const uint32_t slot_bytes = static_cast<uint32_t>(cpc) * kBlockR * 4;
   bool acc_ok = true;
   if (is_epi) {
-    acc_ok = mbar_wait(acc_bar, 0, status);                    // the ring is idle from here on: every load was consumed
+    pdl_wait();                                                  // `out` may still be read by a predecessor
+    acc_ok = mbar_wait(acc_bar, 0, status);                      // this CTA's ring is idle from here on
     tcgen05_fence_after();
+    if (et == 0) trace_point(cta_id, 3);                         // accumulators complete
   }
-  // SiLU with a single split needs no cross-CTA sum: combine gate and up while leaving tensor memory.
-  // With several splits the gate sums must be complete before the nonlinearity: pass 0 reduces the gate
-  // tile into this CTA's gate_red buffer (after the partial tile; fits because a split CTA owns at most
-  // BLOCK_C / 2 columns), pass 1 reduces the up tile and combines.
-  const bool fuse = kEpi == kEpiSiluMul && nsplit == 1;
-  const int passes = (kEpi == kEpiSiluMul && !fuse) ? 2 : 1;
-  const int cols_per_cta = BLOCK_C / static_cast<int>(nsplit);
-  float* gate_red = reinterpret_cast<float*>(smem + Cfg::kPartialBytes);   // [cols_per_cta][128]
-  __syncwarp();
-  for (int pass = 0; pass < passes; ++pass) {
+  for (int round = 0; round < rounds; ++round) {
     if (is_epi) {
-      // TMEM -> own shared memory, layout [col][row]: lanes write consecutive floats (no bank conflicts)
+      if (et == 0) mbar_expect_tx(recv_bar, static_cast<uint32_t>(Cfg::kTileBytes));
       constexpr int kChunk = BLOCK_C >= 32 ? 32 : 16;
 #pragma unroll 1
       for (int cc = 0; cc < BLOCK_C; cc += kChunk) {
         uint32_t v[kChunk];
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + pass * BLOCK_C + cc;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + round * BLOCK_C + cc;
         if (my_kb > 0 && acc_ok) {
           if constexpr (kChunk == 32) tmem_ld_x32(taddr, v); else tmem_ld_x16(taddr, v);
           if constexpr (kEpi == kEpiSiluMul) {
@@ -319,50 +369,61 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           for (int j = 0; j < kChunk; ++j) v[j] = 0u;
         }
 #pragma unroll
-        for (int j = 0; j < kChunk; ++j) partial[(cc + j) * kBlockR + et] = __uint_as_float(v[j]);
+        for (int j = 0; j < kChunk; ++j) send[(cc + j) * kBlockR + et] = __uint_as_float(v[j]);   // lanes -> consecutive floats
       }
-    }
-    __syncwarp();
-    cluster_sync();                                            // every CTA's partial tile is visible
-    if (is_epi) {
-      // this CTA reduces columns [split * cols_per_cta, +cols_per_cta); a warp handles one column at a time,
-      // lane l owns rows 4l..4l+3 (16-byte DSMEM reads, 8-byte global stores)
-      const uint32_t my_base = smem_u32(partial);
-      const int c_first = static_cast<int>(split) * cols_per_cta;
-      for (int c = c_first + quad; c < c_first + cols_per_cta; c += 4) {
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t p = 0; p < nsplit; ++p) {
-          const float4 v = ld_dsmem_f4(dsmem_addr(my_base + (c * kBlockR + lane * 4) * 4, p));
-          a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
-        }
-        if constexpr (kEpi == kEpiSiluMul) {
-          if (!fuse) {
-            float4* g = reinterpret_cast<float4*>(gate_red + (c - c_first) * kBlockR + lane * 4);   // same thread both passes
-            if (pass == 0) {
-              *g = a;
-              continue;
+      fence_proxy_async_smem();                                  // generic-proxy writes -> visible to the bulk-copy engine
+      named_barrier_sync(1, 128);                                // the four epilogue warps
+      if (et == 0) trace_point(cta_id, 4);                       // tile written to shared memory
+      if (et == 0) {
+        for (uint32_t d = 0; d < nsplit; ++d)
+          bulk_copy_to_peer(dsmem_addr(smem_u32(recv) + split * slot_bytes, d), smem_u32(send) + d * slot_bytes, slot_bytes,
+                            dsmem_addr(smem_u32(recv_bar), d));
+      }
+      const bool got = mbar_wait(recv_bar, round & 1, status);   // all S slots of my columns have landed
+      if (et == 0) trace_point(cta_id, 5);                       // partials received
+      if (got) {
+        // a warp handles one column at a time; lane l owns rows 4l..4l+3
+        for (int lc = quad; lc < cpc; lc += 4) {
+          float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (uint32_t p = 0; p < nsplit; ++p) {
+            const float4 t = *reinterpret_cast<const float4*>(recv + (p * cpc + lc) * kBlockR + lane * 4);
+            a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
+          }
+          if constexpr (kEpi == kEpiSiluMul) {
+            if (!fuse) {
+              float4* g = reinterpret_cast<float4*>(gate_red + lc * kBlockR + lane * 4);   // same thread in both rounds
+              if (round == 0) {
+                *g = a;
+                continue;
+              }
+              const float4 gv = *g;
+              a.x = silu(gv.x) * a.x; a.y = silu(gv.y) * a.y; a.z = silu(gv.z) * a.z; a.w = silu(gv.w) * a.w;
             }
-            const float4 gv = *g;
-            a.x = silu(gv.x) * a.x; a.y = silu(gv.y) * a.y; a.z = silu(gv.z) * a.z; a.w = silu(gv.w) * a.w;
           }
-        }
-        const int n = r0 + lane * 4;
-        if (c < m_total && n < n_total) {
-          __nv_bfloat16* dst = out + static_cast<size_t>(c) * ldo + n;
-          if (n + 4 <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0)) {
-            uint2 pk;
-            pk.x = pack_bf16x2(a.x, a.y);
-            pk.y = pack_bf16x2(a.z, a.w);
-            *reinterpret_cast<uint2*>(dst) = pk;
-          } else {
-            const float f[4] = {a.x, a.y, a.z, a.w};
-            for (int j = 0; j < 4 && n + j < n_total; ++j) dst[j] = __float2bfloat16_rn(f[j]);
+          const int c = tok0 + static_cast<int>(split) * cpc + lc;
+          const int n = r0 + lane * 4;
+          if (c < m_total && n < n_total) {
+            __nv_bfloat16* dst = out + static_cast<size_t>(c) * ldo + n;
+            if (n + 4 <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0)) {
+              uint2 pk;
+              pk.x = pack_bf16x2(a.x, a.y);
+              pk.y = pack_bf16x2(a.z, a.w);
+              *reinterpret_cast<uint2*>(dst) = pk;
+            } else {
+              const float f[4] = {a.x, a.y, a.z, a.w};
+              for (int j = 0; j < 4 && n + j < n_total; ++j) dst[j] = __float2bfloat16_rn(f[j]);
+            }
           }
         }
       }
     }
-    cluster_sync();                                            // peers are done reading this CTA's partial tile
+    // Every peer has received (hence my outgoing copies have finished reading `send`) and consumed its slots:
+    // the buffers may be reused by the next round, or released at exit.
+    if (is_epi && et == 0) trace_point(cta_id, 6);               // output stored
+    __syncwarp();
+    cluster_sync();
   }
+  if (threadIdx.x == 0) trace_point(cta_id, 7);                  // after the final cluster barrier
 
   tcgen05_fence_before();
   __syncthreads();
@@ -407,6 +468,10 @@ extern "C" int forge_make_tmap_2d(CUtensorMap* tm, const void* base, uint64_t ro
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+extern "C" int forge_gemm_set_trace(unsigned long long* buf) {
+  return cudaMemcpyToSymbol(g_gemm_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : -1;
+}
+
 template <int BLOCK_C, int kEpi>
 static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int ldw, __nv_bfloat16* out, int ldo, int M,
                          int n_out, int K, unsigned* status, cudaStream_t stream) {
@@ -421,8 +486,8 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
     attr_set = true;
   }
   dim3 grid((M + kBlockR - 1) / kBlockR, (n_out + BLOCK_C - 1) / BLOCK_C);
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tm_x, tm_w, out, ldo, M, n_out, K, n_out, status);
-  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+  return launch_kernel(kern, grid, dim3(kGemmThreads), Cfg::kSmemBytes, stream, 0, tm_x, tm_w, out, ldo, M, n_out, K, n_out,
+                       status) == cudaSuccess ? 0 : -5;
 }
 
 // Cluster size (K splits) for the decode kernel: double while the grid stays within one wave of 148 SMs and
@@ -447,25 +512,14 @@ static int launch_weights(const void* x, int ldx, const void* w, int w_rows, int
     attr_set = true;
   }
   const int tiles = (n_out + kBlockR - 1) / kBlockR;
+  const int tok_tiles = (M + BLOCK_C - 1) / BLOCK_C;
   const int num_kb = (K + kBlockK - 1) / kBlockK;
-  int splits = force_splits > 0 ? force_splits : choose_splits(tiles, num_kb);
+  int splits = force_splits > 0 ? force_splits : choose_splits(tiles * tok_tiles, num_kb);
   if (splits > BLOCK_C / 4) splits = BLOCK_C / 4 < 1 ? 1 : BLOCK_C / 4;   // every CTA reduces >= 4 columns (one per warp)
   if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return -6;
   const int kb_per_split = (num_kb + splits - 1) / splits;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(tiles, splits, 1);
-  cfg.blockDim = dim3(kGemmThreads, 1, 1);
-  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = splits;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tm_w, tm_x, out, ldo, n_out, M, K, kb_per_split, n_out, status);
-  return e == cudaSuccess ? 0 : -5;
+  return launch_kernel(kern, dim3(tiles, splits, tok_tiles), dim3(kGemmThreads), Cfg::kSmemBytes, stream, splits, tm_w, tm_x,
+                       out, ldo, n_out, M, K, kb_per_split, n_out, status) == cudaSuccess ? 0 : -5;
 }
 
 // out[M, n_out] = epilogue(X[M, K] * W[*, K]^T).  epi = 0: W has n_out rows.  epi = 1: W is [2 * n_out, K]
@@ -482,7 +536,7 @@ extern "C" int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, v
   const bool decode = force_mode == 2 || (force_mode == 0 && M <= 256);
   if (decode) {
     if (M > 256) return -7;
-    const int bc = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    const int bc = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;     // more than 128 tokens: several token tiles
 #define FORGE_W(BC)                                                                                                          \
   case BC:                                                                                                                   \
     return epi == kEpiSiluMul                                                                                                \
@@ -493,7 +547,6 @@ extern "C" int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, v
       FORGE_W(32)
       FORGE_W(64)
       FORGE_W(128)
-      FORGE_W(256)
     }
 #undef FORGE_W
     return -6;

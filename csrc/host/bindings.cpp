@@ -10,6 +10,7 @@
 extern "C" {
 int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K, int epi,
                     int force_mode, int force_splits, unsigned* status, cudaStream_t stream);
+int forge_gemm_set_trace(unsigned long long* buf);
 int forge_rms_norm(const void* x, void* residual, const void* w, void* y, int rows, int H, float eps, cudaStream_t stream);
 int forge_qk_norm_rope_store(const void* qkv, int ld_qkv, const void* qw, const void* kw, float eps, const float* rope,
                              int rope_rows, const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache,
@@ -65,6 +66,16 @@ void gemm(const Tensor& x, const Tensor& w, Tensor& out, int64_t epi, int64_t fo
                         static_cast<int>(epi), static_cast<int>(force_mode), static_cast<int>(force_splits), status_ptr(status),
                         stream_of(x)),
         "forge_gemm_bf16");
+}
+
+// Phase timeline of the decode GEMM (profiling aid): int64 CUDA tensor of >= 8 * CTAs entries, or None to switch off.
+void gemm_set_trace(const c10::optional<Tensor>& buf) {
+  unsigned long long* p = nullptr;
+  if (buf.has_value()) {
+    TORCH_CHECK(buf->is_cuda() && buf->is_contiguous() && buf->scalar_type() == at::kLong, "trace buffer must be a CUDA int64 tensor");
+    p = reinterpret_cast<unsigned long long*>(buf->data_ptr<int64_t>());
+  }
+  check(forge_gemm_set_trace(p), "forge_gemm_set_trace");
 }
 
 void rms_norm(const Tensor& x, const c10::optional<Tensor>& residual, const Tensor& w, Tensor& y, double eps) {
@@ -226,6 +237,7 @@ void prefill_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "tinyllmforge_b200 sm_100a kernels";
   m.def("gemm", &gemm);
+  m.def("gemm_set_trace", &gemm_set_trace);
   m.def("rms_norm", &rms_norm);
   m.def("qk_norm_rope_store", &qk_norm_rope_store);
   m.def("silu_mul", &silu_mul);

@@ -1,0 +1,57 @@
+// One way to launch every kernel of the library: cudaLaunchKernelEx with
+//   * programmatic dependent launch (PDL): the kernel may start while its predecessor in the stream is still
+//     running; it executes `griddepcontrol.wait` (pdl_wait) before touching anything the predecessor produces.
+//     Every kernel calls pdl_wait exactly once on every path, so completion stays transitive along the stream.
+//     What a kernel does BEFORE pdl_wait overlaps with the predecessor's tail: barrier and tensor-memory set-up,
+//     tensor-map prefetch and, in the decode GEMM, the first weight tiles (weights never depend on a predecessor).
+//   * an optional thread-block cluster dimension along y (cluster_y >= 1; 0 = not a cluster kernel).  A kernel
+//     that executes cluster instructions (barrier.cluster, mapa, shared::cluster bulk copies) is ALWAYS launched
+//     with the attribute, also for a cluster of one CTA: launched without it, the decode GEMM raised
+//     "illegal instruction" on B200.
+// CUDA-graph capture records these launches with programmatic edges.  FORGE_PDL=0 in the environment switches
+// the attribute off (kernels then see griddepcontrol.* as no-ops).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdlib>
+
+namespace forge {
+
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = std::getenv("FORGE_PDL");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 int cluster_y, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (cluster_y >= 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = 1;
+    attr[n].val.clusterDim.y = static_cast<unsigned>(cluster_y);
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+}  // namespace forge

@@ -41,6 +41,12 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// ---- programmatic dependent launch (see launch.cuh) ------------------------------------------------
+// Let the next kernel in the stream begin its own prologue.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// Block until every kernel this one depends on has completed and its writes are visible.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- mbarrier ------------------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
@@ -223,6 +229,24 @@ __device__ __forceinline__ float4 ld_dsmem_f4(uint32_t addr) {
   float4 v;
   asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
   return v;
+}
+
+// Bulk copy from this CTA's shared memory into a peer's (dst and mbar are shared::cluster addresses of the
+// SAME destination CTA); the destination mbarrier is credited with `bytes`.  16-byte alignment and size.
+__device__ __forceinline__ void bulk_copy_to_peer(uint32_t remote_dst, uint32_t local_src, uint32_t bytes, uint32_t remote_mbar) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(remote_dst), "r"(local_src), "r"(bytes), "r"(remote_mbar) : "memory");
+}
+// Barrier over a subset of the CTA's warps (id 1..15; 0 is __syncthreads).
+__device__ __forceinline__ void named_barrier_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Remote shared-memory store that credits `bytes stored` to an mbarrier in the destination CTA.
+// Both addresses are shared::cluster addresses (dsmem_addr) of the SAME destination CTA.
+__device__ __forceinline__ void st_async_b32(uint32_t remote_addr, uint32_t value, uint32_t remote_mbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+               ::"r"(remote_addr), "r"(value), "r"(remote_mbar) : "memory");
 }
 
 // ---- small math helpers --------------------------------------------------------------------------------
