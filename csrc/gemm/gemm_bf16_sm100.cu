@@ -346,7 +346,6 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   }
   for (int round = 0; round < rounds; ++round) {
     if (is_epi) {
-      if (et == 0) mbar_expect_tx(recv_bar, static_cast<uint32_t>(Cfg::kTileBytes));
       constexpr int kChunk = BLOCK_C >= 32 ? 32 : 16;
 #pragma unroll 1
       for (int cc = 0; cc < BLOCK_C; cc += kChunk) {
@@ -371,47 +370,69 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
         for (int j = 0; j < kChunk; ++j) send[(cc + j) * kBlockR + et] = __uint_as_float(v[j]);   // lanes -> consecutive floats
       }
-      fence_proxy_async_smem();                                  // generic-proxy writes -> visible to the bulk-copy engine
-      named_barrier_sync(1, 128);                                // the four epilogue warps
-      if (et == 0) trace_point(cta_id, 4);                       // tile written to shared memory
-      if (et == 0) {
-        for (uint32_t d = 0; d < nsplit; ++d)
-          bulk_copy_to_peer(dsmem_addr(smem_u32(recv) + split * slot_bytes, d), smem_u32(send) + d * slot_bytes, slot_bytes,
-                            dsmem_addr(smem_u32(recv_bar), d));
+      const float* src = recv;                                   // where this CTA's columns are summed from
+      bool got = true;
+      if (nsplit > 1) {
+        fence_proxy_async_smem();                                // generic-proxy writes -> visible to the bulk-copy engine
+        named_barrier_sync(1, 128);                              // the four epilogue warps
+        if (et == 0) trace_point(cta_id, 4);                     // tile written to shared memory
+        if (et == 0) {
+          mbar_expect_tx(recv_bar, static_cast<uint32_t>(Cfg::kTileBytes));
+          for (uint32_t d = 0; d < nsplit; ++d)
+            bulk_copy_to_peer(dsmem_addr(smem_u32(recv) + split * slot_bytes, d), smem_u32(send) + d * slot_bytes, slot_bytes,
+                              dsmem_addr(smem_u32(recv_bar), d));
+        }
+        got = mbar_wait(recv_bar, round & 1, status);            // all S slots of my columns have landed
+      } else {
+        named_barrier_sync(1, 128);                              // single split: the tile is already where it is needed
+        src = send;
       }
-      const bool got = mbar_wait(recv_bar, round & 1, status);   // all S slots of my columns have landed
       if (et == 0) trace_point(cta_id, 5);                       // partials received
       if (got) {
-        // a warp handles one column at a time; lane l owns rows 4l..4l+3
-        for (int lc = quad; lc < cpc; lc += 4) {
-          float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (uint32_t p = 0; p < nsplit; ++p) {
-            const float4 t = *reinterpret_cast<const float4*>(recv + (p * cpc + lc) * kBlockR + lane * 4);
-            a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
-          }
-          if constexpr (kEpi == kEpiSiluMul) {
-            if (!fuse) {
-              float4* g = reinterpret_cast<float4*>(gate_red + lc * kBlockR + lane * 4);   // same thread in both rounds
-              if (round == 0) {
-                *g = a;
-                continue;
+        // a warp handles one column at a time; lane l owns rows 4l..4l+3.  Two columns per iteration keep
+        // several shared-memory loads in flight.
+        for (int lc0 = quad; lc0 < cpc; lc0 += 8) {
+          float4 a[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            a[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            const int lc = lc0 + 4 * u;
+            if (lc < cpc) {
+              for (uint32_t p = 0; p < nsplit; ++p) {
+                const float4 t = *reinterpret_cast<const float4*>(src + (p * cpc + lc) * kBlockR + lane * 4);
+                a[u].x += t.x; a[u].y += t.y; a[u].z += t.z; a[u].w += t.w;
               }
-              const float4 gv = *g;
-              a.x = silu(gv.x) * a.x; a.y = silu(gv.y) * a.y; a.z = silu(gv.z) * a.z; a.w = silu(gv.w) * a.w;
             }
           }
-          const int c = tok0 + static_cast<int>(split) * cpc + lc;
-          const int n = r0 + lane * 4;
-          if (c < m_total && n < n_total) {
-            __nv_bfloat16* dst = out + static_cast<size_t>(c) * ldo + n;
-            if (n + 4 <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0)) {
-              uint2 pk;
-              pk.x = pack_bf16x2(a.x, a.y);
-              pk.y = pack_bf16x2(a.z, a.w);
-              *reinterpret_cast<uint2*>(dst) = pk;
-            } else {
-              const float f[4] = {a.x, a.y, a.z, a.w};
-              for (int j = 0; j < 4 && n + j < n_total; ++j) dst[j] = __float2bfloat16_rn(f[j]);
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int lc = lc0 + 4 * u;
+            if (lc >= cpc) continue;
+            float4 v = a[u];
+            if constexpr (kEpi == kEpiSiluMul) {
+              if (!fuse) {
+                float4* g = reinterpret_cast<float4*>(gate_red + lc * kBlockR + lane * 4);   // same thread in both rounds
+                if (round == 0) {
+                  *g = v;
+                  continue;
+                }
+                const float4 gv = *g;
+                v.x = silu(gv.x) * v.x; v.y = silu(gv.y) * v.y; v.z = silu(gv.z) * v.z; v.w = silu(gv.w) * v.w;
+              }
+            }
+            const int c = tok0 + static_cast<int>(split) * cpc + lc;
+            const int n = r0 + lane * 4;
+            if (c < m_total && n < n_total) {
+              __nv_bfloat16* dst = out + static_cast<size_t>(c) * ldo + n;
+              if (n + 4 <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0)) {
+                uint2 pk;
+                pk.x = pack_bf16x2(v.x, v.y);
+                pk.y = pack_bf16x2(v.z, v.w);
+                *reinterpret_cast<uint2*>(dst) = pk;
+              } else {
+                const float f[4] = {v.x, v.y, v.z, v.w};
+                for (int j = 0; j < 4 && n + j < n_total; ++j) dst[j] = __float2bfloat16_rn(f[j]);
+              }
             }
           }
         }
@@ -490,17 +511,21 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
                        status) == cudaSuccess ? 0 : -5;
 }
 
-// Cluster size (K splits) for the decode kernel: double while the grid stays within one wave of 148 SMs and
-// every split keeps at least two K blocks.
-static int choose_splits(int tiles, int num_kb) {
+// Cluster size (K splits) of the decode kernel.  Measured on B200 (sweep over token tile x splits for the
+// Qwen3 layer shapes): a CTA streams at most ~100 GB/s (ring bytes in flight / memory latency), so the grid
+// should be about one wave of the 148 SMs; the cross-CTA exchange over DSMEM runs at only ~20 GB/s per SM, so
+// tiles are kept small (<= 64 tokens when splitting) and the split count is the largest power of two that
+// keeps the grid within ~one wave, leaves each split >= 2 K blocks and each CTA >= 4 columns to reduce.
+static int choose_splits(int ctas_unsplit, int num_kb, int block_c) {
   int s = 1;
-  while (s < 8 && tiles * s * 2 <= 148 && num_kb / (s * 2) >= 2) s *= 2;
+  while (s < 8 && ctas_unsplit * s * 2 <= 160 && num_kb / (s * 2) >= 2 && s * 2 <= block_c / 4) s *= 2;
   return s;
 }
 
 template <int BLOCK_C, int kEpi>
 static int launch_weights(const void* x, int ldx, const void* w, int w_rows, int ldw, __nv_bfloat16* out, int ldo, int M,
                           int n_out, int K, int force_splits, unsigned* status, cudaStream_t stream) {
+  // force_splits: 0 = choose, else the cluster size
   using Cfg = WgtCfg<BLOCK_C, kEpi>;
   CUtensorMap tm_x, tm_w;
   if (forge_make_tmap_2d(&tm_w, w, w_rows, K, ldw, kBlockR, 2) != 0) return -2;
@@ -514,7 +539,7 @@ static int launch_weights(const void* x, int ldx, const void* w, int w_rows, int
   const int tiles = (n_out + kBlockR - 1) / kBlockR;
   const int tok_tiles = (M + BLOCK_C - 1) / BLOCK_C;
   const int num_kb = (K + kBlockK - 1) / kBlockK;
-  int splits = force_splits > 0 ? force_splits : choose_splits(tiles * tok_tiles, num_kb);
+  int splits = force_splits > 0 ? force_splits : choose_splits(tiles * tok_tiles, num_kb, BLOCK_C);
   if (splits > BLOCK_C / 4) splits = BLOCK_C / 4 < 1 ? 1 : BLOCK_C / 4;   // every CTA reduces >= 4 columns (one per warp)
   if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return -6;
   const int kb_per_split = (num_kb + splits - 1) / splits;
@@ -525,9 +550,11 @@ static int launch_weights(const void* x, int ldx, const void* w, int w_rows, int
 // out[M, n_out] = epilogue(X[M, K] * W[*, K]^T).  epi = 0: W has n_out rows.  epi = 1: W is [2 * n_out, K]
 // (gate rows then up rows) and out = silu(gate) * up.  Requirements: K % 8 == 0, x/w 16-byte aligned,
 // ldx/ldw % 8 == 0.  force_mode: 0 auto, 1 token-tile kernel, 2 weight-tile (decode) kernel (needs M <= 256).
-// force_splits: 0 auto, else the cluster size of the decode kernel.  Returns 0 on success.
+// tune: 0 auto; else bits 0..7 = cluster size (K splits) and bits 8..15 = token tile (16/32/64/128) of the decode
+// kernel, either may be 0 = choose.  Returns 0 on success.
 extern "C" int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out,
-                               int K, int epi, int force_mode, int force_splits, unsigned* status, cudaStream_t stream) {
+                               int K, int epi, int force_mode, int tune, unsigned* status, cudaStream_t stream) {
+  const int force_splits = tune & 0xff, force_bc = (tune >> 8) & 0xff;
   if (M <= 0 || n_out <= 0 || K <= 0) return 0;
   if ((K & 7) || (ldx & 7) || (ldw & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
     return -1;
@@ -536,7 +563,11 @@ extern "C" int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, v
   const bool decode = force_mode == 2 || (force_mode == 0 && M <= 256);
   if (decode) {
     if (M > 256) return -7;
-    const int bc = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;     // more than 128 tokens: several token tiles
+    // token tile: few feature tiles -> small token tiles (parallelism, cheap exchange; extra token tiles re-read the
+    // weights from L2); many feature tiles (LM head) -> the widest tile, so weights cross L2 -> SM only once or twice
+    const int feature_tiles = (n_out + kBlockR - 1) / kBlockR;
+    int bc = M <= 16 ? 16 : M <= 32 ? 32 : (M <= 64 || feature_tiles < 148) ? 64 : 128;
+    if (force_bc == 16 || force_bc == 32 || force_bc == 64 || force_bc == 128) bc = force_bc;
 #define FORGE_W(BC)                                                                                                          \
   case BC:                                                                                                                   \
     return epi == kEpiSiluMul                                                                                                \

@@ -67,21 +67,25 @@ class CudaOps:
             raise RuntimeError(f"a CUDA kernel reported: {', '.join(what) or hex(word)}")
 
     # ------------------------------------------------------------------ GEMMs
-    def linear(self, x: torch.Tensor, w: torch.Tensor, force_mode: int = 0, force_splits: int = 0) -> torch.Tensor:
+    def linear(self, x: torch.Tensor, w: torch.Tensor, force_mode: int = 0, force_splits: int = 0,
+               force_block_c: int = 0) -> torch.Tensor:
+        """x @ w.T.  ``w`` must not be the output of the kernel launched just before this call: the decode
+        kernel starts streaming weights before it waits for its predecessor (weights are static in the engine)."""
         out = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
         if self.use_cublas_gemm:
             return torch.matmul(x, w.t(), out=out)
-        self.C.gemm(x, w, out, 0, force_mode, force_splits, self.status)
+        self.C.gemm(x, w, out, 0, force_mode, force_splits | (force_block_c << 8), self.status)
         self.launches += 1
         return out
 
-    def linear_silu_mul(self, x: torch.Tensor, w_gate_up: torch.Tensor, force_mode: int = 0, force_splits: int = 0) -> torch.Tensor:
+    def linear_silu_mul(self, x: torch.Tensor, w_gate_up: torch.Tensor, force_mode: int = 0, force_splits: int = 0,
+                        force_block_c: int = 0) -> torch.Tensor:
         out = torch.empty(x.shape[0], w_gate_up.shape[0] // 2, dtype=x.dtype, device=x.device)
         if self.use_cublas_gemm:
             tmp = torch.matmul(x, w_gate_up.t())
             self.C.silu_mul(tmp, out)
             return out
-        self.C.gemm(x, w_gate_up, out, 1, force_mode, force_splits, self.status)
+        self.C.gemm(x, w_gate_up, out, 1, force_mode, force_splits | (force_block_c << 8), self.status)
         self.launches += 1
         return out
 
