@@ -330,4 +330,83 @@ extern "C" int forge_decode_attention(const void* q, const void* kc, const void*
 #undef FORGE_DEC
 }
 
+
+// =========================================================================================================
+// Allocation-free entry point (declared in include/forge_noalloc.h; no counterpart in the reference).
+//
+// Who needs it: code that drives this kernel from a place where device memory cannot be requested -- a host
+// callback or a plug-in running inside someone else's memory plan, a real-time loop that must not touch the
+// allocator, or a process whose memory pool is sized up front and then frozen.  The regular entry point asks
+// its caller for split-context scratch (per-chunk partial outputs plus their softmax max/sum); a caller that
+// cannot allocate has nowhere to get it from.  Here that scratch is a fixed array that lives in the library's
+// device image, so the caller passes only the operation's real inputs and outputs.
+//
+// Properties a caller must know:
+//   * The array is kForgeNoAllocScratchFloats floats (16 MiB).  Every GPU that loads this library carries it
+//     from module load until the process exits, whether or not this entry point is ever called.
+//   * A problem needs B * nq * max_chunks * 130 floats.  Larger requests are refused with
+//     FORGE_NOALLOC_TOO_LARGE before anything is launched; forge_decode_attention_noalloc_strerror() turns the
+//     code into text.
+//   * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+//     device current) and remembers it.  Make that first call outside of any stream capture: the lookup is a
+//     synchronous runtime query, not a stream operation.
+//   * All calls on a device share the one array, and it keeps whatever the last call left in it.  Nothing in
+//     it has to start at zero: every partial the merge kernel reads was written by the attention kernel of the
+//     same call.  Two calls whose kernels overlap on the GPU (different streams, or a graph branch) race on it;
+//     keep calls on one device ordered.
+//   * No cudaMalloc, cudaFree, or allocating library routine is called on any path.
+// =========================================================================================================
+constexpr size_t kForgeNoAllocScratchFloats = static_cast<size_t>(4) << 20;
+
+static __device__ __align__(256) float g_noalloc_scratch[kForgeNoAllocScratchFloats];
+
+// The symbol above is a host-side handle, not a device pointer: handing `g_noalloc_scratch` itself to a kernel
+// launch would pass a host address.  The device address is looked up once per device and cached here.
+static float* g_noalloc_scratch_dev[64] = {};
+
+enum ForgeNoAllocError {
+  FORGE_NOALLOC_OK = 0,
+  FORGE_NOALLOC_BAD_ARGUMENT = -1,
+  FORGE_NOALLOC_TOO_LARGE = -20,
+  FORGE_NOALLOC_SYMBOL_LOOKUP_FAILED = -21,
+  FORGE_NOALLOC_LAUNCH_FAILED = -22,
+};
+
+extern "C" const char* forge_decode_attention_noalloc_strerror(int code) {
+  switch (code) {
+    case FORGE_NOALLOC_OK: return "ok";
+    case FORGE_NOALLOC_BAD_ARGUMENT: return "bad argument: head_dim must be 128, block_size a power of two >= 16, chunk a multiple of min(block_size, 64)";
+    case FORGE_NOALLOC_TOO_LARGE: return "B * nq * max_chunks * 130 floats exceed the built-in 16 MiB scratch array; use forge_decode_attention with caller-provided scratch";
+    case FORGE_NOALLOC_SYMBOL_LOOKUP_FAILED: return "cudaGetSymbolAddress failed for the built-in scratch array on the current device";
+    case FORGE_NOALLOC_LAUNCH_FAILED: return "kernel launch failed";
+    default: return "unknown error";
+  }
+}
+
+extern "C" size_t forge_decode_attention_noalloc_capacity_floats() { return kForgeNoAllocScratchFloats; }
+
+extern "C" int forge_decode_attention_noalloc(const void* q, const void* kc, const void* vc, const int* bt, const int* lens,
+                                              void* out, int B, int nq, int nkv, int head_dim, int block_size, int table_width,
+                                              int num_blocks, int chunk, int max_chunks, float scale, unsigned* status,
+                                              cudaStream_t stream) {
+  if (B <= 0) return FORGE_NOALLOC_OK;
+  if (nq <= 0 || nkv <= 0 || max_chunks < 1 || chunk < 1) return FORGE_NOALLOC_BAD_ARGUMENT;
+  const size_t slots = static_cast<size_t>(B) * nq * max_chunks;
+  if (slots * (kD + 2) > kForgeNoAllocScratchFloats) return FORGE_NOALLOC_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FORGE_NOALLOC_SYMBOL_LOOKUP_FAILED;
+  if (g_noalloc_scratch_dev[dev] == nullptr) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch) != cudaSuccess || p == nullptr)
+      return FORGE_NOALLOC_SYMBOL_LOOKUP_FAILED;
+    g_noalloc_scratch_dev[dev] = p;
+  }
+  float* part_o = g_noalloc_scratch_dev[dev];
+  float* part_ml = part_o + slots * kD;
+  const int rc = forge_decode_attention(q, kc, vc, bt, lens, out, part_o, part_ml, B, nq, nkv, head_dim, block_size, table_width,
+                                        num_blocks, chunk, max_chunks, scale, status, stream);
+  if (rc == -1) return FORGE_NOALLOC_BAD_ARGUMENT;
+  return rc == 0 ? FORGE_NOALLOC_OK : FORGE_NOALLOC_LAUNCH_FAILED;
+}
+
 }  // namespace forge
