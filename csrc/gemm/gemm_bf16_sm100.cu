@@ -20,6 +20,7 @@
 // (TMEM lane quadrant = warp % 4).  All mbarrier waits are bounded (see ptx.cuh).
 #include "../include/launch.cuh"
 #include "../include/ptx.cuh"
+#include "../include/tp_comm.cuh"
 
 namespace forge {
 
@@ -228,7 +229,7 @@ template <int BLOCK_C, int kEpi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                     __nv_bfloat16* __restrict__ out, int ldo, int n_total, int m_total, int K, int kb_per_split,
-                    int dual_off, unsigned* status) {
+                    int dual_off, unsigned* status, const TpPush push) {
   using Cfg = WgtCfg<BLOCK_C, kEpi>;
   extern __shared__ uint8_t smem_raw[];
   // The dynamic shared window starts at the same offset in every CTA of the cluster, so equal local
@@ -423,15 +424,21 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             const int c = tok0 + static_cast<int>(split) * cpc + lc;
             const int n = r0 + lane * 4;
             if (c < m_total && n < n_total) {
-              __nv_bfloat16* dst = out + static_cast<size_t>(c) * ldo + n;
-              if (n + 4 <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0)) {
-                uint2 pk;
-                pk.x = pack_bf16x2(v.x, v.y);
-                pk.y = pack_bf16x2(v.z, v.w);
-                *reinterpret_cast<uint2*>(dst) = pk;
-              } else {
-                const float f[4] = {v.x, v.y, v.z, v.w};
-                for (int j = 0; j < 4 && n + j < n_total; ++j) dst[j] = __float2bfloat16_rn(f[j]);
+              // Row-parallel layer under tensor parallelism: this rank's partial sums go straight into slot
+              // [rank] of EVERY rank's buffer (peer stores over NVLink), tile by tile while other CTAs still
+              // compute; the consumer kernel adds the slots up.  Otherwise: a local store.
+              const int ndst = push.size > 1 ? push.size : 1;
+              for (int pd = 0; pd < ndst; ++pd) {
+                __nv_bfloat16* dst = (push.size > 1 ? push.slot[pd] : out) + static_cast<size_t>(c) * ldo + n;
+                if (n + 4 <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0)) {
+                  uint2 pk;
+                  pk.x = pack_bf16x2(v.x, v.y);
+                  pk.y = pack_bf16x2(v.z, v.w);
+                  *reinterpret_cast<uint2*>(dst) = pk;
+                } else {
+                  const float f[4] = {v.x, v.y, v.z, v.w};
+                  for (int j = 0; j < 4 && n + j < n_total; ++j) dst[j] = __float2bfloat16_rn(f[j]);
+                }
               }
             }
           }
@@ -445,6 +452,7 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     cluster_sync();
   }
   if (threadIdx.x == 0) trace_point(cta_id, 7);                  // after the final cluster barrier
+  if (push.size > 1) tp_push_done(push, gridDim.x * gridDim.y * gridDim.z);   // last CTA of the grid signals every rank
 
   tcgen05_fence_before();
   __syncthreads();
@@ -524,7 +532,7 @@ static int choose_splits(int ctas_unsplit, int num_kb, int block_c) {
 
 template <int BLOCK_C, int kEpi>
 static int launch_weights(const void* x, int ldx, const void* w, int w_rows, int ldw, __nv_bfloat16* out, int ldo, int M,
-                          int n_out, int K, int force_splits, unsigned* status, cudaStream_t stream) {
+                          int n_out, int K, int force_splits, unsigned* status, cudaStream_t stream, const TpPush& push) {
   // force_splits: 0 = choose, else the cluster size
   using Cfg = WgtCfg<BLOCK_C, kEpi>;
   CUtensorMap tm_x, tm_w;
@@ -544,7 +552,7 @@ static int launch_weights(const void* x, int ldx, const void* w, int w_rows, int
   if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return -6;
   const int kb_per_split = (num_kb + splits - 1) / splits;
   return launch_kernel(kern, dim3(tiles, splits, tok_tiles), dim3(kGemmThreads), Cfg::kSmemBytes, stream, splits, tm_w, tm_x,
-                       out, ldo, n_out, M, K, kb_per_split, n_out, status) == cudaSuccess ? 0 : -5;
+                       out, ldo, n_out, M, K, kb_per_split, n_out, status, push) == cudaSuccess ? 0 : -5;
 }
 
 // out[M, n_out] = epilogue(X[M, K] * W[*, K]^T).  epi = 0: W has n_out rows.  epi = 1: W is [2 * n_out, K]
@@ -552,8 +560,11 @@ static int launch_weights(const void* x, int ldx, const void* w, int w_rows, int
 // ldx/ldw % 8 == 0.  force_mode: 0 auto, 1 token-tile kernel, 2 weight-tile (decode) kernel (needs M <= 256).
 // tune: 0 auto; else bits 0..7 = cluster size (K splits) and bits 8..15 = token tile (16/32/64/128) of the decode
 // kernel, either may be 0 = choose.  Returns 0 on success.
-extern "C" int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out,
-                               int K, int epi, int force_mode, int tune, unsigned* status, cudaStream_t stream) {
+TpPush make_tp_push(int tp_size, int tp_rank, const long long* slot_ptrs, const long long* signal_ptrs, unsigned* arrive,
+                    unsigned* epoch);
+
+static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K, int epi,
+                         int force_mode, int tune, unsigned* status, cudaStream_t stream, const TpPush& push) {
   const int force_splits = tune & 0xff, force_bc = (tune >> 8) & 0xff;
   if (M <= 0 || n_out <= 0 || K <= 0) return 0;
   if ((K & 7) || (ldx & 7) || (ldw & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
@@ -571,8 +582,8 @@ extern "C" int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, v
 #define FORGE_W(BC)                                                                                                          \
   case BC:                                                                                                                   \
     return epi == kEpiSiluMul                                                                                                \
-               ? launch_weights<BC, kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, force_splits, status, stream) \
-               : launch_weights<BC, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, force_splits, status, stream);
+               ? launch_weights<BC, kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, force_splits, status, stream, push) \
+               : launch_weights<BC, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, force_splits, status, stream, push);
     switch (bc) {
       FORGE_W(16)
       FORGE_W(32)
@@ -582,8 +593,26 @@ extern "C" int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, v
 #undef FORGE_W
     return -6;
   }
+  if (push.size > 1) return -8;   // the token-tile kernel has no push epilogue; callers use the library collective there
   if (epi == kEpiSiluMul) return launch_tokens<128, kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream);
   return launch_tokens<128, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream);
+}
+
+extern "C" int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out,
+                               int K, int epi, int force_mode, int tune, unsigned* status, cudaStream_t stream) {
+  TpPush none = {};
+  return gemm_dispatch(x, ldx, w, ldw, out, ldo, M, n_out, K, epi, force_mode, tune, status, stream, none);
+}
+
+// Row-parallel GEMM whose epilogue pushes the partial sums into slot [tp_rank] of every rank's buffer and signals
+// completion (decode kernel only, M <= 256).  slot_ptrs / signal_ptrs: tp_size addresses in peer order.
+// The row stride of the slots is n_out.
+extern "C" int forge_gemm_bf16_tp_push(const void* x, int ldx, const void* w, int ldw, int M, int n_out, int K, int tune,
+                                       int tp_size, int tp_rank, const long long* slot_ptrs, const long long* signal_ptrs,
+                                       unsigned* arrive, unsigned* epoch, unsigned* status, cudaStream_t stream) {
+  if (tp_size < 2 || tp_size > kMaxTp || M > 256) return -7;
+  const TpPush push = make_tp_push(tp_size, tp_rank, slot_ptrs, signal_ptrs, arrive, epoch);
+  return gemm_dispatch(x, ldx, w, ldw, nullptr, n_out, M, n_out, K, kEpiStore, 2, tune, status, stream, push);
 }
 
 }  // namespace forge

@@ -11,6 +11,21 @@ extern "C" {
 int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K, int epi,
                     int force_mode, int force_splits, unsigned* status, cudaStream_t stream);
 int forge_gemm_set_trace(unsigned long long* buf);
+int forge_gemm_bf16_tp_push(const void* x, int ldx, const void* w, int ldw, int M, int n_out, int K, int tune, int tp_size,
+                            int tp_rank, const long long* slot_ptrs, const long long* signal_ptrs, unsigned* arrive,
+                            unsigned* epoch, unsigned* status, cudaStream_t stream);
+int forge_tp_reduce_rms_norm(int tp_size, int num_slots, const void* slots, long long slot_stride, const unsigned* signal,
+                             const unsigned* epoch, long long timeout_ns, const void* residual_in, void* sum_out, const void* w,
+                             void* y, int rows, int H, float eps, unsigned* status, cudaStream_t stream);
+int forge_tp_embedding_push(const int* ids, const void* w, int T, int H, int vocab_start, int vocab_n, int tp_size, int tp_rank,
+                            const long long* slot_ptrs, const long long* signal_ptrs, unsigned* arrive, unsigned* epoch,
+                            cudaStream_t stream);
+int forge_tp_rows_push(const void* src, int rows, int H, int tp_size, int tp_rank, const long long* slot_ptrs,
+                       const long long* signal_ptrs, unsigned* arrive, unsigned* epoch, cudaStream_t stream);
+int forge_tp_sample_pairs(const float* vals, const int* ids, int rows, int tp_size, int tp_rank, const long long* slot_ptrs,
+                          const long long* signal_ptrs, unsigned* arrive, unsigned* epoch, const void* local_slots,
+                          long long slot_stride, const unsigned* signal_local, long long timeout_ns, int* out_i, unsigned* status,
+                          cudaStream_t stream);
 int forge_rms_norm(const void* x, void* residual, const void* w, void* y, int rows, int H, float eps, cudaStream_t stream);
 int forge_qk_norm_rope_store(const void* qkv, int ld_qkv, const void* qw, const void* kw, float eps, const float* rope,
                              int rope_rows, const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache,
@@ -232,12 +247,93 @@ void prefill_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
         "forge_prefill_attention");
 }
 
+// ---- tensor-parallel exchange.  A "site" is described by plain integers (addresses inside the symmetric
+// allocation, resolved once in Python): slot_ptrs[p] / signal_ptrs[p] = where THIS rank writes in peer p;
+// local_slots / local_signal = where this rank reads; arrive / epoch = two private device words.
+using PtrList = std::vector<int64_t>;
+
+const long long* ptrs(const PtrList& v) { return reinterpret_cast<const long long*>(v.data()); }
+unsigned* word(int64_t addr) { return reinterpret_cast<unsigned*>(addr); }
+
+void gemm_tp_push(const Tensor& x, const Tensor& w, int64_t tune, int64_t tp_rank, const PtrList& slot_ptrs,
+                  const PtrList& signal_ptrs, int64_t arrive, int64_t epoch, const Tensor& status) {
+  CHECK_BF16(x); CHECK_BF16(w);
+  TORCH_CHECK(x.is_cuda() && w.is_cuda() && x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1, "gemm_tp_push: operands");
+  TORCH_CHECK(w.size(1) == x.size(1) && slot_ptrs.size() == signal_ptrs.size() && slot_ptrs.size() >= 2, "gemm_tp_push: shapes");
+  const c10::cuda::CUDAGuard guard(x.device());
+  check(forge_gemm_bf16_tp_push(x.data_ptr(), static_cast<int>(x.stride(0)), w.data_ptr(), static_cast<int>(w.stride(0)),
+                                static_cast<int>(x.size(0)), static_cast<int>(w.size(0)), static_cast<int>(x.size(1)),
+                                static_cast<int>(tune), static_cast<int>(slot_ptrs.size()), static_cast<int>(tp_rank),
+                                ptrs(slot_ptrs), ptrs(signal_ptrs), word(arrive), word(epoch), status_ptr(status), stream_of(x)),
+        "forge_gemm_bf16_tp_push");
+}
+
+// sum_out = sum over slots (+ residual_in); y = rms_norm(sum_out) * w when y is given.
+void tp_reduce_rms_norm(int64_t tp_size, int64_t num_slots, int64_t local_slots, int64_t slot_stride, int64_t local_signal,
+                        int64_t epoch, int64_t timeout_ns, const c10::optional<Tensor>& residual_in, Tensor& sum_out,
+                        const c10::optional<Tensor>& w, const c10::optional<Tensor>& y, double eps, const Tensor& status) {
+  CHECK_CUDA_CONTIG(sum_out); CHECK_BF16(sum_out);
+  const int64_t H = sum_out.size(-1), rows = sum_out.numel() / H;
+  const void* res = nullptr; const void* wp = nullptr; void* yp = nullptr;
+  if (residual_in.has_value()) { CHECK_CUDA_CONTIG(*residual_in); CHECK_BF16(*residual_in); TORCH_CHECK(residual_in->numel() == sum_out.numel()); res = residual_in->data_ptr(); }
+  if (y.has_value()) {
+    TORCH_CHECK(w.has_value(), "tp_reduce_rms_norm: norm weight needed");
+    CHECK_CUDA_CONTIG(*w); CHECK_BF16(*w); CHECK_CUDA_CONTIG(*y); CHECK_BF16(*y);
+    TORCH_CHECK(w->numel() == H && y->numel() == sum_out.numel());
+    wp = w->data_ptr(); yp = y->data_ptr();
+  }
+  const c10::cuda::CUDAGuard guard(sum_out.device());
+  check(forge_tp_reduce_rms_norm(static_cast<int>(tp_size), static_cast<int>(num_slots), reinterpret_cast<const void*>(local_slots),
+                                 slot_stride, word(local_signal), word(epoch), timeout_ns, res, sum_out.data_ptr(), wp, yp,
+                                 static_cast<int>(rows), static_cast<int>(H), static_cast<float>(eps), status_ptr(status),
+                                 stream_of(sum_out)),
+        "forge_tp_reduce_rms_norm");
+}
+
+void tp_embedding_push(const Tensor& ids, const Tensor& w, int64_t vocab_start, int64_t tp_rank, const PtrList& slot_ptrs,
+                       const PtrList& signal_ptrs, int64_t arrive, int64_t epoch) {
+  CHECK_CUDA_CONTIG(ids); CHECK_I32(ids); CHECK_CUDA_CONTIG(w); CHECK_BF16(w);
+  const c10::cuda::CUDAGuard guard(w.device());
+  check(forge_tp_embedding_push(ids.data_ptr<int>(), w.data_ptr(), static_cast<int>(ids.numel()), static_cast<int>(w.size(1)),
+                                static_cast<int>(vocab_start), static_cast<int>(w.size(0)), static_cast<int>(slot_ptrs.size()),
+                                static_cast<int>(tp_rank), ptrs(slot_ptrs), ptrs(signal_ptrs), word(arrive), word(epoch), stream_of(w)),
+        "forge_tp_embedding_push");
+}
+
+void tp_rows_push(const Tensor& src, int64_t tp_rank, const PtrList& slot_ptrs, const PtrList& signal_ptrs, int64_t arrive,
+                  int64_t epoch) {
+  CHECK_CUDA_CONTIG(src); CHECK_BF16(src);
+  const int64_t H = src.size(-1), rows = src.numel() / H;
+  const c10::cuda::CUDAGuard guard(src.device());
+  check(forge_tp_rows_push(src.data_ptr(), static_cast<int>(rows), static_cast<int>(H), static_cast<int>(slot_ptrs.size()),
+                           static_cast<int>(tp_rank), ptrs(slot_ptrs), ptrs(signal_ptrs), word(arrive), word(epoch), stream_of(src)),
+        "forge_tp_rows_push");
+}
+
+void tp_sample_pairs(const Tensor& vals, const Tensor& ids, int64_t tp_rank, const PtrList& slot_ptrs, const PtrList& signal_ptrs,
+                     int64_t arrive, int64_t epoch, int64_t local_slots, int64_t slot_stride, int64_t local_signal,
+                     int64_t timeout_ns, Tensor& out_i, const Tensor& status) {
+  CHECK_CUDA_CONTIG(vals); CHECK_F32(vals); CHECK_CUDA_CONTIG(ids); CHECK_I32(ids); CHECK_CUDA_CONTIG(out_i); CHECK_I32(out_i);
+  TORCH_CHECK(ids.numel() == vals.numel() && out_i.numel() >= vals.numel(), "tp_sample_pairs: lengths");
+  const c10::cuda::CUDAGuard guard(vals.device());
+  check(forge_tp_sample_pairs(vals.data_ptr<float>(), ids.data_ptr<int>(), static_cast<int>(vals.numel()),
+                              static_cast<int>(slot_ptrs.size()), static_cast<int>(tp_rank), ptrs(slot_ptrs), ptrs(signal_ptrs),
+                              word(arrive), word(epoch), reinterpret_cast<const void*>(local_slots), slot_stride, word(local_signal),
+                              timeout_ns, out_i.data_ptr<int>(), status_ptr(status), stream_of(vals)),
+        "forge_tp_sample_pairs");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "tinyllmforge_b200 sm_100a kernels";
   m.def("gemm", &gemm);
   m.def("gemm_set_trace", &gemm_set_trace);
+  m.def("gemm_tp_push", &gemm_tp_push);
+  m.def("tp_reduce_rms_norm", &tp_reduce_rms_norm);
+  m.def("tp_embedding_push", &tp_embedding_push);
+  m.def("tp_rows_push", &tp_rows_push);
+  m.def("tp_sample_pairs", &tp_sample_pairs);
   m.def("rms_norm", &rms_norm);
   m.def("qk_norm_rope_store", &qk_norm_rope_store);
   m.def("silu_mul", &silu_mul);

@@ -237,7 +237,7 @@ class LLMEngine:
             return
         self._closed = True
         try:
-            if self.chan is not None and self.rank == 0:
+            if self.chan is not None and self.rank == 0 and self.procs:      # launcher-mode ranks leave on their own
                 try:
                     self.chan.publish(rpc.KIND_EXIT)
                     self.chan.drain(timeout_s=10.0)

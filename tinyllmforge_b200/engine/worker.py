@@ -87,8 +87,8 @@ class Worker:
                 init_dummy_weights(self.model, config.seed)
             else:
                 load_weights(self.model, config.model)
-            if hasattr(ops, "prepare_model"):
-                ops.prepare_model(self.model)
+            if self.is_cuda and tp.size > 1 and config.comm == "fused":
+                ops.enable_fused_comm(hf.hidden_size, config.max_num_batched_tokens)
             # staging: the largest step is a full prefill (3 token-sized sections) or the widest decode bucket
             max_seqs = config.max_num_seqs
             _, words_prefill = section_offsets(config.max_num_batched_tokens, max_seqs, self.table_width)

@@ -110,22 +110,25 @@ class Qwen3ForCausalLM:
 
     # ------------------------------------------------------------------ forward
     def forward(self, batch) -> torch.Tensor:
-        """Hidden states ``[tokens, hidden]`` after the final norm."""
+        """Hidden states ``[tokens, hidden]`` after the final norm.
+
+        The loop carries ``x`` (the normalised input of the next block) and ``residual``.  Each row-parallel
+        projection is issued together with the cross-rank sum, the residual add and the norm that follows it,
+        so that an op set can fuse the three (``row_linear_add_rms_norm``)."""
+        from ..parallel.symm import SITE_DOWN, SITE_O
         ops = self.ops
-        h = self.embed_tokens.forward(ops, batch.input_ids)
-        residual = None
-        for i, l in enumerate(self.layers):
-            x, residual = ops.add_rms_norm(h, residual, l.input_layernorm, self.eps)
+        layers = self.layers
+        x, residual = ops.embed_norm(batch.input_ids, self.embed_tokens, layers[0].input_layernorm, self.eps)
+        for i, l in enumerate(layers):
             qkv = l.qkv_proj.forward(ops, x)
             kc, vc = self.kv_cache[i, 0], self.kv_cache[i, 1]
             q = ops.qk_norm_rope_store(qkv, l.q_norm, l.k_norm, self.eps, self.rope, batch.positions,
                                        batch.slot_mapping, kc, vc, self.num_heads, self.num_kv_heads, self.head_dim)
             a = ops.attention(q, kc, vc, batch, self.scale)
-            h = l.o_proj.forward(ops, a)
-            x, residual = ops.add_rms_norm(h, residual, l.post_attention_layernorm, self.eps)
-            x = l.gate_up_proj.forward_silu_mul(ops, x)
-            h = l.down_proj.forward(ops, x)
-        x, _ = ops.add_rms_norm(h, residual, self.norm, self.eps)
+            x, residual = ops.row_linear_add_rms_norm(a, l.o_proj, residual, l.post_attention_layernorm, self.eps, SITE_O)
+            g = l.gate_up_proj.forward_silu_mul(ops, x)
+            next_norm = layers[i + 1].input_layernorm if i + 1 < len(layers) else self.norm
+            x, residual = ops.row_linear_add_rms_norm(g, l.down_proj, residual, next_norm, self.eps, SITE_DOWN)
         return x
 
     def compute_logits(self, hidden: torch.Tensor, batch) -> torch.Tensor:

@@ -56,6 +56,7 @@ class CudaOps:
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.use_cublas_gemm = use_cublas_gemm     # bring-up switch for tests; never set by the engine
         self.launches = 0                          # kernels of this library launched so far
+        self.fused = None                          # FusedTPComm once enable_fused_comm() ran
 
     # ------------------------------------------------------------------ status word
     def check_status(self) -> None:
@@ -155,9 +156,56 @@ class CudaOps:
         self.launches += 2 if max_chunks > 1 else 1
         return out
 
-    # ------------------------------------------------------------------ collectives (library path; fused path later)
+    # ------------------------------------------------------------------ tensor-parallel exchange
     def tp_all_reduce(self, y, tp):
+        """Library collective (NCCL): the baseline path and the path of steps too large for the push buffers."""
         return tp.all_reduce(y)
+
+    def enable_fused_comm(self, hidden_size: int, max_tokens: int) -> None:
+        """Allocate the symmetric region; afterwards row-parallel layers, the embedding and the sampler exchange
+        data from inside their kernels."""
+        from ..parallel.symm import FusedTPComm
+        self.fused = FusedTPComm(self.tp, hidden_size, max_tokens, self.device)
+
+    def embed_norm(self, ids, embed, norm_weight, eps):
+        """Embedding lookup + cross-rank exchange + first RMSNorm -> (normed, residual)."""
+        tp = embed.tp
+        if tp.size == 1:
+            return self.add_rms_norm(self.embedding(ids, embed.weight, embed.vocab_start), None, norm_weight, eps)
+        T, H = ids.shape[0], embed.weight.shape[1]
+        if self.fused is None or T > self.fused.max_tokens:
+            h = tp.all_reduce(self.embedding(ids, embed.weight, embed.vocab_start))
+            return self.add_rms_norm(h, None, norm_weight, eps)
+        from ..parallel.symm import SITE_EMBED
+        st = self.fused.sites[SITE_EMBED]
+        self.C.tp_embedding_push(ids, embed.weight, embed.vocab_start, tp.rank, st.slot_ptrs, st.signal_ptrs, st.arrive, st.epoch)
+        residual = torch.empty(T, H, dtype=embed.weight.dtype, device=ids.device)
+        y = torch.empty_like(residual)
+        self.C.tp_reduce_rms_norm(tp.size, 1, st.local_slots, st.slot_stride, st.local_signal, st.epoch, self.fused.timeout_ns,
+                                  None, residual, norm_weight, y, eps, self.status)
+        self.launches += 2
+        return y, residual
+
+    def row_linear_add_rms_norm(self, x, layer, residual, norm_weight, eps, site):
+        """Row-parallel GEMM + sum over ranks + residual add + RMSNorm -> (normed, residual).
+
+        Fused path (decode-sized batches): the GEMM epilogue pushes its partial sums into every rank's slot
+        buffer over NVLink; one consumer kernel waits for all ranks, adds the slots in rank order, adds the
+        residual and normalises.  Larger batches: GEMM, NCCL all-reduce, add + RMSNorm."""
+        tp = layer.tp
+        if tp.size == 1:
+            return self.add_rms_norm(self.linear(x, layer.weight), residual, norm_weight, eps)
+        M = x.shape[0]
+        from ..parallel.symm import MAX_PUSH_ROWS
+        if self.fused is None or M > MAX_PUSH_ROWS:
+            return self.add_rms_norm(tp.all_reduce(self.linear(x, layer.weight)), residual, norm_weight, eps)
+        st = self.fused.sites[site]
+        self.C.gemm_tp_push(x, layer.weight, 0, tp.rank, st.slot_ptrs, st.signal_ptrs, st.arrive, st.epoch, self.status)
+        y = torch.empty(M, layer.weight.shape[0], dtype=x.dtype, device=x.device)
+        self.C.tp_reduce_rms_norm(tp.size, tp.size, st.local_slots, st.slot_stride, st.local_signal, st.epoch, self.fused.timeout_ns,
+                                  residual, residual, norm_weight, y, eps, self.status)
+        self.launches += 2
+        return y, residual
 
     # ------------------------------------------------------------------ sampling
     def sample_shard(self, logits, temperatures, header, vocab_start):
@@ -176,6 +224,14 @@ class CudaOps:
         ids, best = self.sample_shard(logits, batch.temperatures, batch.header, vocab_start)
         if tp.size == 1:
             return ids
+        if self.fused is not None and ids.shape[0] <= 512:
+            from ..parallel.symm import SITE_SAMPLE
+            st = self.fused.sites[SITE_SAMPLE]
+            out = torch.empty_like(ids)
+            self.C.tp_sample_pairs(best, ids, tp.rank, st.slot_ptrs, st.signal_ptrs, st.arrive, st.epoch, st.local_slots,
+                                   st.slot_stride, st.local_signal, self.fused.timeout_ns, out, self.status)
+            self.launches += 2
+            return out
         all_best = tp.all_gather_stack(best)
         all_ids = tp.all_gather_stack(ids)
         out = torch.empty_like(ids)
@@ -184,4 +240,6 @@ class CudaOps:
         return out
 
     def close(self):
-        pass
+        if self.fused is not None:
+            self.fused.close()
+            self.fused = None

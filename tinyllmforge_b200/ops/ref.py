@@ -242,6 +242,16 @@ class RefOps:
         return tp.all_reduce(y)
 
     @staticmethod
+    def embed_norm(ids, embed, norm_weight, eps):
+        h = embed.tp.all_reduce(embedding(ids, embed.weight, embed.vocab_start))
+        return add_rms_norm(h, None, norm_weight, eps)
+
+    @staticmethod
+    def row_linear_add_rms_norm(x, layer, residual, norm_weight, eps, site):
+        h = layer.tp.all_reduce(linear(x, layer.weight))
+        return add_rms_norm(h, residual, norm_weight, eps)
+
+    @staticmethod
     def sample(logits, batch, vocab_start, tp):
         """Token ids [rows] (int64), identical on every rank."""
         ids, best = sample(logits, batch.temperatures, batch.seed, batch.step_index, vocab_start)
