@@ -125,7 +125,7 @@ def run_ours(args) -> dict:
     rank = int(os.environ.get("RANK", "0")) if n > 1 else 0
     prompts, max_tokens = make_workload()
     sps = [SamplingParams(temperature=0.6, ignore_eos=True, max_tokens=m) for m in max_tokens]
-    kw = dict(enforce_eager=False, max_model_len=4096, tensor_parallel_size=n, extra={"device_timing": True})
+    kw = dict(enforce_eager=False, max_model_len=4096, tensor_parallel_size=n, comm=args.comm, extra={"device_timing": True})
     if args.load == "dummy":
         llm = LLM(args.model, hf_config=preset(args.model), load_format="dummy", skip_tokenizer_init=True, **kw)
     else:
@@ -164,7 +164,7 @@ def run_ours(args) -> dict:
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
             "config": {"model": args.model, "global_batch": NUM_SEQS, "seq_len": "prompt U[100,1024] + output U[100,1024]",
-                       "parallelism": f"tp{n}", "weights": "random-init N(0,0.02), seed 0", "step": "one generate() pass over 256 requests",
+                       "parallelism": f"tp{n}", "comm": args.comm if n > 1 else "none", "weights": "random-init N(0,0.02), seed 0", "step": "one generate() pass over 256 requests",
                        "l2": "inputs larger than L2: every engine step streams the weights and the KV cache (> 126 MB)",
                        "timing": "value: sum of per-engine-step CUDA-event times, max over ranks; e2e: wall clock of generate()"},
             "e2e": {"value": total / wall, "unit": "tok/s", "h2d_bytes_per_step": worker.h2d_bytes // args.steps,
@@ -268,6 +268,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default=os.environ.get("FORGE_BENCH_MODEL", "qwen3-0.6b"))
+    ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
+                    help="tensor-parallel exchange: in-kernel NVLink pushes (fused) or torch.distributed/NCCL calls")
     ap.add_argument("--load", default="auto", choices=["auto", "dummy"],
                     help="auto: write and load a safetensors checkpoint; dummy: random-init on the device (large models)")
     args = ap.parse_args()
