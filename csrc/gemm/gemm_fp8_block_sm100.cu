@@ -1,0 +1,226 @@
+// Block-scaled fp8 (e4m3) weight GEMM:  out[M, N] = (Xq * sx)[M, K] * (Wq * sw)[N, K]^T  in bf16, where
+//   Wq  e4m3 weights with one fp32 scale per 128 x 128 block          sw[N / 128][K / 128]
+//   Xq  e4m3 activations with one fp32 scale per token per 128 of K   sx[K / 128][M]   (K-block major)
+// The reference has no quantised path (bf16 only); this is the quantised-weight capability of the engine
+// (`quantization="fp8_block"`), which halves the weight bytes a decode step must stream.
+//
+// tcgen05.mma kind::f8f6f4 multiplies e4m3 x e4m3 into fp32 tensor memory.  Scales differ per 128-wide K block,
+// so products cannot simply accumulate in tensor memory across K: each K block is multiplied into one of TWO
+// tensor-memory buffers (four UMMAs of K = 32), and while the tensor core works on the next block the epilogue
+// warps read the finished buffer, multiply by sw[tile][kb] * sx[kb][token] and accumulate in registers.
+//
+// Orientation as in the bf16 decode kernel: the 128-row UMMA side is a tile of 128 weight rows (= exactly one
+// row of scale blocks), tokens ride the N side in tiles of BLOCK_C.  Grid (N / 128, token tiles).
+// Warp roles: warp 0 TMA producer, warp 1 UMMA issuer + TMEM owner, warps 2..5 scale-accumulate + store.
+#include <cuda_fp8.h>
+
+#include "../include/launch.cuh"
+#include "../include/ptx.cuh"
+
+namespace forge {
+
+constexpr int kF8BlockR = 128;
+constexpr int kF8BlockK = 128;   // 128 e4m3 = one 128-byte swizzle row = one scale block
+constexpr int kF8UmmaK = 32;
+constexpr int kF8Threads = 192;
+
+template <int BLOCK_C>
+struct F8Cfg {
+  static constexpr int kRBytes = kF8BlockR * kF8BlockK;
+  static constexpr int kCBytes = BLOCK_C * kF8BlockK;
+  static constexpr int kStageBytes = kRBytes + kCBytes;
+  static constexpr int kStagesRaw = (192 * 1024) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kTmemCols = 2 * BLOCK_C < 32 ? 32 : (2 * BLOCK_C <= 64 ? 64 : (2 * BLOCK_C <= 128 ? 128 : 256));
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 512 + 2 * 128 * 4;
+};
+
+template <int BLOCK_C>
+__global__ void __launch_bounds__(kF8Threads, 1)
+gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                      const float* __restrict__ w_scale, const float* __restrict__ x_scale, __nv_bfloat16* __restrict__ out,
+                      int ldo, int n_total, int m_total, int K, int x_scale_ld, unsigned* status) {
+  using Cfg = F8Cfg<BLOCK_C>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* empty_bar = full_bar + Cfg::kStages;
+  uint64_t* acc_full = empty_bar + Cfg::kStages;     // [2]
+  uint64_t* acc_empty = acc_full + 2;                // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  float* s_xs = reinterpret_cast<float*>(tmem_slot + 4);   // [2][128] activation scales of the current K block
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r0 = blockIdx.x * kF8BlockR;
+  const int tok0 = blockIdx.y * BLOCK_C;
+  const int num_kb = K / kF8BlockK;
+
+  pdl_launch_dependents();
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&tm_w);
+    prefetch_tensormap(&tm_x);
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);     // one arrival per epilogue warp
+    }
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % Cfg::kStages;
+        const uint32_t ph = (kb / Cfg::kStages) & 1;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1, status)) break;
+        uint8_t* st = smem + s * Cfg::kStageBytes;
+        mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
+        tma_load_2d(st, &tm_w, &full_bar[s], kb * kF8BlockK, r0);
+        tma_load_2d(st + Cfg::kRBytes, &tm_x, &full_bar[s], kb * kF8BlockK, tok0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(kF8BlockR, BLOCK_C, 0, 0);     // e4m3 x e4m3 -> fp32
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % Cfg::kStages;
+        const int buf = kb & 1;
+        if (!mbar_wait(&acc_empty[buf], ((kb >> 1) & 1) ^ 1, status)) break;   // epilogue has drained this buffer
+        if (!mbar_wait(&full_bar[s], (kb / Cfg::kStages) & 1, status)) break;
+        tcgen05_fence_after();
+        const uint32_t st = smem_u32(smem + s * Cfg::kStageBytes);
+#pragma unroll
+        for (int k = 0; k < kF8BlockK / kF8UmmaK; ++k) {
+          const uint32_t koff = k * kF8UmmaK;     // bytes along the 128-byte row
+          umma_f8(tmem_base + buf * BLOCK_C, umma_desc_k_sw128(st + koff), umma_desc_k_sw128(st + Cfg::kRBytes + koff), idesc,
+                  k != 0);
+        }
+        umma_commit(&empty_bar[s]);
+        umma_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int et = quad * 32 + lane;
+    const int r = r0 + et;
+    const int scale_cols = K / kF8BlockK;
+    float acc[BLOCK_C];
+#pragma unroll
+    for (int c = 0; c < BLOCK_C; ++c) acc[c] = 0.f;
+    bool ok = true;
+    for (int kb = 0; kb < num_kb && ok; ++kb) {
+      const int buf = kb & 1;
+      // activation scales of this K block -> shared memory (one value per token of the tile)
+      if (et < BLOCK_C) s_xs[buf * 128 + et] = (tok0 + et < m_total) ? x_scale[static_cast<size_t>(kb) * x_scale_ld + tok0 + et] : 0.f;
+      const float ws = w_scale[static_cast<size_t>(blockIdx.x) * scale_cols + kb];
+      named_barrier_sync(1, 128);
+      ok = mbar_wait(&acc_full[buf], (kb >> 1) & 1, status);
+      tcgen05_fence_after();
+      if (ok) {
+        constexpr int kChunk = BLOCK_C >= 32 ? 32 : 16;
+#pragma unroll
+        for (int cc = 0; cc < BLOCK_C; cc += kChunk) {
+          uint32_t v[kChunk];
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * BLOCK_C + cc;
+          if constexpr (kChunk == 32) tmem_ld_x32(taddr, v); else tmem_ld_x16(taddr, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < kChunk; ++j) acc[cc + j] = fmaf(__uint_as_float(v[j]), ws * s_xs[buf * 128 + cc + j], acc[cc + j]);
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+    if (r < n_total) {
+#pragma unroll
+      for (int c = 0; c < BLOCK_C; ++c)
+        if (tok0 + c < m_total) out[static_cast<size_t>(tok0 + c) * ldo + r] = __float2bfloat16_rn(acc[c]);   // lanes -> consecutive features
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Activation quantiser: one warp per (token, 128-wide K block); scale = amax / 448.
+// ---------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) quant_fp8_1x128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ xq,
+                                                              float* __restrict__ scale, int M, int K, int scale_ld) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int kbs = K >> 7;
+  const long long wid = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  if (wid >= static_cast<long long>(M) * kbs) return;
+  const int lane = threadIdx.x & 31;
+  const int m = static_cast<int>(wid / kbs), kb = static_cast<int>(wid % kbs);
+  const uint2 raw = *reinterpret_cast<const uint2*>(x + static_cast<size_t>(m) * K + kb * 128 + lane * 4);
+  const float f[4] = {bf16_lo(raw.x), bf16_hi(raw.x), bf16_lo(raw.y), bf16_hi(raw.y)};
+  float amax = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3])));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float s = amax > 0.f ? amax / 448.f : 1.f;
+  const float inv = 1.f / s;
+  const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(f[0] * inv, f[1] * inv), __NV_SATFINITE, __NV_E4M3);
+  const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(f[2] * inv, f[3] * inv), __NV_SATFINITE, __NV_E4M3);
+  *reinterpret_cast<uint32_t*>(xq + static_cast<size_t>(m) * K + kb * 128 + lane * 4) = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+  if (lane == 0) scale[static_cast<size_t>(kb) * scale_ld + m] = s;
+}
+
+extern "C" int forge_make_tmap_2d(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                                  uint32_t box_rows, int elem_bytes);
+
+extern "C" int forge_quant_fp8_1x128(const void* x, void* xq, float* scale, int M, int K, int scale_ld, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (K & 127) return -1;
+  const long long warps = static_cast<long long>(M) * (K >> 7);
+  return launch_kernel(quant_fp8_1x128_kernel, dim3(static_cast<unsigned>((warps + 3) / 4)), dim3(128), 0, stream, 0,
+                       static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(xq), scale, M, K, scale_ld) == cudaSuccess ? 0 : -2;
+}
+
+template <int BLOCK_C>
+static int launch_f8(const void* xq, const float* xs, int xs_ld, const void* wq, const float* ws, void* out, int ldo, int M, int N,
+                     int K, unsigned* status, cudaStream_t stream) {
+  using Cfg = F8Cfg<BLOCK_C>;
+  CUtensorMap tm_w, tm_x;
+  if (forge_make_tmap_2d(&tm_w, wq, N, K, K, kF8BlockR, 1) != 0) return -2;
+  if (forge_make_tmap_2d(&tm_x, xq, M, K, K, BLOCK_C, 1) != 0) return -3;
+  auto kern = gemm_fp8_block_kernel<BLOCK_C>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return -4;
+    attr_set = true;
+  }
+  dim3 grid((N + kF8BlockR - 1) / kF8BlockR, (M + BLOCK_C - 1) / BLOCK_C);
+  return launch_kernel(kern, grid, dim3(kF8Threads), Cfg::kSmemBytes, stream, 0, tm_w, tm_x, ws, xs, static_cast<__nv_bfloat16*>(out),
+                       ldo, N, M, K, xs_ld, status) == cudaSuccess ? 0 : -5;
+}
+
+// xq [M, K] e4m3, xs [K / 128][xs_ld >= M]; wq [N, K] e4m3, ws [ceil(N / 128)][K / 128]; out [M, N] bf16 (row stride ldo).
+extern "C" int forge_gemm_fp8_block(const void* xq, const float* xs, int xs_ld, const void* wq, const float* ws, void* out, int ldo,
+                                    int M, int N, int K, unsigned* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((K & 127) || (reinterpret_cast<uintptr_t>(xq) & 15) || (reinterpret_cast<uintptr_t>(wq) & 15)) return -1;
+  if (M <= 16) return launch_f8<16>(xq, xs, xs_ld, wq, ws, out, ldo, M, N, K, status, stream);
+  if (M <= 32) return launch_f8<32>(xq, xs, xs_ld, wq, ws, out, ldo, M, N, K, status, stream);
+  return launch_f8<64>(xq, xs, xs_ld, wq, ws, out, ldo, M, N, K, status, stream);
+}
+
+}  // namespace forge

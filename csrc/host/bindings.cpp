@@ -11,6 +11,9 @@ extern "C" {
 int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K, int epi,
                     int force_mode, int force_splits, unsigned* status, cudaStream_t stream);
 int forge_gemm_set_trace(unsigned long long* buf);
+int forge_quant_fp8_1x128(const void* x, void* xq, float* scale, int M, int K, int scale_ld, cudaStream_t stream);
+int forge_gemm_fp8_block(const void* xq, const float* xs, int xs_ld, const void* wq, const float* ws, void* out, int ldo, int M,
+                         int N, int K, unsigned* status, cudaStream_t stream);
 int forge_gemm_bf16_tp_push(const void* x, int ldx, const void* w, int ldw, int M, int n_out, int K, int tune, int tp_size,
                             int tp_rank, const long long* slot_ptrs, const long long* signal_ptrs, unsigned* arrive,
                             unsigned* epoch, unsigned* status, cudaStream_t stream);
@@ -247,6 +250,33 @@ void prefill_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_c
         "forge_prefill_attention");
 }
 
+// ---- block-scaled fp8: xq/wq are uint8 views of e4m3 data.
+void quant_fp8(const Tensor& x, Tensor& xq, Tensor& scale) {
+  CHECK_CUDA_CONTIG(x); CHECK_BF16(x); CHECK_CUDA_CONTIG(xq); CHECK_CUDA_CONTIG(scale); CHECK_F32(scale);
+  TORCH_CHECK(x.dim() == 2 && xq.numel() == x.numel() && xq.element_size() == 1, "quant_fp8: shapes");
+  const int64_t M = x.size(0), K = x.size(1);
+  TORCH_CHECK(K % 128 == 0 && scale.dim() == 2 && scale.size(0) == K / 128 && scale.size(1) >= M, "quant_fp8: scale must be [K / 128, >= M]");
+  const c10::cuda::CUDAGuard guard(x.device());
+  check(forge_quant_fp8_1x128(x.data_ptr(), xq.data_ptr(), scale.data_ptr<float>(), static_cast<int>(M), static_cast<int>(K),
+                              static_cast<int>(scale.size(1)), stream_of(x)),
+        "forge_quant_fp8_1x128");
+}
+
+void gemm_fp8_block(const Tensor& xq, const Tensor& xs, const Tensor& wq, const Tensor& ws, Tensor& out, const Tensor& status) {
+  CHECK_CUDA_CONTIG(xq); CHECK_CUDA_CONTIG(wq); CHECK_CUDA_CONTIG(xs); CHECK_F32(xs); CHECK_CUDA_CONTIG(ws); CHECK_F32(ws);
+  CHECK_CUDA_CONTIG(out); CHECK_BF16(out);
+  TORCH_CHECK(xq.element_size() == 1 && wq.element_size() == 1 && xq.dim() == 2 && wq.dim() == 2, "gemm_fp8_block: e4m3 operands");
+  const int64_t M = xq.size(0), K = xq.size(1), N = wq.size(0);
+  TORCH_CHECK(wq.size(1) == K && K % 128 == 0 && out.size(0) == M && out.size(1) == N, "gemm_fp8_block: shapes");
+  TORCH_CHECK(xs.dim() == 2 && xs.size(0) == K / 128 && xs.size(1) >= M && ws.dim() == 2 && ws.size(0) == (N + 127) / 128 && ws.size(1) == K / 128,
+              "gemm_fp8_block: scale shapes");
+  const c10::cuda::CUDAGuard guard(xq.device());
+  check(forge_gemm_fp8_block(xq.data_ptr(), xs.data_ptr<float>(), static_cast<int>(xs.size(1)), wq.data_ptr(), ws.data_ptr<float>(),
+                             out.data_ptr(), static_cast<int>(out.stride(0)), static_cast<int>(M), static_cast<int>(N),
+                             static_cast<int>(K), status_ptr(status), stream_of(xq)),
+        "forge_gemm_fp8_block");
+}
+
 // ---- tensor-parallel exchange.  A "site" is described by plain integers (addresses inside the symmetric
 // allocation, resolved once in Python): slot_ptrs[p] / signal_ptrs[p] = where THIS rank writes in peer p;
 // local_slots / local_signal = where this rank reads; arrive / epoch = two private device words.
@@ -329,6 +359,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "tinyllmforge_b200 sm_100a kernels";
   m.def("gemm", &gemm);
   m.def("gemm_set_trace", &gemm_set_trace);
+  m.def("quant_fp8", &quant_fp8);
+  m.def("gemm_fp8_block", &gemm_fp8_block);
   m.def("gemm_tp_push", &gemm_tp_push);
   m.def("tp_reduce_rms_norm", &tp_reduce_rms_norm);
   m.def("tp_embedding_push", &tp_embedding_push);

@@ -82,6 +82,31 @@ def test_gemm_decode_kernel_silu_split_k(ops, M, I, K, splits):
     ops.check_status()
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 128, 128), (16, 1280, 1024), (50, 1024, 3200 - 3200 % 128), (64, 6400, 5120), (200, 1024, 2048), (600, 384, 256)])
+def test_gemm_fp8_block_scaled(ops, M, N, K):
+    """e4m3 weights with 128 x 128 block scales, activations quantised per token and 128 features."""
+    from tinyllmforge_b200.ops.quant import Fp8BlockWeight, linear_fp8_ref, quantize_activations_ref
+    torch.manual_seed(M + N)
+    x, w = _rand(M, K), _rand(N, K, scale=0.05)
+    wq = Fp8BlockWeight.quantize(w)
+    # the CUDA quantiser agrees with the PyTorch statement
+    xq = torch.empty(M, K, dtype=torch.uint8, device="cuda")
+    xs = torch.empty(K // 128, (M + 3) // 4 * 4, dtype=torch.float32, device="cuda")
+    ops.C.quant_fp8(x, xq, xs)
+    q_ref, s_ref = quantize_activations_ref(x)
+    assert torch.allclose(xs[:, :M], s_ref, rtol=1e-6)
+    assert (xq.view(torch.float8_e4m3fn).float() - q_ref.float()).abs().max() <= 32          # at most one e4m3 step at the top of the range
+    out = ops.linear(x, wq)
+    # the GEMM itself, checked on exactly the operands it saw: the CUDA-quantised activations, dequantised in fp32
+    xd = xq.view(torch.float8_e4m3fn).float().view(M, K // 128, 128) * xs[:, :M].t()[..., None]
+    _close(out, xd.view(M, K) @ wq.dequantize().t(), atol=2e-2, rtol=2e-2)
+    _close(out, linear_fp8_ref(x, wq), atol=0.15, rtol=5e-2)          # PyTorch quantiser may round ties differently
+    exact = x.float() @ w.float().t()
+    rel = (out.float() - exact).norm() / exact.norm()
+    assert rel < 0.06, rel                                              # quantisation error itself stays small
+    ops.check_status()
+
+
 def test_gemm_strided_input(ops):
     big = _rand(64, 3 * 256)
     x = big[:, 256:512]          # row stride 768, 16-byte aligned start

@@ -87,6 +87,11 @@ class Worker:
                 init_dummy_weights(self.model, config.seed)
             else:
                 load_weights(self.model, config.model)
+            if config.quantization == "fp8_block":
+                from ..ops.quant import Fp8BlockWeight
+                for l in self.model.layers:          # the four projections of every block; embeddings and LM head stay bf16
+                    for lin in (l.qkv_proj, l.o_proj, l.gate_up_proj, l.down_proj):
+                        lin.weight = Fp8BlockWeight.quantize(lin.weight)
             if self.is_cuda and tp.size > 1 and config.comm == "fused":
                 ops.enable_fused_comm(hf.hidden_size, config.max_num_batched_tokens)
             # staging: the largest step is a full prefill (3 token-sized sections) or the widest decode bucket

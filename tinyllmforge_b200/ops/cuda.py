@@ -15,6 +15,7 @@ import torch
 
 from ..config import Config
 from ..parallel.comm import TPGroup
+from .quant import Fp8BlockWeight
 
 try:
     from .. import _C
@@ -72,6 +73,8 @@ class CudaOps:
                force_block_c: int = 0) -> torch.Tensor:
         """x @ w.T.  ``w`` must not be the output of the kernel launched just before this call: the decode
         kernel starts streaming weights before it waits for its predecessor (weights are static in the engine)."""
+        if isinstance(w, Fp8BlockWeight):
+            return self.linear_fp8(x, w)
         out = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
         if self.use_cublas_gemm:
             return torch.matmul(x, w.t(), out=out)
@@ -81,6 +84,8 @@ class CudaOps:
 
     def linear_silu_mul(self, x: torch.Tensor, w_gate_up: torch.Tensor, force_mode: int = 0, force_splits: int = 0,
                         force_block_c: int = 0) -> torch.Tensor:
+        if isinstance(w_gate_up, Fp8BlockWeight):
+            return self.silu_mul(self.linear_fp8(x, w_gate_up))
         out = torch.empty(x.shape[0], w_gate_up.shape[0] // 2, dtype=x.dtype, device=x.device)
         if self.use_cublas_gemm:
             tmp = torch.matmul(x, w_gate_up.t())
@@ -88,6 +93,18 @@ class CudaOps:
             return out
         self.C.gemm(x, w_gate_up, out, 1, force_mode, force_splits | (force_block_c << 8), self.status)
         self.launches += 1
+        return out
+
+    def linear_fp8(self, x: torch.Tensor, w: "Fp8BlockWeight") -> torch.Tensor:
+        """Block-scaled fp8 GEMM: quantise activations per token and 128 features, multiply on the e4m3 tensor-core
+        path, apply the scales per K block while accumulating."""
+        M, K = x.shape
+        xq = torch.empty(M, K, dtype=torch.uint8, device=x.device)
+        xs = torch.empty(K // 128, (M + 3) // 4 * 4, dtype=torch.float32, device=x.device)
+        self.C.quant_fp8(x, xq, xs)
+        out = torch.empty(M, w.shape[0], dtype=x.dtype, device=x.device)
+        self.C.gemm_fp8_block(xq, xs, w.q.view(torch.uint8), w.scale, out, self.status)
+        self.launches += 2
         return out
 
     # ------------------------------------------------------------------ elementwise
@@ -197,7 +214,7 @@ class CudaOps:
             return self.add_rms_norm(self.linear(x, layer.weight), residual, norm_weight, eps)
         M = x.shape[0]
         from ..parallel.symm import MAX_PUSH_ROWS
-        if self.fused is None or M > MAX_PUSH_ROWS:
+        if self.fused is None or M > MAX_PUSH_ROWS or isinstance(layer.weight, Fp8BlockWeight):
             return self.add_rms_norm(tp.all_reduce(self.linear(x, layer.weight)), residual, norm_weight, eps)
         st = self.fused.sites[site]
         self.C.gemm_tp_push(x, layer.weight, 0, tp.rank, st.slot_ptrs, st.signal_ptrs, st.arrive, st.epoch, self.status)

@@ -69,12 +69,15 @@ def silu_mul(x: torch.Tensor) -> torch.Tensor:
 
 
 # ----------------------------------------------------------------------------- linear
-def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+def linear(x: torch.Tensor, w) -> torch.Tensor:
+    if hasattr(w, "dequantize"):            # block-scaled fp8 weight: same arithmetic as the fp8 kernel
+        from .quant import linear_fp8_ref
+        return linear_fp8_ref(x, w)
     return F.linear(x, w)
 
 
-def linear_silu_mul(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
-    return silu_mul(F.linear(x, w_gate_up))
+def linear_silu_mul(x: torch.Tensor, w_gate_up) -> torch.Tensor:
+    return silu_mul(linear(x, w_gate_up))
 
 
 # ----------------------------------------------------------------------------- KV cache
