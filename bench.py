@@ -184,9 +184,8 @@ def run_reference(args) -> dict:
         return {"impl": "reference", "unavailable": "baseline/_ref/tinyvllm is not installed"}
     n = args.gpus
     rank = int(os.environ.get("RANK", "0")) if n > 1 else 0
-    if n > 1:
-        return {"impl": "reference", "unavailable": "the reference does not start at tensor_parallel_size > 1 as written "
-                "(unhashable worker args, broken Sequence unpickling, un-splatted RPC args, lm-head typo)"} if rank == 0 else None
+    if n > 1 and rank != 0:
+        return None            # the reference spawns its own worker processes from rank 0; the launcher's other ranks stand by
     import torch
     sys.path.insert(0, ref_dir)
     shims = []
@@ -210,6 +209,10 @@ def run_reference(args) -> dict:
             shims.append("transformers>=5 config: restored legacy rope_theta / rope_scaling=None attributes")
         from tinyvllm import LLM, SamplingParams
         from tinyvllm.engine.model_runner import ModelRunner
+        if n > 1:
+            # as written the reference cannot start with more than one GPU: repair the four spots in memory
+            from baseline import ref_repairs
+            shims += ["TP>1 run-time repairs: " + r for r in ref_repairs.apply()]
     except Exception as e:  # missing dependency of the reference
         return {"impl": "reference", "unavailable": f"import failed: {type(e).__name__}: {e}"}
     path = ensure_checkpoint(args.model, 0)
@@ -234,7 +237,7 @@ def run_reference(args) -> dict:
         return out
 
     ModelRunner.run = timed_run
-    llm = LLM(path, enforce_eager=False, max_model_len=4096)
+    llm = LLM(path, enforce_eager=False, max_model_len=4096, tensor_parallel_size=n)
     for _ in range(args.warmup):
         llm.generate(prompts, sps, use_tqdm=False)
     torch.cuda.synchronize()
@@ -249,12 +252,13 @@ def run_reference(args) -> dict:
     clocks = sampler.stop()
     total = args.steps * sum(max_tokens)
     return {
-        "metric": "output_tokens_per_second", "value": total / (acc["ms"] / 1e3), "unit": "tok/s", "n_gpus": 1,
+        "metric": "output_tokens_per_second", "value": total / (acc["ms"] / 1e3), "unit": "tok/s", "n_gpus": n,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": acc["ms"] / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
         "config": {"model": args.model, "global_batch": NUM_SEQS, "seq_len": "prompt U[100,1024] + output U[100,1024]",
-                   "parallelism": "tp1", "weights": "random-init N(0,0.02), seed 0", "step": "one generate() pass over 256 requests",
-                   "l2": "inputs larger than L2", "timing": "value: CUDA events around ModelRunner.run, summed; e2e: wall clock of generate()"},
+                   "parallelism": f"tp{n}", "weights": "random-init N(0,0.02), seed 0", "step": "one generate() pass over 256 requests",
+                   "l2": "inputs larger than L2", "timing": "value: CUDA events around ModelRunner.run on rank 0 (every step ends in a "
+                   "collective and a host sync, so rank 0 spans the slowest rank), summed; e2e: wall clock of generate()"},
         "e2e": {"value": total / wall, "unit": "tok/s", "h2d_bytes_per_step": acc["h2d"] // args.steps,
                 "d2h_bytes_per_step": acc["d2h"] // args.steps, "wall_s_per_step": wall / args.steps},
         "engine_steps_per_pass": acc["steps"] // args.steps, "clocks": clocks, "shims": shims,
