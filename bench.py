@@ -237,7 +237,25 @@ def run_reference(args) -> dict:
         return out
 
     ModelRunner.run = timed_run
+    # Under torchrun the reference's own rendezvous ("tcp://localhost:2333", rank 0 hosts the store) would be turned
+    # into a client of the launcher's agent store by these variables; the reference is its own launcher.
+    for k in [k for k in os.environ if k.startswith("TORCHELASTIC")]:
+        os.environ.pop(k)
+
+    def give_up():       # start-up watchdog: never sit in a rendezvous for the library's default ten minutes
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference engine did not start within {args.ref_start_timeout} s"}), flush=True)
+        try:
+            import psutil
+            for c in psutil.Process(os.getpid()).children(recursive=True):
+                c.kill()
+        finally:
+            os._exit(0)
+    import threading
+    watchdog = threading.Timer(args.ref_start_timeout, give_up)
+    watchdog.daemon = True
+    watchdog.start()
     llm = LLM(path, enforce_eager=False, max_model_len=4096, tensor_parallel_size=n)
+    watchdog.cancel()
     for _ in range(args.warmup):
         llm.generate(prompts, sps, use_tqdm=False)
     torch.cuda.synchronize()
@@ -274,6 +292,7 @@ def main():
     ap.add_argument("--model", default=os.environ.get("FORGE_BENCH_MODEL", "qwen3-0.6b"))
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
                     help="tensor-parallel exchange: in-kernel NVLink pushes (fused) or torch.distributed/NCCL calls")
+    ap.add_argument("--ref-start-timeout", type=float, default=300.0, help="seconds the reference engine gets to start")
     ap.add_argument("--load", default="auto", choices=["auto", "dummy"],
                     help="auto: write and load a safetensors checkpoint; dummy: random-init on the device (large models)")
     args = ap.parse_args()
