@@ -8,6 +8,9 @@ and the four spots are replaced in memory, in the parent and (through ``worker_e
   B2  tinyvllm/engine/sequence.py:75-85  ``__setstate__`` unpacks ``state[-1]`` and assigns a read-only property
   B3  tinyvllm/engine/model_runner.py:104  ``write_shm(method_name, args)`` forgets to splat ``args``
   B4  tinyvllm/layers/embed_head.py:69   ``self.tp.rank`` typo; logits concatenated along the batch, not the vocabulary
+  B14 tinyvllm/layers/linear.py:128-130  QKVParallelLinear hands the PER-RANK output size to a base class that divides
+      by the TP size again, so the parameter is tp times too small and the k/v shards do not fit (found when the
+      repaired engine first reached weight loading at TP = 2)
 
 Each replacement restates the surrounding reference lines with only the defect removed.  Single-GPU runs do not
 use this module.
@@ -60,6 +63,20 @@ def apply() -> list[str]:
         return logits
     embed_head.ParallelLMHead.forward = lm_head_forward
 
+    # B14 ------------------------------------------------------------------------------------------------
+    from tinyvllm.layers import linear
+
+    def qkv_init(self, hidden_size, head_size, total_num_heads, total_num_kv_heads=None, bias=False):
+        self.head_size = head_size
+        self.total_num_heads = total_num_heads
+        self.total_num_kv_heads = total_num_kv_heads or total_num_heads
+        tp_size = dist.get_world_size()
+        self.num_heads = linear.divide(self.total_num_heads, tp_size)
+        self.num_kv_heads = linear.divide(self.total_num_kv_heads, tp_size)
+        output_size = (self.total_num_heads + 2 * self.total_num_kv_heads) * head_size     # full size: the base class shards it
+        linear.ColumnParallelLinear.__init__(self, hidden_size, output_size, bias)
+    linear.QKVParallelLinear.__init__ = qkv_init
+
     # B1 -------------------------------------------------------------------------------------------------
     def engine_init(self, model, **kwargs):
         from dataclasses import fields
@@ -82,7 +99,8 @@ def apply() -> list[str]:
         self.scheduler = llm_engine.Scheduler(config)
         atexit.register(self.exit)
     llm_engine.LLMEngine.__init__ = engine_init
-    return ["B1 worker args tuple", "B2 Sequence pickling", "B3 RPC args splat", "B4 LM-head gather along vocabulary"]
+    return ["B1 worker args tuple", "B2 Sequence pickling", "B3 RPC args splat", "B4 LM-head gather along vocabulary",
+            "B14 QKV parameter size"]
 
 
 def worker_entry(config, rank, event):
