@@ -56,3 +56,34 @@ def test_round_trip_through_bytes():
     raw = sb.buf.tobytes()
     sb2 = StepBatch(np.frombuffer(raw, dtype=np.int32))
     assert sb2.input_ids.tolist() == sb.input_ids.tolist() and sb2.seed == 11 and sb2.step_index == 3
+
+
+def test_incremental_decode_builder_equals_full_rebuild():
+    """Drive a scheduler through a workload; every decode step built incrementally must equal the full build."""
+    import random
+    from tinyllmforge_b200.config import Config, preset
+    from tinyllmforge_b200.engine.scheduler import Scheduler
+    from tinyllmforge_b200.engine.step_batch import DecodeBuilder
+    rng = random.Random(0)
+    cfg = Config("x", hf_config=preset("tiny"), num_kvcache_blocks=400, kvcache_block_size=8, device="cpu",
+                 max_num_seqs=16, max_num_batched_tokens=512, max_model_len=512)
+    s = Scheduler(cfg)
+    for _ in range(12):
+        s.add(Request([rng.randrange(100) for _ in range(rng.randint(3, 40))],
+                      SamplingParams(max_tokens=rng.randint(2, 40), ignore_eos=True)))
+    builder = DecodeBuilder(8)
+    fast = steps = 0
+    while not s.is_finished():
+        reqs, is_prefill = s.schedule()
+        if not is_prefill:
+            for pad, width in ((None, None), (16, 64)):
+                b = DecodeBuilder(8) if pad is None else builder
+                was_cached = b.reqs is not None and b.reqs == reqs
+                got = b.build(reqs, steps, 7, pad, width)
+                want = build_decode(reqs, 8, steps, 7, pad_to=pad, table_width=width)
+                assert got.num_words == want.num_words
+                assert np.array_equal(got.buf[:got.num_words], want.buf[:want.num_words]), steps
+                fast += bool(was_cached)
+        steps += 1
+        s.postprocess(reqs, [rng.randrange(100) for _ in reqs])
+    assert fast > 10

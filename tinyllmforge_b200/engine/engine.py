@@ -32,7 +32,7 @@ from . import rpc
 from .request import Request
 from .scheduler import Scheduler
 from .stats import EngineStats
-from .step_batch import build_decode, build_prefill
+from .step_batch import DecodeBuilder, build_prefill
 from .worker import Worker, follower_loop, follower_main
 
 
@@ -100,6 +100,7 @@ class LLMEngine:
         if self.tokenizer is not None and self.tokenizer.eos_token_id is not None:
             config.eos = self.tokenizer.eos_token_id
         self.scheduler = Scheduler(config) if self.rank == 0 else None
+        self.decode_builder = DecodeBuilder(config.kvcache_block_size)
         atexit.register(self.exit)
 
     # ------------------------------------------------------------------ liveness
@@ -137,9 +138,10 @@ class LLMEngine:
         bs = self.config.kvcache_block_size
         if is_prefill:
             sb = build_prefill(reqs, bs, self.step_index, self.config.seed)
+            self.decode_builder.reset()
         else:
             pad, width = self.worker.decode_padding(len(reqs))
-            sb = build_decode(reqs, bs, self.step_index, self.config.seed, pad_to=pad, table_width=width)
+            sb = self.decode_builder.build(reqs, self.step_index, self.config.seed, pad, width)
         t2 = time.perf_counter()
         try:
             if self.chan is not None:

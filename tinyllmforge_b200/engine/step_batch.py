@@ -179,3 +179,64 @@ def build_decode(reqs, block_size: int, step_index: int = 0, seed: int = 0,
         bt = r.block_table
         tables[i, :len(bt)] = bt
     return StepBatch(buf)
+
+
+class DecodeBuilder:
+    """Builds consecutive decode steps incrementally.
+
+    While the set of running requests does not change (most steps), a decode step differs from the previous one
+    only by: every length + 1, the new input token of every request, and an occasional new block id.  The packed
+    buffer of the previous step is updated in place with a few vector operations instead of being rebuilt from
+    the request objects (the reference rebuilds five Python lists over all sequences every step,
+    tinyvllm/engine/model_runner.py:210-228).  Produces exactly what ``build_decode`` produces.
+    """
+
+    def __init__(self, block_size: int):
+        self.block_size = block_size
+        self.reqs: list | None = None
+        self.sb: StepBatch | None = None
+        self.key = None
+        self.lens = None
+
+    def reset(self) -> None:
+        self.reqs = None
+
+    def build(self, reqs, step_index: int, seed: int, pad_to: int | None, table_width: int | None) -> StepBatch:
+        bs = self.block_size
+        S = len(reqs)
+        if self.reqs is not None and self.key == (pad_to, table_width) and reqs == self.reqs:
+            lens = self.lens
+            lens += 1
+            if table_width is None and int(lens.max()) > self.sb.table_width * bs:
+                self.reqs = None                                    # table would widen: rebuild
+            else:
+                sb = self.sb
+                buf = sb.buf
+                buf[H_STEP] = step_index & 0x7FFFFFFF
+                buf[H_MAXK] = int(lens.max())
+                o, _ = sb.offsets["input_ids"]
+                buf[o:o + S] = [r.token_ids[-1] for r in reqs]
+                o, _ = sb.offsets["positions"]
+                buf[o:o + S] = lens - 1
+                o, _ = sb.offsets["context_lens"]
+                buf[o:o + S] = lens
+                grew = np.nonzero(lens % bs == 1)[0]
+                if grew.size:
+                    to, _ = sb.offsets["block_tables"]
+                    w = sb.table_width
+                    for i in grew.tolist():
+                        bt = reqs[i].block_table
+                        buf[to + i * w + len(bt) - 1] = bt[-1]
+                        self.last_block[i] = bt[-1]
+                o, _ = sb.offsets["slot_mapping"]
+                buf[o:o + S] = self.last_block * bs + (lens - 1) % bs
+                sb.step_index = step_index
+                sb.max_seqlen_k = int(buf[H_MAXK])
+                return sb
+        sb = build_decode(reqs, bs, step_index, seed, pad_to=pad_to, table_width=table_width)
+        self.reqs = list(reqs)
+        self.key = (pad_to, table_width)
+        self.sb = sb
+        self.lens = np.fromiter((len(r) for r in reqs), dtype=np.int64, count=S)
+        self.last_block = np.fromiter((r.block_table[-1] for r in reqs), dtype=np.int64, count=S)
+        return sb

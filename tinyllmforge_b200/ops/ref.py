@@ -70,7 +70,7 @@ def silu_mul(x: torch.Tensor) -> torch.Tensor:
 
 # ----------------------------------------------------------------------------- linear
 def linear(x: torch.Tensor, w) -> torch.Tensor:
-    if hasattr(w, "dequantize"):            # block-scaled fp8 weight: same arithmetic as the fp8 kernel
+    if not isinstance(w, torch.Tensor):     # Fp8BlockWeight: same arithmetic as the fp8 kernel
         from .quant import linear_fp8_ref
         return linear_fp8_ref(x, w)
     return F.linear(x, w)
@@ -196,8 +196,11 @@ def gumbel_noise(rows: int, vocab: int, seed: int, step: int, vocab_start: int =
                       seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
     lane = (ids % 4)[None, :]
     bits = np.choose(np.broadcast_to(lane, outs[0].shape), outs)
-    u = (bits >> np.uint32(8)).astype(np.float32) * np.float32(1.0 / 16777216.0) + np.float32(0.5 / 16777216.0)
-    return -np.log(-np.log(u))
+    # u = (k + 0.5) / 2^24 with k the top 24 bits.  The winners of the arg-max have u close to 1, where fp32 cannot
+    # resolve 1 - u; work from w = 1 - u = (2^24 - k - 0.5) / 2^24 in fp64: E = -log(u) = -log1p(-w), noise = -log(E).
+    k = (bits >> np.uint32(8)).astype(np.float64)
+    w = (16777216.0 - k - 0.5) / 16777216.0
+    return (-np.log(-np.log1p(-w))).astype(np.float32)
 
 
 def sample(logits: torch.Tensor, temperatures: torch.Tensor, seed: int, step: int, vocab_start: int = 0):
