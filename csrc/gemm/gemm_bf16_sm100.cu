@@ -199,18 +199,20 @@ struct WgtCfg {
   static constexpr int kCBytes = BLOCK_C * kBlockK * 2;
   static constexpr int kStageBytes = kNumR * kRBytes + kCBytes;
   static constexpr int kTileBytes = BLOCK_C * kBlockR * 4;        // one fp32 partial tile [BLOCK_C][128]
-  static constexpr int kRecvBytes = kTileBytes;                   // [splits][cols per CTA][128]
-  // the idle ring later holds this CTA's outgoing tile and, for SiLU with several splits, the reduced gate values
-  static constexpr int kRingMin = kTileBytes + (kEpi == kEpiSiluMul ? kTileBytes / 2 : 0);
-  static constexpr int kBudget = 227 * 1024 - 1024 - 256 - kRecvBytes;
+  // Shared memory is kept under half an SM (~98 KB) so that TWO CTAs fit: with programmatic dependent launch the
+  // next GEMM's CTAs become resident while this one still runs and stream their first weight tiles early.
+  // After the main loop the idle ring is reused: [send tile][receive slots][reduced gate values].
+  static constexpr int kEpilogueBytes = BLOCK_C <= 64 ? 2 * kTileBytes + (kEpi == kEpiSiluMul ? kTileBytes / 2 : 0) : kTileBytes;
+  static constexpr int kBudget = 96 * 1024;
   static constexpr int kStagesRaw = kBudget / kStageBytes;
-  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kRingBytes = kStages * kStageBytes > kRingMin ? kStages * kStageBytes : kRingMin;
+  static constexpr int kStages = kStagesRaw > 6 ? 6 : (kStagesRaw < 2 ? 2 : kStagesRaw);
+  static constexpr int kRingBytes = kStages * kStageBytes > kEpilogueBytes ? kStages * kStageBytes : kEpilogueBytes;
+  static constexpr bool kCanSplit = BLOCK_C <= 64;                // wider tiles have no room for receive slots
   static constexpr int kTmemCols = tmem_cols_for(BLOCK_C * kNumR);
-  static constexpr int kSmemBytes = kRingBytes + kRecvBytes + 1024 + 256;
+  static constexpr int kSmemBytes = kRingBytes + 1024 + 256;
   static_assert(BLOCK_C % 16 == 0 && BLOCK_C >= 16 && BLOCK_C <= 128, "token tile of the decode kernel");
   static_assert(kStages >= 2, "need at least a double buffer");
-  static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
+  static_assert(kSmemBytes <= 113 * 1024, "two CTAs per SM");
 };
 
 // out[token, feature] (row stride ldo).  W: [n_total (or 2 * n_total) rows, K]; X: [m_total rows, K].
@@ -226,7 +228,7 @@ struct WgtCfg {
 // SiLU: one split -> combine gate and up on the way out of tensor memory.  Several splits -> the gate sum must
 // be complete before the nonlinearity: round 0 reduces the gate tile into gate_red, round 1 the up tile.
 template <int BLOCK_C, int kEpi>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreads, 2)
 gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                     __nv_bfloat16* __restrict__ out, int ldo, int n_total, int m_total, int K, int kb_per_split,
                     int dual_off, unsigned* status, const TpPush push) {
@@ -236,9 +238,9 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   // addresses name corresponding buffers in all peers.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* send = reinterpret_cast<float*>(smem);                               // [BLOCK_C][128], after the main loop
-  float* gate_red = reinterpret_cast<float*>(smem + Cfg::kTileBytes);         // [cpc][128]
-  float* recv = reinterpret_cast<float*>(smem + Cfg::kRingBytes);             // [nsplit][cpc][128]
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kRingBytes + Cfg::kRecvBytes);
+  float* recv = reinterpret_cast<float*>(smem + Cfg::kTileBytes);             // [nsplit][cpc][128]
+  float* gate_red = reinterpret_cast<float*>(smem + 2 * Cfg::kTileBytes);     // [cpc][128]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kRingBytes);
   uint64_t* empty_bar = full_bar + Cfg::kStages;
   uint64_t* acc_bar = empty_bar + Cfg::kStages;
   uint64_t* recv_bar = acc_bar + 1;
@@ -344,6 +346,10 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     acc_ok = mbar_wait(acc_bar, 0, status);                      // this CTA's ring is idle from here on
     tcgen05_fence_after();
     if (et == 0) trace_point(cta_id, 3);                         // accumulators complete
+  }
+  if (nsplit > 1) {                                              // receive slots alias the ring: every peer's main loop must be over
+    __syncwarp();
+    cluster_sync();
   }
   for (int round = 0; round < rounds; ++round) {
     if (is_epi) {
@@ -549,6 +555,7 @@ static int launch_weights(const void* x, int ldx, const void* w, int w_rows, int
   const int num_kb = (K + kBlockK - 1) / kBlockK;
   int splits = force_splits > 0 ? force_splits : choose_splits(tiles * tok_tiles, num_kb, BLOCK_C);
   if (splits > BLOCK_C / 4) splits = BLOCK_C / 4 < 1 ? 1 : BLOCK_C / 4;   // every CTA reduces >= 4 columns (one per warp)
+  if (!Cfg::kCanSplit) splits = 1;
   if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return -6;
   const int kb_per_split = (num_kb + splits - 1) / splits;
   return launch_kernel(kern, dim3(tiles, splits, tok_tiles), dim3(kGemmThreads), Cfg::kSmemBytes, stream, splits, tm_w, tm_x,

@@ -280,3 +280,27 @@ def test_sampler_distribution(ops):
     freq = torch.bincount(ids.long().cpu(), minlength=vocab).float() / n
     want = torch.softmax(logits[0].float().cpu() / T, -1)
     assert (freq - want).abs().max() < 0.03
+
+
+# ----------------------------------------------------------------------------- bounded waits
+def test_peer_flag_wait_runs_out_and_reports_status(ops):
+    """Failure detection on the device: a consumer waits for a peer that never signals (the flag word is simply
+    never written), gives up after its time limit, sets the status bit, and the context stays usable."""
+    import time
+    H, rows = 1024, 4
+    slots = torch.zeros(2, rows, H, dtype=BF, device="cuda")
+    signal = torch.zeros(8, dtype=torch.int32, device="cuda")
+    epoch = torch.ones(1, dtype=torch.int32, device="cuda")            # this rank claims one completed push ...
+    signal[0] = 1                                                       # ... rank 0's flag is there, rank 1's never arrives
+    out = torch.empty(rows, H, dtype=BF, device="cuda")
+    torch.cuda.synchronize()
+    t0 = time.monotonic()
+    ops.C.tp_reduce_rms_norm(2, 2, slots.data_ptr(), rows * H, signal.data_ptr(), epoch.data_ptr(), int(0.2e9), None, out,
+                             None, None, 1e-6, ops.status)
+    torch.cuda.synchronize()
+    assert 0.15 < time.monotonic() - t0 < 5.0
+    with pytest.raises(RuntimeError, match="peer flag wait ran out"):
+        ops.check_status()
+    ops.check_status()                                                  # the word was cleared; nothing else is wrong
+    x = _rand(8, 1024)
+    assert torch.isfinite(ops.rms_norm(x, torch.ones(1024, dtype=BF, device="cuda"), 1e-6).float()).all()
