@@ -5,7 +5,8 @@
 // four linear layers of a decoder block and the LM head:
 //
 //   gemm_tokens_kernel  (prefill, many tokens): the UMMA's 128-row side is a tile of 128 tokens, the N side a
-//       tile of BLOCK_C output features.  One output tile per CTA.
+//       tile of BLOCK_C output features.  Persistent CTAs, two accumulator sets in tensor memory so the epilogue
+//       of one tile overlaps the main loop of the next.
 //
 //   gemm_weights_kernel (decode, <= 256 tokens): operands swapped.  The 128-row side is a tile of 128 weight
 //       rows, so the weight stream fills the tensor core and no rows are wasted on token padding; up to 128
@@ -46,8 +47,12 @@ __device__ __forceinline__ void trace_point(int cta, int k) {
 constexpr int tmem_cols_for(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
 
 // =========================================================================================================
-// prefill: R = X tile (128 tokens), C = W tile (BLOCK_C features; two tiles for SiLU)
+// prefill: R = X tile (128 tokens), C = W tile (BLOCK_C features; two tiles for SiLU).  Persistent CTAs.
 // =========================================================================================================
+// One CTA per SM walks the output tiles (token tiles fastest, so CTAs running at the same time share weight
+// tiles in L2).  The TMA ring never drains between tiles, and tensor memory holds TWO accumulator sets: while the
+// epilogue warps drain set b (tcgen05.ld -> bf16 -> global), the UMMA warp already fills set b ^ 1 with the next
+// tile.  Plain GEMM: 128 x 256 tiles (2 x 256 TMEM columns).  SiLU: 128 x 128 gate + 128 x 128 up per set.
 template <int BLOCK_C, int kEpi>
 struct TokCfg {
   static constexpr int kNumC = kEpi == kEpiSiluMul ? 2 : 1;
@@ -56,9 +61,11 @@ struct TokCfg {
   static constexpr int kStageBytes = kRBytes + kNumC * kCBytes;
   static constexpr int kStagesRaw = (200 * 1024) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
-  static constexpr int kTmemCols = tmem_cols_for(BLOCK_C * kNumC);
+  static constexpr int kAccCols = BLOCK_C * kNumC;               // TMEM columns of one accumulator set
+  static constexpr int kTmemCols = tmem_cols_for(2 * kAccCols);
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
   static_assert(BLOCK_C % 16 == 0 && BLOCK_C >= 16 && BLOCK_C <= 256, "UMMA N for M = 128");
+  static_assert(2 * kAccCols <= 512, "two accumulator sets must fit tensor memory");
 };
 
 template <int BLOCK_C, int kEpi>
@@ -70,13 +77,14 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
   uint64_t* empty_bar = full_bar + Cfg::kStages;
-  uint64_t* acc_bar = empty_bar + Cfg::kStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+  uint64_t* acc_full = empty_bar + Cfg::kStages;       // [2]
+  uint64_t* acc_empty = acc_full + 2;                  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // consecutive CTAs share the weight tile (blockIdx.x walks the token tiles), so it stays in L2
-  const int r0 = blockIdx.x * kBlockR;
-  const int c0 = blockIdx.y * BLOCK_C;
+  const int m_tiles = (m_total + kBlockR - 1) / kBlockR;
+  const int n_tiles = (n_total + BLOCK_C - 1) / BLOCK_C;
+  const int num_tiles = m_tiles * n_tiles;
   const int num_kb = (K + kBlockK - 1) / kBlockK;
 
   if (warp == 0 && lane == 0) {
@@ -86,7 +94,10 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(acc_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);                     // one arrival per epilogue warp
+    }
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -102,82 +113,104 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % Cfg::kStages;
-        const uint32_t ph = (kb / Cfg::kStages) & 1;
-        if (!mbar_wait(&empty_bar[s], ph ^ 1, status)) break;
-        uint8_t* st = smem + s * Cfg::kStageBytes;
-        mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
-        tma_load_2d(st, &tm_x, &full_bar[s], kb * kBlockK, r0);
-        for (int i = 0; i < Cfg::kNumC; ++i)
-          tma_load_2d(st + Cfg::kRBytes + i * Cfg::kCBytes, &tm_w, &full_bar[s], kb * kBlockK, c0 + i * dual_off);
+      int it = 0;                               // running K-block counter across tiles: the ring never drains
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        const int r0 = (t % m_tiles) * kBlockR, c0 = (t / m_tiles) * BLOCK_C;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % Cfg::kStages;
+          const uint32_t ph = (it / Cfg::kStages) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, status)) { t = num_tiles; break; }
+          uint8_t* st = smem + s * Cfg::kStageBytes;
+          mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
+          tma_load_2d(st, &tm_x, &full_bar[s], kb * kBlockK, r0);
+          for (int i = 0; i < Cfg::kNumC; ++i)
+            tma_load_2d(st + Cfg::kRBytes + i * Cfg::kCBytes, &tm_w, &full_bar[s], kb * kBlockK, c0 + i * dual_off);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc(kBlockR, BLOCK_C, 1, 1);
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % Cfg::kStages;
-        const uint32_t ph = (kb / Cfg::kStages) & 1;
-        if (!mbar_wait(&full_bar[s], ph, status)) break;
+      int it = 0, n = 0;
+      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++n) {
+        const int buf = n & 1;
+        if (!mbar_wait(&acc_empty[buf], ((n >> 1) & 1) ^ 1, status)) break;      // the epilogue has drained this set
         tcgen05_fence_after();
-        const uint32_t st = smem_u32(smem + s * Cfg::kStageBytes);
+        const uint32_t acc_addr = tmem_base + buf * Cfg::kAccCols;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % Cfg::kStages;
+          const uint32_t ph = (it / Cfg::kStages) & 1;
+          if (!mbar_wait(&full_bar[s], ph, status)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t st = smem_u32(smem + s * Cfg::kStageBytes);
 #pragma unroll
-        for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-          const uint32_t koff = k * kUmmaK * 2;
-          const uint32_t acc = (kb | k) != 0;
-          const uint64_t dx = umma_desc_k_sw128(st + koff);
-          umma_f16(tmem_base, dx, umma_desc_k_sw128(st + Cfg::kRBytes + koff), idesc, acc);
-          if constexpr (kEpi == kEpiSiluMul)
-            umma_f16(tmem_base + BLOCK_C, dx, umma_desc_k_sw128(st + Cfg::kRBytes + Cfg::kCBytes + koff), idesc, acc);
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            const uint32_t koff = k * kUmmaK * 2;
+            const uint32_t acc = (kb | k) != 0;
+            const uint64_t dx = umma_desc_k_sw128(st + koff);
+            umma_f16(acc_addr, dx, umma_desc_k_sw128(st + Cfg::kRBytes + koff), idesc, acc);
+            if constexpr (kEpi == kEpiSiluMul)
+              umma_f16(acc_addr + BLOCK_C, dx, umma_desc_k_sw128(st + Cfg::kRBytes + Cfg::kCBytes + koff), idesc, acc);
+          }
+          umma_commit(&empty_bar[s]);
         }
-        umma_commit(&empty_bar[s]);
+        umma_commit(&acc_full[buf]);
+        if (!ok) break;
       }
-      umma_commit(acc_bar);
     }
   } else {
     const int quad = warp & 3;
-    const int r = r0 + quad * 32 + lane;
-    const bool ok = mbar_wait(acc_bar, 0, status);
-    tcgen05_fence_after();
-    if (ok) {
-      constexpr int kChunk = BLOCK_C >= 32 ? 32 : 16;
+    int n = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++n) {
+      const int buf = n & 1;
+      const int r = (t % m_tiles) * kBlockR + quad * 32 + lane;
+      const int c0 = (t / m_tiles) * BLOCK_C;
+      const bool ok = mbar_wait(&acc_full[buf], (n >> 1) & 1, status);
+      tcgen05_fence_after();
+      if (ok) {
+        constexpr int kChunk = BLOCK_C >= 32 ? 32 : 16;
 #pragma unroll 1
-      for (int cc = 0; cc < BLOCK_C; cc += kChunk) {
-        uint32_t v[kChunk];
-        uint32_t u[kEpi == kEpiSiluMul ? kChunk : 1];
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + cc;
-        if constexpr (kChunk == 32) tmem_ld_x32(taddr, v); else tmem_ld_x16(taddr, v);
-        if constexpr (kEpi == kEpiSiluMul) {
-          if constexpr (kChunk == 32) tmem_ld_x32(taddr + BLOCK_C, u); else tmem_ld_x16(taddr + BLOCK_C, u);
-        }
-        tmem_ld_wait();
-        float f[kChunk];
+        for (int cc = 0; cc < BLOCK_C; cc += kChunk) {
+          uint32_t v[kChunk];
+          uint32_t u[kEpi == kEpiSiluMul ? kChunk : 1];
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * Cfg::kAccCols + cc;
+          if constexpr (kChunk == 32) tmem_ld_x32(taddr, v); else tmem_ld_x16(taddr, v);
+          if constexpr (kEpi == kEpiSiluMul) {
+            if constexpr (kChunk == 32) tmem_ld_x32(taddr + BLOCK_C, u); else tmem_ld_x16(taddr + BLOCK_C, u);
+          }
+          tmem_ld_wait();
+          float f[kChunk];
 #pragma unroll
-        for (int j = 0; j < kChunk; ++j) {
-          f[j] = __uint_as_float(v[j]);
-          if constexpr (kEpi == kEpiSiluMul) f[j] = silu(f[j]) * __uint_as_float(u[j]);
-        }
-        const int c = c0 + cc;
-        if (r < m_total) {
-          __nv_bfloat16* dst = out + static_cast<size_t>(r) * ldo + c;
-          if (c + kChunk <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+          for (int j = 0; j < kChunk; ++j) {
+            f[j] = __uint_as_float(v[j]);
+            if constexpr (kEpi == kEpiSiluMul) f[j] = silu(f[j]) * __uint_as_float(u[j]);
+          }
+          const int c = c0 + cc;
+          if (r < m_total) {
+            __nv_bfloat16* dst = out + static_cast<size_t>(r) * ldo + c;
+            if (c + kChunk <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
-            for (int j = 0; j < kChunk; j += 8) {
-              uint4 pk;
-              pk.x = pack_bf16x2(f[j], f[j + 1]);
-              pk.y = pack_bf16x2(f[j + 2], f[j + 3]);
-              pk.z = pack_bf16x2(f[j + 4], f[j + 5]);
-              pk.w = pack_bf16x2(f[j + 6], f[j + 7]);
-              *reinterpret_cast<uint4*>(dst + j) = pk;
+              for (int j = 0; j < kChunk; j += 8) {
+                uint4 pk;
+                pk.x = pack_bf16x2(f[j], f[j + 1]);
+                pk.y = pack_bf16x2(f[j + 2], f[j + 3]);
+                pk.z = pack_bf16x2(f[j + 4], f[j + 5]);
+                pk.w = pack_bf16x2(f[j + 6], f[j + 7]);
+                *reinterpret_cast<uint4*>(dst + j) = pk;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < kChunk; ++j)
+                if (c + j < n_total) dst[j] = __float2bfloat16_rn(f[j]);
             }
-          } else {
-#pragma unroll
-            for (int j = 0; j < kChunk; ++j)
-              if (c + j < n_total) dst[j] = __float2bfloat16_rn(f[j]);
           }
         }
       }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);     // this accumulator set may be overwritten
+      if (!ok) break;
     }
   }
 
@@ -520,7 +553,14 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return -4;
     attr_set = true;
   }
-  dim3 grid((M + kBlockR - 1) / kBlockR, (n_out + BLOCK_C - 1) / BLOCK_C);
+  const int tiles = ((M + kBlockR - 1) / kBlockR) * ((n_out + BLOCK_C - 1) / BLOCK_C);
+  static int num_sms = 0;
+  if (num_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
+  }
+  dim3 grid(tiles < num_sms ? tiles : num_sms);
   return launch_kernel(kern, grid, dim3(kGemmThreads), Cfg::kSmemBytes, stream, 0, tm_x, tm_w, out, ldo, M, n_out, K, n_out,
                        status) == cudaSuccess ? 0 : -5;
 }
@@ -602,6 +642,7 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
   }
   if (push.size > 1) return -8;   // the token-tile kernel has no push epilogue; callers use the library collective there
   if (epi == kEpiSiluMul) return launch_tokens<128, kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream);
+  if (n_out % 256 == 0 || n_out >= 1024) return launch_tokens<256, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream);
   return launch_tokens<128, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream);
 }
 
