@@ -40,6 +40,14 @@ def make_workload():
     return prompts, max_tokens
 
 
+def prompts_for_pass(prompts, p: int):
+    """Pass p of the benchmark: the same lengths (the same work), different token ids, so that the prefix cache
+    cannot serve one pass from the blocks of an earlier one.  Pass 0 is the reference's workload verbatim."""
+    if p == 0:
+        return prompts
+    return [[(t + 7919 * p) % 10001 for t in q] for q in prompts]
+
+
 # ---------------------------------------------------------------------------------------------- clocks
 class ClockSampler:
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
@@ -132,8 +140,10 @@ def run_ours(args) -> dict:
         llm = LLM(ensure_checkpoint(args.model, rank), **kw)
     worker = llm.worker
 
+    passes = iter(range(1 << 30))
+
     def one_pass():
-        return llm.generate(prompts, sps, use_tqdm=False)
+        return llm.generate(prompts_for_pass(prompts, next(passes)), sps, use_tqdm=False)
 
     for _ in range(args.warmup):
         one_pass()
@@ -164,7 +174,7 @@ def run_ours(args) -> dict:
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
             "config": {"model": args.model, "global_batch": NUM_SEQS, "seq_len": "prompt U[100,1024] + output U[100,1024]",
-                       "parallelism": f"tp{n}", "comm": args.comm if n > 1 else "none", "weights": "random-init N(0,0.02), seed 0", "step": "one generate() pass over 256 requests",
+                       "parallelism": f"tp{n}", "comm": args.comm if n > 1 else "none", "weights": "random-init N(0,0.02), seed 0", "step": "one generate() pass over 256 requests; every pass uses fresh token ids of the same lengths (no cross-pass prefix-cache hits)",
                        "l2": "inputs larger than L2: every engine step streams the weights and the KV cache (> 126 MB)",
                        "timing": "value: sum of per-engine-step CUDA-event times, max over ranks; e2e: wall clock of generate()"},
             "e2e": {"value": total / wall, "unit": "tok/s", "h2d_bytes_per_step": worker.h2d_bytes // args.steps,
@@ -256,15 +266,15 @@ def run_reference(args) -> dict:
     watchdog.start()
     llm = LLM(path, enforce_eager=False, max_model_len=4096, tensor_parallel_size=n)
     watchdog.cancel()
-    for _ in range(args.warmup):
-        llm.generate(prompts, sps, use_tqdm=False)
+    for p in range(args.warmup):
+        llm.generate(prompts_for_pass(prompts, p), sps, use_tqdm=False)
     torch.cuda.synchronize()
     sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()
     acc.update(ms=0.0, steps=0, h2d=0, d2h=0)
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        outs = llm.generate(prompts, sps, use_tqdm=False)
+    for p in range(args.steps):
+        outs = llm.generate(prompts_for_pass(prompts, args.warmup + p), sps, use_tqdm=False)
     torch.cuda.synchronize()
     wall = time.perf_counter() - t0
     clocks = sampler.stop()
@@ -274,7 +284,7 @@ def run_reference(args) -> dict:
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": acc["ms"] / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "reference",
         "config": {"model": args.model, "global_batch": NUM_SEQS, "seq_len": "prompt U[100,1024] + output U[100,1024]",
-                   "parallelism": f"tp{n}", "weights": "random-init N(0,0.02), seed 0", "step": "one generate() pass over 256 requests",
+                   "parallelism": f"tp{n}", "weights": "random-init N(0,0.02), seed 0", "step": "one generate() pass over 256 requests; every pass uses fresh token ids of the same lengths (no cross-pass prefix-cache hits)",
                    "l2": "inputs larger than L2", "timing": "value: CUDA events around ModelRunner.run on rank 0 (every step ends in a "
                    "collective and a host sync, so rank 0 spans the slowest rank), summed; e2e: wall clock of generate()"},
         "e2e": {"value": total / wall, "unit": "tok/s", "h2d_bytes_per_step": acc["h2d"] // args.steps,
