@@ -152,8 +152,12 @@ __global__ void __launch_bounds__(128) rows_push_kernel(const __nv_bfloat16* __r
 }
 
 TpPush make_tp_push(int tp_size, int tp_rank, const long long* slot_ptrs, const long long* signal_ptrs, unsigned* arrive,
-                    unsigned* epoch) {
+                    unsigned* epoch, long long mc_slot = 0);
+
+TpPush make_tp_push(int tp_size, int tp_rank, const long long* slot_ptrs, const long long* signal_ptrs, unsigned* arrive,
+                    unsigned* epoch, long long mc_slot) {
   TpPush tp = {};
+  tp.mc_slot = reinterpret_cast<__nv_bfloat16*>(mc_slot);
   tp.size = tp_size;
   tp.rank = tp_rank;
   for (int p = 0; p < tp_size && p < kMaxTp; ++p) {

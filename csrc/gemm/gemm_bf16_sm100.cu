@@ -466,6 +466,12 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
               // Row-parallel layer under tensor parallelism: this rank's partial sums go straight into slot
               // [rank] of EVERY rank's buffer (peer stores over NVLink), tile by tile while other CTAs still
               // compute; the consumer kernel adds the slots up.  Otherwise: a local store.
+              const bool vec_ok = n + 4 <= n_total;
+              if (push.size > 1 && push.mc_slot != nullptr && vec_ok) {
+                // NVLS: one multicast store; the switch writes it into slot [rank] of every rank
+                multimem_st_v2(push.mc_slot + static_cast<size_t>(c) * ldo + n, pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
+                continue;
+              }
               const int ndst = push.size > 1 ? push.size : 1;
               for (int pd = 0; pd < ndst; ++pd) {
                 __nv_bfloat16* dst = (push.size > 1 ? push.slot[pd] : out) + static_cast<size_t>(c) * ldo + n;
@@ -608,7 +614,7 @@ static int launch_weights(const void* x, int ldx, const void* w, int w_rows, int
 // tune: 0 auto; else bits 0..7 = cluster size (K splits) and bits 8..15 = token tile (16/32/64/128) of the decode
 // kernel, either may be 0 = choose.  Returns 0 on success.
 TpPush make_tp_push(int tp_size, int tp_rank, const long long* slot_ptrs, const long long* signal_ptrs, unsigned* arrive,
-                    unsigned* epoch);
+                    unsigned* epoch, long long mc_slot = 0);
 
 static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K, int epi,
                          int force_mode, int tune, unsigned* status, cudaStream_t stream, const TpPush& push) {
@@ -657,9 +663,10 @@ extern "C" int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, v
 // The row stride of the slots is n_out.
 extern "C" int forge_gemm_bf16_tp_push(const void* x, int ldx, const void* w, int ldw, int M, int n_out, int K, int tune,
                                        int tp_size, int tp_rank, const long long* slot_ptrs, const long long* signal_ptrs,
-                                       unsigned* arrive, unsigned* epoch, unsigned* status, cudaStream_t stream) {
+                                       unsigned* arrive, unsigned* epoch, long long mc_slot, unsigned* status, cudaStream_t stream) {
   if (tp_size < 2 || tp_size > kMaxTp || M > 256) return -7;
-  const TpPush push = make_tp_push(tp_size, tp_rank, slot_ptrs, signal_ptrs, arrive, epoch);
+  if (mc_slot != 0 && (n_out & 3)) mc_slot = 0;       // the multicast store writes four features at a time
+  const TpPush push = make_tp_push(tp_size, tp_rank, slot_ptrs, signal_ptrs, arrive, epoch, mc_slot);
   return gemm_dispatch(x, ldx, w, ldw, nullptr, n_out, M, n_out, K, kEpiStore, 2, tune, status, stream, push);
 }
 

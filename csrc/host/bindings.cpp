@@ -16,7 +16,7 @@ int forge_gemm_fp8_block(const void* xq, const float* xs, int xs_ld, const void*
                          int N, int K, unsigned* status, cudaStream_t stream);
 int forge_gemm_bf16_tp_push(const void* x, int ldx, const void* w, int ldw, int M, int n_out, int K, int tune, int tp_size,
                             int tp_rank, const long long* slot_ptrs, const long long* signal_ptrs, unsigned* arrive,
-                            unsigned* epoch, unsigned* status, cudaStream_t stream);
+                            unsigned* epoch, long long mc_slot, unsigned* status, cudaStream_t stream);
 int forge_tp_reduce_rms_norm(int tp_size, int num_slots, const void* slots, long long slot_stride, const unsigned* signal,
                              const unsigned* epoch, long long timeout_ns, const void* residual_in, void* sum_out, const void* w,
                              void* y, int rows, int H, float eps, unsigned* status, cudaStream_t stream);
@@ -286,7 +286,7 @@ const long long* ptrs(const PtrList& v) { return reinterpret_cast<const long lon
 unsigned* word(int64_t addr) { return reinterpret_cast<unsigned*>(addr); }
 
 void gemm_tp_push(const Tensor& x, const Tensor& w, int64_t tune, int64_t tp_rank, const PtrList& slot_ptrs,
-                  const PtrList& signal_ptrs, int64_t arrive, int64_t epoch, const Tensor& status) {
+                  const PtrList& signal_ptrs, int64_t arrive, int64_t epoch, int64_t mc_slot, const Tensor& status) {
   CHECK_BF16(x); CHECK_BF16(w);
   TORCH_CHECK(x.is_cuda() && w.is_cuda() && x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1, "gemm_tp_push: operands");
   TORCH_CHECK(w.size(1) == x.size(1) && slot_ptrs.size() == signal_ptrs.size() && slot_ptrs.size() >= 2, "gemm_tp_push: shapes");
@@ -294,7 +294,7 @@ void gemm_tp_push(const Tensor& x, const Tensor& w, int64_t tune, int64_t tp_ran
   check(forge_gemm_bf16_tp_push(x.data_ptr(), static_cast<int>(x.stride(0)), w.data_ptr(), static_cast<int>(w.stride(0)),
                                 static_cast<int>(x.size(0)), static_cast<int>(w.size(0)), static_cast<int>(x.size(1)),
                                 static_cast<int>(tune), static_cast<int>(slot_ptrs.size()), static_cast<int>(tp_rank),
-                                ptrs(slot_ptrs), ptrs(signal_ptrs), word(arrive), word(epoch), status_ptr(status), stream_of(x)),
+                                ptrs(slot_ptrs), ptrs(signal_ptrs), word(arrive), word(epoch), mc_slot, status_ptr(status), stream_of(x)),
         "forge_gemm_bf16_tp_push");
 }
 

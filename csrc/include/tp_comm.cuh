@@ -35,6 +35,7 @@ struct TpPush {
   int size;                              // <= 1: not tensor-parallel, fields below unused
   int rank;
   __nv_bfloat16* slot[kMaxTp];           // peer p: base of slot [rank] inside p's slot buffer
+  __nv_bfloat16* mc_slot;                // NVLS multicast address of slot [rank] (one store lands on every rank), or null
   unsigned* signal[kMaxTp];              // peer p: address of word [rank] in p's signal array of this site
   unsigned* arrive;                      // local: CTAs finished in the current launch
   unsigned* epoch;                       // local: completed pushes of this rank at this site
@@ -58,6 +59,10 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
 }
 __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// One 8-byte store through the NVSwitch multicast address: the switch replicates it into every rank's copy.
+__device__ __forceinline__ void multimem_st_v2(void* mc_addr, uint32_t a, uint32_t b) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(mc_addr), "f"(__uint_as_float(a)), "f"(__uint_as_float(b)) : "memory");
 }
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;

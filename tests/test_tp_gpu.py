@@ -72,6 +72,8 @@ def case_row_linear(rank, world):
     ops, tp = _ops(rank, world)
     H, Kfull = 1024, 2048
     ops.enable_fused_comm(H, 4096)
+    if rank == 0:
+        print("NVLS multicast address:", hex(ops.fused.multicast_ptr), flush=True)
     g = torch.Generator(device="cuda").manual_seed(1)           # same stream of numbers on every rank
     w_full = (torch.randn(H, Kfull, device="cuda", generator=g) * 0.05).bfloat16()
     norm_w = (1 + 0.1 * torch.randn(H, device="cuda", generator=g)).bfloat16()

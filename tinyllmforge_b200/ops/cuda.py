@@ -217,7 +217,7 @@ class CudaOps:
         if self.fused is None or M > MAX_PUSH_ROWS or isinstance(layer.weight, Fp8BlockWeight):
             return self.add_rms_norm(tp.all_reduce(self.linear(x, layer.weight)), residual, norm_weight, eps)
         st = self.fused.sites[site]
-        self.C.gemm_tp_push(x, layer.weight, 0, tp.rank, st.slot_ptrs, st.signal_ptrs, st.arrive, st.epoch, self.status)
+        self.C.gemm_tp_push(x, layer.weight, 0, tp.rank, st.slot_ptrs, st.signal_ptrs, st.arrive, st.epoch, st.mc_slot, self.status)
         y = torch.empty(M, layer.weight.shape[0], dtype=x.dtype, device=x.device)
         self.C.tp_reduce_rms_norm(tp.size, tp.size, st.local_slots, st.slot_stride, st.local_signal, st.epoch, self.fused.timeout_ns,
                                   residual, residual, norm_weight, y, eps, self.status)

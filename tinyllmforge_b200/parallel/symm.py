@@ -16,6 +16,7 @@ Replaces the NCCL calls at tinyvllm/layers/linear.py:183 and tinyvllm/layers/emb
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import torch
@@ -42,6 +43,7 @@ class Site:
     local_signal: int
     arrive: int
     epoch: int
+    mc_slot: int = 0           # NVLS multicast address of this rank's slot (0: no multicast support)
 
 
 class FusedTPComm:
@@ -65,6 +67,8 @@ class FusedTPComm:
         self.handle = symm_mem.rendezvous(self.region, group=tp.group)
         self.bases = [int(p) for p in self.handle.buffer_ptrs]
         self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        if os.environ.get("FORGE_NVLS", "1") == "0":
+            self.multicast_ptr = 0
         self.counters = torch.zeros(2 * NUM_SITES, dtype=torch.int32, device=device)     # private: arrive, epoch per site
         torch.cuda.synchronize()
         tp.barrier()                       # nobody pushes before every region is zeroed
@@ -79,7 +83,8 @@ class FusedTPComm:
                 signal_ptrs=[b + off["signals"] + (index * 8 + self.rank) * 4 for b in self.bases],
                 local_slots=me + off[name], slot_stride=slot_bytes // 2, num_slots=1 if shared_slot else self.size,
                 local_signal=me + off["signals"] + index * 8 * 4,
-                arrive=cbase + (2 * index) * 4, epoch=cbase + (2 * index + 1) * 4)
+                arrive=cbase + (2 * index) * 4, epoch=cbase + (2 * index + 1) * 4,
+                mc_slot=(self.multicast_ptr + off[name] + (0 if shared_slot else self.rank * slot_bytes)) if self.multicast_ptr else 0)
 
         self.sites = {
             SITE_EMBED: site(SITE_EMBED, "embed", max_tokens * H * 2, shared_slot=True),
