@@ -577,8 +577,12 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
 // tiles are kept small (<= 64 tokens when splitting) and the split count is the largest power of two that
 // keeps the grid within ~one wave, leaves each split >= 2 K blocks and each CTA >= 4 columns to reduce.
 static int choose_splits(int ctas_unsplit, int num_kb, int block_c) {
+  // two CTAs fit per SM, so small token tiles (cheap exchange) may use up to two CTAs per SM: fewer K blocks per
+  // CTA means the whole K slice is prefetched into the ring before the predecessor kernel has finished
+  static const int small_limit = std::getenv("FORGE_SPLIT_LIMIT") ? std::atoi(std::getenv("FORGE_SPLIT_LIMIT")) : 296;
+  const int limit = block_c <= 32 ? small_limit : 160;
   int s = 1;
-  while (s < 8 && ctas_unsplit * s * 2 <= 160 && num_kb / (s * 2) >= 2 && s * 2 <= block_c / 4) s *= 2;
+  while (s < 8 && ctas_unsplit * s * 2 <= limit && num_kb / (s * 2) >= 2 && s * 2 <= block_c / 4) s *= 2;
   return s;
 }
 
