@@ -131,75 +131,111 @@ extern "C" int forge_rms_norm(const void* x, void* residual, const void* w, void
 // Lane l owns elements {l*E .. l*E+E-1} of the first half and the same of the second half (E = D / 64),
 // i.e. exactly the pairs the rotation mixes.
 // ---------------------------------------------------------------------------------------------------------
+// E consecutive bf16 values as one memory access.
+template <int E> struct BfVec;
+template <> struct BfVec<1> { using T = unsigned short; };
+template <> struct BfVec<2> { using T = uint32_t; };
+template <> struct BfVec<4> { using T = uint2; };
+
+template <int E>
+__device__ __forceinline__ void load_bf(const __nv_bfloat16* p, float* f) {
+  const typename BfVec<E>::T raw = *reinterpret_cast<const typename BfVec<E>::T*>(p);
+  if constexpr (E == 1) {
+    f[0] = __uint_as_float(static_cast<uint32_t>(raw) << 16);
+  } else if constexpr (E == 2) {
+    f[0] = bf16_lo(raw); f[1] = bf16_hi(raw);
+  } else {
+    f[0] = bf16_lo(raw.x); f[1] = bf16_hi(raw.x); f[2] = bf16_lo(raw.y); f[3] = bf16_hi(raw.y);
+  }
+}
+template <int E>
+__device__ __forceinline__ void store_bf(__nv_bfloat16* p, const float* f) {
+  if constexpr (E == 1) {
+    *p = __float2bfloat16_rn(f[0]);
+  } else if constexpr (E == 2) {
+    *reinterpret_cast<uint32_t*>(p) = pack_bf16x2(f[0], f[1]);
+  } else {
+    *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]));
+  }
+}
+
+// One warp handles `hpw` consecutive heads of one token, so the token's position, slot and its cos/sin row are
+// fetched once per warp (the table row is twice the size of a head).
 template <int D>
 __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(
     const __nv_bfloat16* __restrict__ qkv, int ld_qkv, const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
     float eps, const float* __restrict__ rope, int rope_rows, const int* __restrict__ positions, const int* __restrict__ slots,
     __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
-    int T, int nq, int nkv, int block_size, long long num_slots, int do_rope, unsigned* status) {
+    int T, int nq, int nkv, int block_size, long long num_slots, int do_rope, int hpw, unsigned* status) {
   constexpr int E = D / 64;           // elements per lane per half
   static_assert(D == 64 || D == 128 || D == 256, "head_dim");
   pdl_launch_dependents();
   pdl_wait();
   const int heads = nq + 2 * nkv;
+  const int groups = (heads + hpw - 1) / hpw;
   const long long wid = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (wid >= static_cast<long long>(T) * heads) return;
+  if (wid >= static_cast<long long>(T) * groups) return;
   const int lane = threadIdx.x & 31;
-  const int t = static_cast<int>(wid / heads);
-  const int h = static_cast<int>(wid % heads);
-  const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * ld_qkv + static_cast<size_t>(h) * D;
+  const int t = static_cast<int>(wid / groups);
+  const int h_begin = static_cast<int>(wid % groups) * hpw;
+  const int h_end = min(h_begin + hpw, heads);
 
-  float a[E], b[E];   // first-half and second-half elements
+  float cosv[E], sinv[E], wq1[E], wq2[E], wk1[E], wk2[E];
+  if (do_rope) {
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= rope_rows ? rope_rows - 1 : pos);
+    const float* cs = rope + static_cast<size_t>(pos) * D;
 #pragma unroll
-  for (int e = 0; e < E; ++e) {
-    a[e] = __bfloat162float(src[lane * E + e]);
-    b[e] = __bfloat162float(src[D / 2 + lane * E + e]);
+    for (int e = 0; e < E; ++e) {
+      cosv[e] = cs[lane * E + e];
+      sinv[e] = cs[D / 2 + lane * E + e];
+    }
   }
-  const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
-  if (is_q || is_k) {
-    const __nv_bfloat16* w = is_q ? qw : kw;
-    if (w != nullptr) {
-      float ss = 0.f;
+  if (qw != nullptr) { load_bf<E>(qw + lane * E, wq1); load_bf<E>(qw + D / 2 + lane * E, wq2); }
+  if (kw != nullptr) { load_bf<E>(kw + lane * E, wk1); load_bf<E>(kw + D / 2 + lane * E, wk2); }
+  const long long slot = slots[t];
+  const bool slot_ok = slot >= 0 && slot < num_slots;
+  if (slot >= num_slots && lane == 0) set_status(status, kStatusBadIndex);
+
+  for (int h = h_begin; h < h_end; ++h) {
+    const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * ld_qkv + static_cast<size_t>(h) * D;
+    float a[E], b[E];   // first-half and second-half elements: exactly the pairs the rotation mixes
+    load_bf<E>(src + lane * E, a);
+    load_bf<E>(src + D / 2 + lane * E, b);
+    const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+    if (is_q || is_k) {
+      const bool has_w = is_q ? qw != nullptr : kw != nullptr;
+      if (has_w) {
+        float ss = 0.f;
 #pragma unroll
-      for (int e = 0; e < E; ++e) ss += a[e] * a[e] + b[e] * b[e];
-      const float inv = rsqrtf(warp_sum(ss) / static_cast<float>(D) + eps);
+        for (int e = 0; e < E; ++e) ss += a[e] * a[e] + b[e] * b[e];
+        const float inv = rsqrtf(warp_sum(ss) / static_cast<float>(D) + eps);
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
-        a[e] = bf16_round(bf16_round(a[e] * inv) * __bfloat162float(w[lane * E + e]));
-        b[e] = bf16_round(bf16_round(b[e] * inv) * __bfloat162float(w[D / 2 + lane * E + e]));
+        for (int e = 0; e < E; ++e) {
+          a[e] = bf16_round(bf16_round(a[e] * inv) * (is_q ? wq1[e] : wk1[e]));
+          b[e] = bf16_round(bf16_round(b[e] * inv) * (is_q ? wq2[e] : wk2[e]));
+        }
+      }
+      if (do_rope) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const float x1 = a[e], x2 = b[e];
+          a[e] = x1 * cosv[e] - x2 * sinv[e];
+          b[e] = x2 * cosv[e] + x1 * sinv[e];
+        }
       }
     }
-    if (do_rope) {
-      int pos = positions[t];
-      pos = pos < 0 ? 0 : (pos >= rope_rows ? rope_rows - 1 : pos);
-      const float* cs = rope + static_cast<size_t>(pos) * D;
-#pragma unroll
-      for (int e = 0; e < E; ++e) {
-        const float c = cs[lane * E + e], s = cs[D / 2 + lane * E + e];
-        const float x1 = a[e], x2 = b[e];
-        a[e] = x1 * c - x2 * s;
-        b[e] = x2 * c + x1 * s;
-      }
+    __nv_bfloat16* dst;
+    if (is_q) {
+      dst = q_out + (static_cast<size_t>(t) * nq + h) * D;
+    } else {
+      if (!slot_ok) continue;
+      const int kvh = is_k ? h - nq : h - nq - nkv;
+      const long long blk = slot / block_size, off = slot % block_size;
+      dst = (is_k ? k_cache : v_cache) + ((blk * nkv + kvh) * block_size + off) * D;
     }
-  }
-  __nv_bfloat16* dst;
-  if (is_q) {
-    dst = q_out + (static_cast<size_t>(t) * nq + h) * D;
-  } else {
-    const long long slot = slots[t];
-    if (slot < 0) return;
-    if (slot >= num_slots) {
-      if (lane == 0) set_status(status, kStatusBadIndex);
-      return;
-    }
-    const int kvh = is_k ? h - nq : h - nq - nkv;
-    const long long blk = slot / block_size, off = slot % block_size;
-    dst = (is_k ? k_cache : v_cache) + ((blk * nkv + kvh) * block_size + off) * D;
-  }
-#pragma unroll
-  for (int e = 0; e < E; ++e) {
-    dst[lane * E + e] = __float2bfloat16_rn(a[e]);
-    dst[D / 2 + lane * E + e] = __float2bfloat16_rn(b[e]);
+    store_bf<E>(dst + lane * E, a);
+    store_bf<E>(dst + D / 2 + lane * E, b);
   }
 }
 
@@ -209,7 +245,9 @@ extern "C" int forge_qk_norm_rope_store(const void* qkv, int ld_qkv, const void*
                                         int block_size, long long num_slots, int do_rope, unsigned* status,
                                         cudaStream_t stream) {
   if (T <= 0) return 0;
-  const long long warps = static_cast<long long>(T) * (nq + 2 * nkv);
+  const int heads = nq + 2 * nkv;
+  const int hpw = T >= 4096 ? 8 : (T >= 1024 ? 4 : 1);        // heads per warp: amortise the per-token loads when there is enough work
+  const long long warps = static_cast<long long>(T) * ((heads + hpw - 1) / hpw);
   const int grid = static_cast<int>((warps + 3) / 4);
   cudaError_t e;
 #define FORGE_QK(DD)                                                                                                      \
@@ -217,7 +255,7 @@ extern "C" int forge_qk_norm_rope_store(const void* qkv, int ld_qkv, const void*
                     static_cast<const __nv_bfloat16*>(qkv), ld_qkv, static_cast<const __nv_bfloat16*>(qw),               \
                     static_cast<const __nv_bfloat16*>(kw), eps, rope, rope_rows, positions, slots,                       \
                     static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),                            \
-                    static_cast<__nv_bfloat16*>(v_cache), T, nq, nkv, block_size, num_slots, do_rope, status)
+                    static_cast<__nv_bfloat16*>(v_cache), T, nq, nkv, block_size, num_slots, do_rope, hpw, status)
   if (D == 128) FORGE_QK(128);
   else if (D == 64) FORGE_QK(64);
   else if (D == 256) FORGE_QK(256);

@@ -628,7 +628,11 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
     return -1;
   const int w_rows = epi == kEpiSiluMul ? 2 * n_out : n_out;
   __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
-  const bool decode = force_mode == 2 || (force_mode == 0 && M <= 256);
+  // Few tokens -> the weight-tile (decode) kernel, except for very wide layers (the LM head: ~1200 feature tiles), where the
+  // persistent token-tile kernel streams weights best: its ring never drains between tiles and its epilogue overlaps
+  // the next tile (measured 58-91 us vs 60-182 us for 8..256 tokens x 151936 x 1024; cuBLAS 55-83 us).
+  const bool wide = (n_out + kBlockR - 1) / kBlockR >= 296 && epi == kEpiStore && push.size <= 1 && M >= 8;
+  const bool decode = force_mode == 2 || (force_mode == 0 && M <= 256 && !wide);
   if (decode) {
     if (M > 256) return -7;
     // token tile: few feature tiles -> small token tiles (parallelism, cheap exchange; extra token tiles re-read the
