@@ -338,4 +338,22 @@ extern "C" int forge_gather_rows(const int* idx, const void* x, void* out, int S
                        static_cast<__nv_bfloat16*>(out), H, x_rows) == cudaSuccess ? 0 : -2;
 }
 
+// ids[i] = prev_tokens[src_rows[i]] where src_rows[i] >= 0: the input token of a sequence is the token the previous
+// step sampled for it, taken on the device so that the host can run one step ahead of the results it reads back.
+__global__ void __launch_bounds__(128) feed_tokens_kernel(int* __restrict__ ids, const int* __restrict__ src_rows,
+                                                          const int* __restrict__ prev_tokens, int n, int prev_n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int s = src_rows[i];
+  if (s >= 0 && s < prev_n) ids[i] = prev_tokens[s];
+}
+
+extern "C" int forge_feed_tokens(int* ids, const int* src_rows, const int* prev_tokens, int n, int prev_n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  return launch_kernel(feed_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, 0, ids, src_rows, prev_tokens, n, prev_n) ==
+                 cudaSuccess ? 0 : -2;
+}
+
 }  // namespace forge

@@ -37,6 +37,7 @@ int forge_qk_norm_rope_store(const void* qkv, int ld_qkv, const void* qw, const 
 int forge_silu_mul(const void* x, void* out, long long rows, int I, cudaStream_t stream);
 int forge_embedding(const int* ids, const void* w, void* out, int T, int H, int vocab_start, int vocab_n, cudaStream_t stream);
 int forge_gather_rows(const int* idx, const void* x, void* out, int S, int H, int x_rows, cudaStream_t stream);
+int forge_feed_tokens(int* ids, const int* src_rows, const int* prev_tokens, int n, int prev_n, cudaStream_t stream);
 int forge_sample_nsplit(int rows, int vocab);
 int forge_sample(const void* logits, int ld, int rows, int vocab, int vocab_start, const float* temps, const int* header,
                  float* part_v, int* part_i, int nsplit, int* out_i, float* out_v, cudaStream_t stream);
@@ -166,6 +167,15 @@ void gather_rows(const Tensor& idx, const Tensor& x, Tensor& out) {
   check(forge_gather_rows(idx.data_ptr<int>(), x.data_ptr(), out.data_ptr(), static_cast<int>(S), static_cast<int>(H),
                           static_cast<int>(x.size(0)), stream_of(x)),
         "forge_gather_rows");
+}
+
+void feed_tokens(Tensor& ids, const Tensor& src_rows, const Tensor& prev_tokens) {
+  CHECK_CUDA_CONTIG(ids); CHECK_I32(ids); CHECK_CUDA_CONTIG(src_rows); CHECK_I32(src_rows); CHECK_CUDA_CONTIG(prev_tokens); CHECK_I32(prev_tokens);
+  TORCH_CHECK(src_rows.numel() >= ids.numel(), "feed_tokens: src_rows too short");
+  const c10::cuda::CUDAGuard guard(ids.device());
+  check(forge_feed_tokens(ids.data_ptr<int>(), src_rows.data_ptr<int>(), prev_tokens.data_ptr<int>(), static_cast<int>(ids.numel()),
+                          static_cast<int>(prev_tokens.numel()), stream_of(ids)),
+        "forge_feed_tokens");
 }
 
 int64_t sample_nsplit(int64_t rows, int64_t vocab) { return forge_sample_nsplit(static_cast<int>(rows), static_cast<int>(vocab)); }
@@ -371,6 +381,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("silu_mul", &silu_mul);
   m.def("embedding", &embedding);
   m.def("gather_rows", &gather_rows);
+  m.def("feed_tokens", &feed_tokens);
   m.def("sample_nsplit", &sample_nsplit);
   m.def("sample", &sample);
   m.def("sample_merge_ranks", &sample_merge_ranks);

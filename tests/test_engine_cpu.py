@@ -147,3 +147,27 @@ def test_dead_follower_is_reported_not_hung(ckpt, prompts):
         assert time.monotonic() - t0 < 60
     finally:
         llm.exit()
+
+
+def test_pipelined_loop_equals_step_by_step_loop(ckpt):
+    """The loop that schedules step t+1 before it reads step t's tokens (used when no request can stop on a token
+    value) must produce the same tokens as the plain loop: sampling, different lengths, a KV pool small enough to
+    force preemption, and a prompt that shares a prefix produced by an earlier decode."""
+    rng = random.Random(5)
+    prompts = [[rng.randrange(4096) for _ in range(rng.randint(5, 70))] for _ in range(6)]
+    sps = [SamplingParams(temperature=0.8 if i % 2 else 0.0, max_tokens=20 + 7 * i, ignore_eos=True) for i in range(6)]
+    results = {}
+    for pipelined in (True, False):
+        llm = _llm(ckpt, num_kvcache_blocks=14, max_num_seqs=4, seed=3, extra={"pipeline": pipelined})
+        outs = llm.generate(prompts, sps, use_tqdm=False)
+        first = [o["token_ids"] for o in outs]
+        # second call: prompt + completion of the first call -> its sealed decode blocks must be reusable and right
+        again = llm.generate([prompts[0] + first[0]], SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True), use_tqdm=False)
+        llm.scheduler.pool.check_invariants()
+        results[pipelined] = (first, again[0]["token_ids"], llm.stats.to_dict())
+        llm.exit()
+    assert results[True][0] == results[False][0]
+    assert results[True][1] == results[False][1]
+    assert results[True][2]["preemptions"] > 0
+    assert all(len(t) == sp.max_tokens for t, sp in zip(results[True][0], sps))
+    assert all(tok >= 0 for t in results[True][0] for tok in t)

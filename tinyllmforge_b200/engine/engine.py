@@ -30,7 +30,7 @@ from ..parallel.comm import TPGroup, find_free_port
 from ..sampling_params import SamplingParams
 from . import rpc
 from .request import Request
-from .scheduler import Scheduler
+from .scheduler import PLACEHOLDER, Scheduler
 from .stats import EngineStats
 from .step_batch import DecodeBuilder, build_prefill
 from .worker import Worker, follower_loop, follower_main
@@ -207,7 +207,10 @@ class LLMEngine:
         ids = [self.add_request(p, sp) for p, sp in zip(prompts, sampling_params)]
         outputs: dict[int, list[int]] = {}
         prefill_tps = decode_tps = 0.0
+        pipelined = self._can_pipeline()
         try:
+            if pipelined:
+                self._run_pipelined(outputs, pbar)
             while not self.is_finished():
                 t = time.perf_counter()
                 finished, count = self.step()
@@ -232,6 +235,88 @@ class LLMEngine:
             text = self.tokenizer.decode(toks) if self.tokenizer is not None else ""
             result.append({"text": text, "token_ids": toks})
         return result
+
+    # ------------------------------------------------------------------ pipelined loop
+    def _can_pipeline(self) -> bool:
+        """The host may run one step ahead of the tokens it reads back when no request can end on a token VALUE:
+        every queued request ignores EOS (or there is no EOS id).  Lengths, finish-by-max_tokens, block growth and
+        slots do not depend on token values; the values themselves travel device-to-device."""
+        if not self.config.extra.get("pipeline", True):
+            return False
+        sch = self.scheduler
+        return all(r.ignore_eos or self.config.eos < 0 for q in (sch.waiting, sch.running) for r in q)
+
+    def _run_pipelined(self, outputs: dict, pbar) -> None:
+        """schedule/build/launch step t+1, THEN read step t's tokens: scheduling, building, publishing and output
+        handling overlap with the GPU.  Prefill steps are launched only when nothing is in flight (a preempted
+        request must have all its real tokens before it is prefilled again)."""
+        sch, st, bs = self.scheduler, self.stats, self.config.kvcache_block_size
+        inflight = None             # (reqs, ticket, finished requests) of the step not yet read back
+
+        def drain():
+            nonlocal inflight
+            if inflight is None:
+                return
+            reqs, ticket, finished = inflight
+            inflight = None
+            try:
+                toks = self.worker.collect(ticket)
+            except RuntimeError as e:
+                raise EngineDeadError(str(e)) from e
+            for (r, idx), tok in zip(reqs, toks):
+                r.token_ids[idx] = tok
+            for r in finished:
+                outputs[r.req_id] = r.completion_token_ids
+            if pbar is not None:
+                pbar.update(len(finished))
+
+        while not sch.is_finished():
+            if sch.has_waiting() and inflight is not None:
+                drain()                                  # the next step may be a prefill: needs real token ids
+            t0 = time.perf_counter()
+            reqs, is_prefill = sch.schedule(defer_seal=True)
+            t1 = time.perf_counter()
+            if is_prefill:
+                sb = build_prefill(reqs, bs, self.step_index, self.config.seed)
+                self.decode_builder.reset()
+            else:
+                pad, width = self.worker.decode_padding(len(reqs))
+                sb = self.decode_builder.build(reqs, self.step_index, self.config.seed, pad, width)
+                src = sb.src_rows
+                src[:] = -1
+                if inflight is not None:
+                    prev_row = {id(r): i for i, (r, _) in enumerate(inflight[0])}
+                    src[:len(reqs)] = [prev_row.get(id(r), -1) for r in reqs]
+            t2 = time.perf_counter()
+            try:
+                if self.chan is not None:
+                    if self.procs:
+                        self._check_followers_alive()
+                    self.chan.publish(rpc.KIND_STEP, sb.buf[:sb.num_words])
+                ticket = self.worker.launch(sb)
+            except (rpc.PeerFailed, rpc.ChannelTimeout) as e:
+                raise EngineDeadError(str(e)) from e
+            t3 = time.perf_counter()
+            self.step_index += 1
+            drain()                                      # read the PREVIOUS step while this one runs
+            finished = sch.postprocess(reqs, [PLACEHOLDER] * len(reqs))
+            inflight = ([(r, len(r.token_ids) - 1) for r in reqs], ticket, finished)
+            t4 = time.perf_counter()
+            st.schedule_s += t1 - t0
+            st.build_s += t2 - t1
+            st.run_s += t3 - t2
+            st.postprocess_s += t4 - t3
+            if is_prefill:
+                st.prefill_steps += 1
+                st.prefill_tokens += sb.num_tokens
+                st.prefix_cached_tokens += sum(r.num_cached_tokens for r in reqs)
+            else:
+                st.decode_steps += 1
+                st.decode_tokens += len(reqs)
+                st.decode_batch_hist[len(reqs)] += 1
+            st.preemptions = sch.num_preemptions
+            st.finished_requests += len(finished)
+        drain()
 
     # ------------------------------------------------------------------ teardown
     def exit(self) -> None:

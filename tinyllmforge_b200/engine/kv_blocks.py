@@ -150,19 +150,32 @@ class KVBlockPool:
         """True if the pool can hold the KV entry of ``req``'s newest token."""
         return len(self.free) >= (1 if len(req) % self.block_size == 1 else 0)
 
-    def grow(self, req: Request) -> None:
-        """Make room for the newest token's KV entry; seal the last block when it fills up."""
+    def grow(self, req: Request, defer_seal: bool = False) -> None:
+        """Make room for the newest token's KV entry; seal the last block when it fills up.
+
+        ``defer_seal``: the pipelined engine loop schedules a step before the previous step's tokens have been read
+        back, so the newest token id is still a placeholder.  The block it completes is then sealed one step later
+        (when the next block is opened), by which time every token of it is known."""
         bs = self.block_size
         n = len(req)
         rem = n % bs
         if rem == 1:
+            if defer_seal and len(req.block_table) >= 1:
+                self._seal_block(req, len(req.block_table) - 1, n - 1)
             req.block_table.append(self._take_oldest())
-        elif rem == 0:
-            last = req.block_table[-1]
-            if self.block_hash[last] == -1:
-                parent = self.block_hash[req.block_table[-2]] if len(req.block_table) > 1 else -1
-                chunk = tuple(req.token_ids[n - bs:n])
-                self._seal(last, chain_hash(chunk, parent), chunk)
+        elif rem == 0 and not defer_seal:
+            self._seal_block(req, len(req.block_table) - 1, n)
+
+    def _seal_block(self, req: Request, index: int, end: int) -> None:
+        """Hash and register block ``index`` of ``req``, whose last token is token ``end - 1``."""
+        block_id = req.block_table[index]
+        if self.block_hash[block_id] != -1 or self.ref_count[block_id] != 1:
+            return
+        parent = self.block_hash[req.block_table[index - 1]] if index > 0 else -1
+        if index > 0 and parent == -1:
+            return                                  # the chain is broken (an earlier block was never sealed)
+        chunk = tuple(req.token_ids[end - self.block_size:end])
+        self._seal(block_id, chain_hash(chunk, parent), chunk)
 
     # ------------------------------------------------------------------ checks (tests)
     def check_invariants(self) -> None:

@@ -23,6 +23,9 @@ from .kv_blocks import KVBlockPool
 from .request import Request, RequestStatus
 
 
+PLACEHOLDER = -2          # token id not read back yet (never equals an EOS id, never a valid id)
+
+
 class Scheduler:
     def __init__(self, config: Config):
         self.max_num_seqs = config.max_num_seqs
@@ -43,8 +46,8 @@ class Scheduler:
             raise ValueError("prompt does not fit in the KV cache")
         self.waiting.append(req)
 
-    def schedule(self) -> tuple[list[Request], bool]:
-        """Pick the next batch. Returns (requests, is_prefill)."""
+    def schedule(self, defer_seal: bool = False) -> tuple[list[Request], bool]:
+        """Pick the next batch. Returns (requests, is_prefill).  ``defer_seal``: see ``KVBlockPool.grow``."""
         batch: list[Request] = []
         budget = self.max_num_batched_tokens
         while self.waiting and len(self.running) < self.max_num_seqs:
@@ -75,7 +78,7 @@ class Scheduler:
                     break
             if req is None:
                 break
-            self.pool.grow(req)
+            self.pool.grow(req, defer_seal)
             batch.append(req)
         self.running.extend(batch)
         if not batch:
@@ -90,8 +93,12 @@ class Scheduler:
         self.pool.release(req)
         self.waiting.appendleft(req)
 
+    def has_waiting(self) -> bool:
+        return bool(self.waiting)
+
     def postprocess(self, batch: list[Request], token_ids: list[int]) -> list[Request]:
-        """Append the sampled tokens; retire finished requests. Returns the finished ones."""
+        """Append the sampled tokens; retire finished requests. Returns the finished ones.
+        The pipelined engine loop passes ``PLACEHOLDER`` ids and patches the real ones in later."""
         finished = []
         for req, tok in zip(batch, token_ids):
             req.token_ids.append(tok)

@@ -20,6 +20,8 @@ Layout (all int32 words, every section starts on a 16-byte boundary):
     cu_seqlens_q[padded_seqs + 1] context_lens[padded_seqs] last_index[padded_seqs]
     temperatures[padded_seqs] (float32 bit patterns)
     block_tables[padded_seqs * table_width]
+    src_rows[padded_seqs]    decode only: >= 0 -> this sequence's input token is row src_rows[i] of the PREVIOUS step's
+                             sampled tokens, still on the device (pipelined engine loop); -1 -> input_ids[i] is valid
 
 Padding rows use slot -1 (the KV store skips them), context length 0 and block id -1.
 Decode positions are ``len - 1``: the index of the token whose KV entry is being
@@ -34,7 +36,7 @@ HEADER_WORDS = 16
 H_MAGIC, H_PREFILL, H_NSEQ, H_NTOK, H_PSEQ, H_PTOK, H_WIDTH, H_MAXQ, H_MAXK, H_STEP, H_SEEDLO, H_SEEDHI = range(12)
 
 SECTIONS = ("input_ids", "positions", "slot_mapping", "cu_seqlens_q", "context_lens", "last_index",
-            "temperatures", "block_tables")
+            "temperatures", "block_tables", "src_rows")
 
 
 def _align4(n: int) -> int:
@@ -46,7 +48,7 @@ def section_offsets(padded_tokens: int, padded_seqs: int, table_width: int) -> t
     sizes = {
         "input_ids": padded_tokens, "positions": padded_tokens, "slot_mapping": padded_tokens,
         "cu_seqlens_q": padded_seqs + 1, "context_lens": padded_seqs, "last_index": padded_seqs,
-        "temperatures": padded_seqs, "block_tables": padded_seqs * table_width,
+        "temperatures": padded_seqs, "block_tables": padded_seqs * table_width, "src_rows": padded_seqs,
     }
     off = HEADER_WORDS
     out = {}
@@ -147,6 +149,7 @@ def build_prefill(reqs, block_size: int, step_index: int = 0, seed: int = 0) -> 
     sec("context_lens")[:] = k_lens
     sec("last_index")[:] = cu[1:] - 1
     sec("temperatures").view(np.float32)[:] = [r.temperature for r in reqs]
+    sec("src_rows")[:] = -1
     return StepBatch(buf)
 
 
@@ -178,6 +181,7 @@ def build_decode(reqs, block_size: int, step_index: int = 0, seed: int = 0,
     for i, r in enumerate(reqs):
         bt = r.block_table
         tables[i, :len(bt)] = bt
+    sec("src_rows")[:] = -1
     return StepBatch(buf)
 
 

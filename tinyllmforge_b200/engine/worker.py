@@ -72,6 +72,7 @@ class Worker:
         self.graphs: dict[int, object] = {}
         self.graph_launches: dict[int, int] = {}
         self.time_steps = bool(config.extra.get("device_timing", False))
+        self.prev_tokens_host = np.zeros(0, dtype=np.int64)
         self.num_steps = 0
         self.reset_counters()
 
@@ -99,9 +100,11 @@ class Worker:
             _, words_prefill = section_offsets(config.max_num_batched_tokens, max_seqs, self.table_width)
             self.max_words = words_prefill
             if self.is_cuda:
-                self.host_words = torch.empty(self.max_words, dtype=torch.int32, pin_memory=True)
+                # two staging buffers: the host fills one while the copy out of the other may still be in flight
+                self.host_words = [torch.empty(self.max_words, dtype=torch.int32, pin_memory=True) for _ in range(2)]
                 self.dev_words = torch.zeros(self.max_words, dtype=torch.int32, device=self.device)
-                self.host_tokens = torch.empty(max(max_seqs, 512), dtype=torch.int32, pin_memory=True)
+                self.host_tokens = [torch.empty(max(max_seqs, 512), dtype=torch.int32, pin_memory=True) for _ in range(2)]
+                self.prev_tokens_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
             self._allocate_kv_cache()
             if self.buckets:
                 self._capture_graphs()
@@ -181,20 +184,36 @@ class Worker:
         n = sb.num_words
         if not self.is_cuda:
             return DeviceBatch(sb, torch.from_numpy(sb.buf[:n]))
-        self.host_words[:n].numpy()[:] = sb.buf[:n]
-        self.dev_words[:n].copy_(self.host_words[:n], non_blocking=True)
+        host = self.host_words[self.num_steps & 1]
+        host[:n].numpy()[:] = sb.buf[:n]
+        self.dev_words[:n].copy_(host[:n], non_blocking=True)
         return DeviceBatch(sb, self.dev_words[:n])
 
     @torch.inference_mode()
-    def run(self, sb: StepBatch) -> list[int]:
-        """Execute one step; returns the sampled token of each of the ``num_seqs`` sequences."""
+    def launch(self, sb: StepBatch):
+        """Start one step and return a ticket for :meth:`collect`.  Nothing here waits for the GPU, so the caller
+        may schedule and build the next step while this one runs.  When ``sb.src_rows`` names rows of the previous
+        step, the input tokens are taken from that step's sampled tokens on the device."""
         if not self.is_cuda:
-            return self.model.step(self._stage(sb))[:sb.num_seqs].tolist()
+            buf = sb.buf
+            src = sb.src_rows[:sb.num_seqs]
+            if not sb.is_prefill and (src >= 0).any():
+                ids = sb.input_ids
+                take = src >= 0
+                ids[:sb.num_seqs][take] = self.prev_tokens_host[src[take]]
+            tokens = self.model.step(self._stage(sb))[:sb.num_seqs]
+            self.prev_tokens_host = np.asarray(tokens.tolist(), dtype=np.int64)
+            self.num_steps += 1
+            return ("cpu", self.prev_tokens_host.tolist())
         timed = self.time_steps
+        e0 = None
         if timed:
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0 = torch.cuda.Event(enable_timing=True)
             e0.record()
         batch = self._stage(sb)
+        if not sb.is_prefill and self.feed_rows(sb):
+            self.ops.C.feed_tokens(batch.input_ids[:sb.num_seqs], batch.src_rows, self.prev_tokens_dev)
+            self.kernel_launches += 1
         graph = None if sb.is_prefill else self.graphs.get(sb.padded_seqs)
         if graph is not None and sb.table_width == self.table_width:
             graph.replay()
@@ -204,19 +223,37 @@ class Worker:
             before = self.ops.launches
             tokens = self.model.step(batch)
             self.kernel_launches += self.ops.launches - before
-        out = self.host_tokens[:sb.num_seqs]
-        out.copy_(tokens[:sb.num_seqs], non_blocking=True)
-        if timed:
-            e1.record()
-        torch.cuda.current_stream().synchronize()
-        if timed:
-            self.device_ms += e0.elapsed_time(e1)
+        n = sb.num_seqs
+        self.prev_tokens_dev = tokens                  # stays on the device: the next step may take its inputs from here
+        host = self.host_tokens[self.num_steps & 1]
+        host[:n].copy_(tokens[:n], non_blocking=True)
+        done = torch.cuda.Event(enable_timing=timed)
+        done.record()
         self.h2d_bytes += sb.nbytes
-        self.d2h_bytes += sb.num_seqs * 4
+        self.d2h_bytes += n * 4
         self.num_steps += 1
-        if sb.is_prefill or (self.num_steps & 127) == 0:
+        check = sb.is_prefill or (self.num_steps & 127) == 0
+        return ("cuda", host, n, e0, done, check)
+
+    @staticmethod
+    def feed_rows(sb: StepBatch) -> bool:
+        return bool((sb.src_rows[:sb.num_seqs] >= 0).any())
+
+    def collect(self, ticket) -> list[int]:
+        """Wait for a launched step; returns the sampled token of each of its sequences."""
+        if ticket[0] == "cpu":
+            return ticket[1]
+        _, host, n, e0, done, check = ticket
+        done.synchronize()
+        if e0 is not None:
+            self.device_ms += e0.elapsed_time(done)
+        if check:
             self.ops.check_status()
-        return out.tolist() if self.rank == 0 else []
+        return host[:n].tolist() if self.rank == 0 else []
+
+    def run(self, sb: StepBatch) -> list[int]:
+        """Execute one step and wait for it."""
+        return self.collect(self.launch(sb))
 
     @torch.inference_mode()
     def _capture_graphs(self) -> None:
@@ -256,12 +293,20 @@ class Worker:
 def follower_loop(worker: Worker, chan: rpc.ShmChannel) -> int:
     """Ranks 1..tp-1: execute every published step until told to exit (KIND_EXIT) or until rank 0 marks
     the end of a ``generate`` call (KIND_PING); returns which (tinyvllm/engine/model_runner.py:73-89)."""
+    pending = None
     while True:
         kind, data = chan.receive()
         if kind in (rpc.KIND_EXIT, rpc.KIND_PING):
+            if pending is not None:
+                worker.collect(pending)
             return kind
         if kind == rpc.KIND_STEP:
-            worker.run(StepBatch(data.view(np.int32)))
+            # Launch first, then wait for the step before: the GPU always has the next step queued, and this
+            # rank is never more than one step ahead of what it has checked.
+            ticket = worker.launch(StepBatch(data.view(np.int32)))
+            if pending is not None:
+                worker.collect(pending)
+            pending = ticket
 
 
 def follower_main(config: Config, rank: int, chan_name: str, init_method: str) -> None:
