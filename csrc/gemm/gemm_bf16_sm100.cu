@@ -60,7 +60,7 @@ struct TokCfg {
   static constexpr int kCBytes = BLOCK_C * kBlockK * 2;
   static constexpr int kStageBytes = kRBytes + kNumC * kCBytes;
   static constexpr int kStagesRaw = (200 * 1024) / kStageBytes;
-  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kStages = kStagesRaw > 10 ? 10 : kStagesRaw;
   static constexpr int kAccCols = BLOCK_C * kNumC;               // TMEM columns of one accumulator set
   static constexpr int kTmemCols = tmem_cols_for(2 * kAccCols);
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
@@ -109,26 +109,42 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  pdl_wait();                                   // x and out belong to predecessors; set-up above overlapped their tail
 
-  if (warp == 0) {
-    if (lane == 0) {
-      int it = 0;                               // running K-block counter across tiles: the ring never drains
-      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-        const int r0 = (t % m_tiles) * kBlockR, c0 = (t / m_tiles) * BLOCK_C;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % Cfg::kStages;
-          const uint32_t ph = (it / Cfg::kStages) & 1;
-          if (!mbar_wait(&empty_bar[s], ph ^ 1, status)) { t = num_tiles; break; }
-          uint8_t* st = smem + s * Cfg::kStageBytes;
-          mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
+  if (warp == 0 && lane == 0) {
+    // Weights never depend on a predecessor kernel: the weight halves of the first ring stages are requested
+    // before waiting for it, the activation halves after (the stage's barrier counts the bytes of both).
+    const int pre = blockIdx.x < num_tiles ? min(num_kb, Cfg::kStages) : 0;
+    const int c_first = (blockIdx.x / m_tiles) * BLOCK_C;
+    for (int i = 0; i < pre; ++i) {
+      uint8_t* st = smem + i * Cfg::kStageBytes;
+      mbar_expect_tx(&full_bar[i], Cfg::kStageBytes);
+      for (int j = 0; j < Cfg::kNumC; ++j)
+        tma_load_2d(st + Cfg::kRBytes + j * Cfg::kCBytes, &tm_w, &full_bar[i], i * kBlockK, c_first + j * dual_off);
+    }
+    pdl_wait();                                 // x and out belong to predecessors
+    int it = 0;                                 // running K-block counter across tiles: the ring never drains
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      const int r0 = (t % m_tiles) * kBlockR, c0 = (t / m_tiles) * BLOCK_C;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % Cfg::kStages;
+        uint8_t* st = smem + s * Cfg::kStageBytes;
+        if (it < pre) {                         // first tile, stage already armed and its weights under way
           tma_load_2d(st, &tm_x, &full_bar[s], kb * kBlockK, r0);
-          for (int i = 0; i < Cfg::kNumC; ++i)
-            tma_load_2d(st + Cfg::kRBytes + i * Cfg::kCBytes, &tm_w, &full_bar[s], kb * kBlockK, c0 + i * dual_off);
+          continue;
         }
+        const uint32_t ph = (it / Cfg::kStages) & 1;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1, status)) { t = num_tiles; break; }
+        mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
+        tma_load_2d(st, &tm_x, &full_bar[s], kb * kBlockK, r0);
+        for (int i = 0; i < Cfg::kNumC; ++i)
+          tma_load_2d(st + Cfg::kRBytes + i * Cfg::kCBytes, &tm_w, &full_bar[s], kb * kBlockK, c0 + i * dual_off);
       }
     }
-  } else if (warp == 1) {
+  } else {
+    pdl_wait();
+  }
+
+  if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc(kBlockR, BLOCK_C, 1, 1);
       int it = 0, n = 0;
@@ -159,7 +175,7 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         if (!ok) break;
       }
     }
-  } else {
+  } else if (warp >= 2) {
     const int quad = warp & 3;
     int n = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++n) {
@@ -225,7 +241,7 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 // =========================================================================================================
 // decode: R = W tile (128 features; two tiles for SiLU), C = X tile (up to 128 tokens), split-K over a cluster
 // =========================================================================================================
-template <int BLOCK_C, int kEpi>
+template <int BLOCK_C, int kEpi, bool kDeep>
 struct WgtCfg {
   static constexpr int kNumR = kEpi == kEpiSiluMul ? 2 : 1;
   static constexpr int kRBytes = kBlockR * kBlockK * 2;
@@ -236,16 +252,20 @@ struct WgtCfg {
   // next GEMM's CTAs become resident while this one still runs and stream their first weight tiles early.
   // After the main loop the idle ring is reused: [send tile][receive slots][reduced gate values].
   static constexpr int kEpilogueBytes = BLOCK_C <= 64 ? 2 * kTileBytes + (kEpi == kEpiSiluMul ? kTileBytes / 2 : 0) : kTileBytes;
-  static constexpr int kBudget = 96 * 1024;
+  // kDeep: one CTA per SM with a ~200 KB ring.  A CTA streams (ring bytes in flight / ~1.7 us latency), so when the
+  // grid has at most one CTA per SM anyway (many tokens: no K split, ~128 CTAs of 300-600 KB each) the deep ring
+  // doubles the rate of every CTA; the price is that a following deep GEMM cannot become resident early.
+  static constexpr int kBudget = (kDeep ? 200 : 96) * 1024;
+  static constexpr int kMaxStages = kDeep ? 10 : 6;
   static constexpr int kStagesRaw = kBudget / kStageBytes;
-  static constexpr int kStages = kStagesRaw > 6 ? 6 : (kStagesRaw < 2 ? 2 : kStagesRaw);
+  static constexpr int kStages = kStagesRaw > kMaxStages ? kMaxStages : (kStagesRaw < 2 ? 2 : kStagesRaw);
   static constexpr int kRingBytes = kStages * kStageBytes > kEpilogueBytes ? kStages * kStageBytes : kEpilogueBytes;
   static constexpr bool kCanSplit = BLOCK_C <= 64;                // wider tiles have no room for receive slots
   static constexpr int kTmemCols = tmem_cols_for(BLOCK_C * kNumR);
   static constexpr int kSmemBytes = kRingBytes + 1024 + 256;
   static_assert(BLOCK_C % 16 == 0 && BLOCK_C >= 16 && BLOCK_C <= 128, "token tile of the decode kernel");
   static_assert(kStages >= 2, "need at least a double buffer");
-  static_assert(kSmemBytes <= 113 * 1024, "two CTAs per SM");
+  static_assert(kSmemBytes <= (kDeep ? 227 : 113) * 1024, "two CTAs per SM (one for the deep ring)");
 };
 
 // out[token, feature] (row stride ldo).  W: [n_total (or 2 * n_total) rows, K]; X: [m_total rows, K].
@@ -260,12 +280,12 @@ struct WgtCfg {
 // No global scratch, no atomics, no remote loads.
 // SiLU: one split -> combine gate and up on the way out of tensor memory.  Several splits -> the gate sum must
 // be complete before the nonlinearity: round 0 reduces the gate tile into gate_red, round 1 the up tile.
-template <int BLOCK_C, int kEpi>
-__global__ void __launch_bounds__(kGemmThreads, 2)
+template <int BLOCK_C, int kEpi, bool kDeep>
+__global__ void __launch_bounds__(kGemmThreads, kDeep ? 1 : 2)
 gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                     __nv_bfloat16* __restrict__ out, int ldo, int n_total, int m_total, int K, int kb_per_split,
                     int dual_off, unsigned* status, const TpPush push) {
-  using Cfg = WgtCfg<BLOCK_C, kEpi>;
+  using Cfg = WgtCfg<BLOCK_C, kEpi, kDeep>;
   extern __shared__ uint8_t smem_raw[];
   // The dynamic shared window starts at the same offset in every CTA of the cluster, so equal local
   // addresses name corresponding buffers in all peers.
@@ -586,15 +606,20 @@ static int choose_splits(int ctas_unsplit, int num_kb, int block_c) {
   return s;
 }
 
-template <int BLOCK_C, int kEpi>
+// Rows of 128 bytes a CTA streams (K blocks x (token tile + weight rows)) from which the deep ring pays off.
+static int deep_threshold() {
+  static const int v = std::getenv("FORGE_DEEP_ROWS") ? std::atoi(std::getenv("FORGE_DEEP_ROWS")) : 1536;
+  return v;
+}
+
+template <int BLOCK_C, int kEpi, bool kDeep>
 static int launch_weights(const void* x, int ldx, const void* w, int w_rows, int ldw, __nv_bfloat16* out, int ldo, int M,
-                          int n_out, int K, int force_splits, unsigned* status, cudaStream_t stream, const TpPush& push) {
-  // force_splits: 0 = choose, else the cluster size
-  using Cfg = WgtCfg<BLOCK_C, kEpi>;
+                          int n_out, int K, int splits, unsigned* status, cudaStream_t stream, const TpPush& push) {
+  using Cfg = WgtCfg<BLOCK_C, kEpi, kDeep>;
   CUtensorMap tm_x, tm_w;
   if (forge_make_tmap_2d(&tm_w, w, w_rows, K, ldw, kBlockR, 2) != 0) return -2;
   if (forge_make_tmap_2d(&tm_x, x, M, K, ldx, BLOCK_C, 2) != 0) return -3;
-  auto kern = gemm_weights_kernel<BLOCK_C, kEpi>;
+  auto kern = gemm_weights_kernel<BLOCK_C, kEpi, kDeep>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return -4;
@@ -603,10 +628,6 @@ static int launch_weights(const void* x, int ldx, const void* w, int w_rows, int
   const int tiles = (n_out + kBlockR - 1) / kBlockR;
   const int tok_tiles = (M + BLOCK_C - 1) / BLOCK_C;
   const int num_kb = (K + kBlockK - 1) / kBlockK;
-  int splits = force_splits > 0 ? force_splits : choose_splits(tiles * tok_tiles, num_kb, BLOCK_C);
-  if (splits > BLOCK_C / 4) splits = BLOCK_C / 4 < 1 ? 1 : BLOCK_C / 4;   // every CTA reduces >= 4 columns (one per warp)
-  if (!Cfg::kCanSplit) splits = 1;
-  if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return -6;
   const int kb_per_split = (num_kb + splits - 1) / splits;
   return launch_kernel(kern, dim3(tiles, splits, tok_tiles), dim3(kGemmThreads), Cfg::kSmemBytes, stream, splits, tm_w, tm_x,
                        out, ldo, n_out, M, K, kb_per_split, n_out, status, push) == cudaSuccess ? 0 : -5;
@@ -615,14 +636,15 @@ static int launch_weights(const void* x, int ldx, const void* w, int w_rows, int
 // out[M, n_out] = epilogue(X[M, K] * W[*, K]^T).  epi = 0: W has n_out rows.  epi = 1: W is [2 * n_out, K]
 // (gate rows then up rows) and out = silu(gate) * up.  Requirements: K % 8 == 0, x/w 16-byte aligned,
 // ldx/ldw % 8 == 0.  force_mode: 0 auto, 1 token-tile kernel, 2 weight-tile (decode) kernel (needs M <= 256).
-// tune: 0 auto; else bits 0..7 = cluster size (K splits) and bits 8..15 = token tile (16/32/64/128) of the decode
-// kernel, either may be 0 = choose.  Returns 0 on success.
+// tune: 0 auto; else bits 0..7 = cluster size (K splits), bits 8..15 = token tile (16/32/64/128) of the decode
+// kernel, bits 16..23 = ring depth (1 = two CTAs per SM, 2 = deep ring); each may be 0 = choose.  Returns 0 on success.
 TpPush make_tp_push(int tp_size, int tp_rank, const long long* slot_ptrs, const long long* signal_ptrs, unsigned* arrive,
                     unsigned* epoch, long long mc_slot = 0);
 
 static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K, int epi,
                          int force_mode, int tune, unsigned* status, cudaStream_t stream, const TpPush& push) {
-  const int force_splits = tune & 0xff, force_bc = (tune >> 8) & 0xff;
+  const int force_splits = tune & 0xff, force_deep = (tune >> 16) & 0xff;
+  int force_bc = (tune >> 8) & 0xff;
   if (M <= 0 || n_out <= 0 || K <= 0) return 0;
   if ((K & 7) || (ldx & 7) || (ldw & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
     return -1;
@@ -632,19 +654,46 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
   // persistent token-tile kernel streams weights best: its ring never drains between tiles and its epilogue overlaps
   // the next tile (measured 58-91 us vs 60-182 us for 8..256 tokens x 151936 x 1024; cuBLAS 55-83 us).
   const bool wide = (n_out + kBlockR - 1) / kBlockR >= 296 && epi == kEpiStore && push.size <= 1 && M >= 8;
+  // Many tokens of a decode step (64..256) on a layer with enough output features and a short K: the token-tile
+  // kernel with narrow feature tiles (32 or 64) gives ~100-128 CTAs without splitting K, and its epilogue goes
+  // straight from tensor memory to global rows (no exchange through shared memory).  Measured on the Qwen3-0.6B
+  // shapes: qkv 6.5-7.4 us vs 7.7-12.2 us, gate_up at 128..256 tokens 10.7-12.9 us vs 17-18.5 us.
+  int narrow = 0;
+  if (force_mode == 0 && M >= (epi == kEpiSiluMul ? 112 : 64) && M <= 256 && K <= 2048 && push.size <= 1 && !wide) {
+    const int m_tiles = (M + kBlockR - 1) / kBlockR;
+    const int t32 = ((n_out + 31) / 32) * m_tiles, t64 = ((n_out + 63) / 64) * m_tiles;
+    if (t32 >= 64 && t32 <= 148) narrow = 32;
+    else if (t64 >= 64 && t64 <= 148) narrow = 64;
+  }
+  if (narrow) {
+    force_mode = 1;
+    force_bc = narrow;
+  }
   const bool decode = force_mode == 2 || (force_mode == 0 && M <= 256 && !wide);
   if (decode) {
     if (M > 256) return -7;
-    // token tile: few feature tiles -> small token tiles (parallelism, cheap exchange; extra token tiles re-read the
-    // weights from L2); many feature tiles (LM head) -> the widest tile, so weights cross L2 -> SM only once or twice
+    // token tile: few feature tiles -> 32-token tiles (parallelism, cheap exchange, two CTAs per SM; extra token tiles
+    // re-read the weights from L2); many feature tiles (LM head) -> the widest tile, so weights cross L2 -> SM only once or twice
     const int feature_tiles = (n_out + kBlockR - 1) / kBlockR;
-    int bc = M <= 16 ? 16 : M <= 32 ? 32 : (M <= 64 || feature_tiles < 148) ? 64 : 128;
+    int bc = M <= 16 ? 16 : (M <= 32 || feature_tiles < 148) ? 32 : M <= 64 ? 64 : 128;
     if (force_bc == 16 || force_bc == 32 || force_bc == 64 || force_bc == 128) bc = force_bc;
-#define FORGE_W(BC)                                                                                                          \
-  case BC:                                                                                                                   \
-    return epi == kEpiSiluMul                                                                                                \
-               ? launch_weights<BC, kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, force_splits, status, stream, push) \
-               : launch_weights<BC, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, force_splits, status, stream, push);
+    const int num_kb = (K + kBlockK - 1) / kBlockK;
+    const int ctas_unsplit = feature_tiles * ((M + bc - 1) / bc);
+    int splits = force_splits > 0 ? force_splits : choose_splits(ctas_unsplit, num_kb, bc);
+    if (splits > bc / 4) splits = bc / 4;                               // every CTA reduces >= 4 columns (one per warp)
+    if (bc > 64) splits = 1;                                            // wide tiles have no room for receive slots
+    if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return -6;
+    // ring depth: the deep ring when the grid is at most one CTA per SM and every CTA has many K blocks to stream
+    const int kb_per_cta = (num_kb + splits - 1) / splits;
+    bool deep = ctas_unsplit * splits <= 148 && kb_per_cta * (bc + (epi == kEpiSiluMul ? 256 : 128)) >= deep_threshold();
+    if (force_deep == 1) deep = false;
+    if (force_deep == 2) deep = true;
+#define FORGE_W2(BC, EPI)                                                                                                   \
+  (deep ? launch_weights<BC, EPI, true>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, splits, status, stream, push)          \
+        : launch_weights<BC, EPI, false>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, splits, status, stream, push))
+#define FORGE_W(BC) \
+  case BC:          \
+    return epi == kEpiSiluMul ? FORGE_W2(BC, kEpiSiluMul) : FORGE_W2(BC, kEpiStore);
     switch (bc) {
       FORGE_W(16)
       FORGE_W(32)
@@ -652,9 +701,22 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
       FORGE_W(128)
     }
 #undef FORGE_W
+#undef FORGE_W2
     return -6;
   }
   if (push.size > 1) return -8;   // the token-tile kernel has no push epilogue; callers use the library collective there
+  if (force_mode == 1 && (force_bc == 16 || force_bc == 32 || force_bc == 64)) {       // narrow feature tiles: many tokens of a decode step
+#define FORGE_T(BC)                                                                                                           \
+  case BC:                                                                                                                    \
+    return epi == kEpiSiluMul ? launch_tokens<BC, kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream)   \
+                              : launch_tokens<BC, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream);
+    switch (force_bc) {
+      FORGE_T(16)
+      FORGE_T(32)
+      FORGE_T(64)
+    }
+#undef FORGE_T
+  }
   if (epi == kEpiSiluMul) return launch_tokens<128, kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream);
   if (n_out % 256 == 0 || n_out >= 1024) return launch_tokens<256, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream);
   return launch_tokens<128, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream);

@@ -82,6 +82,42 @@ def test_gemm_decode_kernel_silu_split_k(ops, M, I, K, splits):
     ops.check_status()
 
 
+@pytest.mark.parametrize("M,N,K,bc,silu", [
+    (256, 4096, 1024, 64, False), (200, 1024, 2048, 16, False), (130, 1000, 512, 32, False), (96, 3072, 1024, 32, True),
+    (256, 3072, 1024, 64, True), (140, 1536, 256, 16, True), (700, 2048, 1024, 32, False),
+])
+def test_gemm_token_kernel_narrow_feature_tiles(ops, M, N, K, bc, silu):
+    """Token-tile kernel with 16/32/64-feature tiles (large decode batches: direct epilogue, no K split)."""
+    torch.manual_seed(M + N + bc)
+    x, w = _rand(M, K), _rand((2 if silu else 1) * N, K, scale=0.05)
+    f = ops.linear_silu_mul if silu else ops.linear
+    out = f(x, w, force_mode=1, force_block_c=bc)
+    ref = x.float() @ w.float().t()
+    if silu:
+        ref = torch.nn.functional.silu(ref[:, :N]) * ref[:, N:]
+    _close(out, ref, atol=2e-2, rtol=2e-2)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("M,N,K,bc,splits,silu", [
+    (256, 4096, 1024, 64, 1, False), (256, 1024, 2048, 64, 4, False), (200, 1024, 3072, 32, 2, False), (130, 2048, 4096, 128, 1, False),
+    (256, 3072, 1024, 64, 1, True), (96, 1536, 2048, 32, 2, True), (256, 512, 1024, 128, 1, True), (8, 256, 128, 16, 1, False),
+])
+def test_gemm_decode_kernel_deep_ring(ops, M, N, K, bc, splits, silu):
+    """The one-CTA-per-SM variant of the weight-tile kernel (ring of ~200 KB) gives the same bits as the two-per-SM one."""
+    torch.manual_seed(M + N + bc)
+    x, w = _rand(M, K), _rand((2 if silu else 1) * N, K, scale=0.05)
+    f = ops.linear_silu_mul if silu else ops.linear
+    deep = f(x, w, force_mode=2, force_splits=splits, force_block_c=bc, force_deep=2)
+    shallow = f(x, w, force_mode=2, force_splits=splits, force_block_c=bc, force_deep=1)
+    ref = x.float() @ w.float().t()
+    if silu:
+        ref = torch.nn.functional.silu(ref[:, :N]) * ref[:, N:]
+    _close(deep, ref, atol=2e-2, rtol=2e-2)
+    assert torch.equal(deep, shallow)
+    ops.check_status()
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 128, 128), (16, 1280, 1024), (50, 1024, 3200 - 3200 % 128), (64, 6400, 5120), (200, 1024, 2048), (600, 384, 256)])
 def test_gemm_fp8_block_scaled(ops, M, N, K):
     """e4m3 weights with 128 x 128 block scales, activations quantised per token and 128 features."""

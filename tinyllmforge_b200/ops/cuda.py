@@ -70,7 +70,7 @@ class CudaOps:
 
     # ------------------------------------------------------------------ GEMMs
     def linear(self, x: torch.Tensor, w: torch.Tensor, force_mode: int = 0, force_splits: int = 0,
-               force_block_c: int = 0) -> torch.Tensor:
+               force_block_c: int = 0, force_deep: int = 0) -> torch.Tensor:
         """x @ w.T.  ``w`` must not be the output of the kernel launched just before this call: the decode
         kernel starts streaming weights before it waits for its predecessor (weights are static in the engine)."""
         if isinstance(w, Fp8BlockWeight):
@@ -78,12 +78,12 @@ class CudaOps:
         out = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
         if self.use_cublas_gemm:
             return torch.matmul(x, w.t(), out=out)
-        self.C.gemm(x, w, out, 0, force_mode, force_splits | (force_block_c << 8), self.status)
+        self.C.gemm(x, w, out, 0, force_mode, force_splits | (force_block_c << 8) | (force_deep << 16), self.status)
         self.launches += 1
         return out
 
     def linear_silu_mul(self, x: torch.Tensor, w_gate_up: torch.Tensor, force_mode: int = 0, force_splits: int = 0,
-                        force_block_c: int = 0) -> torch.Tensor:
+                        force_block_c: int = 0, force_deep: int = 0) -> torch.Tensor:
         if isinstance(w_gate_up, Fp8BlockWeight):
             return self.silu_mul(self.linear_fp8(x, w_gate_up))
         out = torch.empty(x.shape[0], w_gate_up.shape[0] // 2, dtype=x.dtype, device=x.device)
@@ -91,7 +91,7 @@ class CudaOps:
             tmp = torch.matmul(x, w_gate_up.t())
             self.C.silu_mul(tmp, out)
             return out
-        self.C.gemm(x, w_gate_up, out, 1, force_mode, force_splits | (force_block_c << 8), self.status)
+        self.C.gemm(x, w_gate_up, out, 1, force_mode, force_splits | (force_block_c << 8) | (force_deep << 16), self.status)
         self.launches += 1
         return out
 
