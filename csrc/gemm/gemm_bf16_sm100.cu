@@ -596,11 +596,12 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
 // should be about one wave of the 148 SMs; the cross-CTA exchange over DSMEM runs at only ~20 GB/s per SM, so
 // tiles are kept small (<= 64 tokens when splitting) and the split count is the largest power of two that
 // keeps the grid within ~one wave, leaves each split >= 2 K blocks and each CTA >= 4 columns to reduce.
-static int choose_splits(int ctas_unsplit, int num_kb, int block_c) {
+static int choose_splits(int ctas_unsplit, int num_kb, int block_c, bool silu) {
   // two CTAs fit per SM, so small token tiles (cheap exchange) may use up to two CTAs per SM: fewer K blocks per
   // CTA means the whole K slice is prefetched into the ring before the predecessor kernel has finished
   static const int small_limit = std::getenv("FORGE_SPLIT_LIMIT") ? std::atoi(std::getenv("FORGE_SPLIT_LIMIT")) : 296;
-  const int limit = block_c <= 32 ? small_limit : 160;
+  // SiLU needs the complete gate sum before the nonlinearity, i.e. two exchange rounds: split less eagerly
+  const int limit = silu ? 200 : block_c <= 32 ? small_limit : 160;
   int s = 1;
   while (s < 8 && ctas_unsplit * s * 2 <= limit && num_kb / (s * 2) >= 2 && s * 2 <= block_c / 4) s *= 2;
   return s;
@@ -657,13 +658,14 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
   // Many tokens of a decode step (64..256) on a layer with enough output features and a short K: the token-tile
   // kernel with narrow feature tiles (32 or 64) gives ~100-128 CTAs without splitting K, and its epilogue goes
   // straight from tensor memory to global rows (no exchange through shared memory).  Measured on the Qwen3-0.6B
-  // shapes: qkv 6.5-7.4 us vs 7.7-12.2 us, gate_up at 128..256 tokens 10.7-12.9 us vs 17-18.5 us.
+  // shapes: qkv 6.5-7.4 us vs 7.7-12.2 us, gate_up at 32..256 tokens 9.2-10.2 us vs 11.7-15.3 us.
   int narrow = 0;
-  if (force_mode == 0 && M >= (epi == kEpiSiluMul ? 112 : 64) && M <= 256 && K <= 2048 && push.size <= 1 && !wide) {
+  if (force_mode == 0 && M >= (epi == kEpiSiluMul ? 32 : 64) && M <= 256 && K <= 2048 && push.size <= 1 && !wide) {
     const int m_tiles = (M + kBlockR - 1) / kBlockR;
     const int t32 = ((n_out + 31) / 32) * m_tiles, t64 = ((n_out + 63) / 64) * m_tiles;
-    if (t32 >= 64 && t32 <= 148) narrow = 32;
-    else if (t64 >= 64 && t64 <= 148) narrow = 64;
+    if (n_out < 2048) {}                           // few features (o, down): K must be split, the weight-tile kernel does it
+    else if (t32 <= 148) narrow = 32;
+    else if (t64 <= 148) narrow = 64;
   }
   if (narrow) {
     force_mode = 1;
@@ -679,7 +681,7 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
     if (force_bc == 16 || force_bc == 32 || force_bc == 64 || force_bc == 128) bc = force_bc;
     const int num_kb = (K + kBlockK - 1) / kBlockK;
     const int ctas_unsplit = feature_tiles * ((M + bc - 1) / bc);
-    int splits = force_splits > 0 ? force_splits : choose_splits(ctas_unsplit, num_kb, bc);
+    int splits = force_splits > 0 ? force_splits : choose_splits(ctas_unsplit, num_kb, bc, epi == kEpiSiluMul);
     if (splits > bc / 4) splits = bc / 4;                               // every CTA reduces >= 4 columns (one per warp)
     if (bc > 64) splits = 1;                                            // wide tiles have no room for receive slots
     if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return -6;

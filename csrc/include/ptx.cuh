@@ -256,6 +256,9 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
-__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+// x * sigmoid(x).  The approximate division on purpose: the IEEE `/` takes a slow subroutine whenever the numerator
+// is zero or tiny, and zero rows are common here (padding rows of a graph bucket, rows of a partial token tile):
+// measured 13 -> 20 us on a 256 x 6144 x 1024 GEMM epilogue whose accumulators were zero.
+__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 }  // namespace forge
