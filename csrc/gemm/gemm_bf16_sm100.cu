@@ -591,17 +591,15 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
                        status) == cudaSuccess ? 0 : -5;
 }
 
-// Cluster size (K splits) of the decode kernel.  Measured on B200 (sweep over token tile x splits for the
-// Qwen3 layer shapes): a CTA streams at most ~100 GB/s (ring bytes in flight / memory latency), so the grid
-// should be about one wave of the 148 SMs; the cross-CTA exchange over DSMEM runs at only ~20 GB/s per SM, so
-// tiles are kept small (<= 64 tokens when splitting) and the split count is the largest power of two that
-// keeps the grid within ~one wave, leaves each split >= 2 K blocks and each CTA >= 4 columns to reduce.
+// Cluster size (K splits) of the decode kernel.  Measured on B200 (sweeps over token tile x splits x ring depth for
+// the Qwen3-0.6B and -8B layer shapes): a CTA streams at most ~100 GB/s (ring bytes in flight / memory latency), two
+// CTAs fit per SM, and the cross-CTA exchange over DSMEM runs at only ~20 GB/s per SM.  So: the largest power of two
+// that keeps the grid within two CTAs per SM, leaves each split >= 2 K blocks and each CTA >= 4 columns to reduce.
 static int choose_splits(int ctas_unsplit, int num_kb, int block_c, bool silu) {
-  // two CTAs fit per SM, so small token tiles (cheap exchange) may use up to two CTAs per SM: fewer K blocks per
-  // CTA means the whole K slice is prefetched into the ring before the predecessor kernel has finished
+  // fewer K blocks per CTA also means the whole K slice is prefetched into the ring before the predecessor kernel ends
   static const int small_limit = std::getenv("FORGE_SPLIT_LIMIT") ? std::atoi(std::getenv("FORGE_SPLIT_LIMIT")) : 296;
   // SiLU needs the complete gate sum before the nonlinearity, i.e. two exchange rounds: split less eagerly
-  const int limit = silu ? 200 : block_c <= 32 ? small_limit : 160;
+  const int limit = silu ? 200 : small_limit;
   int s = 1;
   while (s < 8 && ctas_unsplit * s * 2 <= limit && num_kb / (s * 2) >= 2 && s * 2 <= block_c / 4) s *= 2;
   return s;
@@ -674,10 +672,15 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
   const bool decode = force_mode == 2 || (force_mode == 0 && M <= 256 && !wide);
   if (decode) {
     if (M > 256) return -7;
-    // token tile: few feature tiles -> 32-token tiles (parallelism, cheap exchange, two CTAs per SM; extra token tiles
-    // re-read the weights from L2); many feature tiles (LM head) -> the widest tile, so weights cross L2 -> SM only once or twice
     const int feature_tiles = (n_out + kBlockR - 1) / kBlockR;
-    int bc = M <= 16 ? 16 : (M <= 32 || feature_tiles < 148) ? 32 : M <= 64 ? 64 : 128;
+    // Sweeps over the Qwen3-0.6B and -8B layer shapes: 32-token tiles unless that gives more than one CTA per SM before
+    // splitting K; with a long K and many tokens 64, because every extra token tile re-reads its weight tiles from L2.
+    int bc = 16;
+    if (M > 16) {
+      const int cap = M <= 32 ? 32 : M <= 64 ? 64 : 128;
+      bc = (K >= 4096 && M >= 128) ? 64 : 32;
+      while (bc < cap && feature_tiles * ((M + bc - 1) / bc) > 148) bc *= 2;
+    }
     if (force_bc == 16 || force_bc == 32 || force_bc == 64 || force_bc == 128) bc = force_bc;
     const int num_kb = (K + kBlockK - 1) / kBlockK;
     const int ctas_unsplit = feature_tiles * ((M + bc - 1) / bc);
