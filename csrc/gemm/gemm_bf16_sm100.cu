@@ -668,6 +668,8 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
   if (narrow) {
     force_mode = 1;
     force_bc = narrow;
+  } else if (force_mode == 0 && epi == kEpiSiluMul && K >= 4096 && M > 64 && M <= 256 && push.size <= 1) {
+    force_mode = 1;     // a large gated MLP (8B and up) is compute-heavy already at ~100 tokens: full 128 x (128 + 128) tiles
   }
   const bool decode = force_mode == 2 || (force_mode == 0 && M <= 256 && !wide);
   if (decode) {
@@ -678,7 +680,7 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
     int bc = 16;
     if (M > 16) {
       const int cap = M <= 32 ? 32 : M <= 64 ? 64 : 128;
-      bc = (K >= 4096 && M >= 128) ? 64 : 32;
+      bc = (K >= 4096 && M > 64) ? 64 : 32;
       while (bc < cap && feature_tiles * ((M + bc - 1) / bc) > 148) bc *= 2;
     }
     if (force_bc == 16 || force_bc == 32 || force_bc == 64 || force_bc == 128) bc = force_bc;
