@@ -15,14 +15,11 @@
 //     on the device, so the launch is CUDA-graph safe: the grid depends only on the batch bucket.
 //
 // head_dim is 128 (all Qwen3 sizes).  Scores use exp2 with the scale folded into q.
+#include "../include/decode_common.cuh"
 #include "../include/launch.cuh"
 #include "../include/ptx.cuh"
 
 namespace forge {
-
-constexpr int kD = 128;
-constexpr int kDecStages = 3;
-constexpr int kDecThreads = 160;   // 4 consumer warps + 1 producer warp
 
 template <int G, int TILE>
 __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(
@@ -30,8 +27,6 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(
     const int* __restrict__ block_tables, const int* __restrict__ context_lens, __nv_bfloat16* __restrict__ out,
     float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv, int block_size, int table_width, int num_blocks,
     int chunk, int max_chunks, float scale_log2, unsigned* status) {
-  constexpr int TPW = TILE / 4;          // tokens per consumer warp per tile
-  constexpr int ITERS = TPW / 4;         // QK iterations (4 tokens per warp at a time)
   constexpr int kTileBytes = TILE * kD * 2;
   static_assert(TILE >= 16 && TILE <= 64 && (TILE & (TILE - 1)) == 0, "tile");
 
@@ -68,14 +63,8 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(
   }
   __syncthreads();
 
-  float m_run[G], l_run[G], acc[G][4];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    m_run[g] = -INFINITY;
-    l_run[g] = 0.f;
-#pragma unroll
-    for (int e = 0; e < 4; ++e) acc[g][e] = 0.f;
-  }
+  DecodeState<G> st;
+  st.reset();
 
   if (warp == 4) {
     // ------------------------------------------------------------------ producer
@@ -91,144 +80,38 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(
           blk = 0;
         }
         const size_t off = ((static_cast<size_t>(blk) * nkv + kvh) * block_size + (tok0 % block_size)) * kD;
-        uint8_t* st = smem + s * 2 * kTileBytes;
+        uint8_t* stg = smem + s * 2 * kTileBytes;
         mbar_expect_tx(&full_bar[s], 2 * kTileBytes);
-        bulk_load(st, k_cache + off, kTileBytes, &full_bar[s]);
-        bulk_load(st + kTileBytes, v_cache + off, kTileBytes, &full_bar[s]);
+        bulk_load(stg, k_cache + off, kTileBytes, &full_bar[s]);
+        bulk_load(stg + kTileBytes, v_cache + off, kTileBytes, &full_bar[s]);
       }
     }
   } else {
     // ------------------------------------------------------------------ consumers
-    const int grp = lane >> 3, j = lane & 7;
-    // q slices this lane multiplies: elements [8j, 8j+8) and [64+8j, 64+8j+8) of every head of the group
     float qr[G][16];
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const __nv_bfloat16* qp = q + (static_cast<size_t>(b) * nq + qh0 + g) * kD;
-      const uint4 lo = *reinterpret_cast<const uint4*>(qp + 8 * j);
-      const uint4 hi = *reinterpret_cast<const uint4*>(qp + 64 + 8 * j);
-      const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        qr[g][2 * e] = bf16_lo(w[e]) * scale_log2;
-        qr[g][2 * e + 1] = bf16_hi(w[e]) * scale_log2;
-      }
-    }
-    bool ok = true;
-    for (int t = 0; t < n_tiles && ok; ++t) {
+    decode_load_q<G>(q + (static_cast<size_t>(b) * nq + qh0) * kD, lane, scale_log2, qr);
+    for (int t = 0; t < n_tiles; ++t) {
       const int s = t % kDecStages;
       const uint32_t ph = (t / kDecStages) & 1;
-      ok = mbar_wait(&full_bar[s], ph, status);
-      if (!ok) break;
+      if (!mbar_wait(&full_bar[s], ph, status)) break;
       const uint8_t* Ks = smem + s * 2 * kTileBytes;
-      const uint8_t* Vs = Ks + kTileBytes;
-      const int tok0 = tok_begin + t * TILE;
-
-      float sc[ITERS][G];
-#pragma unroll
-      for (int it = 0; it < ITERS; ++it) {
-        const int r = warp * TPW + it * 4 + grp;
-        const uint4 k0 = *reinterpret_cast<const uint4*>(Ks + r * (kD * 2) + j * 16);
-        const uint4 k1 = *reinterpret_cast<const uint4*>(Ks + r * (kD * 2) + 128 + j * 16);
-        const uint32_t w[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
-        float kf[16];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          kf[2 * e] = bf16_lo(w[e]);
-          kf[2 * e + 1] = bf16_hi(w[e]);
-        }
-        const bool valid = tok0 + r < tok_end;
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-          float d = 0.f;
-#pragma unroll
-          for (int e = 0; e < 16; ++e) d = fmaf(qr[g][e], kf[e], d);
-          d += __shfl_xor_sync(0xffffffffu, d, 1);
-          d += __shfl_xor_sync(0xffffffffu, d, 2);
-          d += __shfl_xor_sync(0xffffffffu, d, 4);
-          sc[it][g] = valid ? d : -INFINITY;
-        }
-      }
-      // online softmax over this warp's TPW tokens
-      float alpha[G];
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        float mt = sc[0][g];
-#pragma unroll
-        for (int it = 1; it < ITERS; ++it) mt = fmaxf(mt, sc[it][g]);
-        mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 8));
-        mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 16));
-        const float m_new = fmaxf(m_run[g], mt);
-        const float m_use = m_new == -INFINITY ? 0.f : m_new;      // every token masked so far
-        alpha[g] = exp2f(m_run[g] - m_use);                        // exp2(-inf) = 0 on the first tile
-        float ps = 0.f;
-#pragma unroll
-        for (int it = 0; it < ITERS; ++it) {
-          sc[it][g] = exp2f(sc[it][g] - m_use);                    // masked -> 0
-          ps += sc[it][g];
-        }
-        l_run[g] = l_run[g] * alpha[g] + ps;                       // per token group; summed over groups at the end
-        m_run[g] = m_new;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[g][e] *= alpha[g];
-      }
-      // O += P V : lane owns d = 4*lane .. 4*lane+3
-#pragma unroll
-      for (int i = 0; i < TPW; ++i) {
-        const int r = warp * TPW + i;
-        const uint2 vv = *reinterpret_cast<const uint2*>(Vs + r * (kD * 2) + lane * 8);
-        const float v0 = bf16_lo(vv.x), v1 = bf16_hi(vv.x), v2 = bf16_lo(vv.y), v3 = bf16_hi(vv.y);
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-          const float p = __shfl_sync(0xffffffffu, sc[i / 4][g], (i % 4) * 8);
-          acc[g][0] = fmaf(p, v0, acc[g][0]);
-          acc[g][1] = fmaf(p, v1, acc[g][1]);
-          acc[g][2] = fmaf(p, v2, acc[g][2]);
-          acc[g][3] = fmaf(p, v3, acc[g][3]);
-        }
-      }
+      decode_consume_tile<G, TILE>(Ks, Ks + kTileBytes, tok_end - (tok_begin + t * TILE), warp, lane, qr, st);
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[s]);
-    }
-#pragma unroll
-    for (int g = 0; g < G; ++g) {   // each 8-lane group summed its own tokens: lanes 0, 8, 16, 24 hold the four partial sums
-      l_run[g] += __shfl_xor_sync(0xffffffffu, l_run[g], 8);
-      l_run[g] += __shfl_xor_sync(0xffffffffu, l_run[g], 16);
     }
   }
 
   // ------------------------------------------------------------------ merge the four warps (stage memory is free now)
   __syncthreads();
-  float* s_acc = reinterpret_cast<float*>(smem);                 // [4][G][128]
-  float* s_m = s_acc + 4 * G * kD;                               // [4][G]
-  float* s_l = s_m + 4 * G;                                      // [4][G]
-  if (warp < 4) {
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      *reinterpret_cast<float4*>(s_acc + (warp * G + g) * kD + lane * 4) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
-      if (lane == 0) {
-        s_m[warp * G + g] = m_run[g];
-        s_l[warp * G + g] = l_run[g];
-      }
-    }
-  }
+  float* s_acc = reinterpret_cast<float*>(smem);                 // [4][G][128] + [4][G] + [4][G]
+  if (warp < 4) decode_publish_state<G>(st, s_acc, warp, lane);
   __syncthreads();
   if (threadIdx.x < kD) {
     const int d = threadIdx.x;
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-      float M = -INFINITY;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) M = fmaxf(M, s_m[w * G + g]);
-      float L = 0.f, O = 0.f;
-#pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const float mw = s_m[w * G + g];
-        const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
-        L += s_l[w * G + g] * f;
-        O += s_acc[(w * G + g) * kD + d] * f;
-      }
-      const float o = L > 0.f ? O / L : 0.f;
+      float M, L;
+      const float o = decode_merged<G>(s_acc, g, d, M, L);
       const int qh = qh0 + g;
       if (n_chunks == 1) {
         out[(static_cast<size_t>(b) * nq + qh) * kD + d] = __float2bfloat16_rn(o);
@@ -271,7 +154,7 @@ static int launch_decode(const void* q, const void* kc, const void* vc, const in
                          float* part_ml, int B, int nq, int nkv, int block_size, int table_width, int num_blocks, int chunk,
                          int max_chunks, float scale_log2, unsigned* status, cudaStream_t stream) {
   constexpr int kTileBytes = TILE * kD * 2;
-  constexpr int merge_bytes = (4 * G * kD + 8 * G) * 4;
+  constexpr int merge_bytes = decode_merge_floats(G) * 4;
   constexpr int ring = kDecStages * 2 * kTileBytes;
   constexpr int smem = (ring > merge_bytes ? ring : merge_bytes) + 2 * kDecStages * 8 + 128;
   auto kern = decode_attn_kernel<G, TILE>;
@@ -314,6 +197,316 @@ extern "C" int forge_decode_attention(const void* q, const void* kc, const void*
 #define FORGE_DEC(GG, TT)                                                                                                   \
   return launch_decode<GG, TT>(q, kc, vc, bt, lens, out, part_o, part_ml, B, nq, nkv, block_size, table_width, num_blocks, \
                                chunk, max_chunks, sl2, status, stream)
+  if (tile == 64) {
+    if (G == 4) FORGE_DEC(4, 64);
+    if (G == 2) FORGE_DEC(2, 64);
+    FORGE_DEC(1, 64);
+  } else if (tile == 32) {
+    if (G == 4) FORGE_DEC(4, 32);
+    if (G == 2) FORGE_DEC(2, 32);
+    FORGE_DEC(1, 32);
+  } else {
+    if (G == 4) FORGE_DEC(4, 16);
+    if (G == 2) FORGE_DEC(2, 16);
+    FORGE_DEC(1, 16);
+  }
+#undef FORGE_DEC
+}
+
+
+// =========================================================================================================
+// Flat tile partition.
+//
+// The chunked kernel above gives every (sequence, KV head, chunk) its own CTA; contexts differ in length and the
+// number of CTAs is rarely a multiple of what the GPU runs at once, so its last wave is poorly filled (measured
+// 0.96 of copy bandwidth at batch 256 but 0.72-0.88 at batch 64-128).  Here the work is the flat list of all KV
+// tiles, ordered (sequence, KV head, tile), cut into gridDim.x equal ranges: every CTA streams the same number
+// of tiles (+-0), whatever the lengths.  A CTA walks its range item by item ((sequence, head) = item) with ONE
+// ring that never drains across items.  An item that lies wholly inside one CTA's range is finished there and
+// written to `out`; an item cut by a range boundary leaves normalised partials that the merge kernel combines.
+//
+// Partials: a CTA has at most two cut items, the one it starts in (slot 0) and the one it ends in (slot 1):
+// part_o[cta][slot][g][128], part_ml[cta][slot][g][2].  A cut item's parts are slot 1 of the CTA it starts in and
+// slot 0 of the following CTAs; the CTA it starts in records cta_meta[cta] = (item, number of CTAs it spans), and
+// CTA p of the merge kernel combines the item that starts in attention CTA p.
+// Lengths are read on the device and the grid is fixed, so the launch is CUDA-graph safe.
+// =========================================================================================================
+constexpr int kFlatMaxSeqs = 512;
+
+struct FlatCursor {       // position in the flat tile list
+  int b, h, t, n_b;       // sequence, item within the sequence (KV head x group slice), tile, tiles of this sequence
+};
+
+// cum[b] = tiles of sequences < b (exclusive prefix, cum[B] = total).  Flat index of tile t of item (b, h):
+// items_per_seq * cum[b] + h * n_b + t.
+__device__ __forceinline__ FlatCursor flat_locate(const int* cum, int B, int items_per_seq, int f) {
+  int lo = 0, hi = B;                                  // largest b with items_per_seq * cum[b] <= f
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (items_per_seq * cum[mid] <= f) lo = mid; else hi = mid;
+  }
+  FlatCursor c;
+  c.b = lo;
+  c.n_b = cum[lo + 1] - cum[lo];
+  const int r = f - items_per_seq * cum[lo];
+  c.h = r / c.n_b;
+  c.t = r - c.h * c.n_b;
+  return c;
+}
+
+__device__ __forceinline__ void flat_next_item(FlatCursor& c, const int* cum, int B, int items_per_seq) {
+  c.t = 0;
+  if (++c.h == items_per_seq) {
+    c.h = 0;
+    do { ++c.b; } while (c.b < B && cum[c.b + 1] == cum[c.b]);       // sequences of length 0 have no tiles
+    c.n_b = c.b < B ? cum[c.b + 1] - cum[c.b] : 0;
+  }
+}
+
+template <int G, int TILE>
+__global__ void __launch_bounds__(kDecThreads) decode_attn_flat_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+    const int* __restrict__ block_tables, const int* __restrict__ context_lens, __nv_bfloat16* __restrict__ out,
+    float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ cta_meta, int B, int nq, int nkv, int block_size,
+    int table_width, int num_blocks, int min_tiles, float scale_log2, unsigned* status) {
+  constexpr int kTileBytes = TILE * kD * 2;
+  constexpr int kRing = kDecStages * 2 * kTileBytes;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  float* s_acc = reinterpret_cast<float*>(smem + kRing);                      // merge area, separate from the ring
+  int* cum = reinterpret_cast<int*>(s_acc + decode_merge_floats(G));          // [B + 1]
+  int* chunk_tot = cum + kFlatMaxSeqs + 1;                                    // [16]
+  // mbarriers are 8-byte objects: the int arrays before them have an odd word count, so round the address up
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(chunk_tot + 16) + 15) & ~uintptr_t(15));
+  uint64_t* empty_bar = full_bar + kDecStages;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kDecStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 4);
+    }
+    fence_mbar_init();
+  }
+  pdl_wait();                                           // q, the new K/V entries and the step buffer come from predecessors
+
+  // ---- exclusive prefix sum of tiles per sequence (B <= 512): warp scans of 32, then a scan of the 16 totals
+  const int n_chunks32 = (B + 31) >> 5;
+  for (int ch = warp; ch < n_chunks32; ch += kDecThreads / 32) {
+    const int b = ch * 32 + lane;
+    const int len = b < B ? context_lens[b] : 0;
+    int v = (len + TILE - 1) / TILE;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, v, o);
+      if (lane >= o) v += u;
+    }
+    if (b < B) cum[b + 1] = v;                          // inclusive within the chunk, for now
+    if (lane == 31) chunk_tot[ch] = v;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int v = lane < n_chunks32 ? chunk_tot[lane] : 0;
+    const int own = v;
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, v, o);
+      if (lane >= o) v += u;
+    }
+    if (lane < 16) chunk_tot[lane] = v - own;           // exclusive offset of each chunk
+    if (lane == 0) cum[0] = 0;
+  }
+  __syncthreads();
+  for (int b = threadIdx.x; b < B; b += kDecThreads) cum[b + 1] += chunk_tot[b >> 5];
+  __syncthreads();
+
+  const int groups_per_kv = (nq / nkv) / G;             // > 1 when the GQA group is processed in slices of G
+  const int items_per_seq = nkv * groups_per_kv;
+  const int total = items_per_seq * cum[B];
+  int per_cta = (total + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  if (per_cta < min_tiles) per_cta = min_tiles;
+  const int f0 = blockIdx.x * per_cta;
+  const int f1 = min(f0 + per_cta, total);
+  // rows of length 0 (padding of a graph bucket) belong to no item: give them a defined output
+  for (int b = blockIdx.x; b < B; b += gridDim.x)
+    if (cum[b + 1] == cum[b])
+      for (int i = threadIdx.x; i < nq * kD; i += kDecThreads) out[static_cast<size_t>(b) * nq * kD + i] = __float2bfloat16_rn(0.f);
+  if (threadIdx.x == 0) cta_meta[blockIdx.x * 2] = -1;  // no cut item starts here, unless found below
+  if (f0 >= f1) return;                                 // uniform for the CTA
+  __syncthreads();                                      // orders the default above before the consumers' update
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ producer: one ring across all items
+    if (lane == 0) {
+      FlatCursor c = flat_locate(cum, B, items_per_seq, f0);
+      int it = 0;
+      for (int f = f0; f < f1;) {
+        const int seg = min(c.n_b - c.t, f1 - f);
+        const int kvh = c.h / groups_per_kv;
+        const int* table = block_tables + static_cast<size_t>(c.b) * table_width;
+        for (int i = 0; i < seg; ++i, ++it) {
+          const int s = it % kDecStages;
+          const uint32_t ph = (it / kDecStages) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, status)) { f = f1; break; }
+          const int tok0 = (c.t + i) * TILE;
+          int blk = table[tok0 / block_size];
+          if (blk < 0 || blk >= num_blocks) {
+            set_status(status, kStatusBadIndex);
+            blk = 0;
+          }
+          const size_t off = ((static_cast<size_t>(blk) * nkv + kvh) * block_size + (tok0 % block_size)) * kD;
+          uint8_t* stg = smem + s * 2 * kTileBytes;
+          mbar_expect_tx(&full_bar[s], 2 * kTileBytes);
+          bulk_load(stg, k_cache + off, kTileBytes, &full_bar[s]);
+          bulk_load(stg + kTileBytes, v_cache + off, kTileBytes, &full_bar[s]);
+        }
+        f += seg;
+        flat_next_item(c, cum, B, items_per_seq);
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------------- consumers (warps 0..3, 128 threads)
+  FlatCursor c = flat_locate(cum, B, items_per_seq, f0);
+  DecodeState<G> st;
+  int it = 0;
+  bool ok = true;
+  for (int f = f0; f < f1 && ok;) {
+    const int seg = min(c.n_b - c.t, f1 - f);
+    const int kvh = c.h / groups_per_kv;
+    const int qh0 = kvh * (nq / nkv) + (c.h % groups_per_kv) * G;
+    const int len = context_lens[c.b];
+    float qr[G][16];
+    decode_load_q<G>(q + (static_cast<size_t>(c.b) * nq + qh0) * kD, lane, scale_log2, qr);
+    st.reset();
+    for (int i = 0; i < seg; ++i, ++it) {
+      const int s = it % kDecStages;
+      const uint32_t ph = (it / kDecStages) & 1;
+      ok = mbar_wait(&full_bar[s], ph, status);
+      if (!ok) break;
+      const uint8_t* Ks = smem + s * 2 * kTileBytes;
+      decode_consume_tile<G, TILE>(Ks, Ks + kTileBytes, len - (c.t + i) * TILE, warp, lane, qr, st);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
+    }
+    if (!ok) break;
+    // ---- end of this CTA's part of the item: merge the four warps, then final output or a partial
+    decode_publish_state<G>(st, s_acc, warp, lane);
+    named_barrier_sync(1, 128);
+    const bool starts_here = c.t == 0, whole = starts_here && seg == c.n_b;
+    const int d = threadIdx.x;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float M, L;
+      const float o = decode_merged<G>(s_acc, g, d, M, L);
+      if (whole) {
+        out[(static_cast<size_t>(c.b) * nq + qh0 + g) * kD + d] = __float2bfloat16_rn(o);
+      } else {
+        const size_t p = (static_cast<size_t>(blockIdx.x) * 2 + (starts_here ? 1 : 0)) * G + g;
+        part_o[p * kD + d] = o;
+        if (d == 0) {
+          part_ml[p * 2] = M;
+          part_ml[p * 2 + 1] = L;
+        }
+      }
+    }
+    if (starts_here && !whole && d == 0) {
+      const int item_end = f + c.n_b;                   // flat index one past the item's last tile (f is its first tile here)
+      cta_meta[blockIdx.x * 2] = c.b * items_per_seq + c.h;
+      cta_meta[blockIdx.x * 2 + 1] = (item_end - 1) / per_cta - static_cast<int>(blockIdx.x) + 1;
+    }
+    named_barrier_sync(1, 128);                         // the merge area is reused by the next item
+    f += seg;
+    flat_next_item(c, cum, B, items_per_seq);
+  }
+}
+
+// Merge the partials of items cut by a range boundary: CTA p handles the item that starts in attention CTA p.
+template <int G>
+__global__ void __launch_bounds__(kD) decode_flat_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                                 const int* __restrict__ cta_meta, __nv_bfloat16* __restrict__ out,
+                                                                 int nq, int nkv) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int first = blockIdx.x, d = threadIdx.x;
+  const int item = cta_meta[first * 2], n = cta_meta[first * 2 + 1];
+  if (item < 0) return;
+  const int group = nq / nkv, groups_per_kv = group / G, items_per_seq = nkv * groups_per_kv;
+  const int b = item / items_per_seq, h = item % items_per_seq;
+  const int qh0 = (h / groups_per_kv) * group + (h % groups_per_kv) * G;
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    float M = -INFINITY;
+    for (int k = 0; k < n; ++k) {
+      const size_t p = (static_cast<size_t>(first + k) * 2 + (k == 0 ? 1 : 0)) * G + g;
+      M = fmaxf(M, part_ml[p * 2]);
+    }
+    float L = 0.f, O = 0.f;
+    for (int k = 0; k < n; ++k) {
+      const size_t p = (static_cast<size_t>(first + k) * 2 + (k == 0 ? 1 : 0)) * G + g;
+      const float w = part_ml[p * 2 + 1] * exp2f(part_ml[p * 2] - M);
+      L += w;
+      O += part_o[p * kD + d] * w;
+    }
+    out[(static_cast<size_t>(b) * nq + qh0 + g) * kD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+  }
+}
+
+template <int G, int TILE>
+static int launch_decode_flat(const void* q, const void* kc, const void* vc, const int* bt, const int* lens, void* out,
+                              float* scratch, int num_ctas, int B, int nq, int nkv, int block_size, int table_width, int num_blocks,
+                              float scale_log2, unsigned* status, cudaStream_t stream) {
+  constexpr int kTileBytes = TILE * kD * 2;
+  constexpr int smem = kDecStages * 2 * kTileBytes + decode_merge_floats(G) * 4 + (kFlatMaxSeqs + 1 + 16) * 4 + 16 + 2 * kDecStages * 8 + 128;
+  static_assert(smem <= 113 * 1024, "two CTAs per SM");
+  auto kern = decode_attn_flat_kernel<G, TILE>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
+    attr_set = true;
+  }
+  float* part_o = scratch;
+  float* part_ml = part_o + static_cast<size_t>(num_ctas) * 2 * G * kD;
+  int* cta_meta = reinterpret_cast<int*>(part_ml + static_cast<size_t>(num_ctas) * 2 * G * 2);
+  const int min_tiles = 256 / TILE < 2 ? 2 : 256 / TILE;        // at least ~256 tokens per CTA: below that the start-up dominates
+  if (launch_kernel(kern, dim3(num_ctas), dim3(kDecThreads), smem, stream, 0, static_cast<const __nv_bfloat16*>(q),
+                    static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc), bt, lens,
+                    static_cast<__nv_bfloat16*>(out), part_o, part_ml, cta_meta, B, nq, nkv, block_size, table_width, num_blocks,
+                    min_tiles, scale_log2, status) != cudaSuccess)
+    return -5;
+  if (launch_kernel(decode_flat_combine_kernel<G>, dim3(num_ctas), dim3(kD), 0, stream, 0, static_cast<const float*>(part_o),
+                    static_cast<const float*>(part_ml), static_cast<const int*>(cta_meta), static_cast<__nv_bfloat16*>(out), nq,
+                    nkv) != cudaSuccess)
+    return -5;
+  return 0;
+}
+
+// Floats of scratch the flat kernel needs for a grid of num_ctas CTAs and up to B sequences.
+extern "C" size_t forge_decode_attention_flat_scratch_floats(int num_ctas, int B, int nq, int nkv) {
+  const int group = nkv > 0 ? nq / nkv : 1;
+  const int G = group % 4 == 0 ? 4 : (group % 2 == 0 ? 2 : 1);
+  (void)B;
+  return static_cast<size_t>(num_ctas) * 2 * G * (kD + 2) + static_cast<size_t>(num_ctas) * 2 + 64;
+}
+
+// Same operands as forge_decode_attention; scratch: forge_decode_attention_flat_scratch_floats() floats, contents
+// irrelevant on entry.  num_ctas: grid size, normally two per SM.  B <= 512.
+extern "C" int forge_decode_attention_flat(const void* q, const void* kc, const void* vc, const int* bt, const int* lens, void* out,
+                                           float* scratch, int num_ctas, int B, int nq, int nkv, int head_dim, int block_size,
+                                           int table_width, int num_blocks, float scale, unsigned* status, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (head_dim != kD || nq % nkv != 0 || block_size < 16 || (block_size & (block_size - 1)) || B > kFlatMaxSeqs || num_ctas < 1 ||
+      scratch == nullptr)
+    return -1;
+  const int tile = block_size < 64 ? block_size : 64;
+  const int group = nq / nkv;
+  const int G = group % 4 == 0 ? 4 : (group % 2 == 0 ? 2 : 1);
+  const float sl2 = scale * 1.4426950408889634f;
+#define FORGE_DEC(GG, TT)                                                                                                       \
+  return launch_decode_flat<GG, TT>(q, kc, vc, bt, lens, out, scratch, num_ctas, B, nq, nkv, block_size, table_width, num_blocks, \
+                                    sl2, status, stream)
   if (tile == 64) {
     if (G == 4) FORGE_DEC(4, 64);
     if (G == 2) FORGE_DEC(2, 64);

@@ -45,6 +45,10 @@ int forge_sample_merge_ranks(const float* vals, const int* ids, int ranks, int r
 int forge_decode_attention(const void* q, const void* kc, const void* vc, const int* bt, const int* lens, void* out,
                            float* part_o, float* part_ml, int B, int nq, int nkv, int head_dim, int block_size, int table_width,
                            int num_blocks, int chunk, int max_chunks, float scale, unsigned* status, cudaStream_t stream);
+size_t forge_decode_attention_flat_scratch_floats(int num_ctas, int B, int nq, int nkv);
+int forge_decode_attention_flat(const void* q, const void* kc, const void* vc, const int* bt, const int* lens, void* out,
+                                float* scratch, int num_ctas, int B, int nq, int nkv, int head_dim, int block_size, int table_width,
+                                int num_blocks, float scale, unsigned* status, cudaStream_t stream);
 int forge_prefill_attention(const void* q, const void* kc, const void* vc, const int* cu_q, const int* lens, const int* bt,
                             void* out, int T, int num_seqs, int max_q, int nq, int nkv, int head_dim, int block_size,
                             int table_width, int num_blocks, float scale, unsigned* status, cudaStream_t stream);
@@ -237,6 +241,34 @@ void decode_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
         "forge_decode_attention");
 }
 
+int64_t decode_attention_flat_scratch_floats(int64_t num_ctas, int64_t B, int64_t nq, int64_t nkv) {
+  return static_cast<int64_t>(forge_decode_attention_flat_scratch_floats(static_cast<int>(num_ctas), static_cast<int>(B),
+                                                                         static_cast<int>(nq), static_cast<int>(nkv)));
+}
+
+// Decode attention with the flat tile partition: num_ctas CTAs share all KV tiles equally.  scratch: fp32, at least
+// decode_attention_flat_scratch_floats(num_ctas, B, nq, nkv) elements.
+void decode_attention_flat(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& block_tables,
+                           const Tensor& context_lens, Tensor& out, Tensor& scratch, int64_t num_ctas, double scale, const Tensor& status) {
+  CHECK_CUDA_CONTIG(q); CHECK_BF16(q); CHECK_CUDA_CONTIG(k_cache); CHECK_BF16(k_cache); CHECK_CUDA_CONTIG(v_cache); CHECK_BF16(v_cache);
+  CHECK_CUDA_CONTIG(block_tables); CHECK_I32(block_tables); CHECK_CUDA_CONTIG(context_lens); CHECK_I32(context_lens);
+  CHECK_CUDA_CONTIG(out); CHECK_BF16(out); CHECK_CUDA_CONTIG(scratch); CHECK_F32(scratch);
+  TORCH_CHECK(q.dim() == 3 && k_cache.dim() == 4 && v_cache.sizes() == k_cache.sizes() && block_tables.dim() == 2, "decode_attention_flat: ranks");
+  const int64_t B = q.size(0), nq = q.size(1), D = q.size(2), nkv = k_cache.size(1), bs = k_cache.size(2);
+  TORCH_CHECK(k_cache.size(3) == D && block_tables.size(0) >= B && context_lens.numel() >= B && out.numel() == B * nq * D,
+              "decode_attention_flat: shape mismatch");
+  TORCH_CHECK(B <= 512, "decode_attention_flat: at most 512 sequences");
+  TORCH_CHECK(num_ctas >= 1 && scratch.numel() >= decode_attention_flat_scratch_floats(num_ctas, B, nq, nkv),
+              "decode_attention_flat: scratch too small");
+  const c10::cuda::CUDAGuard guard(q.device());
+  check(forge_decode_attention_flat(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr<int>(),
+                                    context_lens.data_ptr<int>(), out.data_ptr(), scratch.data_ptr<float>(), static_cast<int>(num_ctas),
+                                    static_cast<int>(B), static_cast<int>(nq), static_cast<int>(nkv), static_cast<int>(D),
+                                    static_cast<int>(bs), static_cast<int>(block_tables.size(1)), static_cast<int>(k_cache.size(0)),
+                                    static_cast<float>(scale), status_ptr(status), stream_of(q)),
+        "forge_decode_attention_flat");
+}
+
 void prefill_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& cu_seqlens_q,
                        const Tensor& context_lens, const Tensor& block_tables, Tensor& out, int64_t num_seqs, int64_t max_q,
                        double scale, const Tensor& status) {
@@ -386,5 +418,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sample", &sample);
   m.def("sample_merge_ranks", &sample_merge_ranks);
   m.def("decode_attention", &decode_attention);
+  m.def("decode_attention_flat", &decode_attention_flat);
+  m.def("decode_attention_flat_scratch_floats", &decode_attention_flat_scratch_floats);
   m.def("prefill_attention", &prefill_attention);
 }

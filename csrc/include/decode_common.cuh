@@ -1,0 +1,157 @@
+// Pieces shared by the two decode-attention kernels (context split into fixed chunks; flat tile partition):
+// the per-lane query slice, one tile of online softmax for a consumer warp, and the merge of the four
+// consumer warps' states.  head_dim is 128; scores use exp2 with the scale folded into q.
+#pragma once
+#include "ptx.cuh"
+
+namespace forge {
+
+constexpr int kD = 128;
+constexpr int kDecStages = 3;
+constexpr int kDecThreads = 160;   // 4 consumer warps + 1 producer warp
+
+template <int G>
+struct DecodeState {
+  float m[G], l[G], acc[G][4];
+  __device__ __forceinline__ void reset() {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      m[g] = -INFINITY;
+      l[g] = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[g][e] = 0.f;
+    }
+  }
+};
+
+// q slices this lane multiplies: elements [8j, 8j+8) and [64+8j, 64+8j+8) of every head of the group (j = lane % 8)
+template <int G>
+__device__ __forceinline__ void decode_load_q(const __nv_bfloat16* __restrict__ q_row0, int lane, float scale_log2, float (&qr)[G][16]) {
+  const int j = lane & 7;
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const __nv_bfloat16* qp = q_row0 + static_cast<size_t>(g) * kD;
+    const uint4 lo = *reinterpret_cast<const uint4*>(qp + 8 * j);
+    const uint4 hi = *reinterpret_cast<const uint4*>(qp + 64 + 8 * j);
+    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      qr[g][2 * e] = bf16_lo(w[e]) * scale_log2;
+      qr[g][2 * e + 1] = bf16_hi(w[e]) * scale_log2;
+    }
+  }
+}
+
+// One tile (TILE tokens of K and V in shared memory) for consumer warp `warp`: scores of its TILE / 4 tokens,
+// online softmax update, O += P V.  `valid_tokens`: tokens of the tile that exist (the rest is masked).
+template <int G, int TILE>
+__device__ __forceinline__ void decode_consume_tile(const uint8_t* Ks, const uint8_t* Vs, int valid_tokens, int warp, int lane,
+                                                    const float (&qr)[G][16], DecodeState<G>& st) {
+  constexpr int TPW = TILE / 4;          // tokens per consumer warp per tile
+  constexpr int ITERS = TPW / 4;         // QK iterations (4 tokens per warp at a time)
+  const int grp = lane >> 3, j = lane & 7;
+  float sc[ITERS][G];
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int r = warp * TPW + it * 4 + grp;
+    const uint4 k0 = *reinterpret_cast<const uint4*>(Ks + r * (kD * 2) + j * 16);
+    const uint4 k1 = *reinterpret_cast<const uint4*>(Ks + r * (kD * 2) + 128 + j * 16);
+    const uint32_t w[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+    float kf[16];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      kf[2 * e] = bf16_lo(w[e]);
+      kf[2 * e + 1] = bf16_hi(w[e]);
+    }
+    const bool valid = r < valid_tokens;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float d = 0.f;
+#pragma unroll
+      for (int e = 0; e < 16; ++e) d = fmaf(qr[g][e], kf[e], d);
+      d += __shfl_xor_sync(0xffffffffu, d, 1);
+      d += __shfl_xor_sync(0xffffffffu, d, 2);
+      d += __shfl_xor_sync(0xffffffffu, d, 4);
+      sc[it][g] = valid ? d : -INFINITY;
+    }
+  }
+  // online softmax over this warp's TPW tokens
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    float mt = sc[0][g];
+#pragma unroll
+    for (int it = 1; it < ITERS; ++it) mt = fmaxf(mt, sc[it][g]);
+    mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 8));
+    mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 16));
+    const float m_new = fmaxf(st.m[g], mt);
+    const float m_use = m_new == -INFINITY ? 0.f : m_new;      // every token masked so far
+    const float alpha = exp2f(st.m[g] - m_use);                // exp2(-inf) = 0 on the first tile
+    float ps = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      sc[it][g] = exp2f(sc[it][g] - m_use);                    // masked -> 0
+      ps += sc[it][g];
+    }
+    st.l[g] = st.l[g] * alpha + ps;                            // per token group; summed over groups at the end
+    st.m[g] = m_new;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) st.acc[g][e] *= alpha;
+  }
+  // O += P V : lane owns d = 4*lane .. 4*lane+3
+#pragma unroll
+  for (int i = 0; i < TPW; ++i) {
+    const int r = warp * TPW + i;
+    const uint2 vv = *reinterpret_cast<const uint2*>(Vs + r * (kD * 2) + lane * 8);
+    const float v0 = bf16_lo(vv.x), v1 = bf16_hi(vv.x), v2 = bf16_lo(vv.y), v3 = bf16_hi(vv.y);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float p = __shfl_sync(0xffffffffu, sc[i / 4][g], (i % 4) * 8);
+      st.acc[g][0] = fmaf(p, v0, st.acc[g][0]);
+      st.acc[g][1] = fmaf(p, v1, st.acc[g][1]);
+      st.acc[g][2] = fmaf(p, v2, st.acc[g][2]);
+      st.acc[g][3] = fmaf(p, v3, st.acc[g][3]);
+    }
+  }
+}
+
+// After the last tile: each 8-lane group summed its own tokens (lanes 0, 8, 16, 24 hold the four partial sums);
+// then every consumer warp publishes its state to shared memory ([4][G][128] + [4][G] + [4][G] floats).
+template <int G>
+__device__ __forceinline__ void decode_publish_state(DecodeState<G>& st, float* s_acc, int warp, int lane) {
+  float* s_m = s_acc + 4 * G * kD;
+  float* s_l = s_m + 4 * G;
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    st.l[g] += __shfl_xor_sync(0xffffffffu, st.l[g], 8);
+    st.l[g] += __shfl_xor_sync(0xffffffffu, st.l[g], 16);
+    *reinterpret_cast<float4*>(s_acc + (warp * G + g) * kD + lane * 4) = make_float4(st.acc[g][0], st.acc[g][1], st.acc[g][2], st.acc[g][3]);
+    if (lane == 0) {
+      s_m[warp * G + g] = st.m[g];
+      s_l[warp * G + g] = st.l[g];
+    }
+  }
+}
+
+// Thread d (0..127) merges the four warps' states for head g: normalised output element d, running max M, sum L.
+template <int G>
+__device__ __forceinline__ float decode_merged(const float* s_acc, int g, int d, float& M, float& L) {
+  const float* s_m = s_acc + 4 * G * kD;
+  const float* s_l = s_m + 4 * G;
+  M = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) M = fmaxf(M, s_m[w * G + g]);
+  L = 0.f;
+  float O = 0.f;
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    const float mw = s_m[w * G + g];
+    const float f = mw == -INFINITY ? 0.f : exp2f(mw - M);
+    L += s_l[w * G + g] * f;
+    O += s_acc[(w * G + g) * kD + d] * f;
+  }
+  return L > 0.f ? O / L : 0.f;
+}
+
+constexpr int decode_merge_floats(int G) { return 4 * G * kD + 8 * G; }
+
+}  // namespace forge

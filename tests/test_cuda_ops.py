@@ -234,11 +234,13 @@ def _paged_case(q_lens, k_lens, nq, nkv, bs, seed=0):
     return q, kc, vc, b
 
 
+@pytest.mark.parametrize("mode", ["flat", "chunked"])
 @pytest.mark.parametrize("k_lens,nq,nkv,bs", [
     ([1], 16, 8, 256), ([5, 300, 64, 1000], 16, 8, 256), ([17, 33, 250], 8, 2, 16), ([700, 2011, 129], 32, 8, 256),
     ([40, 90], 8, 8, 32), ([513, 77], 8, 1, 64),
 ])
-def test_decode_attention(ops, k_lens, nq, nkv, bs):
+def test_decode_attention(ops, k_lens, nq, nkv, bs, mode, monkeypatch):
+    monkeypatch.setattr(ops, "decode_attention_mode", mode)
     q, kc, vc, b = _paged_case([1] * len(k_lens), k_lens, nq, nkv, bs)
     b.is_prefill = False
     got = ops.attention(q, kc, vc, b, 128 ** -0.5)
@@ -247,13 +249,36 @@ def test_decode_attention(ops, k_lens, nq, nkv, bs):
     ops.check_status()
 
 
-def test_decode_attention_padding_rows(ops):
+@pytest.mark.parametrize("mode", ["flat", "chunked"])
+def test_decode_attention_padding_rows(ops, mode, monkeypatch):
+    monkeypatch.setattr(ops, "decode_attention_mode", mode)
     q, kc, vc, b = _paged_case([1, 1, 1], [100, 0, 7], 16, 8, 256)
     b.is_prefill = False
     got = ops.attention(q, kc, vc, b, 128 ** -0.5)
     assert torch.count_nonzero(got[1]) == 0
     want = ref.attention(q, kc, vc, b.cu_seqlens_q, b.context_lens, b.block_tables, 128 ** -0.5, 3)
     _close(got[[0, 2]], want[[0, 2]], 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("batch,lo,hi,nq,nkv", [(64, 100, 1500, 16, 8), (200, 1, 700, 16, 8), (300, 3000, 3100, 8, 2), (7, 1, 4000, 32, 8)])
+def test_decode_attention_flat_partition_many_sequences(ops, batch, lo, hi, nq, nkv, monkeypatch):
+    """Enough tiles that every CTA's range spans several (sequence, head) items and most items are cut at most once;
+    lengths from 1 token to several thousand, zero-length rows in between; both kernels against the fp32 statement,
+    twice in a row (the scratch keeps stale partials from the first call)."""
+    g = torch.Generator().manual_seed(batch)
+    k_lens = torch.randint(lo, hi + 1, (batch,), generator=g).tolist()
+    for i in range(3, batch, 17):
+        k_lens[i] = 0
+    q, kc, vc, b = _paged_case([1] * batch, k_lens, nq, nkv, 256, seed=batch)
+    b.is_prefill = False
+    want = ref.attention(q, kc, vc, b.cu_seqlens_q, b.context_lens, b.block_tables, 128 ** -0.5, b.num_seqs)
+    live = [i for i, n in enumerate(k_lens) if n > 0]
+    for mode in ("flat", "flat", "chunked"):
+        monkeypatch.setattr(ops, "decode_attention_mode", mode)
+        got = ops.attention(q, kc, vc, b, 128 ** -0.5)
+        _close(got[live], want[live], 2e-2, 2e-2)
+        assert torch.count_nonzero(got[3]) == 0
+    ops.check_status()
 
 
 @pytest.mark.parametrize("q_lens,k_lens,nq,nkv,bs", [
