@@ -8,7 +8,11 @@
 // CTA = 64 query rows of one (sequence, q head), four warps of 16 rows.  K and V tiles of 64 keys come in by
 // TMA with the 128-byte swizzle (two boxes of 64 x 64 per tile, one per half of head_dim) through a two-stage
 // ring, so shared-memory reads by ldmatrix are conflict-free.  This version multiplies with mma.sync
-// m16n8k16 (fp32 accumulate, online softmax in registers).
+// m16n8k16 (fp32 accumulate, online softmax in registers); it serves cache blocks smaller than 128 tokens.
+// Blocks of >= 128 tokens go to the tcgen05 kernel in prefill_umma.cu.
+#include <cstdlib>
+#include <string>
+
 #include "../include/launch.cuh"
 #include "../include/ptx.cuh"
 
@@ -229,6 +233,10 @@ __global__ void __launch_bounds__(128) prefill_attn_kernel(
 
 extern "C" int forge_make_tmap_2d(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                                   uint32_t box_rows, int elem_bytes);
+extern "C" int forge_prefill_attention_umma(const void* q, const void* kc, const void* vc, const int* cu_q, const int* lens,
+                                            const int* bt, void* out, int T, int num_seqs, int max_q, int nq, int nkv, int head_dim,
+                                            int block_size, int table_width, int num_blocks, float scale, unsigned* status,
+                                            cudaStream_t stream);
 
 // q [T, nq, 128] bf16 (contiguous); caches [num_blocks, nkv, block_size, 128]; out [T, nq * 128].
 extern "C" int forge_prefill_attention(const void* q, const void* kc, const void* vc, const int* cu_q, const int* lens,
@@ -237,6 +245,11 @@ extern "C" int forge_prefill_attention(const void* q, const void* kc, const void
                                        cudaStream_t stream) {
   if (T <= 0 || num_seqs <= 0) return 0;
   if (head_dim != kPD || nq % nkv != 0 || block_size < 16 || (block_size & (block_size - 1))) return -1;
+  // cache blocks of >= 128 tokens (the engine's default is 256): the tcgen05 kernel; FORGE_PREFILL_ATTN=mma keeps this one
+  static const bool force_mma = std::getenv("FORGE_PREFILL_ATTN") != nullptr && std::string(std::getenv("FORGE_PREFILL_ATTN")) == "mma";
+  if (block_size >= 128 && !force_mma)
+    return forge_prefill_attention_umma(q, kc, vc, cu_q, lens, bt, out, T, num_seqs, max_q, nq, nkv, head_dim, block_size, table_width,
+                                        num_blocks, scale, status, stream);
   const uint32_t box_rows = block_size < kPN ? block_size : kPN;
   CUtensorMap tm_q, tm_k, tm_v;
   if (forge_make_tmap_2d(&tm_q, q, T, static_cast<uint64_t>(nq) * kPD, static_cast<uint64_t>(nq) * kPD, kPM, 2) != 0) return -2;

@@ -284,6 +284,7 @@ def test_decode_attention_flat_partition_many_sequences(ops, batch, lo, hi, nq, 
 @pytest.mark.parametrize("q_lens,k_lens,nq,nkv,bs", [
     ([64], [64], 16, 8, 256), ([1, 100, 257], [1, 100, 257], 16, 8, 256), ([30, 70], [286, 70], 8, 2, 256),
     ([50, 200], [50, 200], 4, 4, 16), ([10], [522], 8, 1, 32), ([1000], [1000], 2, 1, 256),
+    ([300, 129, 128, 1], [812, 129, 640, 1], 8, 2, 128), ([513, 40], [513, 1064], 4, 1, 256), ([128, 256], [128, 256], 16, 8, 512),
 ])
 def test_prefill_attention(ops, q_lens, k_lens, nq, nkv, bs):
     q, kc, vc, b = _paged_case(q_lens, k_lens, nq, nkv, bs, seed=1)

@@ -95,6 +95,16 @@ def case_row_linear(rank, world):
         # every rank must hold bit-identical results
         both = tp.all_gather_stack(y)
         assert all(torch.equal(both[0], both[r]) for r in range(world))
+    # standalone all-reduce and barrier through the same region
+    for shape in ((1, 8), (256, H), (3, 5, 64), (100, 2048)):
+        mine = (torch.randn(*shape, device="cuda", generator=g) + rank).bfloat16()
+        parts = tp.all_gather_stack(mine)
+        got = ops.fused_all_reduce(mine)
+        want = parts.float().sum(0)
+        assert got.shape == mine.shape and (got.float() - want).abs().max().item() <= 0.04 * want.abs().max().item() + 1e-3
+        gathered = tp.all_gather_stack(got)
+        assert all(torch.equal(gathered[0], gathered[r]) for r in range(world))
+    ops.fused_barrier()
     ops.check_status()
     ops.close()
     return worst

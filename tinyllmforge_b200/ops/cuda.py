@@ -203,6 +203,32 @@ class CudaOps:
         from ..parallel.symm import FusedTPComm
         self.fused = FusedTPComm(self.tp, hidden_size, max_tokens, self.device)
 
+    def fused_all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        """Sum over the ranks of a bf16 tensor of at most 256 x hidden elements (last dimension a multiple of 8) through
+        the symmetric region: one kernel pushes this rank's rows into every rank's slot, one kernel waits for all ranks
+        and adds the slots in rank order (fp32), so every rank gets the same bits.  Larger tensors: library collective."""
+        from ..parallel.symm import MAX_PUSH_ROWS, SITE_ALLREDUCE
+        tp = self.tp
+        if tp.size == 1:
+            return x
+        H = x.shape[-1]
+        if (self.fused is None or x.dtype != torch.bfloat16 or H % 8 or H > 8192 or x.numel() > MAX_PUSH_ROWS * self.fused.hidden):
+            return tp.all_reduce(x)
+        st = self.fused.sites[SITE_ALLREDUCE]
+        x = x.contiguous()
+        out = torch.empty_like(x)
+        self.C.tp_rows_push(x, tp.rank, st.slot_ptrs, st.signal_ptrs, st.arrive, st.epoch)
+        self.C.tp_reduce_rms_norm(tp.size, tp.size, st.local_slots, st.slot_stride, st.local_signal, st.epoch, self.fused.timeout_ns,
+                                  None, out, None, None, 0.0, self.status)
+        self.launches += 2
+        return out
+
+    def fused_barrier(self) -> None:
+        """Device-side barrier over the ranks: the stream of every rank passes only after every rank's stream got here
+        (an all-reduce of one 8-element row; bounded wait, a timeout sets the status word)."""
+        if self.tp.size > 1:
+            self.fused_all_reduce(torch.zeros(1, 8, dtype=torch.bfloat16, device=self.device))
+
     def embed_norm(self, ids, embed, norm_weight, eps):
         """Embedding lookup + cross-rank exchange + first RMSNorm -> (normed, residual)."""
         tp = embed.tp

@@ -11,6 +11,7 @@ Region layout (identical on every rank, byte offsets):
     embed     max_tokens x H bf16        embedding rows, each written by the rank that owns the token id
     slots_o   tp x 256 x H bf16          o_proj partial sums, slot r written by rank r
     slots_d   tp x 256 x H bf16          down_proj partial sums
+    slots_ar  tp x 256 x H bf16          operands of the standalone all-reduce / barrier
 
 Replaces the NCCL calls at tinyvllm/layers/linear.py:183 and tinyvllm/layers/embed_head.py:41,66-67.
 """
@@ -21,7 +22,7 @@ from dataclasses import dataclass
 
 import torch
 
-SITE_EMBED, SITE_O, SITE_DOWN, SITE_SAMPLE = 0, 1, 2, 3
+SITE_EMBED, SITE_O, SITE_DOWN, SITE_SAMPLE, SITE_ALLREDUCE = 0, 1, 2, 3, 4
 NUM_SITES = 8
 MAX_PUSH_ROWS = 256          # rows the decode GEMM can push (its token limit)
 MAX_PAIR_ROWS = 512
@@ -58,7 +59,7 @@ class FusedTPComm:
         cur = 0
         for name, nbytes in (("signals", NUM_SITES * 8 * 4), ("pairs", self.size * MAX_PAIR_ROWS * 8),
                              ("embed", max_tokens * H * 2), ("slots_o", self.size * MAX_PUSH_ROWS * H * 2),
-                             ("slots_d", self.size * MAX_PUSH_ROWS * H * 2)):
+                             ("slots_d", self.size * MAX_PUSH_ROWS * H * 2), ("slots_ar", self.size * MAX_PUSH_ROWS * H * 2)):
             off[name] = cur
             cur = _align(cur + nbytes)
         self.offsets, self.nbytes = off, cur
@@ -91,6 +92,7 @@ class FusedTPComm:
             SITE_O: site(SITE_O, "slots_o", MAX_PUSH_ROWS * H * 2),
             SITE_DOWN: site(SITE_DOWN, "slots_d", MAX_PUSH_ROWS * H * 2),
             SITE_SAMPLE: site(SITE_SAMPLE, "pairs", MAX_PAIR_ROWS * 8),
+            SITE_ALLREDUCE: site(SITE_ALLREDUCE, "slots_ar", MAX_PUSH_ROWS * H * 2),
         }
         self.max_tokens = max_tokens
 
