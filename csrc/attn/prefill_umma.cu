@@ -11,10 +11,12 @@
 //
 // Warp roles (192 threads): warp 0 = TMA producer (2-stage K ring, 2-stage V ring), warp 1 = tensor-memory owner and
 // UMMA issuer, warps 2..5 = softmax: thread = one query row (its TMEM lane), so row max and row sum need no
-// shuffles.  S is double-buffered in tensor memory and S of tile j+1 is issued before P V of tile j, so the tensor
-// pipe computes the next scores while the softmax warps work on the current ones.  The running output stays in
-// registers (128 fp32 per thread) and is rescaled there; each tile's P V product is a fresh accumulator that the
-// softmax warps read back and add, which keeps tensor memory free of read-modify-write rescaling.
+// shuffles.  S and P are double-buffered and S of tile j+1 is issued before P V of tile j, so the tensor pipe
+// computes the next scores while the softmax warps work on the current ones, and P V of tile j overlaps the softmax
+// of tile j+1.  O accumulates in tensor memory across tiles.  The exponentials use a reference maximum that is only
+// raised when the true row maximum has grown by more than 2^8 since it was set (exact arithmetic either way: O and
+// the row sum carry the same factor); only then do the softmax warps read O back, scale it and store it again
+// (tcgen05.ld / tcgen05.st), which happens a few times per row instead of once per tile.
 //
 // The query rows of a sequence are its LAST q_len positions; with a cached prefix the causal mask is aligned to the
 // bottom-right corner: query row i sees keys 0 .. (k_len - q_len + i).  All waits are bounded (ptx.cuh).
@@ -44,6 +46,47 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint3
   return d;
 }
 
+// Row maximum of the raw scores of one tile; kMasked: only keys kbase + i < limit count.  Four chains, not one.
+template <bool kMasked>
+__device__ __forceinline__ float umma_row_max(const uint32_t (&v)[kUN], int kbase, int limit) {
+  float m[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int i = 0; i < kUN; i += 4) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float x = __uint_as_float(v[i + e]);
+      m[e] = fmaxf(m[e], (!kMasked || kbase + i + e < limit) ? x : -INFINITY);
+    }
+  }
+  return fmaxf(fmaxf(m[0], m[1]), fmaxf(m[2], m[3]));
+}
+
+// p = 2^(s * scale - m_ref) for one row of a tile -> bf16 -> shared memory (K-major, 128-byte swizzle: 16-byte chunk
+// index ^ (row % 8)); returns the row sum.
+template <bool kMasked>
+__device__ __forceinline__ float umma_probs_to_smem(const uint32_t (&v)[kUN], int kbase, int limit, float scale_log2, float m_ref,
+                                                    uint8_t* p_row, int r) {
+  float ps[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int c = 0; c < kUN; c += 8) {
+    uint32_t pk[4];
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+      float p0 = ex2_approx(fmaf(__uint_as_float(v[c + i]), scale_log2, -m_ref));
+      float p1 = ex2_approx(fmaf(__uint_as_float(v[c + i + 1]), scale_log2, -m_ref));
+      if (kMasked) {
+        p0 = kbase + c + i < limit ? p0 : 0.f;
+        p1 = kbase + c + i + 1 < limit ? p1 : 0.f;
+      }
+      ps[i >> 1] += p0 + p1;
+      pk[i >> 1] = pack_bf16x2(p0, p1);
+    }
+    const int chunk = (c & 63) >> 3;                   // 16-byte chunk (8 keys) within the 64-key half
+    *reinterpret_cast<uint4*>(p_row + (c >> 6) * kUHalf + ((chunk ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+  }
+  return (ps[0] + ps[1]) + (ps[2] + ps[3]);
+}
+
 // tm_q: 2-D view [T, nq * 128] of q, box 128 rows x 64 cols.  tm_k / tm_v: 2-D view [blocks * nkv * block_size, 128]
 // of a cache, box 128 rows x 64 cols.
 __global__ void __launch_bounds__(kUThreads, 1) prefill_attn_umma_kernel(
@@ -56,8 +99,8 @@ __global__ void __launch_bounds__(kUThreads, 1) prefill_attn_umma_kernel(
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + kUTile;                        // [2 stages]
   uint8_t* sV = sK + kUStages * kUTile;             // [2 stages]
-  uint8_t* sP = sV + kUStages * kUTile;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + kUTile);
+  uint8_t* sP = sV + kUStages * kUTile;             // [2]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * kUTile);
   uint64_t* q_full = bars;                          // 1
   uint64_t* k_full = bars + 1;                      // [2]
   uint64_t* k_empty = bars + 3;                     // [2]
@@ -65,10 +108,9 @@ __global__ void __launch_bounds__(kUThreads, 1) prefill_attn_umma_kernel(
   uint64_t* v_empty = bars + 7;                     // [2]
   uint64_t* s_full = bars + 9;                      // [2]
   uint64_t* s_empty = bars + 11;                    // [2], one arrival per softmax warp
-  uint64_t* p_full = bars + 13;                     // one arrival per softmax warp
-  uint64_t* o_full = bars + 14;
-  uint64_t* o_empty = bars + 15;                    // one arrival per softmax warp
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* p_full = bars + 13;                     // [2], one arrival per softmax warp
+  uint64_t* pv_done = bars + 15;                    // [2]: P V of the tiles that used P buffer b is complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
 
   pdl_launch_dependents();
   pdl_wait();
@@ -96,10 +138,9 @@ __global__ void __launch_bounds__(kUThreads, 1) prefill_attn_umma_kernel(
       mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
       mbar_init(&s_empty[s], 4);
+      mbar_init(&p_full[s], 4);
+      mbar_init(&pv_done[s], 1);
     }
-    mbar_init(p_full, 4);
-    mbar_init(o_full, 1);
-    mbar_init(o_empty, 4);
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -128,11 +169,11 @@ __global__ void __launch_bounds__(kUThreads, 1) prefill_attn_umma_kernel(
           blk = 0;
         }
         const int row = (blk * nkv + kvh) * block_size + (tok % block_size);
-        if (!mbar_wait(&k_empty[s], ph ^ 1, status)) break;
+        if (!mbar_wait_parked(&k_empty[s], ph ^ 1, status)) break;
         mbar_expect_tx(&k_full[s], kUTile);
         tma_load_2d(sK + s * kUTile, &tm_k, &k_full[s], 0, row);
         tma_load_2d(sK + s * kUTile + kUHalf, &tm_k, &k_full[s], 64, row);
-        if (!mbar_wait(&v_empty[s], ph ^ 1, status)) break;
+        if (!mbar_wait_parked(&v_empty[s], ph ^ 1, status)) break;
         mbar_expect_tx(&v_full[s], kUTile);
         tma_load_2d(sV + s * kUTile, &tm_v, &v_full[s], 0, row);
         tma_load_2d(sV + s * kUTile + kUHalf, &tm_v, &v_full[s], 64, row);
@@ -148,8 +189,8 @@ __global__ void __launch_bounds__(kUThreads, 1) prefill_attn_umma_kernel(
       auto issue_s = [&](int j) -> bool {
         const int s = j % kUStages;
         const uint32_t ph = (j / kUStages) & 1;
-        if (!mbar_wait(&k_full[s], ph, status)) return false;
-        if (!mbar_wait(&s_empty[j & 1], ((j >> 1) & 1) ^ 1, status)) return false;     // softmax has read S of tile j - 2
+        if (!mbar_wait_parked(&k_full[s], ph, status)) return false;
+        if (!mbar_wait_parked(&s_empty[j & 1], ((j >> 1) & 1) ^ 1, status)) return false;     // softmax has read S of tile j - 2
         tcgen05_fence_after();
         const uint32_t k_addr = smem_u32(sK + s * kUTile);
 #pragma unroll
@@ -167,19 +208,20 @@ __global__ void __launch_bounds__(kUThreads, 1) prefill_attn_umma_kernel(
         if (!ok) break;
         const int s = j % kUStages;
         const uint32_t ph = (j / kUStages) & 1;
-        if (!mbar_wait(&v_full[s], ph, status) || !mbar_wait(p_full, j & 1, status) || !mbar_wait(o_empty, (j & 1) ^ 1, status)) {
+        if (!mbar_wait_parked(&v_full[s], ph, status) || !mbar_wait_parked(&p_full[j & 1], (j >> 1) & 1, status)) {
           ok = false;
           break;
         }
         tcgen05_fence_after();
         const uint32_t v_addr = smem_u32(sV + s * kUTile);
+        const uint32_t pj_addr = p_addr + (j & 1) * kUTile;
 #pragma unroll
         for (int k = 0; k < kUN / 16; ++k) {                                           // 16 keys per instruction
           const uint32_t a_off = (k >> 2) * kUHalf + (k & 3) * 32;                     // P: K-major, K = keys
           const uint32_t b_off = k * 16 * 128;                                         // V: 16 key rows of 128 bytes
-          umma_f16(tmem_o, umma_desc_k_sw128(p_addr + a_off), umma_desc_mn_sw128(v_addr + b_off, kUHalf), idesc_o, k != 0);
+          umma_f16(tmem_o, umma_desc_k_sw128(pj_addr + a_off), umma_desc_mn_sw128(v_addr + b_off, kUHalf), idesc_o, (j | k) != 0);
         }
-        umma_commit(o_full);
+        umma_commit(&pv_done[j & 1]);
         umma_commit(&v_empty[s]);
       }
     }
@@ -190,10 +232,7 @@ __global__ void __launch_bounds__(kUThreads, 1) prefill_attn_umma_kernel(
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const int qpos = past + m0 + r;                      // keys <= qpos are visible
     const int limit = min(qpos + 1, k_len);              // visible keys: [0, limit)
-    float o_acc[kUD];
-#pragma unroll
-    for (int i = 0; i < kUD; ++i) o_acc[i] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f;
+    float m_ref = 0.f, l_run = 0.f;                     // reference maximum of the exponentials (scaled, log2 domain), row sum
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, status);
@@ -201,80 +240,78 @@ __global__ void __launch_bounds__(kUThreads, 1) prefill_attn_umma_kernel(
       tcgen05_fence_after();
       const uint32_t s_addr = tmem_base + lane_addr + (j & 1) * kUN;
       const int kbase = j * kUN;
-      // pass 1: row maximum of the visible scores
-      float mt = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < kUN; c += 32) {
-        uint32_t v[32];
-        tmem_ld_x32(s_addr + c, v);
-        tmem_ld_wait();
+      uint32_t v[kUN];
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (kbase + c + i < limit) mt = fmaxf(mt, __uint_as_float(v[i]));
-      }
-      mt *= scale_log2;                                  // scale > 0: max commutes with the scaling
-      const float m_new = fmaxf(m_run, mt);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = exp2f(m_run - m_use);
-      m_run = m_new;
-      // pass 2: probabilities -> bf16 -> shared memory (K-major, 128-byte swizzle: 16-byte chunk index ^ (row % 8))
-      float ps = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < kUN; c += 32) {
-        uint32_t v[32];
-        tmem_ld_x32(s_addr + c, v);
-        tmem_ld_wait();
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = kbase + c + i < limit ? exp2f(__uint_as_float(v[i]) * scale_log2 - m_use) : 0.f;
-          const float p1 = kbase + c + i + 1 < limit ? exp2f(__uint_as_float(v[i + 1]) * scale_log2 - m_use) : 0.f;
-          ps += p0 + p1;
-          pk[i >> 1] = pack_bf16x2(p0, p1);
-        }
-        uint8_t* base = sP + (c >> 6) * kUHalf + r * 128;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int chunk = ((c & 63) >> 3) + q4;        // 16-byte chunk (8 keys) within the 64-key half
-          *reinterpret_cast<uint4*>(base + ((chunk ^ (r & 7)) << 4)) = make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
-        }
-      }
-      l_run = l_run * alpha + ps;
-      // S buffer may be overwritten (tile j + 2); P is complete
+      for (int c = 0; c < kUN; c += 32) tmem_ld_x32(s_addr + c, v + c);
+      tmem_ld_wait();
       tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[j & 1]);       // the scores are in registers: S may be overwritten (tile j + 2)
+      // tiles left of the diagonal and inside the sequence need no mask (warp-uniform choice)
+      const bool masked = !__all_sync(0xffffffffu, kbase + kUN <= limit);
+      float mt = masked ? umma_row_max<true>(v, kbase, limit) : umma_row_max<false>(v, kbase, limit);
+      mt *= scale_log2;                                  // scale > 0: max commutes with the scaling
+      if (j == 0) {
+        m_ref = mt == -INFINITY ? 0.f : mt;              // O is not valid yet: nothing to rescale
+      } else {
+        const bool grow = mt - m_ref > 8.f;
+        if (__any_sync(0xffffffffu, grow)) {             // tcgen05.ld / .st are warp-wide: the whole warp rescales
+          ok = mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, status);            // every earlier P V has landed in O
+          if (!ok) break;
+          tcgen05_fence_after();
+          const float m_new = fmaxf(m_ref, mt);
+          const float alpha = exp2f(m_ref - m_new);      // 1 for rows whose maximum did not move
+#pragma unroll 1
+          for (int c = 0; c < kUD; c += 32) {
+            uint32_t o[32];
+            tmem_ld_x32(tmem_o + lane_addr + c, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_x32(tmem_o + lane_addr + c, o);
+          }
+          tmem_st_wait();
+          tcgen05_fence_before();
+          l_run *= alpha;
+          m_ref = m_new;
+        }
+      }
+      // P buffer j & 1 was last read by P V of tile j - 2
+      if (j >= 2) {
+        ok = mbar_wait(&pv_done[j & 1], ((j >> 1) - 1) & 1, status);
+        if (!ok) break;
+      }
+      uint8_t* p_row = sP + (j & 1) * kUTile + r * 128;
+      const float ps = masked ? umma_probs_to_smem<true>(v, kbase, limit, scale_log2, m_ref, p_row, r)
+                              : umma_probs_to_smem<false>(v, kbase, limit, scale_log2, m_ref, p_row, r);
+      l_run += ps;
       fence_proxy_async_smem();                          // generic-proxy writes of P -> visible to the tensor core
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&s_empty[j & 1]);
-        mbar_arrive(p_full);
-      }
-      // O = alpha * O + P V
-      ok = mbar_wait(o_full, j & 1, status);
-      if (!ok) break;
-      tcgen05_fence_after();
-#pragma unroll
-      for (int c = 0; c < kUD; c += 32) {
-        uint32_t v[32];
-        tmem_ld_x32(tmem_o + lane_addr + c, v);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o_acc[c + i] = fmaf(o_acc[c + i], alpha, __uint_as_float(v[i]));
-      }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(o_empty);               // the next P V may overwrite O; P may be rewritten (ordered by o_full)
+      if (lane == 0) mbar_arrive(&p_full[j & 1]);
     }
-    if (ok && m0 + r < q_len) {
+    // all of O: wait for the last P V, normalise, store
+    if (ok) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, status);
+    if (ok) {
+      tcgen05_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const bool store = m0 + r < q_len;
       __nv_bfloat16* dst = out + static_cast<size_t>(q_begin + m0 + r) * nq * kUD + h * kUD;
+#pragma unroll 1
+      for (int c = 0; c < kUD; c += 32) {
+        uint32_t o[32];
+        tmem_ld_x32(tmem_o + lane_addr + c, o);
+        tmem_ld_wait();
+        if (store) {
 #pragma unroll
-      for (int c = 0; c < kUD; c += 8) {
-        uint4 pk;
-        pk.x = pack_bf16x2(o_acc[c] * inv, o_acc[c + 1] * inv);
-        pk.y = pack_bf16x2(o_acc[c + 2] * inv, o_acc[c + 3] * inv);
-        pk.z = pack_bf16x2(o_acc[c + 4] * inv, o_acc[c + 5] * inv);
-        pk.w = pack_bf16x2(o_acc[c + 6] * inv, o_acc[c + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + c) = pk;
+          for (int i = 0; i < 32; i += 8) {
+            uint4 pk;
+            pk.x = pack_bf16x2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+            pk.y = pack_bf16x2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+            pk.z = pack_bf16x2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+            pk.w = pack_bf16x2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c + i) = pk;
+          }
+        }
       }
     }
   }
@@ -302,7 +339,7 @@ extern "C" int forge_prefill_attention_umma(const void* q, const void* kc, const
   const uint64_t rows = static_cast<uint64_t>(num_blocks) * nkv * block_size;
   if (forge_make_tmap_2d(&tm_k, kc, rows, kUD, kUD, kUN, 2) != 0) return -2;
   if (forge_make_tmap_2d(&tm_v, vc, rows, kUD, kUD, kUN, 2) != 0) return -2;
-  constexpr int smem = (1 + 2 * kUStages + 1) * kUTile + 256 + 1024;
+  constexpr int smem = (1 + 2 * kUStages + 2) * kUTile + 256 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(prefill_attn_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
