@@ -133,7 +133,7 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           continue;
         }
         const uint32_t ph = (it / Cfg::kStages) & 1;
-        if (!mbar_wait(&empty_bar[s], ph ^ 1, status)) { t = num_tiles; break; }
+        if (!mbar_wait_parked(&empty_bar[s], ph ^ 1, status)) { t = num_tiles; break; }
         mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
         tma_load_2d(st, &tm_x, &full_bar[s], kb * kBlockK, r0);
         for (int i = 0; i < Cfg::kNumC; ++i)
@@ -150,14 +150,14 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       int it = 0, n = 0;
       for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++n) {
         const int buf = n & 1;
-        if (!mbar_wait(&acc_empty[buf], ((n >> 1) & 1) ^ 1, status)) break;      // the epilogue has drained this set
+        if (!mbar_wait_parked(&acc_empty[buf], ((n >> 1) & 1) ^ 1, status)) break;      // the epilogue has drained this set
         tcgen05_fence_after();
         const uint32_t acc_addr = tmem_base + buf * Cfg::kAccCols;
         bool ok = true;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % Cfg::kStages;
           const uint32_t ph = (it / Cfg::kStages) & 1;
-          if (!mbar_wait(&full_bar[s], ph, status)) { ok = false; break; }
+          if (!mbar_wait_parked(&full_bar[s], ph, status)) { ok = false; break; }
           tcgen05_fence_after();
           const uint32_t st = smem_u32(smem + s * Cfg::kStageBytes);
 #pragma unroll
