@@ -23,10 +23,10 @@ namespace forge {
 
 template <int G, int TILE>
 __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(
-    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+    const __nv_bfloat16* __restrict__ q, __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
     const int* __restrict__ block_tables, const int* __restrict__ context_lens, __nv_bfloat16* __restrict__ out,
     float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv, int block_size, int table_width, int num_blocks,
-    int chunk, int max_chunks, float scale_log2, unsigned* status) {
+    int chunk, int max_chunks, float scale_log2, unsigned* status, const DecodeFuse fuse) {
   constexpr int kTileBytes = TILE * kD * 2;
   static_assert(TILE >= 16 && TILE <= 64 && (TILE & (TILE - 1)) == 0, "tile");
 
@@ -89,12 +89,26 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(
   } else {
     // ------------------------------------------------------------------ consumers
     float qr[G][16];
-    decode_load_q<G>(q + (static_cast<size_t>(b) * nq + qh0) * kD, lane, scale_log2, qr);
+    // the newest token (position len - 1) is not in the cache yet: the warp that owns its row of its tile prepares it now
+    const int row_new = (len - 1) % TILE, t_new = (len - 1 - tok_begin) / TILE;
+    const bool owner = fuse.qkv != nullptr && len - 1 >= tok_begin && len - 1 < tok_end && warp == row_new / (TILE / 4);
+    DecodeNewToken fresh = {};
+    if (owner) fresh = decode_new_token(fuse, b, kvh, nq, nkv, len, lane);
+    if (fuse.qkv != nullptr) decode_load_q_fused<G>(fuse, b, qh0, len, lane, scale_log2, qr);
+    else decode_load_q<G>(q + (static_cast<size_t>(b) * nq + qh0) * kD, lane, scale_log2, qr);
     for (int t = 0; t < n_tiles; ++t) {
       const int s = t % kDecStages;
       const uint32_t ph = (t / kDecStages) & 1;
       if (!mbar_wait(&full_bar[s], ph, status)) break;
-      const uint8_t* Ks = smem + s * 2 * kTileBytes;
+      uint8_t* Ks = smem + s * 2 * kTileBytes;
+      if (owner && t == t_new) {
+        int blk = block_tables[static_cast<size_t>(b) * table_width + (len - 1) / block_size];
+        const bool blk_ok = blk >= 0 && blk < num_blocks;
+        if (!blk_ok) blk = 0;
+        const size_t off = ((static_cast<size_t>(blk) * nkv + kvh) * block_size + ((len - 1) % block_size)) * kD;
+        decode_patch_new_token(fresh, row_new, Ks, Ks + kTileBytes, k_cache + off, v_cache + off, blk_ok && blockIdx.x % groups_per_kv == 0,
+                               lane);
+      }
       decode_consume_tile<G, TILE>(Ks, Ks + kTileBytes, tok_end - (tok_begin + t * TILE), warp, lane, qr, st);
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[s]);
@@ -152,7 +166,7 @@ __global__ void __launch_bounds__(kD) decode_combine_kernel(const float* __restr
 template <int G, int TILE>
 static int launch_decode(const void* q, const void* kc, const void* vc, const int* bt, const int* lens, void* out, float* part_o,
                          float* part_ml, int B, int nq, int nkv, int block_size, int table_width, int num_blocks, int chunk,
-                         int max_chunks, float scale_log2, unsigned* status, cudaStream_t stream) {
+                         int max_chunks, float scale_log2, unsigned* status, cudaStream_t stream, const DecodeFuse& fuse) {
   constexpr int kTileBytes = TILE * kD * 2;
   constexpr int merge_bytes = decode_merge_floats(G) * 4;
   constexpr int ring = kDecStages * 2 * kTileBytes;
@@ -166,9 +180,9 @@ static int launch_decode(const void* q, const void* kc, const void* vc, const in
   const int groups_per_kv = (nq / nkv) / G;
   dim3 grid(nkv * groups_per_kv, B, max_chunks);
   if (launch_kernel(kern, grid, dim3(kDecThreads), smem, stream, 0, static_cast<const __nv_bfloat16*>(q),
-                    static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc), bt, lens,
+                    static_cast<__nv_bfloat16*>(const_cast<void*>(kc)), static_cast<__nv_bfloat16*>(const_cast<void*>(vc)), bt, lens,
                     static_cast<__nv_bfloat16*>(out), part_o, part_ml, nq, nkv, block_size, table_width, num_blocks, chunk,
-                    max_chunks, scale_log2, status) != cudaSuccess)
+                    max_chunks, scale_log2, status, fuse) != cudaSuccess)
     return -5;
   if (max_chunks > 1) {
     dim3 g2(nq, B);
@@ -182,10 +196,10 @@ static int launch_decode(const void* q, const void* kc, const void* vc, const in
 // q [B, nq, 128] bf16; caches [num_blocks, nkv, block_size, 128] bf16; block_tables [B, table_width]; out [B, nq * 128].
 // part_o: fp32 [B, nq, max_chunks, 128], part_ml: fp32 [B, nq, max_chunks, 2] (may be null when max_chunks == 1).
 // chunk: tokens per grid.z slice, a multiple of min(block_size, 64); max_chunks * chunk must cover the longest context.
-extern "C" int forge_decode_attention(const void* q, const void* kc, const void* vc, const int* bt, const int* lens, void* out,
-                                      float* part_o, float* part_ml, int B, int nq, int nkv, int head_dim, int block_size,
-                                      int table_width, int num_blocks, int chunk, int max_chunks, float scale, unsigned* status,
-                                      cudaStream_t stream) {
+static int decode_chunked_impl(const void* q, const void* kc, const void* vc, const int* bt, const int* lens, void* out,
+                               float* part_o, float* part_ml, int B, int nq, int nkv, int head_dim, int block_size,
+                               int table_width, int num_blocks, int chunk, int max_chunks, float scale, unsigned* status,
+                               cudaStream_t stream, const DecodeFuse& fuse) {
   if (B <= 0) return 0;
   if (head_dim != kD || nq % nkv != 0 || block_size < 16 || (block_size & (block_size - 1))) return -1;
   const int tile = block_size < 64 ? block_size : 64;
@@ -196,7 +210,7 @@ extern "C" int forge_decode_attention(const void* q, const void* kc, const void*
   const float sl2 = scale * 1.4426950408889634f;
 #define FORGE_DEC(GG, TT)                                                                                                   \
   return launch_decode<GG, TT>(q, kc, vc, bt, lens, out, part_o, part_ml, B, nq, nkv, block_size, table_width, num_blocks, \
-                               chunk, max_chunks, sl2, status, stream)
+                               chunk, max_chunks, sl2, status, stream, fuse)
   if (tile == 64) {
     if (G == 4) FORGE_DEC(4, 64);
     if (G == 2) FORGE_DEC(2, 64);
@@ -211,6 +225,15 @@ extern "C" int forge_decode_attention(const void* q, const void* kc, const void*
     FORGE_DEC(1, 16);
   }
 #undef FORGE_DEC
+}
+
+extern "C" int forge_decode_attention(const void* q, const void* kc, const void* vc, const int* bt, const int* lens, void* out,
+                                      float* part_o, float* part_ml, int B, int nq, int nkv, int head_dim, int block_size,
+                                      int table_width, int num_blocks, int chunk, int max_chunks, float scale, unsigned* status,
+                                      cudaStream_t stream) {
+  const DecodeFuse none = {};
+  return decode_chunked_impl(q, kc, vc, bt, lens, out, part_o, part_ml, B, nq, nkv, head_dim, block_size, table_width, num_blocks,
+                             chunk, max_chunks, scale, status, stream, none);
 }
 
 
@@ -265,10 +288,10 @@ __device__ __forceinline__ void flat_next_item(FlatCursor& c, const int* cum, in
 
 template <int G, int TILE>
 __global__ void __launch_bounds__(kDecThreads) decode_attn_flat_kernel(
-    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+    const __nv_bfloat16* __restrict__ q, __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
     const int* __restrict__ block_tables, const int* __restrict__ context_lens, __nv_bfloat16* __restrict__ out,
     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ cta_meta, int B, int nq, int nkv, int block_size,
-    int table_width, int num_blocks, int min_tiles, float scale_log2, unsigned* status) {
+    int table_width, int num_blocks, int min_tiles, float scale_log2, unsigned* status, const DecodeFuse fuse) {
   constexpr int kTileBytes = TILE * kD * 2;
   constexpr int kRing = kDecStages * 2 * kTileBytes;
   extern __shared__ uint8_t smem_raw[];
@@ -379,14 +402,28 @@ __global__ void __launch_bounds__(kDecThreads) decode_attn_flat_kernel(
     const int qh0 = kvh * (nq / nkv) + (c.h % groups_per_kv) * G;
     const int len = context_lens[c.b];
     float qr[G][16];
-    decode_load_q<G>(q + (static_cast<size_t>(c.b) * nq + qh0) * kD, lane, scale_log2, qr);
+    // the newest token (position len - 1) is not in the cache yet: if this CTA streams the item's last tile, the warp that
+    // owns the token's row prepares it now, under the latency of the q loads and the first tiles
+    const int row_new = (len - 1) % TILE;
+    const bool owner = fuse.qkv != nullptr && c.t + seg == c.n_b && warp == row_new / (TILE / 4);
+    DecodeNewToken fresh = {};
+    if (owner) fresh = decode_new_token(fuse, c.b, kvh, nq, nkv, len, lane);
+    if (fuse.qkv != nullptr) decode_load_q_fused<G>(fuse, c.b, qh0, len, lane, scale_log2, qr);
+    else decode_load_q<G>(q + (static_cast<size_t>(c.b) * nq + qh0) * kD, lane, scale_log2, qr);
     st.reset();
     for (int i = 0; i < seg; ++i, ++it) {
       const int s = it % kDecStages;
       const uint32_t ph = (it / kDecStages) & 1;
       ok = mbar_wait(&full_bar[s], ph, status);
       if (!ok) break;
-      const uint8_t* Ks = smem + s * 2 * kTileBytes;
+      uint8_t* Ks = smem + s * 2 * kTileBytes;
+      if (owner && i == seg - 1) {
+        int blk = block_tables[static_cast<size_t>(c.b) * table_width + (len - 1) / block_size];
+        const bool blk_ok = blk >= 0 && blk < num_blocks;
+        if (!blk_ok) blk = 0;
+        const size_t off = ((static_cast<size_t>(blk) * nkv + kvh) * block_size + ((len - 1) % block_size)) * kD;
+        decode_patch_new_token(fresh, row_new, Ks, Ks + kTileBytes, k_cache + off, v_cache + off, blk_ok && c.h % groups_per_kv == 0, lane);
+      }
       decode_consume_tile<G, TILE>(Ks, Ks + kTileBytes, len - (c.t + i) * TILE, warp, lane, qr, st);
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty_bar[s]);
@@ -457,7 +494,7 @@ __global__ void __launch_bounds__(kD) decode_flat_combine_kernel(const float* __
 template <int G, int TILE>
 static int launch_decode_flat(const void* q, const void* kc, const void* vc, const int* bt, const int* lens, void* out,
                               float* scratch, int num_ctas, int B, int nq, int nkv, int block_size, int table_width, int num_blocks,
-                              float scale_log2, unsigned* status, cudaStream_t stream) {
+                              float scale_log2, unsigned* status, cudaStream_t stream, const DecodeFuse& fuse) {
   constexpr int kTileBytes = TILE * kD * 2;
   constexpr int smem = kDecStages * 2 * kTileBytes + decode_merge_floats(G) * 4 + (kFlatMaxSeqs + 1 + 16) * 4 + 16 + 2 * kDecStages * 8 + 128;
   static_assert(smem <= 113 * 1024, "two CTAs per SM");
@@ -472,9 +509,9 @@ static int launch_decode_flat(const void* q, const void* kc, const void* vc, con
   int* cta_meta = reinterpret_cast<int*>(part_ml + static_cast<size_t>(num_ctas) * 2 * G * 2);
   const int min_tiles = 256 / TILE < 2 ? 2 : 256 / TILE;        // at least ~256 tokens per CTA: below that the start-up dominates
   if (launch_kernel(kern, dim3(num_ctas), dim3(kDecThreads), smem, stream, 0, static_cast<const __nv_bfloat16*>(q),
-                    static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc), bt, lens,
+                    static_cast<__nv_bfloat16*>(const_cast<void*>(kc)), static_cast<__nv_bfloat16*>(const_cast<void*>(vc)), bt, lens,
                     static_cast<__nv_bfloat16*>(out), part_o, part_ml, cta_meta, B, nq, nkv, block_size, table_width, num_blocks,
-                    min_tiles, scale_log2, status) != cudaSuccess)
+                    min_tiles, scale_log2, status, fuse) != cudaSuccess)
     return -5;
   if (launch_kernel(decode_flat_combine_kernel<G>, dim3(num_ctas), dim3(kD), 0, stream, 0, static_cast<const float*>(part_o),
                     static_cast<const float*>(part_ml), static_cast<const int*>(cta_meta), static_cast<__nv_bfloat16*>(out), nq,
@@ -493,9 +530,9 @@ extern "C" size_t forge_decode_attention_flat_scratch_floats(int num_ctas, int B
 
 // Same operands as forge_decode_attention; scratch: forge_decode_attention_flat_scratch_floats() floats, contents
 // irrelevant on entry.  num_ctas: grid size, normally two per SM.  B <= 512.
-extern "C" int forge_decode_attention_flat(const void* q, const void* kc, const void* vc, const int* bt, const int* lens, void* out,
-                                           float* scratch, int num_ctas, int B, int nq, int nkv, int head_dim, int block_size,
-                                           int table_width, int num_blocks, float scale, unsigned* status, cudaStream_t stream) {
+static int decode_flat_impl(const void* q, const void* kc, const void* vc, const int* bt, const int* lens, void* out,
+                            float* scratch, int num_ctas, int B, int nq, int nkv, int head_dim, int block_size,
+                            int table_width, int num_blocks, float scale, unsigned* status, cudaStream_t stream, const DecodeFuse& fuse) {
   if (B <= 0) return 0;
   if (head_dim != kD || nq % nkv != 0 || block_size < 16 || (block_size & (block_size - 1)) || B > kFlatMaxSeqs || num_ctas < 1 ||
       scratch == nullptr)
@@ -506,7 +543,7 @@ extern "C" int forge_decode_attention_flat(const void* q, const void* kc, const 
   const float sl2 = scale * 1.4426950408889634f;
 #define FORGE_DEC(GG, TT)                                                                                                       \
   return launch_decode_flat<GG, TT>(q, kc, vc, bt, lens, out, scratch, num_ctas, B, nq, nkv, block_size, table_width, num_blocks, \
-                                    sl2, status, stream)
+                                    sl2, status, stream, fuse)
   if (tile == 64) {
     if (G == 4) FORGE_DEC(4, 64);
     if (G == 2) FORGE_DEC(2, 64);
@@ -521,6 +558,40 @@ extern "C" int forge_decode_attention_flat(const void* q, const void* kc, const 
     FORGE_DEC(1, 16);
   }
 #undef FORGE_DEC
+}
+
+extern "C" int forge_decode_attention_flat(const void* q, const void* kc, const void* vc, const int* bt, const int* lens, void* out,
+                                           float* scratch, int num_ctas, int B, int nq, int nkv, int head_dim, int block_size,
+                                           int table_width, int num_blocks, float scale, unsigned* status, cudaStream_t stream) {
+  const DecodeFuse none = {};
+  return decode_flat_impl(q, kc, vc, bt, lens, out, scratch, num_ctas, B, nq, nkv, head_dim, block_size, table_width, num_blocks, scale,
+                          status, stream, none);
+}
+
+// Decode attention straight from the raw qkv projection: q/k RMSNorm (weights may be null), NeoX rotation at position
+// len - 1 (rope may be null) and the KV-cache store of the step's token happen inside the attention kernel (replaces a
+// separate qk_norm_rope_store launch).  qkv: [B, (nq + 2 nkv) * 128] bf16 with row stride ld_qkv.  num_ctas > 0: flat tile
+// partition (scratch as for forge_decode_attention_flat); num_ctas == 0: context chunks (part_o / part_ml, chunk, max_chunks
+// as for forge_decode_attention).  Sequences of length 0 (padding rows) store nothing.
+extern "C" int forge_decode_attention_qkv(const void* qkv, int ld_qkv, const void* q_w, const void* k_w, float eps, const float* rope,
+                                          int rope_rows, void* kc, void* vc, const int* bt, const int* lens, void* out, float* scratch,
+                                          int num_ctas, float* part_o, float* part_ml, int chunk, int max_chunks, int B, int nq, int nkv,
+                                          int head_dim, int block_size, int table_width, int num_blocks, float scale, unsigned* status,
+                                          cudaStream_t stream) {
+  if (qkv == nullptr || (ld_qkv & 7) || (reinterpret_cast<uintptr_t>(qkv) & 15)) return -1;
+  DecodeFuse fuse;
+  fuse.qkv = static_cast<const __nv_bfloat16*>(qkv);
+  fuse.ld_qkv = ld_qkv;
+  fuse.q_w = static_cast<const __nv_bfloat16*>(q_w);
+  fuse.k_w = static_cast<const __nv_bfloat16*>(k_w);
+  fuse.eps = eps;
+  fuse.rope = rope;
+  fuse.rope_rows = rope_rows;
+  if (num_ctas > 0)
+    return decode_flat_impl(nullptr, kc, vc, bt, lens, out, scratch, num_ctas, B, nq, nkv, head_dim, block_size, table_width, num_blocks,
+                            scale, status, stream, fuse);
+  return decode_chunked_impl(nullptr, kc, vc, bt, lens, out, part_o, part_ml, B, nq, nkv, head_dim, block_size, table_width, num_blocks,
+                             chunk, max_chunks, scale, status, stream, fuse);
 }
 
 

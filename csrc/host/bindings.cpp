@@ -49,6 +49,11 @@ size_t forge_decode_attention_flat_scratch_floats(int num_ctas, int B, int nq, i
 int forge_decode_attention_flat(const void* q, const void* kc, const void* vc, const int* bt, const int* lens, void* out,
                                 float* scratch, int num_ctas, int B, int nq, int nkv, int head_dim, int block_size, int table_width,
                                 int num_blocks, float scale, unsigned* status, cudaStream_t stream);
+int forge_decode_attention_qkv(const void* qkv, int ld_qkv, const void* q_w, const void* k_w, float eps, const float* rope,
+                               int rope_rows, void* kc, void* vc, const int* bt, const int* lens, void* out, float* scratch,
+                               int num_ctas, float* part_o, float* part_ml, int chunk, int max_chunks, int B, int nq, int nkv,
+                               int head_dim, int block_size, int table_width, int num_blocks, float scale, unsigned* status,
+                               cudaStream_t stream);
 int forge_prefill_attention(const void* q, const void* kc, const void* vc, const int* cu_q, const int* lens, const int* bt,
                             void* out, int T, int num_seqs, int max_q, int nq, int nkv, int head_dim, int block_size,
                             int table_width, int num_blocks, float scale, unsigned* status, cudaStream_t stream);
@@ -269,6 +274,51 @@ void decode_attention_flat(const Tensor& q, const Tensor& k_cache, const Tensor&
         "forge_decode_attention_flat");
 }
 
+// Decode attention from the raw qkv projection [B, (nq + 2 nkv) * D]: q/k-norm, rotation and the KV store of the step's
+// token are done inside the attention kernel.  num_ctas > 0: flat partition with `scratch`; num_ctas == 0: context chunks
+// with part_o / part_ml.
+void decode_attention_qkv(const Tensor& qkv, const c10::optional<Tensor>& qw, const c10::optional<Tensor>& kw, double eps,
+                          const c10::optional<Tensor>& rope, Tensor& k_cache, Tensor& v_cache, const Tensor& block_tables,
+                          const Tensor& context_lens, Tensor& out, const c10::optional<Tensor>& scratch, int64_t num_ctas,
+                          const c10::optional<Tensor>& part_o, const c10::optional<Tensor>& part_ml, int64_t chunk, int64_t max_chunks,
+                          int64_t nq, double scale, const Tensor& status) {
+  CHECK_BF16(qkv); CHECK_CUDA_CONTIG(k_cache); CHECK_BF16(k_cache); CHECK_CUDA_CONTIG(v_cache); CHECK_BF16(v_cache);
+  CHECK_CUDA_CONTIG(block_tables); CHECK_I32(block_tables); CHECK_CUDA_CONTIG(context_lens); CHECK_I32(context_lens);
+  CHECK_CUDA_CONTIG(out); CHECK_BF16(out);
+  TORCH_CHECK(qkv.is_cuda() && qkv.dim() == 2 && qkv.stride(1) == 1, "qkv must be [B, (nq + 2 nkv) * D]");
+  TORCH_CHECK(k_cache.dim() == 4 && v_cache.sizes() == k_cache.sizes() && block_tables.dim() == 2, "decode_attention_qkv: ranks");
+  const int64_t B = qkv.size(0), nkv = k_cache.size(1), bs = k_cache.size(2), D = k_cache.size(3);
+  TORCH_CHECK(qkv.size(1) == (nq + 2 * nkv) * D && block_tables.size(0) >= B && context_lens.numel() >= B && out.numel() == B * nq * D,
+              "decode_attention_qkv: shape mismatch");
+  const void* qwp = nullptr; const void* kwp = nullptr; const float* rp = nullptr; int rope_rows = 0;
+  if (qw.has_value()) { CHECK_CUDA_CONTIG(*qw); CHECK_BF16(*qw); TORCH_CHECK(qw->numel() == D); qwp = qw->data_ptr(); }
+  if (kw.has_value()) { CHECK_CUDA_CONTIG(*kw); CHECK_BF16(*kw); TORCH_CHECK(kw->numel() == D); kwp = kw->data_ptr(); }
+  if (rope.has_value()) {
+    CHECK_CUDA_CONTIG(*rope); CHECK_F32(*rope); TORCH_CHECK(rope->dim() == 2 && rope->size(1) == D, "rope table must be [positions, D]");
+    rp = rope->data_ptr<float>(); rope_rows = static_cast<int>(rope->size(0));
+  }
+  float* sp = nullptr; float* po = nullptr; float* pml = nullptr;
+  if (num_ctas > 0) {
+    TORCH_CHECK(scratch.has_value() && B <= 512, "decode_attention_qkv: flat partition needs scratch and at most 512 sequences");
+    CHECK_CUDA_CONTIG(*scratch); CHECK_F32(*scratch);
+    TORCH_CHECK(scratch->numel() >= decode_attention_flat_scratch_floats(num_ctas, B, nq, nkv), "decode_attention_qkv: scratch too small");
+    sp = scratch->data_ptr<float>();
+  } else if (max_chunks > 1) {
+    TORCH_CHECK(part_o.has_value() && part_ml.has_value(), "decode_attention_qkv: scratch needed when max_chunks > 1");
+    CHECK_CUDA_CONTIG(*part_o); CHECK_F32(*part_o); CHECK_CUDA_CONTIG(*part_ml); CHECK_F32(*part_ml);
+    TORCH_CHECK(part_o->numel() >= B * nq * max_chunks * D && part_ml->numel() >= B * nq * max_chunks * 2, "decode_attention_qkv: scratch too small");
+    po = part_o->data_ptr<float>(); pml = part_ml->data_ptr<float>();
+  }
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  check(forge_decode_attention_qkv(qkv.data_ptr(), static_cast<int>(qkv.stride(0)), qwp, kwp, static_cast<float>(eps), rp, rope_rows,
+                                   k_cache.data_ptr(), v_cache.data_ptr(), block_tables.data_ptr<int>(), context_lens.data_ptr<int>(),
+                                   out.data_ptr(), sp, static_cast<int>(num_ctas), po, pml, static_cast<int>(chunk),
+                                   static_cast<int>(max_chunks), static_cast<int>(B), static_cast<int>(nq), static_cast<int>(nkv),
+                                   static_cast<int>(D), static_cast<int>(bs), static_cast<int>(block_tables.size(1)),
+                                   static_cast<int>(k_cache.size(0)), static_cast<float>(scale), status_ptr(status), stream_of(qkv)),
+        "forge_decode_attention_qkv");
+}
+
 void prefill_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& cu_seqlens_q,
                        const Tensor& context_lens, const Tensor& block_tables, Tensor& out, int64_t num_seqs, int64_t max_q,
                        double scale, const Tensor& status) {
@@ -419,6 +469,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sample_merge_ranks", &sample_merge_ranks);
   m.def("decode_attention", &decode_attention);
   m.def("decode_attention_flat", &decode_attention_flat);
+  m.def("decode_attention_qkv", &decode_attention_qkv);
   m.def("decode_attention_flat_scratch_floats", &decode_attention_flat_scratch_floats);
   m.def("prefill_attention", &prefill_attention);
 }

@@ -24,6 +24,121 @@ struct DecodeState {
   }
 };
 
+// Optional fusion of the step's q/k-norm + RoPE + KV store into the attention kernel (decode only: one new token per
+// sequence, at position len - 1).  qkv == nullptr: q is final and the cache already holds the newest token.
+struct DecodeFuse {
+  const __nv_bfloat16* qkv;     // [B, (nq + 2 nkv) * 128] raw projections: q heads, k heads, v heads
+  int ld_qkv;
+  const __nv_bfloat16* q_w;     // RMSNorm weights over head_dim, may be null
+  const __nv_bfloat16* k_w;
+  float eps;
+  const float* rope;            // [rope_rows][128]: cos of the 64 frequencies, then sin; null: no rotation
+  int rope_rows;
+};
+
+__device__ __forceinline__ float decode_bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// One head (128 values) of the raw projection -> RMSNorm (weight w, may be null) -> NeoX rotation with the table row
+// `cs` (may be null) -> rounded to bf16, i.e. exactly what qk_norm_rope_store_kernel would have stored.  Lane layout as
+// in decode_load_q: j = lane % 8 holds elements [8j, 8j+8) in x[0..8) and [64+8j, 64+8j+8) in x[8..16): the pairs
+// (i, i + 64) that the rotation mixes sit in the same lane.  The four 8-lane groups compute the same values.
+__device__ __forceinline__ void decode_norm_rope_head(const __nv_bfloat16* __restrict__ src, const __nv_bfloat16* __restrict__ w, float eps,
+                                                      const float* __restrict__ cs, int lane, float (&x)[16]) {
+  const int j = lane & 7;
+  {
+    const uint4 lo = *reinterpret_cast<const uint4*>(src + 8 * j);
+    const uint4 hi = *reinterpret_cast<const uint4*>(src + 64 + 8 * j);
+    const uint32_t r[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      x[2 * e] = bf16_lo(r[e]);
+      x[2 * e + 1] = bf16_hi(r[e]);
+    }
+  }
+  if (w != nullptr) {
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) ss = fmaf(x[e], x[e], ss);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+    const float inv = rsqrtf(ss * (1.0f / kD) + eps);
+    const uint4 lo = *reinterpret_cast<const uint4*>(w + 8 * j);
+    const uint4 hi = *reinterpret_cast<const uint4*>(w + 64 + 8 * j);
+    const uint32_t r[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      x[2 * e] = decode_bf16_round(decode_bf16_round(x[2 * e] * inv) * bf16_lo(r[e]));
+      x[2 * e + 1] = decode_bf16_round(decode_bf16_round(x[2 * e + 1] * inv) * bf16_hi(r[e]));
+    }
+  }
+  if (cs != nullptr) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float c = cs[8 * j + e], sn = cs[64 + 8 * j + e];
+      const float x1 = x[e], x2 = x[8 + e];
+      x[e] = x1 * c - x2 * sn;
+      x[8 + e] = x2 * c + x1 * sn;
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 16; ++e) x[e] = decode_bf16_round(x[e]);
+}
+
+// q of one item from the raw projection: norm, rotation at position len - 1, scale.
+template <int G>
+__device__ __forceinline__ void decode_load_q_fused(const DecodeFuse& f, int b, int qh0, int len, int lane, float scale_log2,
+                                                    float (&qr)[G][16]) {
+  const float* cs = nullptr;
+  if (f.rope != nullptr) cs = f.rope + static_cast<size_t>(min(max(len - 1, 0), f.rope_rows - 1)) * kD;
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    float x[16];
+    decode_norm_rope_head(f.qkv + static_cast<size_t>(b) * f.ld_qkv + static_cast<size_t>(qh0 + g) * kD, f.q_w, f.eps, cs, lane, x);
+#pragma unroll
+    for (int e = 0; e < 16; ++e) qr[g][e] = x[e] * scale_log2;
+  }
+}
+
+// The newest token (position len - 1) of KV head kvh of sequence b: k = norm + rotation of the raw projection, v = raw.
+// Two steps so that the global loads and the arithmetic happen at the START of an item, under the latency of the q loads
+// and of the first tiles, and only register -> shared / global stores remain when the tile with that token arrives.
+struct DecodeNewToken {
+  uint4 k_lo, k_hi;     // lanes 0..7: elements [8 lane, 8 lane + 8) and [64 + 8 lane, ...) of k, bf16
+  uint2 v;              // every lane: elements [4 lane, 4 lane + 4) of v, bf16
+};
+
+__device__ __forceinline__ DecodeNewToken decode_new_token(const DecodeFuse& f, int b, int kvh, int nq, int nkv, int len, int lane) {
+  const float* cs = nullptr;
+  if (f.rope != nullptr) cs = f.rope + static_cast<size_t>(min(max(len - 1, 0), f.rope_rows - 1)) * kD;
+  float x[16];
+  decode_norm_rope_head(f.qkv + static_cast<size_t>(b) * f.ld_qkv + static_cast<size_t>(nq + kvh) * kD, f.k_w, f.eps, cs, lane, x);
+  DecodeNewToken t;
+  t.k_lo = make_uint4(pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
+  t.k_hi = make_uint4(pack_bf16x2(x[8], x[9]), pack_bf16x2(x[10], x[11]), pack_bf16x2(x[12], x[13]), pack_bf16x2(x[14], x[15]));
+  t.v = *reinterpret_cast<const uint2*>(f.qkv + static_cast<size_t>(b) * f.ld_qkv + static_cast<size_t>(nq + nkv + kvh) * kD + lane * 4);
+  return t;
+}
+
+// Executed by the ONE consumer warp that owns row `row` of the tile that has just landed in shared memory (Ks / Vs): the
+// row is replaced there (the cache does not hold it yet) and, if `to_cache`, written to the cache for later steps.
+// Only this warp reads that row of the tile, so __syncwarp orders the patch before the use.
+__device__ __forceinline__ void decode_patch_new_token(const DecodeNewToken& t, int row, uint8_t* Ks, uint8_t* Vs, __nv_bfloat16* k_dst,
+                                                       __nv_bfloat16* v_dst, bool to_cache, int lane) {
+  if (lane < 8) {                                                     // one of the four identical groups writes
+    *reinterpret_cast<uint4*>(Ks + row * (kD * 2) + lane * 16) = t.k_lo;
+    *reinterpret_cast<uint4*>(Ks + row * (kD * 2) + 128 + lane * 16) = t.k_hi;
+    if (to_cache) {
+      *reinterpret_cast<uint4*>(k_dst + 8 * lane) = t.k_lo;
+      *reinterpret_cast<uint4*>(k_dst + 64 + 8 * lane) = t.k_hi;
+    }
+  }
+  *reinterpret_cast<uint2*>(Vs + row * (kD * 2) + lane * 8) = t.v;
+  if (to_cache) *reinterpret_cast<uint2*>(v_dst + lane * 4) = t.v;
+  fence_proxy_async_smem();            // a later bulk copy into this stage must be ordered after these generic writes
+  __syncwarp();
+}
+
 // q slices this lane multiplies: elements [8j, 8j+8) and [64+8j, 64+8j+8) of every head of the group (j = lane % 8)
 template <int G>
 __device__ __forceinline__ void decode_load_q(const __nv_bfloat16* __restrict__ q_row0, int lane, float scale_log2, float (&qr)[G][16]) {

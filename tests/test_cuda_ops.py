@@ -260,6 +260,41 @@ def test_decode_attention_padding_rows(ops, mode, monkeypatch):
     _close(got[[0, 2]], want[[0, 2]], 2e-2, 2e-2)
 
 
+@pytest.mark.parametrize("mode", ["flat", "chunked"])
+@pytest.mark.parametrize("k_lens,nq,nkv,bs", [
+    ([1, 2, 64, 65, 300, 1000, 0, 256, 257, 512], 16, 8, 256), ([17, 33, 250, 16, 1], 8, 2, 16), ([700, 2011, 129, 128], 32, 8, 256),
+    ([40, 90, 64], 8, 8, 32), ([513, 77], 8, 1, 64), (list(range(1, 140, 3)), 16, 8, 128),
+])
+def test_decode_attention_from_raw_qkv(ops, k_lens, nq, nkv, bs, mode, monkeypatch):
+    """q/k-norm + rotation + KV store inside the attention kernel == qk_norm_rope_store followed by attention:
+    same output, same cache contents (the step's token of every sequence sits at position len - 1)."""
+    monkeypatch.setattr(ops, "decode_attention_mode", mode)
+    S, D = len(k_lens), 128
+    _, kc, vc, b = _paged_case([1] * S, [max(k, 1) for k in k_lens], nq, nkv, bs, seed=7)
+    b.context_lens = torch.tensor(k_lens, dtype=torch.int32, device="cuda")
+    b.is_prefill = False
+    torch.manual_seed(11)
+    qkv = _rand(S, (nq + 2 * nkv) * D)
+    qw, kw = _rand(D, scale=0.2) + 1, _rand(D, scale=0.2) + 1
+    table = ref.rope_table(4096, D, 1e6, "cuda")
+    lens = b.context_lens.long()
+    pos = (lens - 1).clamp(min=0).to(torch.int32)
+    blk = b.block_tables.long()[torch.arange(S), ((lens - 1).clamp(min=0) // bs).cpu()]
+    slots = torch.where(lens > 0, blk.cuda() * bs + (lens - 1) % bs, torch.full_like(lens, -1)).to(torch.int32)
+    kc1, vc1, kc2, vc2 = kc.clone(), vc.clone(), kc.clone(), vc.clone()
+    q = ops.qk_norm_rope_store(qkv, qw, kw, 1e-6, table, pos, slots, kc1, vc1, nq, nkv, D)
+    want = ops.attention(q, kc1, vc1, b, D ** -0.5)
+    got = ops.decode_attention_qkv(qkv, qw, kw, 1e-6, table, kc2, vc2, b, nq, D ** -0.5)
+    live = [i for i, n in enumerate(k_lens) if n > 0]
+    _close(got[live], want[live], 2e-2, 2e-2)
+    _close(kc2, kc1, 1e-2, 1e-2)
+    assert torch.equal(vc2, vc1)
+    for i, n in enumerate(k_lens):
+        if n == 0:
+            assert torch.count_nonzero(got[i]) == 0
+    ops.check_status()
+
+
 @pytest.mark.parametrize("batch,lo,hi,nq,nkv", [(64, 100, 1500, 16, 8), (200, 1, 700, 16, 8), (300, 3000, 3100, 8, 2), (7, 1, 4000, 32, 8)])
 def test_decode_attention_flat_partition_many_sequences(ops, batch, lo, hi, nq, nkv, monkeypatch):
     """Enough tiles that every CTA's range spans several (sequence, head) items and most items are cut at most once;

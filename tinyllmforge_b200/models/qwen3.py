@@ -119,12 +119,19 @@ class Qwen3ForCausalLM:
         ops = self.ops
         layers = self.layers
         x, residual = ops.embed_norm(batch.input_ids, self.embed_tokens, layers[0].input_layernorm, self.eps)
+        # small decode steps on the GPU: q/k-norm + rotation + KV store run inside the attention kernel (one launch less per
+        # layer; at large batches the attention kernel is bandwidth-bound and the extra work per sequence costs more)
+        fused_decode = (not batch.is_prefill and self.head_dim == 128 and hasattr(ops, "decode_attention_qkv")
+                        and batch.padded_seqs <= ops.fused_qkv_max_batch)
         for i, l in enumerate(layers):
             qkv = l.qkv_proj.forward(ops, x)
             kc, vc = self.kv_cache[i, 0], self.kv_cache[i, 1]
-            q = ops.qk_norm_rope_store(qkv, l.q_norm, l.k_norm, self.eps, self.rope, batch.positions,
-                                       batch.slot_mapping, kc, vc, self.num_heads, self.num_kv_heads, self.head_dim)
-            a = ops.attention(q, kc, vc, batch, self.scale)
+            if fused_decode:
+                a = ops.decode_attention_qkv(qkv, l.q_norm, l.k_norm, self.eps, self.rope, kc, vc, batch, self.num_heads, self.scale)
+            else:
+                q = ops.qk_norm_rope_store(qkv, l.q_norm, l.k_norm, self.eps, self.rope, batch.positions,
+                                           batch.slot_mapping, kc, vc, self.num_heads, self.num_kv_heads, self.head_dim)
+                a = ops.attention(q, kc, vc, batch, self.scale)
             x, residual = ops.row_linear_add_rms_norm(a, l.o_proj, residual, l.post_attention_layernorm, self.eps, SITE_O)
             g = l.gate_up_proj.forward_silu_mul(ops, x)
             next_norm = layers[i + 1].input_layernorm if i + 1 < len(layers) else self.norm

@@ -66,6 +66,7 @@ class CudaOps:
         # 0.69-0.75 of copy bandwidth at 64-96 sequences, equal from 128, a few us slower below 16).
         # Scratch of the flat kernel, sized for any head grouping (~1.2 MB).
         self.decode_attention_mode = os.environ.get("FORGE_DECODE_ATTN", "auto")
+        self.fused_qkv_max_batch = int(os.environ.get("FORGE_FUSED_QKV_MAX", "32"))   # see models/qwen3.py
         self._flat_scratch = torch.empty(2 * self.num_sms * (2 * 4 * 130 + 2) + 64, dtype=torch.float32, device=self.device)
 
     # ------------------------------------------------------------------ status word
@@ -189,6 +190,29 @@ class CudaOps:
             part_ml = torch.empty(B * H * max_chunks * 2, dtype=torch.float32, device=q.device)
         self.C.decode_attention(q, k_cache, v_cache, batch.block_tables, batch.context_lens, out, part_o, part_ml,
                                 chunk, max_chunks, scale, self.status)
+        self.launches += 2 if max_chunks > 1 else 1
+        return out
+
+    def decode_attention_qkv(self, qkv, q_weight, k_weight, eps, table, k_cache, v_cache, batch, num_heads, scale, do_rope=True):
+        """Decode step: attention straight from the raw qkv projection.  q/k-norm, rotation at position len - 1 and the
+        KV-cache store of the step's token happen inside the attention kernel (one launch less per layer than
+        ``qk_norm_rope_store`` + ``attention``).  Same partition choice as ``attention``."""
+        B, D = batch.padded_seqs, k_cache.shape[3]
+        out = torch.empty(B, num_heads * D, dtype=qkv.dtype, device=qkv.device)
+        rope = table if do_rope else None
+        if self.decode_attention_mode == "flat" or (self.decode_attention_mode == "auto" and 48 <= B <= 512):
+            self.C.decode_attention_qkv(qkv, q_weight, k_weight, eps, rope, k_cache, v_cache, batch.block_tables, batch.context_lens,
+                                        out, self._flat_scratch, 2 * self.num_sms, None, None, 0, 0, num_heads, scale, self.status)
+            self.launches += 2
+            return out
+        max_len = batch.table_width * k_cache.shape[2]
+        chunk, max_chunks = decode_chunking(B, k_cache.shape[1], k_cache.shape[2], max_len)
+        part_o = part_ml = None
+        if max_chunks > 1:
+            part_o = torch.empty(B * num_heads * max_chunks * D, dtype=torch.float32, device=qkv.device)
+            part_ml = torch.empty(B * num_heads * max_chunks * 2, dtype=torch.float32, device=qkv.device)
+        self.C.decode_attention_qkv(qkv, q_weight, k_weight, eps, rope, k_cache, v_cache, batch.block_tables, batch.context_lens,
+                                    out, None, 0, part_o, part_ml, chunk, max_chunks, num_heads, scale, self.status)
         self.launches += 2 if max_chunks > 1 else 1
         return out
 
