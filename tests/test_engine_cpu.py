@@ -171,3 +171,17 @@ def test_pipelined_loop_equals_step_by_step_loop(ckpt):
     assert results[True][2]["preemptions"] > 0
     assert all(len(t) == sp.max_tokens for t, sp in zip(results[True][0], sps))
     assert all(tok >= 0 for t in results[True][0] for tok in t)
+
+
+def test_step_trace_has_one_line_per_step(ckpt, prompts, tmp_path):
+    """``trace_path``: one JSON line per engine step with the phase times, in the pipelined loop and in the plain one."""
+    import json
+    for pipelined in (True, False):
+        path = str(tmp_path / f"trace_{pipelined}.jsonl")
+        llm = _llm(ckpt, trace_path=path, extra={"pipeline": pipelined})
+        llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True), use_tqdm=False)
+        steps = llm.stats.prefill_steps + llm.stats.decode_steps
+        llm.exit()
+        lines = [json.loads(l) for l in open(path)]
+        assert len(lines) == steps and [l["step"] for l in lines] == list(range(steps))
+        assert lines[0]["prefill"] and not lines[-1]["prefill"] and all(l["run_ms"] >= 0 for l in lines)

@@ -60,6 +60,8 @@ class LLMEngine:
         self.step_index = 0
         self.stats = EngineStats()
         self._trace = open(config.trace_path, "a") if config.trace_path else None
+        self._nvtx = bool(config.extra.get("nvtx", False)) and config.device == "cuda"
+        self._nvtx_open = False
 
         env_world = int(os.environ.get("WORLD_SIZE", "1"))
         self.launcher_mode = tp_size > 1 and env_world == tp_size and "RANK" in os.environ
@@ -128,13 +130,33 @@ class LLMEngine:
         return self.scheduler.is_finished()
 
     # ------------------------------------------------------------------ one step
+    # ------------------------------------------------------------------ tracing
+    def _mark(self, name: str | None) -> None:
+        """NVTX range per phase of a step (schedule / build / run / postprocess) when ``extra={"nvtx": True}``: closes
+        the open range and opens ``name`` (None: just close).  Shows the host phases on a profiler's timeline."""
+        if not self._nvtx:
+            return
+        if self._nvtx_open:
+            torch.cuda.nvtx.range_pop()
+        self._nvtx_open = name is not None
+        if name is not None:
+            torch.cuda.nvtx.range_push(name)
+
+    def _trace_step(self, index, is_prefill, seqs, tokens, t0, t1, t2, t3, t4) -> None:
+        if self._trace is not None:
+            self._trace.write(json.dumps({"step": index, "prefill": is_prefill, "seqs": seqs, "tokens": tokens,
+                                          "schedule_ms": (t1 - t0) * 1e3, "build_ms": (t2 - t1) * 1e3, "run_ms": (t3 - t2) * 1e3,
+                                          "post_ms": (t4 - t3) * 1e3}) + "\n")
+
     def step(self):
         """schedule -> build -> (publish) -> run -> postprocess.  Returns (finished, signed token count):
         finished = [(req_id, completion_token_ids)], count > 0: prefill tokens, < 0: decode sequences."""
         st = self.stats
         t0 = time.perf_counter()
+        self._mark("schedule")
         reqs, is_prefill = self.scheduler.schedule()
         t1 = time.perf_counter()
+        self._mark("build")
         bs = self.config.kvcache_block_size
         if is_prefill:
             sb = build_prefill(reqs, bs, self.step_index, self.config.seed)
@@ -143,6 +165,7 @@ class LLMEngine:
             pad, width = self.worker.decode_padding(len(reqs))
             sb = self.decode_builder.build(reqs, self.step_index, self.config.seed, pad, width)
         t2 = time.perf_counter()
+        self._mark("run")
         try:
             if self.chan is not None:
                 if self.procs:
@@ -161,9 +184,11 @@ class LLMEngine:
                     raise EngineDeadError(f"{dead} (while running a step: {e})") from e
             raise
         t3 = time.perf_counter()
+        self._mark("postprocess")
         self.step_index += 1
         finished = self.scheduler.postprocess(reqs, token_ids)
         t4 = time.perf_counter()
+        self._mark(None)
 
         st.schedule_s += t1 - t0
         st.build_s += t2 - t1
@@ -181,11 +206,7 @@ class LLMEngine:
             count = -len(reqs)
         st.preemptions = self.scheduler.num_preemptions
         st.finished_requests += len(finished)
-        if self._trace is not None:
-            self._trace.write(json.dumps({"step": self.step_index - 1, "prefill": is_prefill, "seqs": len(reqs),
-                                          "tokens": sb.num_tokens, "schedule_ms": (t1 - t0) * 1e3,
-                                          "build_ms": (t2 - t1) * 1e3, "run_ms": (t3 - t2) * 1e3,
-                                          "post_ms": (t4 - t3) * 1e3}) + "\n")
+        self._trace_step(self.step_index - 1, is_prefill, len(reqs), sb.num_tokens, t0, t1, t2, t3, t4)
         return [(r.req_id, r.completion_token_ids) for r in finished], count
 
     # ------------------------------------------------------------------ generate
@@ -274,8 +295,10 @@ class LLMEngine:
             if sch.has_waiting() and inflight is not None:
                 drain()                                  # the next step may be a prefill: needs real token ids
             t0 = time.perf_counter()
+            self._mark("schedule")
             reqs, is_prefill = sch.schedule(defer_seal=True)
             t1 = time.perf_counter()
+            self._mark("build")
             if is_prefill:
                 sb = build_prefill(reqs, bs, self.step_index, self.config.seed)
                 self.decode_builder.reset()
@@ -288,6 +311,7 @@ class LLMEngine:
                     prev_row = {id(r): i for i, (r, _) in enumerate(inflight[0])}
                     src[:len(reqs)] = [prev_row.get(id(r), -1) for r in reqs]
             t2 = time.perf_counter()
+            self._mark("launch")
             try:
                 if self.chan is not None:
                     if self.procs:
@@ -297,11 +321,13 @@ class LLMEngine:
             except (rpc.PeerFailed, rpc.ChannelTimeout) as e:
                 raise EngineDeadError(str(e)) from e
             t3 = time.perf_counter()
+            self._mark("collect previous + postprocess")
             self.step_index += 1
             drain()                                      # read the PREVIOUS step while this one runs
             finished = sch.postprocess(reqs, [PLACEHOLDER] * len(reqs))
             inflight = ([(r, len(r.token_ids) - 1) for r in reqs], ticket, finished)
             t4 = time.perf_counter()
+            self._mark(None)
             st.schedule_s += t1 - t0
             st.build_s += t2 - t1
             st.run_s += t3 - t2
@@ -316,6 +342,7 @@ class LLMEngine:
                 st.decode_batch_hist[len(reqs)] += 1
             st.preemptions = sch.num_preemptions
             st.finished_requests += len(finished)
+            self._trace_step(self.step_index - 1, is_prefill, len(reqs), sb.num_tokens, t0, t1, t2, t3, t4)
         drain()
 
     # ------------------------------------------------------------------ teardown
