@@ -252,32 +252,45 @@ def run_reference(args) -> dict:
     for k in [k for k in os.environ if k.startswith("TORCHELASTIC")]:
         os.environ.pop(k)
 
-    def give_up():       # start-up watchdog: never sit in a rendezvous for the library's default ten minutes
-        print(json.dumps({"impl": "reference", "unavailable": f"the reference engine did not start within {args.ref_start_timeout} s"}), flush=True)
+    def kill_children():
         try:
             import psutil
             for c in psutil.Process(os.getpid()).children(recursive=True):
                 c.kill()
-        finally:
-            os._exit(0)
+        except Exception:
+            pass
+
+    def give_up(what, limit):    # watchdogs: never sit in a rendezvous or a lost collective until the caller's limit
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference engine did not {what} within {limit:.0f} s"}), flush=True)
+        kill_children()
+        os._exit(0)
     import threading
-    watchdog = threading.Timer(args.ref_start_timeout, give_up)
+    watchdog = threading.Timer(args.ref_start_timeout, give_up, ("start", args.ref_start_timeout))
     watchdog.daemon = True
     watchdog.start()
-    llm = LLM(path, enforce_eager=False, max_model_len=4096, tensor_parallel_size=n)
-    watchdog.cancel()
-    for p in range(args.warmup):
-        llm.generate(prompts_for_pass(prompts, p), sps, use_tqdm=False)
-    torch.cuda.synchronize()
-    sampler = ClockSampler(torch.cuda.current_device())
-    sampler.start()
-    acc.update(ms=0.0, steps=0, h2d=0, d2h=0)
-    t0 = time.perf_counter()
-    for p in range(args.steps):
-        outs = llm.generate(prompts_for_pass(prompts, args.warmup + p), sps, use_tqdm=False)
-    torch.cuda.synchronize()
-    wall = time.perf_counter() - t0
-    clocks = sampler.stop()
+    try:
+        llm = LLM(path, enforce_eager=False, max_model_len=4096, tensor_parallel_size=n)
+        watchdog.cancel()
+        watchdog = threading.Timer(args.ref_run_timeout, give_up, ("finish its passes", args.ref_run_timeout))
+        watchdog.daemon = True
+        watchdog.start()
+        for p in range(args.warmup):
+            llm.generate(prompts_for_pass(prompts, p), sps, use_tqdm=False)
+        torch.cuda.synchronize()
+        sampler = ClockSampler(torch.cuda.current_device())
+        sampler.start()
+        acc.update(ms=0.0, steps=0, h2d=0, d2h=0)
+        t0 = time.perf_counter()
+        for p in range(args.steps):
+            outs = llm.generate(prompts_for_pass(prompts, args.warmup + p), sps, use_tqdm=False)
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        clocks = sampler.stop()
+        watchdog.cancel()
+    except Exception as e:       # the reference's own code failed (it has no error handling of its own): report, do not crash
+        watchdog.cancel()
+        kill_children()
+        return {"impl": "reference", "unavailable": f"the reference engine failed: {type(e).__name__}: {str(e)[:300]}", "shims": shims}
     total = args.steps * sum(max_tokens)
     return {
         "metric": "output_tokens_per_second", "value": total / (acc["ms"] / 1e3), "unit": "tok/s", "n_gpus": n,
@@ -303,6 +316,7 @@ def main():
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"],
                     help="tensor-parallel exchange: in-kernel NVLink pushes (fused) or torch.distributed/NCCL calls")
     ap.add_argument("--ref-start-timeout", type=float, default=300.0, help="seconds the reference engine gets to start")
+    ap.add_argument("--ref-run-timeout", type=float, default=1500.0, help="seconds the reference engine gets for all its passes")
     ap.add_argument("--load", default="auto", choices=["auto", "dummy"],
                     help="auto: write and load a safetensors checkpoint; dummy: random-init on the device (large models)")
     args = ap.parse_args()
