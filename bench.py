@@ -134,6 +134,8 @@ def run_ours(args) -> dict:
     prompts, max_tokens = make_workload()
     sps = [SamplingParams(temperature=0.6, ignore_eos=True, max_tokens=m) for m in max_tokens]
     kw = dict(enforce_eager=False, max_model_len=4096, tensor_parallel_size=n, comm=args.comm, extra={"device_timing": True})
+    if args.quantization != "none":
+        kw["quantization"] = args.quantization
     if args.load == "dummy":
         llm = LLM(args.model, hf_config=preset(args.model), load_format="dummy", skip_tokenizer_init=True, **kw)
     else:
@@ -172,7 +174,8 @@ def run_ours(args) -> dict:
         result = {
             "metric": "output_tokens_per_second", "value": total / (dev_ms / 1e3), "unit": "tok/s", "n_gpus": n,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if args.quantization == "none" else "bf16 activations, fp8 e4m3 block-scaled weights",
+            "data": "synthetic", "impl": "ours",
             "config": {"model": args.model, "global_batch": NUM_SEQS, "seq_len": "prompt U[100,1024] + output U[100,1024]",
                        "parallelism": f"tp{n}", "comm": args.comm if n > 1 else "none", "weights": "random-init N(0,0.02), seed 0", "step": "one generate() pass over 256 requests; every pass uses fresh token ids of the same lengths (no cross-pass prefix-cache hits)",
                        "l2": "inputs larger than L2: every engine step streams the weights and the KV cache (> 126 MB)",
@@ -317,6 +320,8 @@ def main():
                     help="tensor-parallel exchange: in-kernel NVLink pushes (fused) or torch.distributed/NCCL calls")
     ap.add_argument("--ref-start-timeout", type=float, default=300.0, help="seconds the reference engine gets to start")
     ap.add_argument("--ref-run-timeout", type=float, default=1500.0, help="seconds the reference engine gets for all its passes")
+    ap.add_argument("--quantization", default="none", choices=["none", "fp8_block"],
+                    help="fp8_block: e4m3 weights with 128 x 128 block scales for the four projections of every layer (not the headline)")
     ap.add_argument("--load", default="auto", choices=["auto", "dummy"],
                     help="auto: write and load a safetensors checkpoint; dummy: random-init on the device (large models)")
     args = ap.parse_args()

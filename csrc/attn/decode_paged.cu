@@ -22,7 +22,7 @@
 namespace forge {
 
 template <int G, int TILE>
-__global__ void __launch_bounds__(kDecThreads) decode_attn_kernel(
+__global__ void __launch_bounds__(kDecThreads, 2) decode_attn_kernel(
     const __nv_bfloat16* __restrict__ q, __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
     const int* __restrict__ block_tables, const int* __restrict__ context_lens, __nv_bfloat16* __restrict__ out,
     float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv, int block_size, int table_width, int num_blocks,
@@ -287,7 +287,7 @@ __device__ __forceinline__ void flat_next_item(FlatCursor& c, const int* cum, in
 }
 
 template <int G, int TILE>
-__global__ void __launch_bounds__(kDecThreads) decode_attn_flat_kernel(
+__global__ void __launch_bounds__(kDecThreads, 2) decode_attn_flat_kernel(
     const __nv_bfloat16* __restrict__ q, __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
     const int* __restrict__ block_tables, const int* __restrict__ context_lens, __nv_bfloat16* __restrict__ out,
     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ cta_meta, int B, int nq, int nkv, int block_size,
