@@ -22,7 +22,7 @@
 namespace forge {
 
 template <int G, int TILE>
-__global__ void __launch_bounds__(kDecThreads, 2) decode_attn_kernel(
+__global__ void __launch_bounds__(kDecThreads, decode_ctas_per_sm(G)) decode_attn_kernel(
     const __nv_bfloat16* __restrict__ q, __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
     const int* __restrict__ block_tables, const int* __restrict__ context_lens, __nv_bfloat16* __restrict__ out,
     float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv, int block_size, int table_width, int num_blocks,
@@ -206,21 +206,27 @@ static int decode_chunked_impl(const void* q, const void* kc, const void* vc, co
   if (chunk % tile != 0 || max_chunks < 1) return -1;
   if (max_chunks > 1 && (part_o == nullptr || part_ml == nullptr)) return -1;
   const int group = nq / nkv;
-  const int G = group % 4 == 0 ? 4 : (group % 2 == 0 ? 2 : 1);
+  const int G = decode_group_slice(group);
   const float sl2 = scale * 1.4426950408889634f;
 #define FORGE_DEC(GG, TT)                                                                                                   \
   return launch_decode<GG, TT>(q, kc, vc, bt, lens, out, part_o, part_ml, B, nq, nkv, block_size, table_width, num_blocks, \
                                chunk, max_chunks, sl2, status, stream, fuse)
   if (tile == 64) {
+    if (G == 5) FORGE_DEC(5, 64);
     if (G == 4) FORGE_DEC(4, 64);
+    if (G == 3) FORGE_DEC(3, 64);
     if (G == 2) FORGE_DEC(2, 64);
     FORGE_DEC(1, 64);
   } else if (tile == 32) {
+    if (G == 5) FORGE_DEC(5, 32);
     if (G == 4) FORGE_DEC(4, 32);
+    if (G == 3) FORGE_DEC(3, 32);
     if (G == 2) FORGE_DEC(2, 32);
     FORGE_DEC(1, 32);
   } else {
+    if (G == 5) FORGE_DEC(5, 16);
     if (G == 4) FORGE_DEC(4, 16);
+    if (G == 3) FORGE_DEC(3, 16);
     if (G == 2) FORGE_DEC(2, 16);
     FORGE_DEC(1, 16);
   }
@@ -287,7 +293,7 @@ __device__ __forceinline__ void flat_next_item(FlatCursor& c, const int* cum, in
 }
 
 template <int G, int TILE>
-__global__ void __launch_bounds__(kDecThreads, 2) decode_attn_flat_kernel(
+__global__ void __launch_bounds__(kDecThreads, decode_ctas_per_sm(G)) decode_attn_flat_kernel(
     const __nv_bfloat16* __restrict__ q, __nv_bfloat16* k_cache, __nv_bfloat16* v_cache,
     const int* __restrict__ block_tables, const int* __restrict__ context_lens, __nv_bfloat16* __restrict__ out,
     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ cta_meta, int B, int nq, int nkv, int block_size,
@@ -497,7 +503,7 @@ static int launch_decode_flat(const void* q, const void* kc, const void* vc, con
                               float scale_log2, unsigned* status, cudaStream_t stream, const DecodeFuse& fuse) {
   constexpr int kTileBytes = TILE * kD * 2;
   constexpr int smem = kDecStages * 2 * kTileBytes + decode_merge_floats(G) * 4 + (kFlatMaxSeqs + 1 + 16) * 4 + 16 + 2 * kDecStages * 8 + 128;
-  static_assert(smem <= 113 * 1024, "two CTAs per SM");
+  static_assert(smem <= (decode_ctas_per_sm(G) == 2 ? 113 : 227) * 1024, "two CTAs per SM (one for G > 4)");
   auto kern = decode_attn_flat_kernel<G, TILE>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -523,7 +529,7 @@ static int launch_decode_flat(const void* q, const void* kc, const void* vc, con
 // Floats of scratch the flat kernel needs for a grid of num_ctas CTAs and up to B sequences.
 extern "C" size_t forge_decode_attention_flat_scratch_floats(int num_ctas, int B, int nq, int nkv) {
   const int group = nkv > 0 ? nq / nkv : 1;
-  const int G = group % 4 == 0 ? 4 : (group % 2 == 0 ? 2 : 1);
+  const int G = decode_group_slice(group);
   (void)B;
   return static_cast<size_t>(num_ctas) * 2 * G * (kD + 2) + static_cast<size_t>(num_ctas) * 2 + 64;
 }
@@ -539,21 +545,27 @@ static int decode_flat_impl(const void* q, const void* kc, const void* vc, const
     return -1;
   const int tile = block_size < 64 ? block_size : 64;
   const int group = nq / nkv;
-  const int G = group % 4 == 0 ? 4 : (group % 2 == 0 ? 2 : 1);
+  const int G = decode_group_slice(group);
   const float sl2 = scale * 1.4426950408889634f;
 #define FORGE_DEC(GG, TT)                                                                                                       \
   return launch_decode_flat<GG, TT>(q, kc, vc, bt, lens, out, scratch, num_ctas, B, nq, nkv, block_size, table_width, num_blocks, \
                                     sl2, status, stream, fuse)
   if (tile == 64) {
+    if (G == 5) FORGE_DEC(5, 64);
     if (G == 4) FORGE_DEC(4, 64);
+    if (G == 3) FORGE_DEC(3, 64);
     if (G == 2) FORGE_DEC(2, 64);
     FORGE_DEC(1, 64);
   } else if (tile == 32) {
+    if (G == 5) FORGE_DEC(5, 32);
     if (G == 4) FORGE_DEC(4, 32);
+    if (G == 3) FORGE_DEC(3, 32);
     if (G == 2) FORGE_DEC(2, 32);
     FORGE_DEC(1, 32);
   } else {
+    if (G == 5) FORGE_DEC(5, 16);
     if (G == 4) FORGE_DEC(4, 16);
+    if (G == 3) FORGE_DEC(3, 16);
     if (G == 2) FORGE_DEC(2, 16);
     FORGE_DEC(1, 16);
   }

@@ -237,7 +237,7 @@ def _paged_case(q_lens, k_lens, nq, nkv, bs, seed=0):
 @pytest.mark.parametrize("mode", ["flat", "chunked"])
 @pytest.mark.parametrize("k_lens,nq,nkv,bs", [
     ([1], 16, 8, 256), ([5, 300, 64, 1000], 16, 8, 256), ([17, 33, 250], 8, 2, 16), ([700, 2011, 129], 32, 8, 256),
-    ([40, 90], 8, 8, 32), ([513, 77], 8, 1, 64),
+    ([40, 90], 8, 8, 32), ([513, 77], 8, 1, 64), ([300, 1000, 70, 2], 40, 8, 256), ([129, 640, 33], 64, 8, 256), ([50, 400], 6, 2, 64),
 ])
 def test_decode_attention(ops, k_lens, nq, nkv, bs, mode, monkeypatch):
     monkeypatch.setattr(ops, "decode_attention_mode", mode)
@@ -263,7 +263,8 @@ def test_decode_attention_padding_rows(ops, mode, monkeypatch):
 @pytest.mark.parametrize("mode", ["flat", "chunked"])
 @pytest.mark.parametrize("k_lens,nq,nkv,bs", [
     ([1, 2, 64, 65, 300, 1000, 0, 256, 257, 512], 16, 8, 256), ([17, 33, 250, 16, 1], 8, 2, 16), ([700, 2011, 129, 128], 32, 8, 256),
-    ([40, 90, 64], 8, 8, 32), ([513, 77], 8, 1, 64), (list(range(1, 140, 3)), 16, 8, 128),
+    ([40, 90, 64], 8, 8, 32), ([513, 77], 8, 1, 64), (list(range(1, 140, 3)), 16, 8, 128), ([300, 1000, 70, 2], 40, 8, 256),
+    ([129, 640, 33], 64, 8, 256),
 ])
 def test_decode_attention_from_raw_qkv(ops, k_lens, nq, nkv, bs, mode, monkeypatch):
     """q/k-norm + rotation + KV store inside the attention kernel == qk_norm_rope_store followed by attention:

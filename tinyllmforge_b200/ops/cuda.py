@@ -48,6 +48,15 @@ def decode_chunking(batch: int, num_kv_heads: int, block_size: int, max_len: int
     return chunk, max(1, -(-max_len // chunk))
 
 
+def decode_group_slice(group: int) -> int:
+    """q heads per KV head processed together by the decode attention kernels (``decode_group_slice`` in
+    csrc/include/decode_common.cuh): slices of more than 4 heads run one CTA per SM instead of two."""
+    for g in (5, 4, 3, 2):
+        if group % g == 0:
+            return g
+    return 1
+
+
 class CudaOps:
     name = "cuda"
 
@@ -172,8 +181,8 @@ class CudaOps:
             return out
         B = batch.padded_seqs
         if self.decode_attention_mode == "flat" or (self.decode_attention_mode == "auto" and 48 <= B <= 512):
-            # all KV tiles of the step dealt out equally to two CTAs per SM; lengths are read on the device
-            ctas = 2 * self.num_sms
+            # all KV tiles of the step dealt out equally to two CTAs per SM (one for wide head groups); lengths are read on the device
+            ctas = (1 if decode_group_slice(H // k_cache.shape[1]) > 4 else 2) * self.num_sms
             need = self.C.decode_attention_flat_scratch_floats(ctas, B, H, k_cache.shape[1])
             if self._flat_scratch is None or self._flat_scratch.numel() < need:
                 self._flat_scratch = torch.empty(need, dtype=torch.float32, device=q.device)
@@ -202,7 +211,8 @@ class CudaOps:
         rope = table if do_rope else None
         if self.decode_attention_mode == "flat" or (self.decode_attention_mode == "auto" and 48 <= B <= 512):
             self.C.decode_attention_qkv(qkv, q_weight, k_weight, eps, rope, k_cache, v_cache, batch.block_tables, batch.context_lens,
-                                        out, self._flat_scratch, 2 * self.num_sms, None, None, 0, 0, num_heads, scale, self.status)
+                                        out, self._flat_scratch, (1 if decode_group_slice(num_heads // k_cache.shape[1]) > 4 else 2) * self.num_sms,
+                                        None, None, 0, 0, num_heads, scale, self.status)
             self.launches += 2
             return out
         max_len = batch.table_width * k_cache.shape[2]
