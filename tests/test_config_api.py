@@ -1,6 +1,5 @@
 """Public surface: LLM / SamplingParams / Config (tinyvllm/__init__.py, config.py, sampling_params.py)."""
 import json
-import os
 
 import pytest
 import torch

@@ -1,5 +1,4 @@
 """Every sm_100a kernel against the plain-PyTorch fp32 statement of the same op (ops/ref.py)."""
-import math
 
 import pytest
 import torch

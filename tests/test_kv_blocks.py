@@ -2,7 +2,6 @@
 Behaviour model: tinyvllm/engine/block_manager.py:36-139."""
 import random
 
-import pytest
 from hypothesis import given, settings, strategies as st
 
 from tinyllmforge_b200 import SamplingParams

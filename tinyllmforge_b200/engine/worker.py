@@ -15,8 +15,6 @@ Differences that matter:
 """
 from __future__ import annotations
 
-import os
-import time
 import traceback
 
 import numpy as np
@@ -195,7 +193,6 @@ class Worker:
         may schedule and build the next step while this one runs.  When ``sb.src_rows`` names rows of the previous
         step, the input tokens are taken from that step's sampled tokens on the device."""
         if not self.is_cuda:
-            buf = sb.buf
             src = sb.src_rows[:sb.num_seqs]
             if not sb.is_prefill and (src >= 0).any():
                 ids = sb.input_ids

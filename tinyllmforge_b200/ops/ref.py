@@ -19,7 +19,6 @@ single bulk copy can fetch.
 """
 from __future__ import annotations
 
-import math
 
 import numpy as np
 import torch
