@@ -10,7 +10,10 @@
 // warps read the finished buffer, multiply by sw[tile][kb] * sx[kb][token] and accumulate in registers.
 //
 // Orientation as in the bf16 decode kernel: the 128-row UMMA side is a tile of 128 weight rows (= exactly one
-// row of scale blocks), tokens ride the N side in tiles of BLOCK_C.  Grid (N / 128, token tiles).
+// row of scale blocks), tokens ride the N side in tiles of BLOCK_C.  Grid (N / 128, token tiles, K splits).
+// With few tokens a layer has too few tiles to fill the GPU (and each CTA would stream a very long K): K is then
+// split over grid.z, every split writes its fp32 partial tile to a workspace and a small second kernel adds the
+// partials in split order (deterministic) and stores bf16.
 // Warp roles: warp 0 TMA producer, warp 1 UMMA issuer + TMEM owner, warps 2..5 scale-accumulate + store.
 #include <cuda_fp8.h>
 
@@ -39,7 +42,8 @@ template <int BLOCK_C>
 __global__ void __launch_bounds__(kF8Threads, 1)
 gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                       const float* __restrict__ w_scale, const float* __restrict__ x_scale, __nv_bfloat16* __restrict__ out,
-                      int ldo, int n_total, int m_total, int K, int x_scale_ld, unsigned* status) {
+                      int ldo, int n_total, int m_total, int K, int x_scale_ld, int kb_per_split, float* __restrict__ partial,
+                      unsigned* status) {
   using Cfg = F8Cfg<BLOCK_C>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -53,7 +57,8 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r0 = blockIdx.x * kF8BlockR;
   const int tok0 = blockIdx.y * BLOCK_C;
-  const int num_kb = K / kF8BlockK;
+  const int kb0 = min(static_cast<int>(blockIdx.z) * kb_per_split, K / kF8BlockK);     // this split's K blocks: [kb0, kb0 + num_kb)
+  const int num_kb = min(kb0 + kb_per_split, K / kF8BlockK) - kb0;
 
   pdl_launch_dependents();
   if (warp == 0 && lane == 0) {
@@ -87,8 +92,8 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         if (!mbar_wait(&empty_bar[s], ph ^ 1, status)) break;
         uint8_t* st = smem + s * Cfg::kStageBytes;
         mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
-        tma_load_2d(st, &tm_w, &full_bar[s], kb * kF8BlockK, r0);
-        tma_load_2d(st + Cfg::kRBytes, &tm_x, &full_bar[s], kb * kF8BlockK, tok0);
+        tma_load_2d(st, &tm_w, &full_bar[s], (kb0 + kb) * kF8BlockK, r0);
+        tma_load_2d(st + Cfg::kRBytes, &tm_x, &full_bar[s], (kb0 + kb) * kF8BlockK, tok0);
       }
     }
   } else if (warp == 1) {
@@ -123,8 +128,8 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     for (int kb = 0; kb < num_kb && ok; ++kb) {
       const int buf = kb & 1;
       // activation scales of this K block -> shared memory (one value per token of the tile)
-      if (et < BLOCK_C) s_xs[buf * 128 + et] = (tok0 + et < m_total) ? x_scale[static_cast<size_t>(kb) * x_scale_ld + tok0 + et] : 0.f;
-      const float ws = w_scale[static_cast<size_t>(blockIdx.x) * scale_cols + kb];
+      if (et < BLOCK_C) s_xs[buf * 128 + et] = (tok0 + et < m_total) ? x_scale[static_cast<size_t>(kb0 + kb) * x_scale_ld + tok0 + et] : 0.f;
+      const float ws = w_scale[static_cast<size_t>(blockIdx.x) * scale_cols + kb0 + kb];
       named_barrier_sync(1, 128);
       ok = mbar_wait(&acc_full[buf], (kb >> 1) & 1, status);
       tcgen05_fence_after();
@@ -145,9 +150,16 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
     if (r < n_total) {
+      if (partial != nullptr) {                          // K split: fp32 partial [split][token][feature]
+        float* dst = partial + static_cast<size_t>(blockIdx.z) * m_total * n_total + r;
 #pragma unroll
-      for (int c = 0; c < BLOCK_C; ++c)
-        if (tok0 + c < m_total) out[static_cast<size_t>(tok0 + c) * ldo + r] = __float2bfloat16_rn(acc[c]);   // lanes -> consecutive features
+        for (int c = 0; c < BLOCK_C; ++c)
+          if (tok0 + c < m_total) dst[static_cast<size_t>(tok0 + c) * n_total] = acc[c];
+      } else {
+#pragma unroll
+        for (int c = 0; c < BLOCK_C; ++c)
+          if (tok0 + c < m_total) out[static_cast<size_t>(tok0 + c) * ldo + r] = __float2bfloat16_rn(acc[c]);   // lanes -> consecutive features
+      }
     }
   }
 
@@ -157,6 +169,24 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
+}
+
+// out[m][n] = sum over splits of partial[s][m][n], added in split order; four features per thread.
+__global__ void __launch_bounds__(256) fp8_splitk_reduce_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
+                                                                int splits, int M, int N, int ldo) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int nvec = N >> 2;
+  if (idx >= static_cast<long long>(M) * nvec) return;
+  const int m = static_cast<int>(idx / nvec), n = static_cast<int>(idx % nvec) * 4;
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < splits; ++s) {
+    const float4 t = *reinterpret_cast<const float4*>(partial + (static_cast<size_t>(s) * M + m) * N + n);
+    a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
+  }
+  __nv_bfloat16* dst = out + static_cast<size_t>(m) * ldo + n;
+  dst[0] = __float2bfloat16_rn(a.x); dst[1] = __float2bfloat16_rn(a.y); dst[2] = __float2bfloat16_rn(a.z); dst[3] = __float2bfloat16_rn(a.w);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -197,7 +227,7 @@ extern "C" int forge_quant_fp8_1x128(const void* x, void* xq, float* scale, int 
 
 template <int BLOCK_C>
 static int launch_f8(const void* xq, const float* xs, int xs_ld, const void* wq, const float* ws, void* out, int ldo, int M, int N,
-                     int K, unsigned* status, cudaStream_t stream) {
+                     int K, int splits, float* partial, unsigned* status, cudaStream_t stream) {
   using Cfg = F8Cfg<BLOCK_C>;
   CUtensorMap tm_w, tm_x;
   if (forge_make_tmap_2d(&tm_w, wq, N, K, K, kF8BlockR, 1) != 0) return -2;
@@ -208,19 +238,45 @@ static int launch_f8(const void* xq, const float* xs, int xs_ld, const void* wq,
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return -4;
     attr_set = true;
   }
-  dim3 grid((N + kF8BlockR - 1) / kF8BlockR, (M + BLOCK_C - 1) / BLOCK_C);
-  return launch_kernel(kern, grid, dim3(kF8Threads), Cfg::kSmemBytes, stream, 0, tm_w, tm_x, ws, xs, static_cast<__nv_bfloat16*>(out),
-                       ldo, N, M, K, xs_ld, status) == cudaSuccess ? 0 : -5;
+  const int num_kb = K / kF8BlockK;
+  const int kb_per_split = (num_kb + splits - 1) / splits;
+  dim3 grid((N + kF8BlockR - 1) / kF8BlockR, (M + BLOCK_C - 1) / BLOCK_C, splits);
+  if (launch_kernel(kern, grid, dim3(kF8Threads), Cfg::kSmemBytes, stream, 0, tm_w, tm_x, ws, xs, static_cast<__nv_bfloat16*>(out),
+                    ldo, N, M, K, xs_ld, kb_per_split, splits > 1 ? partial : nullptr, status) != cudaSuccess)
+    return -5;
+  if (splits > 1) {
+    const long long vecs = static_cast<long long>(M) * (N >> 2);
+    if (launch_kernel(fp8_splitk_reduce_kernel, dim3(static_cast<unsigned>((vecs + 255) / 256)), dim3(256), 0, stream, 0,
+                      static_cast<const float*>(partial), static_cast<__nv_bfloat16*>(out), splits, M, N, ldo) != cudaSuccess)
+      return -5;
+  }
+  return 0;
+}
+
+static int f8_token_tile(int M) { return M <= 16 ? 16 : (M <= 32 ? 32 : 64); }
+
+// K splits the kernel will use for this problem: enough CTAs for about one wave of the 148 SMs (one CTA per SM:
+// the ring takes the whole shared memory), at least two K blocks per split, N a multiple of 4 for the reduce kernel.
+extern "C" int forge_gemm_fp8_splits(int M, int N, int K) {
+  if (M <= 0 || N <= 0 || (N & 3)) return 1;
+  const int bc = f8_token_tile(M);
+  const int ctas = ((N + kF8BlockR - 1) / kF8BlockR) * ((M + bc - 1) / bc);
+  const int num_kb = K / kF8BlockK;
+  int s = 1;
+  while (s < 8 && ctas * s * 2 <= 160 && num_kb / (s * 2) >= 2) s *= 2;
+  return s;
 }
 
 // xq [M, K] e4m3, xs [K / 128][xs_ld >= M]; wq [N, K] e4m3, ws [ceil(N / 128)][K / 128]; out [M, N] bf16 (row stride ldo).
+// partial: fp32 workspace of forge_gemm_fp8_splits(M, N, K) * M * N floats (may be null when that is 1).
 extern "C" int forge_gemm_fp8_block(const void* xq, const float* xs, int xs_ld, const void* wq, const float* ws, void* out, int ldo,
-                                    int M, int N, int K, unsigned* status, cudaStream_t stream) {
+                                    int M, int N, int K, float* partial, unsigned* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if ((K & 127) || (reinterpret_cast<uintptr_t>(xq) & 15) || (reinterpret_cast<uintptr_t>(wq) & 15)) return -1;
-  if (M <= 16) return launch_f8<16>(xq, xs, xs_ld, wq, ws, out, ldo, M, N, K, status, stream);
-  if (M <= 32) return launch_f8<32>(xq, xs, xs_ld, wq, ws, out, ldo, M, N, K, status, stream);
-  return launch_f8<64>(xq, xs, xs_ld, wq, ws, out, ldo, M, N, K, status, stream);
+  const int splits = partial != nullptr ? forge_gemm_fp8_splits(M, N, K) : 1;
+  if (M <= 16) return launch_f8<16>(xq, xs, xs_ld, wq, ws, out, ldo, M, N, K, splits, partial, status, stream);
+  if (M <= 32) return launch_f8<32>(xq, xs, xs_ld, wq, ws, out, ldo, M, N, K, splits, partial, status, stream);
+  return launch_f8<64>(xq, xs, xs_ld, wq, ws, out, ldo, M, N, K, splits, partial, status, stream);
 }
 
 }  // namespace forge

@@ -12,8 +12,9 @@ int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, void* out, i
                     int force_mode, int force_splits, unsigned* status, cudaStream_t stream);
 int forge_gemm_set_trace(unsigned long long* buf);
 int forge_quant_fp8_1x128(const void* x, void* xq, float* scale, int M, int K, int scale_ld, cudaStream_t stream);
+int forge_gemm_fp8_splits(int M, int N, int K);
 int forge_gemm_fp8_block(const void* xq, const float* xs, int xs_ld, const void* wq, const float* ws, void* out, int ldo, int M,
-                         int N, int K, unsigned* status, cudaStream_t stream);
+                         int N, int K, float* partial, unsigned* status, cudaStream_t stream);
 int forge_gemm_bf16_tp_push(const void* x, int ldx, const void* w, int ldw, int M, int n_out, int K, int tune, int tp_size,
                             int tp_rank, const long long* slot_ptrs, const long long* signal_ptrs, unsigned* arrive,
                             unsigned* epoch, long long mc_slot, unsigned* status, cudaStream_t stream);
@@ -354,7 +355,13 @@ void quant_fp8(const Tensor& x, Tensor& xq, Tensor& scale) {
         "forge_quant_fp8_1x128");
 }
 
-void gemm_fp8_block(const Tensor& xq, const Tensor& xs, const Tensor& wq, const Tensor& ws, Tensor& out, const Tensor& status) {
+int64_t gemm_fp8_splits(int64_t M, int64_t N, int64_t K) {
+  return forge_gemm_fp8_splits(static_cast<int>(M), static_cast<int>(N), static_cast<int>(K));
+}
+
+// partial: fp32 workspace of gemm_fp8_splits(M, N, K) * M * N elements; without it K is not split.
+void gemm_fp8_block(const Tensor& xq, const Tensor& xs, const Tensor& wq, const Tensor& ws, Tensor& out,
+                    const c10::optional<Tensor>& partial, const Tensor& status) {
   CHECK_CUDA_CONTIG(xq); CHECK_CUDA_CONTIG(wq); CHECK_CUDA_CONTIG(xs); CHECK_F32(xs); CHECK_CUDA_CONTIG(ws); CHECK_F32(ws);
   CHECK_CUDA_CONTIG(out); CHECK_BF16(out);
   TORCH_CHECK(xq.element_size() == 1 && wq.element_size() == 1 && xq.dim() == 2 && wq.dim() == 2, "gemm_fp8_block: e4m3 operands");
@@ -362,10 +369,16 @@ void gemm_fp8_block(const Tensor& xq, const Tensor& xs, const Tensor& wq, const 
   TORCH_CHECK(wq.size(1) == K && K % 128 == 0 && out.size(0) == M && out.size(1) == N, "gemm_fp8_block: shapes");
   TORCH_CHECK(xs.dim() == 2 && xs.size(0) == K / 128 && xs.size(1) >= M && ws.dim() == 2 && ws.size(0) == (N + 127) / 128 && ws.size(1) == K / 128,
               "gemm_fp8_block: scale shapes");
+  float* pp = nullptr;
+  if (partial.has_value()) {
+    CHECK_CUDA_CONTIG(*partial); CHECK_F32(*partial);
+    TORCH_CHECK(partial->numel() >= gemm_fp8_splits(M, N, K) * M * N, "gemm_fp8_block: workspace too small");
+    pp = partial->data_ptr<float>();
+  }
   const c10::cuda::CUDAGuard guard(xq.device());
   check(forge_gemm_fp8_block(xq.data_ptr(), xs.data_ptr<float>(), static_cast<int>(xs.size(1)), wq.data_ptr(), ws.data_ptr<float>(),
                              out.data_ptr(), static_cast<int>(out.stride(0)), static_cast<int>(M), static_cast<int>(N),
-                             static_cast<int>(K), status_ptr(status), stream_of(xq)),
+                             static_cast<int>(K), pp, status_ptr(status), stream_of(xq)),
         "forge_gemm_fp8_block");
 }
 
@@ -453,6 +466,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_set_trace", &gemm_set_trace);
   m.def("quant_fp8", &quant_fp8);
   m.def("gemm_fp8_block", &gemm_fp8_block);
+  m.def("gemm_fp8_splits", &gemm_fp8_splits);
   m.def("gemm_tp_push", &gemm_tp_push);
   m.def("tp_reduce_rms_norm", &tp_reduce_rms_norm);
   m.def("tp_embedding_push", &tp_embedding_push);

@@ -121,9 +121,12 @@ class CudaOps:
         xq = torch.empty(M, K, dtype=torch.uint8, device=x.device)
         xs = torch.empty(K // 128, (M + 3) // 4 * 4, dtype=torch.float32, device=x.device)
         self.C.quant_fp8(x, xq, xs)
-        out = torch.empty(M, w.shape[0], dtype=x.dtype, device=x.device)
-        self.C.gemm_fp8_block(xq, xs, w.q.view(torch.uint8), w.scale, out, self.status)
-        self.launches += 2
+        N = w.shape[0]
+        out = torch.empty(M, N, dtype=x.dtype, device=x.device)
+        splits = self.C.gemm_fp8_splits(M, N, K)         # few tokens: K is split over CTAs, partials added by a second kernel
+        partial = torch.empty(splits * M * N, dtype=torch.float32, device=x.device) if splits > 1 else None
+        self.C.gemm_fp8_block(xq, xs, w.q.view(torch.uint8), w.scale, out, partial, self.status)
+        self.launches += 3 if splits > 1 else 2
         return out
 
     # ------------------------------------------------------------------ elementwise
