@@ -185,3 +185,19 @@ def test_step_trace_has_one_line_per_step(ckpt, prompts, tmp_path):
         lines = [json.loads(l) for l in open(path)]
         assert len(lines) == steps and [l["step"] for l in lines] == list(range(steps))
         assert lines[0]["prefill"] and not lines[-1]["prefill"] and all(l["run_ms"] >= 0 for l in lines)
+
+
+def test_pipelined_loop_short_requests(ckpt, prompts):
+    """Requests that finish on their first or second token (the step that produced the token is still in flight when the
+    request is retired) and an empty follow-up call."""
+    results = {}
+    for pipelined in (True, False):
+        llm = _llm(ckpt, seed=1, extra={"pipeline": pipelined})
+        sps = [SamplingParams(temperature=0.0, max_tokens=1 + (i % 3), ignore_eos=True) for i in range(len(prompts))]
+        outs = llm.generate(prompts, sps, use_tqdm=False)
+        assert llm.generate([], [], use_tqdm=False) == []
+        results[pipelined] = [o["token_ids"] for o in outs]
+        assert llm.scheduler.pool.num_free == llm.scheduler.pool.num_blocks
+        llm.exit()
+    assert results[True] == results[False]
+    assert [len(t) for t in results[True]] == [1 + (i % 3) for i in range(len(prompts))]
