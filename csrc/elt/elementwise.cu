@@ -239,6 +239,102 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_kernel(
   }
 }
 
+
+// head_dim 128: eight lanes per head, each lane holds elements [8j, 8j+8) and [64+8j, 64+8j+8) (j = lane % 8): exactly the
+// pairs the rotation mixes, moved with 16-byte accesses; a warp works on four heads of one token at a time and walks
+// `hpw` consecutive heads, so the token's position, slot and cos/sin values are fetched once per warp.
+__global__ void __launch_bounds__(128) qk_norm_rope_store128_kernel(
+    const __nv_bfloat16* __restrict__ qkv, int ld_qkv, const __nv_bfloat16* __restrict__ qw, const __nv_bfloat16* __restrict__ kw,
+    float eps, const float* __restrict__ rope, int rope_rows, const int* __restrict__ positions, const int* __restrict__ slots,
+    __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+    int T, int nq, int nkv, int block_size, long long num_slots, int do_rope, int hpw, unsigned* status) {
+  constexpr int D = 128;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int heads = nq + 2 * nkv;
+  const int groups = (heads + hpw - 1) / hpw;
+  const long long wid = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wid >= static_cast<long long>(T) * groups) return;
+  const int lane = threadIdx.x & 31, j = lane & 7, sub = lane >> 3;
+  const int t = static_cast<int>(wid / groups);
+  const int h_begin = static_cast<int>(wid % groups) * hpw;
+  const int h_end = min(h_begin + hpw, heads);
+
+  float cosv[8], sinv[8];
+  if (do_rope) {
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= rope_rows ? rope_rows - 1 : pos);
+    const float* cs = rope + static_cast<size_t>(pos) * D;
+    const float4 c0 = *reinterpret_cast<const float4*>(cs + 8 * j), c1 = *reinterpret_cast<const float4*>(cs + 8 * j + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(cs + 64 + 8 * j), s1 = *reinterpret_cast<const float4*>(cs + 64 + 8 * j + 4);
+    cosv[0] = c0.x; cosv[1] = c0.y; cosv[2] = c0.z; cosv[3] = c0.w; cosv[4] = c1.x; cosv[5] = c1.y; cosv[6] = c1.z; cosv[7] = c1.w;
+    sinv[0] = s0.x; sinv[1] = s0.y; sinv[2] = s0.z; sinv[3] = s0.w; sinv[4] = s1.x; sinv[5] = s1.y; sinv[6] = s1.z; sinv[7] = s1.w;
+  }
+  const long long slot = slots[t];
+  const bool slot_ok = slot >= 0 && slot < num_slots;
+  if (slot >= num_slots && lane == 0) set_status(status, kStatusBadIndex);
+
+  for (int h0 = h_begin; h0 < h_end; h0 += 4) {
+    const int h = h0 + sub;
+    const bool live = h < h_end;
+    const __nv_bfloat16* src = qkv + static_cast<size_t>(t) * ld_qkv + static_cast<size_t>(live ? h : h_begin) * D;
+    uint4 lo = *reinterpret_cast<const uint4*>(src + 8 * j);
+    uint4 hi = *reinterpret_cast<const uint4*>(src + 64 + 8 * j);
+    const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+    const __nv_bfloat16* w = is_q ? qw : kw;
+    if (is_q || is_k) {
+      const uint32_t r[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+      float a[8], b[8];                               // first-half and second-half elements
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        a[2 * e] = bf16_lo(r[e]); a[2 * e + 1] = bf16_hi(r[e]);
+        b[2 * e] = bf16_lo(r[4 + e]); b[2 * e + 1] = bf16_hi(r[4 + e]);
+      }
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += a[e] * a[e] + b[e] * b[e];
+      const unsigned gmask = 0xFFu << (sub * 8);        // the four 8-lane groups may hold different kinds of heads
+      ss += __shfl_xor_sync(gmask, ss, 1);
+      ss += __shfl_xor_sync(gmask, ss, 2);
+      ss += __shfl_xor_sync(gmask, ss, 4);
+      if (w != nullptr) {
+        const float inv = rsqrtf(ss / static_cast<float>(D) + eps);
+        const uint4 wl = *reinterpret_cast<const uint4*>(w + 8 * j), wh = *reinterpret_cast<const uint4*>(w + 64 + 8 * j);
+        const uint32_t wr[8] = {wl.x, wl.y, wl.z, wl.w, wh.x, wh.y, wh.z, wh.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          a[2 * e] = bf16_round(bf16_round(a[2 * e] * inv) * bf16_lo(wr[e]));
+          a[2 * e + 1] = bf16_round(bf16_round(a[2 * e + 1] * inv) * bf16_hi(wr[e]));
+          b[2 * e] = bf16_round(bf16_round(b[2 * e] * inv) * bf16_lo(wr[4 + e]));
+          b[2 * e + 1] = bf16_round(bf16_round(b[2 * e + 1] * inv) * bf16_hi(wr[4 + e]));
+        }
+      }
+      if (do_rope) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float x1 = a[e], x2 = b[e];
+          a[e] = x1 * cosv[e] - x2 * sinv[e];
+          b[e] = x2 * cosv[e] + x1 * sinv[e];
+        }
+      }
+      lo = make_uint4(pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]), pack_bf16x2(a[4], a[5]), pack_bf16x2(a[6], a[7]));
+      hi = make_uint4(pack_bf16x2(b[0], b[1]), pack_bf16x2(b[2], b[3]), pack_bf16x2(b[4], b[5]), pack_bf16x2(b[6], b[7]));
+    }
+    if (!live) continue;
+    __nv_bfloat16* dst;
+    if (is_q) {
+      dst = q_out + (static_cast<size_t>(t) * nq + h) * D;
+    } else {
+      if (!slot_ok) continue;
+      const int kvh = is_k ? h - nq : h - nq - nkv;
+      const long long blk = slot / block_size, off = slot % block_size;
+      dst = (is_k ? k_cache : v_cache) + ((blk * nkv + kvh) * block_size + off) * D;
+    }
+    *reinterpret_cast<uint4*>(dst + 8 * j) = lo;
+    *reinterpret_cast<uint4*>(dst + 64 + 8 * j) = hi;
+  }
+}
+
 extern "C" int forge_qk_norm_rope_store(const void* qkv, int ld_qkv, const void* qw, const void* kw, float eps,
                                         const float* rope, int rope_rows, const int* positions, const int* slots,
                                         void* q_out, void* k_cache, void* v_cache, int T, int nq, int nkv, int D,
@@ -246,6 +342,16 @@ extern "C" int forge_qk_norm_rope_store(const void* qkv, int ld_qkv, const void*
                                         cudaStream_t stream) {
   if (T <= 0) return 0;
   const int heads = nq + 2 * nkv;
+  if (D == 128 && (ld_qkv & 7) == 0 && (reinterpret_cast<uintptr_t>(qkv) & 15) == 0) {
+    // four heads per warp at a time; more heads per warp when there are many tokens (amortises the per-token loads)
+    const int hpw128 = T >= 4096 ? 16 : (T >= 512 ? 8 : 4);
+    const long long warps128 = static_cast<long long>(T) * ((heads + hpw128 - 1) / hpw128);
+    return launch_kernel(qk_norm_rope_store128_kernel, dim3(static_cast<unsigned>((warps128 + 3) / 4)), dim3(128), 0, stream, 0,
+                         static_cast<const __nv_bfloat16*>(qkv), ld_qkv, static_cast<const __nv_bfloat16*>(qw),
+                         static_cast<const __nv_bfloat16*>(kw), eps, rope, rope_rows, positions, slots,
+                         static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
+                         static_cast<__nv_bfloat16*>(v_cache), T, nq, nkv, block_size, num_slots, do_rope, hpw128, status) == cudaSuccess ? 0 : -2;
+  }
   const int hpw = T >= 4096 ? 8 : (T >= 1024 ? 4 : 1);        // heads per warp: amortise the per-token loads when there is enough work
   const long long warps = static_cast<long long>(T) * ((heads + hpw - 1) / hpw);
   const int grid = static_cast<int>((warps + 3) / 4);
