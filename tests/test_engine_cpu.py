@@ -201,3 +201,29 @@ def test_pipelined_loop_short_requests(ckpt, prompts):
         llm.exit()
     assert results[True] == results[False]
     assert [len(t) for t in results[True]] == [1 + (i % 3) for i in range(len(prompts))]
+
+
+def test_chunked_prefill_matches_whole_prompt_prefill(ckpt):
+    """A prompt longer than the token budget is prefilled in several steps (not in the reference, which rejects it): same
+    tokens as with a budget that takes the prompt whole; a later prompt reuses the long prompt's blocks through the prefix
+    cache; pipelined and plain loops agree."""
+    rng = random.Random(9)
+    long_prompt = [rng.randrange(4096) for _ in range(150)]
+    prompts = [[rng.randrange(4096) for _ in range(20)], long_prompt, [rng.randrange(4096) for _ in range(33)],
+               long_prompt[:100] + [rng.randrange(4096) for _ in range(70)]]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    whole = _llm(ckpt, max_model_len=400)
+    want = [o["token_ids"] for o in whole.generate(prompts, sp, use_tqdm=False)]
+    whole.exit()
+    with pytest.raises(ValueError):
+        _llm(ckpt, max_model_len=400, max_num_batched_tokens=64)
+    for pipelined in (True, False):
+        llm = _llm(ckpt, max_model_len=400, max_num_batched_tokens=64, chunked_prefill=True, extra={"pipeline": pipelined})
+        got = [o["token_ids"] for o in llm.generate(prompts, sp, use_tqdm=False)]
+        st = llm.stats.to_dict()
+        llm.scheduler.pool.check_invariants()
+        assert llm.scheduler.pool.num_free == llm.scheduler.pool.num_blocks
+        llm.exit()
+        assert got == want
+        assert st["prefill_steps"] >= 3 + 3 + 1               # 150 tokens and 170 tokens at 64 per step, plus the short ones
+        assert st["prefix_cached_tokens"] >= 96                # the fourth prompt found the long prompt's first six blocks

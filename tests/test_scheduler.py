@@ -123,3 +123,35 @@ def test_bench_workload_shape():
             dec_tok += len(batch)
         s.postprocess(batch, [0] * len(batch))
     assert (pre, dec, pre_tok, dec_tok, s.num_preemptions) == (9, 1023, 142827, 133710, 0)
+
+
+def test_chunked_prefill_schedules_a_long_prompt_over_several_steps():
+    from tinyllmforge_b200 import preset
+    from tinyllmforge_b200.config import Config
+    cfg = Config.from_kwargs("x", hf_config=preset("tiny"), device="cpu", load_format="dummy", skip_tokenizer_init=True,
+                             kvcache_block_size=8, num_kvcache_blocks=64, max_num_seqs=4, max_model_len=256,
+                             max_num_batched_tokens=32, chunked_prefill=True)
+    sch = Scheduler(cfg)
+    short, long = Request(list(range(10))), Request(list(range(100, 180)))         # 80 tokens > budget 32
+    sch.add(short)
+    sch.add(long)
+    batch, is_prefill = sch.schedule()
+    assert is_prefill and batch == [short]
+    sch.postprocess(batch, [1])
+    spans = []
+    while sch.has_waiting():
+        batch, is_prefill = sch.schedule()
+        assert is_prefill and batch == [long]
+        spans.append((long.num_computed_tokens, long.prefill_end))
+        before = len(long)
+        sch.postprocess(batch, [7])
+        assert len(long) == before + (0 if sch.partial is long else 1)
+    assert spans == [(0, 32), (32, 64), (64, 80)]
+    assert len(long) == 81 and long.num_computed_tokens == -1 and long in sch.running
+    # blocks were registered chunk by chunk: all ten full prompt blocks are reusable now
+    other = Request(list(range(100, 180)) + [5])
+    sch.add(other)
+    batch, is_prefill = sch.schedule()
+    assert is_prefill and batch == [other] and other.num_cached_tokens == 80
+    batch2, is_prefill2 = sch.schedule()
+    assert not is_prefill2 and set(batch2) == {short, long, other}

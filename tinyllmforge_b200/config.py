@@ -10,7 +10,7 @@ keyword arguments of ``LLM``).  Differences, all deliberate:
 * ``config.json`` is parsed directly into :class:`ModelConfig`, so building an
   engine does not import ``transformers``;
 * extra optional fields: ``seed``, ``dtype``, ``device``, ``comm``,
-  ``quantization``, ``load_format``, ``skip_tokenizer_init``.
+  ``quantization``, ``load_format``, ``skip_tokenizer_init``, ``chunked_prefill``.
 """
 from __future__ import annotations
 
@@ -168,6 +168,7 @@ class Config:
     skip_tokenizer_init: bool = False
     rpc_timeout_s: float = 120.0             # bound on every control-plane wait between ranks
     trace_path: Optional[str] = None         # per-step JSONL trace
+    chunked_prefill: bool = False            # prompts longer than max_num_batched_tokens are prefilled over several steps
     extra: dict = field(default_factory=dict)
 
     def __post_init__(self):
@@ -188,8 +189,11 @@ class Config:
         if hf.vocab_size % self.tensor_parallel_size:
             raise ValueError("vocab_size must divide evenly by tensor_parallel_size")
         self.max_model_len = min(self.max_model_len, hf.max_position_embeddings)
-        if self.max_num_batched_tokens < self.max_model_len:
-            raise ValueError("max_num_batched_tokens must be >= max_model_len (prompts are prefilled whole)")
+        if self.max_num_batched_tokens < self.max_model_len and not self.chunked_prefill:
+            raise ValueError("max_num_batched_tokens must be >= max_model_len (prompts are prefilled whole; "
+                             "chunked_prefill=True lifts this)")
+        if self.max_num_batched_tokens < self.kvcache_block_size:
+            raise ValueError("max_num_batched_tokens must be at least one KV block")
         if self.device == "auto":
             self.device = "cuda" if torch.cuda.is_available() else "cpu"
         if self.device not in ("cuda", "cpu"):

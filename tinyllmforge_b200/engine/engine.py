@@ -196,7 +196,7 @@ class LLMEngine:
         if is_prefill:
             st.prefill_steps += 1
             st.prefill_tokens += sb.num_tokens
-            st.prefix_cached_tokens += sum(r.num_cached_tokens for r in reqs)
+            st.prefix_cached_tokens += self.scheduler.last_admit_cached
             count = sb.num_tokens
         else:
             st.decode_steps += 1
@@ -284,7 +284,8 @@ class LLMEngine:
             except RuntimeError as e:
                 raise EngineDeadError(str(e)) from e
             for (r, idx), tok in zip(reqs, toks):
-                r.token_ids[idx] = tok
+                if idx >= 0:
+                    r.token_ids[idx] = tok
             for r in finished:
                 outputs[r.req_id] = r.completion_token_ids
             if pbar is not None:
@@ -323,8 +324,9 @@ class LLMEngine:
             self._mark("collect previous + postprocess")
             self.step_index += 1
             drain()                                      # read the PREVIOUS step while this one runs
+            partial = sch.partial                        # a long prompt in the middle of its prefill receives no token
             finished = sch.postprocess(reqs, [PLACEHOLDER] * len(reqs))
-            inflight = ([(r, len(r.token_ids) - 1) for r in reqs], ticket, finished)
+            inflight = ([(r, len(r.token_ids) - 1 if r is not partial else -1) for r in reqs], ticket, finished)
             t4 = time.perf_counter()
             self._mark(None)
             st.schedule_s += t1 - t0
@@ -334,7 +336,7 @@ class LLMEngine:
             if is_prefill:
                 st.prefill_steps += 1
                 st.prefill_tokens += sb.num_tokens
-                st.prefix_cached_tokens += sum(r.num_cached_tokens for r in reqs)
+                st.prefix_cached_tokens += self.scheduler.last_admit_cached
             else:
                 st.decode_steps += 1
                 st.decode_tokens += len(reqs)

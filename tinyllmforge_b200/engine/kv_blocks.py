@@ -99,11 +99,17 @@ class KVBlockPool:
     def can_admit(self, req: Request) -> bool:
         return len(self.free) >= self.blocks_needed(len(req))
 
-    def admit(self, req: Request) -> None:
-        """Give ``req`` a block table covering all its tokens, reusing cached prefix blocks."""
+    def admit(self, req: Request, seal_upto: int | None = None) -> None:
+        """Give ``req`` a block table covering all its tokens, reusing cached prefix blocks.
+
+        ``seal_upto``: only blocks that end at or before this token count are registered for reuse now (chunked prefill:
+        a block must not be found by other requests before the step that computes it has been scheduled);
+        ``seal_computed`` registers the rest later."""
         assert not req.block_table, "request already holds blocks"
         bs = self.block_size
         n = len(req)
+        if seal_upto is None:
+            seal_upto = n
         toks = req.token_ids
         parent = -1
         missed = False
@@ -128,13 +134,20 @@ class KVBlockPool:
                     del self.free[block_id]
                     self.ref_count[block_id] = 1
             if full:
-                if self.block_hash[block_id] != h:
+                if self.block_hash[block_id] != h and (i + 1) * bs <= seal_upto:
                     self._seal(block_id, h, chunk)
                 parent = h
             req.block_table.append(block_id)
         req.num_cached_tokens = min(cached, n - 1)
         self.prefix_hit_tokens += req.num_cached_tokens
         self.prefix_query_tokens += n
+
+    def seal_computed(self, req: Request, upto: int) -> None:
+        """Register the prompt blocks of ``req`` that end at or before token ``upto`` and are not registered yet (in order:
+        a block's hash chains on its predecessor's)."""
+        bs = self.block_size
+        for index in range(min(upto // bs, len(req.block_table))):
+            self._seal_block(req, index, (index + 1) * bs)
 
     def release(self, req: Request) -> None:
         for block_id in reversed(req.block_table):
@@ -144,6 +157,7 @@ class KVBlockPool:
                 self.free[block_id] = None
         req.block_table.clear()
         req.num_cached_tokens = 0
+        req.num_computed_tokens = req.prefill_end = -1
 
     # ------------------------------------------------------------------ decode
     def can_grow(self, req: Request) -> bool:

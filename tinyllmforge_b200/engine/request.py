@@ -21,7 +21,7 @@ class RequestStatus(Enum):
 
 
 class Request:
-    __slots__ = ("req_id", "status", "token_ids", "num_prompt_tokens", "num_cached_tokens",
+    __slots__ = ("req_id", "status", "token_ids", "num_prompt_tokens", "num_cached_tokens", "num_computed_tokens", "prefill_end",
                  "block_table", "temperature", "max_tokens", "ignore_eos", "num_preemptions")
 
     _ids = count()
@@ -34,6 +34,11 @@ class Request:
         self.token_ids = list(prompt_token_ids)
         self.num_prompt_tokens = len(self.token_ids)
         self.num_cached_tokens = 0
+        # chunked prefill (a prompt longer than the token budget is prefilled over several steps): tokens whose KV entries
+        # exist already, and the end of the range the current prefill step covers.  -1: not in use (the step starts at
+        # num_cached_tokens and covers the whole request).
+        self.num_computed_tokens = -1
+        self.prefill_end = -1
         self.block_table: list[int] = []
         self.temperature = float(sampling_params.temperature)
         self.max_tokens = int(sampling_params.max_tokens)

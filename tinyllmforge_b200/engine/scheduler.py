@@ -13,6 +13,11 @@ Parity: tinyvllm/engine/scheduler.py:7-72.  Policy is the reference's:
 The admission test charges the same quantity it compares (uncached tokens),
 where the reference compares the full length but charges the uncached part
 (tinyvllm/engine/scheduler.py:29,33).
+
+Not in the reference (it rejects such prompts): with ``chunked_prefill`` a prompt longer
+than the token budget is admitted alone and prefilled over consecutive steps, one budget
+worth of tokens at a time; it joins the running queue when its last chunk is scheduled,
+and its blocks become visible to the prefix cache only as their chunks are scheduled.
 """
 from __future__ import annotations
 
@@ -35,13 +40,20 @@ class Scheduler:
         self.waiting: deque[Request] = deque()
         self.running: deque[Request] = deque()
         self.num_preemptions = 0
+        self.chunked = bool(config.chunked_prefill)
+        self.max_model_len = config.max_model_len
+        self.partial: Request | None = None       # admitted, holds its blocks, prompt not completely prefilled yet
+        self.last_admit_cached = 0                # prefix-cache tokens of the requests admitted by the last schedule()
 
     def is_finished(self) -> bool:
-        return not self.waiting and not self.running
+        return not self.waiting and not self.running and self.partial is None
 
     def add(self, req: Request) -> None:
-        if len(req) > self.max_num_batched_tokens:
-            raise ValueError(f"prompt of {len(req)} tokens exceeds max_num_batched_tokens={self.max_num_batched_tokens}")
+        if len(req) > self.max_num_batched_tokens and not self.chunked:
+            raise ValueError(f"prompt of {len(req)} tokens exceeds max_num_batched_tokens={self.max_num_batched_tokens} "
+                             "(chunked_prefill=True admits it)")
+        if len(req) >= self.max_model_len and self.chunked:
+            raise ValueError(f"prompt of {len(req)} tokens does not fit max_model_len={self.max_model_len}")
         if self.pool.blocks_needed(len(req) + 1) > self.pool.num_blocks:
             raise ValueError("prompt does not fit in the KV cache")
         self.waiting.append(req)
@@ -50,12 +62,40 @@ class Scheduler:
         """Pick the next batch. Returns (requests, is_prefill).  ``defer_seal``: see ``KVBlockPool.grow``."""
         batch: list[Request] = []
         budget = self.max_num_batched_tokens
+        self.last_admit_cached = 0
+        if self.partial is not None:                       # the next chunk of a long prompt, alone
+            req = self.partial
+            req.prefill_end = min(len(req), req.num_computed_tokens + budget)
+            self.pool.seal_computed(req, req.prefill_end)
+            if req.prefill_end == len(req):                # last chunk: the request decodes from the next step on
+                self.partial = None
+                req.status = RequestStatus.RUNNING
+                self.running.append(req)
+            return [req], True
         while self.waiting and len(self.running) < self.max_num_seqs:
             req = self.waiting[0]
+            if self.chunked and len(req) > self.max_num_batched_tokens:
+                # can never be prefilled whole: first chunk, in a step of its own
+                if batch or not self.pool.can_admit(req):
+                    break
+                first = self.max_num_batched_tokens
+                self.pool.admit(req, seal_upto=first)
+                self.last_admit_cached += req.num_cached_tokens
+                req.num_computed_tokens = req.num_cached_tokens
+                req.prefill_end = min(len(req), req.num_computed_tokens + first)
+                self.pool.seal_computed(req, req.prefill_end)
+                self.waiting.popleft()
+                self.partial = req                         # a prefix hit cannot complete it: the prompt exceeds the budget by itself...
+                if req.prefill_end == len(req):            # ...unless most of it was cached
+                    self.partial = None
+                    req.status = RequestStatus.RUNNING
+                    self.running.append(req)
+                return [req], True
             # An upper bound on the work is the whole length; the exact charge is known after admit().
             if len(req) > budget or not self.pool.can_admit(req):
                 break
             self.pool.admit(req)
+            self.last_admit_cached += req.num_cached_tokens
             budget -= len(req) - req.num_cached_tokens
             req.status = RequestStatus.RUNNING
             self.waiting.popleft()
@@ -94,13 +134,19 @@ class Scheduler:
         self.waiting.appendleft(req)
 
     def has_waiting(self) -> bool:
-        return bool(self.waiting)
+        """True if the next step may be a prefill."""
+        return bool(self.waiting) or self.partial is not None
 
     def postprocess(self, batch: list[Request], token_ids: list[int]) -> list[Request]:
         """Append the sampled tokens; retire finished requests. Returns the finished ones.
         The pipelined engine loop passes ``PLACEHOLDER`` ids and patches the real ones in later."""
         finished = []
         for req, tok in zip(batch, token_ids):
+            if req is self.partial:                        # a chunk in the middle of a long prompt: no token yet
+                req.num_computed_tokens = req.prefill_end
+                continue
+            if req.prefill_end >= 0:                       # last (or only) chunk of a chunked prompt: back to the normal state
+                req.num_computed_tokens = req.prefill_end = -1
             req.token_ids.append(tok)
             if (not req.ignore_eos and tok == self.eos) or req.num_completion_tokens >= req.max_tokens:
                 req.status = RequestStatus.FINISHED

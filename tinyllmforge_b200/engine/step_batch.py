@@ -117,10 +117,13 @@ def _new(is_prefill, num_seqs, num_tokens, padded_seqs, padded_tokens, width, ma
 
 
 def build_prefill(reqs, block_size: int, step_index: int = 0, seed: int = 0) -> StepBatch:
-    """Prefill step: every request contributes its not-yet-cached tokens."""
+    """Prefill step: every request contributes its not-yet-cached tokens (or, for a prompt prefilled in chunks, the
+    tokens [num_computed_tokens, prefill_end); the keys it sees then end at prefill_end)."""
     S = len(reqs)
-    q_lens = np.fromiter((len(r) - r.num_cached_tokens for r in reqs), dtype=np.int64, count=S)
-    k_lens = np.fromiter((len(r) for r in reqs), dtype=np.int64, count=S)
+    starts = [r.num_computed_tokens if r.num_computed_tokens >= 0 else r.num_cached_tokens for r in reqs]
+    ends = [r.prefill_end if r.prefill_end >= 0 else len(r) for r in reqs]
+    q_lens = np.fromiter((e - c for c, e in zip(starts, ends)), dtype=np.int64, count=S)
+    k_lens = np.fromiter(ends, dtype=np.int64, count=S)
     T = int(q_lens.sum())
     width = max(len(r.block_table) for r in reqs)
     buf, offs = _new(True, S, T, S, T, width, int(q_lens.max()), int(k_lens.max()), step_index, seed)
@@ -134,9 +137,9 @@ def build_prefill(reqs, block_size: int, step_index: int = 0, seed: int = 0) -> 
     tables[:] = -1
     t = 0
     for i, r in enumerate(reqs):
-        c, n = r.num_cached_tokens, len(r)
+        c, n = starts[i], ends[i]
         q = n - c
-        ids[t:t + q] = r.token_ids[c:]
+        ids[t:t + q] = r.token_ids[c:n]
         p = np.arange(c, n, dtype=np.int64)
         pos[t:t + q] = p
         bt = np.asarray(r.block_table, dtype=np.int64)

@@ -127,12 +127,13 @@ class Worker:
         """One full-budget prefill so the allocator's peak reflects the largest step
         (tinyvllm/engine/model_runner.py:108-116)."""
         cfg = self.config
-        n = min(cfg.max_num_batched_tokens // cfg.max_model_len, cfg.max_num_seqs)
+        seq_len = min(cfg.max_model_len, cfg.max_num_batched_tokens)      # chunked prefill: a step never exceeds the budget
+        n = max(1, min(cfg.max_num_batched_tokens // seq_len, cfg.max_num_seqs))
         from .request import Request
         reqs = []
-        nblk = (cfg.max_model_len + self.block_size - 1) // self.block_size
+        nblk = (seq_len + self.block_size - 1) // self.block_size
         for i in range(n):
-            r = Request([0] * cfg.max_model_len)
+            r = Request([0] * seq_len)
             r.block_table = list(range(i * nblk, (i + 1) * nblk))
             reqs.append(r)
         self.run(build_prefill(reqs, self.block_size))
@@ -144,7 +145,7 @@ class Worker:
         if cfg.num_kvcache_blocks <= 0:
             if self.is_cuda:
                 # temporary cache just large enough for the warm-up prefill
-                n_tmp = min(cfg.max_num_batched_tokens // cfg.max_model_len, cfg.max_num_seqs) * self.table_width
+                n_tmp = max(1, min(cfg.max_num_batched_tokens // min(cfg.max_model_len, cfg.max_num_batched_tokens), cfg.max_num_seqs)) * self.table_width
                 self.model.bind_kv_cache(torch.zeros(hf.num_hidden_layers, 2, n_tmp, kvh, self.block_size, hf.head_dim,
                                                      dtype=cfg.dtype, device=self.device))
                 torch.cuda.reset_peak_memory_stats()
