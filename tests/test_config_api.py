@@ -36,7 +36,8 @@ def test_validation():
         Config("x", hf_config=preset("tiny"), tensor_parallel_size=4, device="cpu")       # 2 KV heads
     with pytest.raises(ValueError):
         Config("x", hf_config=preset("tiny"), max_num_batched_tokens=100, max_model_len=200, device="cpu")
-    c = Config("x", hf_config=preset("tiny"), max_num_batched_tokens=100, max_model_len=200, device="cpu", chunked_prefill=True)
+    c = Config("x", hf_config=preset("tiny"), max_num_batched_tokens=100, max_model_len=200, kvcache_block_size=16, device="cpu",
+               chunked_prefill=True)
     assert c.chunked_prefill and c.max_num_batched_tokens < c.max_model_len          # chunked prefill lifts the whole-prompt rule
     with pytest.raises(ValueError):
         Config("x", hf_config=preset("tiny"), max_num_batched_tokens=8, max_model_len=200, kvcache_block_size=16, device="cpu",
