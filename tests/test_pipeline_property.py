@@ -1,6 +1,7 @@
 """Property test of the engine loops with a fake worker (no model): whatever the prompts, lengths, pool size and
 sequence limit, the loop that runs one step ahead of the tokens it has read back must retire every request with exactly
-the tokens of the plain loop, keep the KV pool consistent and give every block back.
+the tokens of the plain loop, keep the KV pool consistent and give every block back.  In half of the cases the pipelined
+engine also has a token budget so small that long prompts are prefilled in chunks.
 
 The fake worker "samples" a deterministic function of (the sequence's input token, its position), taken from the packed
 step buffer exactly as a real worker would see it, including the device-side hand-over of the previous step's tokens
@@ -48,10 +49,10 @@ class FakeWorker:
         return self.collect(self.launch(sb))
 
 
-def make_engine(num_blocks, max_seqs, pipelined):
+def make_engine(num_blocks, max_seqs, pipelined, budget=128):
     cfg = Config.from_kwargs("fake", hf_config=preset("tiny"), device="cpu", load_format="dummy", skip_tokenizer_init=True,
                              kvcache_block_size=8, num_kvcache_blocks=num_blocks, max_num_seqs=max_seqs, max_model_len=128,
-                             max_num_batched_tokens=128, extra={"pipeline": pipelined})
+                             max_num_batched_tokens=budget, chunked_prefill=budget < 128, extra={"pipeline": pipelined})
     eng = LLMEngine.__new__(LLMEngine)            # the loops only: no model, no processes
     eng.config, eng.worker, eng.scheduler, eng.stats = cfg, FakeWorker(), Scheduler(cfg), EngineStats()
     eng.chan, eng.procs, eng.launcher_mode, eng._closed, eng._trace = None, [], False, False, None
@@ -63,14 +64,16 @@ def make_engine(num_blocks, max_seqs, pipelined):
 workload = st.lists(st.tuples(st.lists(st.integers(0, 50), min_size=1, max_size=30), st.integers(1, 24)), min_size=1, max_size=10)
 
 
-@settings(max_examples=80, deadline=None, suppress_health_check=[HealthCheck.too_slow])
-@given(reqs=workload, num_blocks=st.integers(10, 30), max_seqs=st.integers(1, 6), shared=st.booleans())
-def test_pipelined_loop_matches_plain_loop(reqs, num_blocks, max_seqs, shared):
+@settings(max_examples=100, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@given(reqs=workload, num_blocks=st.integers(10, 30), max_seqs=st.integers(1, 6), shared=st.booleans(),
+       budget=st.sampled_from([128, 128, 16, 24]))
+def test_pipelined_loop_matches_plain_loop(reqs, num_blocks, max_seqs, shared, budget):
     if shared:                                    # a common prefix, so that blocks are shared and revived
         reqs = [([7, 7, 7, 7, 9, 9, 9, 9, 1, 2, 3, 4, 5, 6, 7, 8] + p, m) for p, m in reqs]
     results = []
     for pipelined in (True, False):
-        eng = make_engine(num_blocks, max_seqs, pipelined)
+        # the pipelined engine may also prefill long prompts in chunks (a small token budget); the plain one never does
+        eng = make_engine(num_blocks, max_seqs, pipelined, budget if pipelined else 128)
         prompts = [p for p, _ in reqs]
         sps = [SamplingParams(temperature=0.0, max_tokens=m, ignore_eos=True) for _, m in reqs]
         outs = eng.generate(prompts, sps, use_tqdm=False)
