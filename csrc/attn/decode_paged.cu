@@ -15,11 +15,24 @@
 //     on the device, so the launch is CUDA-graph safe: the grid depends only on the batch bucket.
 //
 // head_dim is 128 (all Qwen3 sizes).  Scores use exp2 with the scale folded into q.
+#include <algorithm>
+
 #include "../include/decode_common.cuh"
 #include "../include/launch.cuh"
 #include "../include/ptx.cuh"
 
 namespace forge {
+
+// A context length the block table (and the partial buffers) cannot describe is a corrupted input: it is clamped, so
+// that every access derived from it stays inside the table and the scratch, and reported through the status word.
+__device__ __forceinline__ int decode_checked_len(const int* __restrict__ context_lens, int b, int cap, unsigned* status) {
+  const int len = context_lens[b];
+  if (len > cap) {
+    set_status(status, kStatusBadIndex);
+    return cap;
+  }
+  return len < 0 ? 0 : len;
+}
 
 template <int G, int TILE>
 __global__ void __launch_bounds__(kDecThreads, decode_ctas_per_sm(G)) decode_attn_kernel(
@@ -42,7 +55,7 @@ __global__ void __launch_bounds__(kDecThreads, decode_ctas_per_sm(G)) decode_att
   const int qh0 = kvh * (nq / nkv) + (blockIdx.x % groups_per_kv) * G;
   const int b = blockIdx.y;
   const int c = blockIdx.z;
-  const int len = context_lens[b];
+  const int len = decode_checked_len(context_lens, b, min(table_width * block_size, max_chunks * chunk), status);
   const int tok_begin = c * chunk;
   if (tok_begin >= len) {                                // uniform for the CTA
     if (c == 0 && threadIdx.x < kD)                      // padding row (length 0): defined output
@@ -144,11 +157,11 @@ __global__ void __launch_bounds__(kDecThreads, decode_ctas_per_sm(G)) decode_att
 // Merge the per-chunk partials of sequences that span more than one chunk.
 __global__ void __launch_bounds__(kD) decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                             const int* __restrict__ context_lens, __nv_bfloat16* __restrict__ out,
-                                                            int nq, int chunk, int max_chunks) {
+                                                            int nq, int chunk, int max_chunks, int cap) {
   pdl_launch_dependents();
   pdl_wait();
   const int b = blockIdx.y, qh = blockIdx.x, d = threadIdx.x;
-  const int len = context_lens[b];
+  const int len = decode_checked_len(context_lens, b, cap, nullptr);      // same clamp as the attention kernel, which reports it
   const int n = (len + chunk - 1) / chunk;
   if (n <= 1) return;
   const size_t base = (static_cast<size_t>(b) * nq + qh) * max_chunks;
@@ -172,11 +185,7 @@ static int launch_decode(const void* q, const void* kc, const void* vc, const in
   constexpr int ring = kDecStages * 2 * kTileBytes;
   constexpr int smem = (ring > merge_bytes ? ring : merge_bytes) + 2 * kDecStages * 8 + 128;
   auto kern = decode_attn_kernel<G, TILE>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
-    attr_set = true;
-  }
+  FORGE_ENSURE_DYN_SMEM(kern, smem);
   const int groups_per_kv = (nq / nkv) / G;
   dim3 grid(nkv * groups_per_kv, B, max_chunks);
   if (launch_kernel(kern, grid, dim3(kDecThreads), smem, stream, 0, static_cast<const __nv_bfloat16*>(q),
@@ -187,7 +196,8 @@ static int launch_decode(const void* q, const void* kc, const void* vc, const in
   if (max_chunks > 1) {
     dim3 g2(nq, B);
     if (launch_kernel(decode_combine_kernel, g2, dim3(kD), 0, stream, 0, static_cast<const float*>(part_o),
-                      static_cast<const float*>(part_ml), lens, static_cast<__nv_bfloat16*>(out), nq, chunk, max_chunks) != cudaSuccess)
+                      static_cast<const float*>(part_ml), lens, static_cast<__nv_bfloat16*>(out), nq, chunk, max_chunks,
+                      std::min(table_width * block_size, max_chunks * chunk)) != cudaSuccess)
       return -5;
   }
   return 0;
@@ -324,7 +334,7 @@ __global__ void __launch_bounds__(kDecThreads, decode_ctas_per_sm(G)) decode_att
   const int n_chunks32 = (B + 31) >> 5;
   for (int ch = warp; ch < n_chunks32; ch += kDecThreads / 32) {
     const int b = ch * 32 + lane;
-    const int len = b < B ? context_lens[b] : 0;
+    const int len = b < B ? decode_checked_len(context_lens, b, table_width * block_size, status) : 0;
     int v = (len + TILE - 1) / TILE;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -406,7 +416,7 @@ __global__ void __launch_bounds__(kDecThreads, decode_ctas_per_sm(G)) decode_att
     const int seg = min(c.n_b - c.t, f1 - f);
     const int kvh = c.h / groups_per_kv;
     const int qh0 = kvh * (nq / nkv) + (c.h % groups_per_kv) * G;
-    const int len = context_lens[c.b];
+    const int len = decode_checked_len(context_lens, c.b, table_width * block_size, nullptr);
     float qr[G][16];
     // the newest token (position len - 1) is not in the cache yet: if this CTA streams the item's last tile, the warp that
     // owns the token's row prepares it now, under the latency of the q loads and the first tiles
@@ -505,11 +515,7 @@ static int launch_decode_flat(const void* q, const void* kc, const void* vc, con
   constexpr int smem = kDecStages * 2 * kTileBytes + decode_merge_floats(G) * 4 + (kFlatMaxSeqs + 1 + 16) * 4 + 16 + 2 * kDecStages * 8 + 128;
   static_assert(smem <= (decode_ctas_per_sm(G) == 2 ? 113 : 227) * 1024, "two CTAs per SM (one for G > 4)");
   auto kern = decode_attn_flat_kernel<G, TILE>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
-    attr_set = true;
-  }
+  FORGE_ENSURE_DYN_SMEM(kern, smem);
   float* part_o = scratch;
   float* part_ml = part_o + static_cast<size_t>(num_ctas) * 2 * G * kD;
   int* cta_meta = reinterpret_cast<int*>(part_ml + static_cast<size_t>(num_ctas) * 2 * G * 2);
@@ -631,6 +637,10 @@ extern "C" int forge_decode_attention_qkv(const void* qkv, int ld_qkv, const voi
 //     same call.  Two calls whose kernels overlap on the GPU (different streams, or a graph branch) race on it;
 //     keep calls on one device ordered.
 //   * No cudaMalloc, cudaFree, or allocating library routine is called on any path.
+//   * `stream` must belong to the device that is current at the call: the array's address and the kernels' shared
+//     memory limit are set up for the current device.
+//   * A context length beyond table_width * block_size or max_chunks * chunk is clamped and reported through
+//     `status` (the bad-index bit, value 4), so a corrupted length can neither read outside the block table nor outside the array.
 // =========================================================================================================
 constexpr size_t kForgeNoAllocScratchFloats = static_cast<size_t>(4) << 20;
 

@@ -257,11 +257,7 @@ extern "C" int forge_prefill_attention(const void* q, const void* kc, const void
   if (forge_make_tmap_2d(&tm_k, kc, rows, kPD, kPD, box_rows, 2) != 0) return -2;
   if (forge_make_tmap_2d(&tm_v, vc, rows, kPD, kPD, box_rows, 2) != 0) return -2;
   constexpr int smem = 2 * kPHalfBytes + 2 * 4 * kPHalfBytes + 64 + 1024;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
-    attr_set = true;
-  }
+  FORGE_ENSURE_DYN_SMEM(prefill_attn_kernel, smem);
   dim3 grid((max_q + kPM - 1) / kPM, nq, num_seqs);
   return launch_kernel(prefill_attn_kernel, grid, dim3(128), smem, stream, 0, tm_q, tm_k, tm_v, cu_q, lens, bt,
                        static_cast<__nv_bfloat16*>(out), nq, nkv, block_size, table_width, num_blocks,

@@ -340,11 +340,7 @@ extern "C" int forge_prefill_attention_umma(const void* q, const void* kc, const
   if (forge_make_tmap_2d(&tm_k, kc, rows, kUD, kUD, kUN, 2) != 0) return -2;
   if (forge_make_tmap_2d(&tm_v, vc, rows, kUD, kUD, kUN, 2) != 0) return -2;
   constexpr int smem = (1 + 2 * kUStages + 2) * kUTile + 256 + 1024;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(prefill_attn_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
-    attr_set = true;
-  }
+  FORGE_ENSURE_DYN_SMEM(prefill_attn_umma_kernel, smem);
   dim3 grid((max_q + kUM - 1) / kUM, nq, num_seqs);
   return launch_kernel(prefill_attn_umma_kernel, grid, dim3(kUThreads), smem, stream, 0, tm_q, tm_k, tm_v, cu_q, lens, bt,
                        static_cast<__nv_bfloat16*>(out), nq, nkv, block_size, table_width, num_blocks,

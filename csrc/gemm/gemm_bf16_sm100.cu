@@ -71,7 +71,8 @@ struct TokCfg {
 template <int BLOCK_C, int kEpi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
-                   __nv_bfloat16* __restrict__ out, int ldo, int m_total, int n_total, int K, int dual_off, unsigned* status) {
+                   __nv_bfloat16* __restrict__ out, int ldo, int m_total, int n_total, int K, int dual_off, unsigned* status,
+                   const TpPush push) {
   using Cfg = TokCfg<BLOCK_C, kEpi>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -229,6 +230,10 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       if (!ok) break;
     }
   }
+
+  // Row-parallel layer under tensor parallelism: `out` is this rank's partial buffer in symmetric memory; the last
+  // CTA of the grid tells every rank that the partial sums are complete.
+  if (push.size > 1) tp_push_done(push, gridDim.x);
 
   tcgen05_fence_before();
   __syncthreads();
@@ -483,27 +488,17 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             const int c = tok0 + static_cast<int>(split) * cpc + lc;
             const int n = r0 + lane * 4;
             if (c < m_total && n < n_total) {
-              // Row-parallel layer under tensor parallelism: this rank's partial sums go straight into slot
-              // [rank] of EVERY rank's buffer (peer stores over NVLink), tile by tile while other CTAs still
-              // compute; the consumer kernel adds the slots up.  Otherwise: a local store.
-              const bool vec_ok = n + 4 <= n_total;
-              if (push.size > 1 && push.mc_slot != nullptr && vec_ok) {
-                // NVLS: one multicast store; the switch writes it into slot [rank] of every rank
-                multimem_st_v2(push.mc_slot + static_cast<size_t>(c) * ldo + n, pack_bf16x2(v.x, v.y), pack_bf16x2(v.z, v.w));
-                continue;
-              }
-              const int ndst = push.size > 1 ? push.size : 1;
-              for (int pd = 0; pd < ndst; ++pd) {
-                __nv_bfloat16* dst = (push.size > 1 ? push.slot[pd] : out) + static_cast<size_t>(c) * ldo + n;
-                if (n + 4 <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0)) {
-                  uint2 pk;
-                  pk.x = pack_bf16x2(v.x, v.y);
-                  pk.y = pack_bf16x2(v.z, v.w);
-                  *reinterpret_cast<uint2*>(dst) = pk;
-                } else {
-                  const float f[4] = {v.x, v.y, v.z, v.w};
-                  for (int j = 0; j < 4 && n + j < n_total; ++j) dst[j] = __float2bfloat16_rn(f[j]);
-                }
+              // Row-parallel layer under tensor parallelism: `out` is this rank's partial buffer in symmetric memory;
+              // the stores are local, the consumer kernels of all ranks pull the sum over NVLink (tp_comm.cuh).
+              __nv_bfloat16* dst = out + static_cast<size_t>(c) * ldo + n;
+              if (n + 4 <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0)) {
+                uint2 pk;
+                pk.x = pack_bf16x2(v.x, v.y);
+                pk.y = pack_bf16x2(v.z, v.w);
+                *reinterpret_cast<uint2*>(dst) = pk;
+              } else {
+                const float f[4] = {v.x, v.y, v.z, v.w};
+                for (int j = 0; j < 4 && n + j < n_total; ++j) dst[j] = __float2bfloat16_rn(f[j]);
               }
             }
           }
@@ -568,17 +563,13 @@ extern "C" int forge_gemm_set_trace(unsigned long long* buf) {
 
 template <int BLOCK_C, int kEpi>
 static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int ldw, __nv_bfloat16* out, int ldo, int M,
-                         int n_out, int K, unsigned* status, cudaStream_t stream) {
+                         int n_out, int K, unsigned* status, cudaStream_t stream, const TpPush& push) {
   using Cfg = TokCfg<BLOCK_C, kEpi>;
   CUtensorMap tm_x, tm_w;
   if (forge_make_tmap_2d(&tm_x, x, M, K, ldx, kBlockR, 2) != 0) return -2;
   if (forge_make_tmap_2d(&tm_w, w, w_rows, K, ldw, BLOCK_C, 2) != 0) return -3;
   auto kern = gemm_tokens_kernel<BLOCK_C, kEpi>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return -4;
-    attr_set = true;
-  }
+  FORGE_ENSURE_DYN_SMEM(kern, Cfg::kSmemBytes);
   const int tiles = ((M + kBlockR - 1) / kBlockR) * ((n_out + BLOCK_C - 1) / BLOCK_C);
   static int num_sms = 0;
   if (num_sms == 0) {
@@ -588,7 +579,7 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
   }
   dim3 grid(tiles < num_sms ? tiles : num_sms);
   return launch_kernel(kern, grid, dim3(kGemmThreads), Cfg::kSmemBytes, stream, 0, tm_x, tm_w, out, ldo, M, n_out, K, n_out,
-                       status) == cudaSuccess ? 0 : -5;
+                       status, push) == cudaSuccess ? 0 : -5;
 }
 
 // Cluster size (K splits) of the decode kernel.  Measured on B200 (sweeps over token tile x splits x ring depth for
@@ -619,11 +610,7 @@ static int launch_weights(const void* x, int ldx, const void* w, int w_rows, int
   if (forge_make_tmap_2d(&tm_w, w, w_rows, K, ldw, kBlockR, 2) != 0) return -2;
   if (forge_make_tmap_2d(&tm_x, x, M, K, ldx, BLOCK_C, 2) != 0) return -3;
   auto kern = gemm_weights_kernel<BLOCK_C, kEpi, kDeep>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return -4;
-    attr_set = true;
-  }
+  FORGE_ENSURE_DYN_SMEM(kern, Cfg::kSmemBytes);
   const int tiles = (n_out + kBlockR - 1) / kBlockR;
   const int tok_tiles = (M + BLOCK_C - 1) / BLOCK_C;
   const int num_kb = (K + kBlockK - 1) / kBlockK;
@@ -638,7 +625,7 @@ static int launch_weights(const void* x, int ldx, const void* w, int w_rows, int
 // tune: 0 auto; else bits 0..7 = cluster size (K splits), bits 8..15 = token tile (16/32/64/128) of the decode
 // kernel, bits 16..23 = ring depth (1 = two CTAs per SM, 2 = deep ring); each may be 0 = choose.  Returns 0 on success.
 TpPush make_tp_push(int tp_size, int tp_rank, const long long* slot_ptrs, const long long* signal_ptrs, unsigned* arrive,
-                    unsigned* epoch, long long mc_slot = 0);
+                    unsigned* epoch);
 
 static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K, int epi,
                          int force_mode, int tune, unsigned* status, cudaStream_t stream, const TpPush& push) {
@@ -711,12 +698,11 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
 #undef FORGE_W2
     return -6;
   }
-  if (push.size > 1) return -8;   // the token-tile kernel has no push epilogue; callers use the library collective there
   if (force_mode == 1 && (force_bc == 16 || force_bc == 32 || force_bc == 64)) {       // narrow feature tiles: many tokens of a decode step
 #define FORGE_T(BC)                                                                                                           \
   case BC:                                                                                                                    \
-    return epi == kEpiSiluMul ? launch_tokens<BC, kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream)   \
-                              : launch_tokens<BC, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream);
+    return epi == kEpiSiluMul ? launch_tokens<BC, kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push)   \
+                              : launch_tokens<BC, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push);
     switch (force_bc) {
       FORGE_T(16)
       FORGE_T(32)
@@ -724,9 +710,9 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
     }
 #undef FORGE_T
   }
-  if (epi == kEpiSiluMul) return launch_tokens<128, kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream);
-  if (n_out % 256 == 0 || n_out >= 1024) return launch_tokens<256, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream);
-  return launch_tokens<128, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream);
+  if (epi == kEpiSiluMul) return launch_tokens<128, kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push);
+  if (n_out % 256 == 0 || n_out >= 1024) return launch_tokens<256, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push);
+  return launch_tokens<128, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push);
 }
 
 extern "C" int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out,
@@ -735,16 +721,15 @@ extern "C" int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, v
   return gemm_dispatch(x, ldx, w, ldw, out, ldo, M, n_out, K, epi, force_mode, tune, status, stream, none);
 }
 
-// Row-parallel GEMM whose epilogue pushes the partial sums into slot [tp_rank] of every rank's buffer and signals
-// completion (decode kernel only, M <= 256).  slot_ptrs / signal_ptrs: tp_size addresses in peer order.
-// The row stride of the slots is n_out.
-extern "C" int forge_gemm_bf16_tp_push(const void* x, int ldx, const void* w, int ldw, int M, int n_out, int K, int tune,
-                                       int tp_size, int tp_rank, const long long* slot_ptrs, const long long* signal_ptrs,
-                                       unsigned* arrive, unsigned* epoch, long long mc_slot, unsigned* status, cudaStream_t stream) {
-  if (tp_size < 2 || tp_size > kMaxTp || M > 256) return -7;
-  if (mc_slot != 0 && (n_out & 3)) mc_slot = 0;       // the multicast store writes four features at a time
-  const TpPush push = make_tp_push(tp_size, tp_rank, slot_ptrs, signal_ptrs, arrive, epoch, mc_slot);
-  return gemm_dispatch(x, ldx, w, ldw, nullptr, n_out, M, n_out, K, kEpiStore, 2, tune, status, stream, push);
+// Row-parallel GEMM under tensor parallelism: `out` is this rank's partial buffer in symmetric memory (row stride ldo);
+// the kernel's last CTA announces completion to every rank through signal_ptrs (tp_size addresses in peer order).
+// Up to 256 rows run on the weight-tile (decode) kernel, more on the persistent token-tile kernel.
+extern "C" int forge_gemm_bf16_tp(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K,
+                                  int tune, int tp_size, int tp_rank, const long long* signal_ptrs, unsigned* arrive,
+                                  unsigned* epoch, unsigned* status, cudaStream_t stream) {
+  if (tp_size < 2 || tp_size > kMaxTp || M <= 0) return -7;
+  const TpPush push = make_tp_push(tp_size, tp_rank, nullptr, signal_ptrs, arrive, epoch);
+  return gemm_dispatch(x, ldx, w, ldw, out, ldo, M, n_out, K, kEpiStore, M <= 256 ? 2 : 1, tune, status, stream, push);
 }
 
 }  // namespace forge

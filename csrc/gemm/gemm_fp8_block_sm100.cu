@@ -233,11 +233,7 @@ static int launch_f8(const void* xq, const float* xs, int xs_ld, const void* wq,
   if (forge_make_tmap_2d(&tm_w, wq, N, K, K, kF8BlockR, 1) != 0) return -2;
   if (forge_make_tmap_2d(&tm_x, xq, M, K, K, BLOCK_C, 1) != 0) return -3;
   auto kern = gemm_fp8_block_kernel<BLOCK_C>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return -4;
-    attr_set = true;
-  }
+  FORGE_ENSURE_DYN_SMEM(kern, Cfg::kSmemBytes);
   const int num_kb = K / kF8BlockK;
   const int kb_per_split = (num_kb + splits - 1) / splits;
   dim3 grid((N + kF8BlockR - 1) / kF8BlockR, (M + BLOCK_C - 1) / BLOCK_C, splits);

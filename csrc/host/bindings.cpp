@@ -15,21 +15,27 @@ int forge_quant_fp8_1x128(const void* x, void* xq, float* scale, int M, int K, i
 int forge_gemm_fp8_splits(int M, int N, int K);
 int forge_gemm_fp8_block(const void* xq, const float* xs, int xs_ld, const void* wq, const float* ws, void* out, int ldo, int M,
                          int N, int K, float* partial, unsigned* status, cudaStream_t stream);
-int forge_gemm_bf16_tp_push(const void* x, int ldx, const void* w, int ldw, int M, int n_out, int K, int tune, int tp_size,
-                            int tp_rank, const long long* slot_ptrs, const long long* signal_ptrs, unsigned* arrive,
-                            unsigned* epoch, long long mc_slot, unsigned* status, cudaStream_t stream);
-int forge_tp_reduce_rms_norm(int tp_size, int num_slots, const void* slots, long long slot_stride, const unsigned* signal,
-                             const unsigned* epoch, long long timeout_ns, const void* residual_in, void* sum_out, const void* w,
-                             void* y, int rows, int H, float eps, unsigned* status, cudaStream_t stream);
+int forge_gemm_bf16_tp(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K, int tune,
+                       int tp_size, int tp_rank, const long long* signal_ptrs, unsigned* arrive, unsigned* epoch, unsigned* status,
+                       cudaStream_t stream);
+int forge_tp_reduce_rms_norm(int tp_size, int tp_rank, const long long* part_ptrs, long long mc_part, const void* slots,
+                             const unsigned* signal, const unsigned* epoch, long long timeout_ns, const unsigned* local_only,
+                             const void* residual_in, void* sum_out, const void* w, void* y, int rows, int H, float eps,
+                             unsigned* status, cudaStream_t stream);
+int forge_tp_rs_norm_ag(int tp_size, int tp_rank, const long long* part_ptrs, long long mc_part, const unsigned* signal1,
+                        const unsigned* epoch1, const long long* y_ptrs, long long mc_y, const long long* signal_ptrs2,
+                        unsigned* arrive2, unsigned* epoch2, const unsigned* signal2, long long timeout_ns,
+                        const unsigned* local_only, const void* residual_in, void* residual_out, const void* w, int rows, int H,
+                        float eps, unsigned* status, cudaStream_t stream);
 int forge_tp_embedding_push(const int* ids, const void* w, int T, int H, int vocab_start, int vocab_n, int tp_size, int tp_rank,
                             const long long* slot_ptrs, const long long* signal_ptrs, unsigned* arrive, unsigned* epoch,
                             cudaStream_t stream);
-int forge_tp_rows_push(const void* src, int rows, int H, int tp_size, int tp_rank, const long long* slot_ptrs,
-                       const long long* signal_ptrs, unsigned* arrive, unsigned* epoch, cudaStream_t stream);
+int forge_tp_rows_publish(const void* src, void* part, int rows, int H, int tp_size, int tp_rank, const long long* signal_ptrs,
+                          unsigned* arrive, unsigned* epoch, cudaStream_t stream);
 int forge_tp_sample_pairs(const float* vals, const int* ids, int rows, int tp_size, int tp_rank, const long long* slot_ptrs,
                           const long long* signal_ptrs, unsigned* arrive, unsigned* epoch, const void* local_slots,
-                          long long slot_stride, const unsigned* signal_local, long long timeout_ns, int* out_i, unsigned* status,
-                          cudaStream_t stream);
+                          long long slot_stride, const unsigned* signal_local, long long timeout_ns, const unsigned* local_only,
+                          int* out_i, unsigned* status, cudaStream_t stream);
 int forge_rms_norm(const void* x, void* residual, const void* w, void* y, int rows, int H, float eps, cudaStream_t stream);
 int forge_qk_norm_rope_store(const void* qkv, int ld_qkv, const void* qw, const void* kw, float eps, const float* rope,
                              int rope_rows, const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache,
@@ -384,31 +390,39 @@ void gemm_fp8_block(const Tensor& xq, const Tensor& xs, const Tensor& wq, const 
 
 // ---- tensor-parallel exchange.  A "site" is described by plain integers (addresses inside the symmetric
 // allocation, resolved once in Python): slot_ptrs[p] / signal_ptrs[p] = where THIS rank writes in peer p;
-// local_slots / local_signal = where this rank reads; arrive / epoch = two private device words.
+// part_ptrs[p] / y_ptrs[p] = rank p's copy of a buffer; mc_* = multicast address of a buffer (0: none);
+// local_slots / local_signal = where this rank reads; arrive / epoch = two private device words;
+// local_only = address of the device word that switches the measurement mode on (see tp_comm.cuh).
 using PtrList = std::vector<int64_t>;
 
 const long long* ptrs(const PtrList& v) { return reinterpret_cast<const long long*>(v.data()); }
 unsigned* word(int64_t addr) { return reinterpret_cast<unsigned*>(addr); }
 
-void gemm_tp_push(const Tensor& x, const Tensor& w, int64_t tune, int64_t tp_rank, const PtrList& slot_ptrs,
-                  const PtrList& signal_ptrs, int64_t arrive, int64_t epoch, int64_t mc_slot, const Tensor& status) {
+// Row-parallel GEMM under tensor parallelism: `part` is this rank's partial buffer inside the symmetric region (an
+// address, row stride = w.size(0)); the kernel's last CTA signals every rank.
+void gemm_tp(const Tensor& x, const Tensor& w, int64_t part, int64_t tune, int64_t tp_rank, const PtrList& signal_ptrs,
+             int64_t arrive, int64_t epoch, const Tensor& status) {
   CHECK_BF16(x); CHECK_BF16(w);
-  TORCH_CHECK(x.is_cuda() && w.is_cuda() && x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1, "gemm_tp_push: operands");
-  TORCH_CHECK(w.size(1) == x.size(1) && slot_ptrs.size() == signal_ptrs.size() && slot_ptrs.size() >= 2, "gemm_tp_push: shapes");
+  TORCH_CHECK(x.is_cuda() && w.is_cuda() && x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1, "gemm_tp: operands");
+  TORCH_CHECK(w.size(1) == x.size(1) && signal_ptrs.size() >= 2 && part != 0 && (part & 15) == 0, "gemm_tp: shapes");
   const c10::cuda::CUDAGuard guard(x.device());
-  check(forge_gemm_bf16_tp_push(x.data_ptr(), static_cast<int>(x.stride(0)), w.data_ptr(), static_cast<int>(w.stride(0)),
-                                static_cast<int>(x.size(0)), static_cast<int>(w.size(0)), static_cast<int>(x.size(1)),
-                                static_cast<int>(tune), static_cast<int>(slot_ptrs.size()), static_cast<int>(tp_rank),
-                                ptrs(slot_ptrs), ptrs(signal_ptrs), word(arrive), word(epoch), mc_slot, status_ptr(status), stream_of(x)),
-        "forge_gemm_bf16_tp_push");
+  check(forge_gemm_bf16_tp(x.data_ptr(), static_cast<int>(x.stride(0)), w.data_ptr(), static_cast<int>(w.stride(0)),
+                           reinterpret_cast<void*>(part), static_cast<int>(w.size(0)), static_cast<int>(x.size(0)),
+                           static_cast<int>(w.size(0)), static_cast<int>(x.size(1)), static_cast<int>(tune),
+                           static_cast<int>(signal_ptrs.size()), static_cast<int>(tp_rank), ptrs(signal_ptrs), word(arrive),
+                           word(epoch), status_ptr(status), stream_of(x)),
+        "forge_gemm_bf16_tp");
 }
 
-// sum_out = sum over slots (+ residual_in); y = rms_norm(sum_out) * w when y is given.
-void tp_reduce_rms_norm(int64_t tp_size, int64_t num_slots, int64_t local_slots, int64_t slot_stride, int64_t local_signal,
-                        int64_t epoch, int64_t timeout_ns, const c10::optional<Tensor>& residual_in, Tensor& sum_out,
-                        const c10::optional<Tensor>& w, const c10::optional<Tensor>& y, double eps, const Tensor& status) {
+// sum_out = sum over ranks of the partial rows (+ residual_in); y = rms_norm(sum_out) * w when y is given.
+// part_ptrs empty: the rows were written into `slots` (a local address) by their owners and are only copied.
+void tp_reduce_rms_norm(int64_t tp_size, int64_t tp_rank, const PtrList& part_ptrs, int64_t mc_part, int64_t slots,
+                        int64_t local_signal, int64_t epoch, int64_t timeout_ns, int64_t local_only,
+                        const c10::optional<Tensor>& residual_in, Tensor& sum_out, const c10::optional<Tensor>& w,
+                        const c10::optional<Tensor>& y, double eps, const Tensor& status) {
   CHECK_CUDA_CONTIG(sum_out); CHECK_BF16(sum_out);
   const int64_t H = sum_out.size(-1), rows = sum_out.numel() / H;
+  TORCH_CHECK(part_ptrs.empty() || static_cast<int64_t>(part_ptrs.size()) == tp_size, "tp_reduce_rms_norm: one partial buffer per rank");
   const void* res = nullptr; const void* wp = nullptr; void* yp = nullptr;
   if (residual_in.has_value()) { CHECK_CUDA_CONTIG(*residual_in); CHECK_BF16(*residual_in); TORCH_CHECK(residual_in->numel() == sum_out.numel()); res = residual_in->data_ptr(); }
   if (y.has_value()) {
@@ -418,11 +432,31 @@ void tp_reduce_rms_norm(int64_t tp_size, int64_t num_slots, int64_t local_slots,
     wp = w->data_ptr(); yp = y->data_ptr();
   }
   const c10::cuda::CUDAGuard guard(sum_out.device());
-  check(forge_tp_reduce_rms_norm(static_cast<int>(tp_size), static_cast<int>(num_slots), reinterpret_cast<const void*>(local_slots),
-                                 slot_stride, word(local_signal), word(epoch), timeout_ns, res, sum_out.data_ptr(), wp, yp,
-                                 static_cast<int>(rows), static_cast<int>(H), static_cast<float>(eps), status_ptr(status),
-                                 stream_of(sum_out)),
+  check(forge_tp_reduce_rms_norm(static_cast<int>(tp_size), static_cast<int>(tp_rank), part_ptrs.empty() ? nullptr : ptrs(part_ptrs),
+                                 mc_part, reinterpret_cast<const void*>(slots), word(local_signal), word(epoch), timeout_ns,
+                                 word(local_only), res, sum_out.data_ptr(), wp, yp, static_cast<int>(rows), static_cast<int>(H),
+                                 static_cast<float>(eps), status_ptr(status), stream_of(sum_out)),
         "forge_tp_reduce_rms_norm");
+}
+
+// Two-shot exchange: reduce-scatter by rows + residual add + RMSNorm on this rank's rows + all-gather of the normalised
+// rows into every rank's broadcast buffer (y_ptrs / mc_y).  `residual` is updated in place on this rank's rows only.
+void tp_rs_norm_ag(int64_t tp_rank, const PtrList& part_ptrs, int64_t mc_part, int64_t signal1, int64_t epoch1,
+                   const PtrList& y_ptrs, int64_t mc_y, const PtrList& signal_ptrs2, int64_t arrive2, int64_t epoch2,
+                   int64_t signal2, int64_t timeout_ns, int64_t local_only, const c10::optional<Tensor>& residual_in,
+                   Tensor& residual_out, const Tensor& w, double eps, const Tensor& status) {
+  CHECK_CUDA_CONTIG(residual_out); CHECK_BF16(residual_out); CHECK_CUDA_CONTIG(w); CHECK_BF16(w);
+  const int64_t H = residual_out.size(-1), rows = residual_out.numel() / H;
+  TORCH_CHECK(part_ptrs.size() >= 2 && y_ptrs.size() == part_ptrs.size() && signal_ptrs2.size() == part_ptrs.size() && w.numel() == H,
+              "tp_rs_norm_ag: shapes");
+  const void* res = nullptr;
+  if (residual_in.has_value()) { CHECK_CUDA_CONTIG(*residual_in); CHECK_BF16(*residual_in); TORCH_CHECK(residual_in->numel() == residual_out.numel()); res = residual_in->data_ptr(); }
+  const c10::cuda::CUDAGuard guard(residual_out.device());
+  check(forge_tp_rs_norm_ag(static_cast<int>(part_ptrs.size()), static_cast<int>(tp_rank), ptrs(part_ptrs), mc_part, word(signal1),
+                            word(epoch1), ptrs(y_ptrs), mc_y, ptrs(signal_ptrs2), word(arrive2), word(epoch2), word(signal2),
+                            timeout_ns, word(local_only), res, residual_out.data_ptr(), w.data_ptr(), static_cast<int>(rows),
+                            static_cast<int>(H), static_cast<float>(eps), status_ptr(status), stream_of(residual_out)),
+        "forge_tp_rs_norm_ag");
 }
 
 void tp_embedding_push(const Tensor& ids, const Tensor& w, int64_t vocab_start, int64_t tp_rank, const PtrList& slot_ptrs,
@@ -435,26 +469,27 @@ void tp_embedding_push(const Tensor& ids, const Tensor& w, int64_t vocab_start, 
         "forge_tp_embedding_push");
 }
 
-void tp_rows_push(const Tensor& src, int64_t tp_rank, const PtrList& slot_ptrs, const PtrList& signal_ptrs, int64_t arrive,
-                  int64_t epoch) {
+void tp_rows_publish(const Tensor& src, int64_t part, int64_t tp_rank, const PtrList& signal_ptrs, int64_t arrive, int64_t epoch) {
   CHECK_CUDA_CONTIG(src); CHECK_BF16(src);
   const int64_t H = src.size(-1), rows = src.numel() / H;
+  TORCH_CHECK(part != 0 && (part & 15) == 0, "tp_rows_publish: partial buffer address");
   const c10::cuda::CUDAGuard guard(src.device());
-  check(forge_tp_rows_push(src.data_ptr(), static_cast<int>(rows), static_cast<int>(H), static_cast<int>(slot_ptrs.size()),
-                           static_cast<int>(tp_rank), ptrs(slot_ptrs), ptrs(signal_ptrs), word(arrive), word(epoch), stream_of(src)),
-        "forge_tp_rows_push");
+  check(forge_tp_rows_publish(src.data_ptr(), reinterpret_cast<void*>(part), static_cast<int>(rows), static_cast<int>(H),
+                              static_cast<int>(signal_ptrs.size()), static_cast<int>(tp_rank), ptrs(signal_ptrs), word(arrive),
+                              word(epoch), stream_of(src)),
+        "forge_tp_rows_publish");
 }
 
 void tp_sample_pairs(const Tensor& vals, const Tensor& ids, int64_t tp_rank, const PtrList& slot_ptrs, const PtrList& signal_ptrs,
                      int64_t arrive, int64_t epoch, int64_t local_slots, int64_t slot_stride, int64_t local_signal,
-                     int64_t timeout_ns, Tensor& out_i, const Tensor& status) {
+                     int64_t timeout_ns, int64_t local_only, Tensor& out_i, const Tensor& status) {
   CHECK_CUDA_CONTIG(vals); CHECK_F32(vals); CHECK_CUDA_CONTIG(ids); CHECK_I32(ids); CHECK_CUDA_CONTIG(out_i); CHECK_I32(out_i);
   TORCH_CHECK(ids.numel() == vals.numel() && out_i.numel() >= vals.numel(), "tp_sample_pairs: lengths");
   const c10::cuda::CUDAGuard guard(vals.device());
   check(forge_tp_sample_pairs(vals.data_ptr<float>(), ids.data_ptr<int>(), static_cast<int>(vals.numel()),
                               static_cast<int>(slot_ptrs.size()), static_cast<int>(tp_rank), ptrs(slot_ptrs), ptrs(signal_ptrs),
                               word(arrive), word(epoch), reinterpret_cast<const void*>(local_slots), slot_stride, word(local_signal),
-                              timeout_ns, out_i.data_ptr<int>(), status_ptr(status), stream_of(vals)),
+                              timeout_ns, word(local_only), out_i.data_ptr<int>(), status_ptr(status), stream_of(vals)),
         "forge_tp_sample_pairs");
 }
 
@@ -467,10 +502,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("quant_fp8", &quant_fp8);
   m.def("gemm_fp8_block", &gemm_fp8_block);
   m.def("gemm_fp8_splits", &gemm_fp8_splits);
-  m.def("gemm_tp_push", &gemm_tp_push);
+  m.def("gemm_tp", &gemm_tp);
   m.def("tp_reduce_rms_norm", &tp_reduce_rms_norm);
   m.def("tp_embedding_push", &tp_embedding_push);
-  m.def("tp_rows_push", &tp_rows_push);
+  m.def("tp_rows_publish", &tp_rows_publish);
+  m.def("tp_rs_norm_ag", &tp_rs_norm_ag);
   m.def("tp_sample_pairs", &tp_sample_pairs);
   m.def("rms_norm", &rms_norm);
   m.def("qk_norm_rope_store", &qk_norm_rope_store);

@@ -13,6 +13,10 @@
  *     before any stream capture begins.
  *   - Calls on one device share the array: keep them ordered (same stream); overlapping calls race.
  *   - Nothing is allocated or freed on any path.
+ *   - `stream` must belong to the device that is current at the call (the array's address and the kernels'
+ *     shared-memory limit are resolved for the current device).
+ *   - A context length that the block table or the slices cannot describe (greater than table_width * block_size
+ *     or max_chunks * chunk) is clamped and reported through `status` (the bad-index bit, value 4); nothing is read out of range.
  *
  * Tensors (all device pointers, bf16 unless noted):
  *   q [B, nq, 128]; k_cache, v_cache [num_blocks, nkv, block_size, 128]; block_tables int32 [B, table_width];

@@ -27,6 +27,19 @@ inline bool pdl_enabled() {
   return v == 1;
 }
 
+// The dynamic shared memory limit of a kernel is a per-DEVICE attribute: raise it once per (call site, device), so a
+// process that drives several GPUs gets it on each of them.  Used inside launchers that return an int code (-4 on failure).
+#define FORGE_ENSURE_DYN_SMEM(kern, bytes)                                                                              \
+  do {                                                                                                                  \
+    static bool forge_attr_set[64] = {};                                                                                \
+    int forge_dev = 0;                                                                                                  \
+    if (cudaGetDevice(&forge_dev) != cudaSuccess || forge_dev < 0 || forge_dev >= 64) return -4;                        \
+    if (!forge_attr_set[forge_dev]) {                                                                                   \
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return -4;     \
+      forge_attr_set[forge_dev] = true;                                                                                 \
+    }                                                                                                                   \
+  } while (0)
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                  int cluster_y, Args... args) {

@@ -5,8 +5,8 @@ the reference has) and tinyvllm/engine/llm_engine.py:18-20 (built from the
 keyword arguments of ``LLM``).  Differences, all deliberate:
 
 * unknown keyword arguments raise instead of being dropped silently;
-* the KV block size may be any power of two >= 8 (the reference's flash-attn
-  call needs a multiple of 256; the attention kernels here do not);
+* the KV block size may be any power of two >= 16 on the GPU and >= 8 on the CPU
+  path (the reference's flash-attn call needs a multiple of 256);
 * ``config.json`` is parsed directly into :class:`ModelConfig`, so building an
   engine does not import ``transformers``;
 * extra optional fields: ``seed``, ``dtype``, ``device``, ``comm``,
@@ -167,6 +167,7 @@ class Config:
     load_format: str = "auto"                # "auto": read *.safetensors; "dummy": seeded N(0, 0.02) weights
     skip_tokenizer_init: bool = False
     rpc_timeout_s: float = 120.0             # bound on every control-plane wait between ranks
+    comm_timeout_s: float = 10.0             # bound on every device-side wait for a peer's flag (comm="fused")
     trace_path: Optional[str] = None         # per-step JSONL trace
     chunked_prefill: bool = False            # prompts longer than max_num_batched_tokens are prefilled over several steps
     extra: dict = field(default_factory=dict)
@@ -198,6 +199,10 @@ class Config:
             self.device = "cuda" if torch.cuda.is_available() else "cpu"
         if self.device not in ("cuda", "cpu"):
             raise ValueError(f"device must be 'cuda' or 'cpu', got {self.device!r}")
+        if self.device == "cuda" and bs < 16:
+            raise ValueError(f"kvcache_block_size must be >= 16 on the GPU (the attention kernels' smallest tile), got {bs}")
+        if not self.comm_timeout_s > 0:
+            raise ValueError("comm_timeout_s must be positive")
         if self.comm not in ("fused", "nccl"):
             raise ValueError("comm must be 'fused' or 'nccl'")
         if self.quantization not in (None, "fp8_block"):

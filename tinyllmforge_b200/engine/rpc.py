@@ -51,7 +51,7 @@ def unique_name(prefix: str = "tlf") -> str:
 class ShmChannel:
     def __init__(self, name: str, world_size: int, rank: int, create: bool, capacity: int = 8 << 20,
                  timeout_s: float = 120.0):
-        assert world_size <= 12
+        assert world_size <= 8       # status words [16 + r] and pid words [24 + r] must not overlap
         self.name, self.world_size, self.rank, self.timeout_s = name, world_size, rank, timeout_s
         self.owner = create
         if create:

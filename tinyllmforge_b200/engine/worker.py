@@ -92,7 +92,7 @@ class Worker:
                     for lin in (l.qkv_proj, l.o_proj, l.gate_up_proj, l.down_proj):
                         lin.weight = Fp8BlockWeight.quantize(lin.weight)
             if self.is_cuda and tp.size > 1 and config.comm == "fused":
-                ops.enable_fused_comm(hf.hidden_size, config.max_num_batched_tokens)
+                ops.enable_fused_comm(hf.hidden_size, config.max_num_batched_tokens, config.comm_timeout_s)
             # staging: the largest step is a full prefill (3 token-sized sections) or the widest decode bucket
             max_seqs = config.max_num_seqs
             _, words_prefill = section_offsets(config.max_num_batched_tokens, max_seqs, self.table_width)
@@ -101,7 +101,9 @@ class Worker:
                 # two staging buffers: the host fills one while the copy out of the other may still be in flight
                 self.host_words = [torch.empty(self.max_words, dtype=torch.int32, pin_memory=True) for _ in range(2)]
                 self.dev_words = torch.zeros(self.max_words, dtype=torch.int32, device=self.device)
-                self.host_tokens = [torch.empty(max(max_seqs, 512), dtype=torch.int32, pin_memory=True) for _ in range(2)]
+                # sampled tokens of a step, followed by one word that receives the kernels' status word of that step
+                self.status_slot = max(max_seqs, 512)
+                self.host_tokens = [torch.zeros(self.status_slot + 1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
                 self.prev_tokens_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
             self._allocate_kv_cache()
             if self.buckets:
@@ -114,6 +116,7 @@ class Worker:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.kernel_launches = 0
+        self.step_times: list[tuple[bool, int, int, float]] = []      # (is_prefill, sequences, tokens, device ms) per timed step
         if getattr(self, "ops", None) is not None and hasattr(self.ops, "launches"):
             self.ops.launches = 0
 
@@ -225,13 +228,14 @@ class Worker:
         self.prev_tokens_dev = tokens                  # stays on the device: the next step may take its inputs from here
         host = self.host_tokens[self.num_steps & 1]
         host[:n].copy_(tokens[:n], non_blocking=True)
+        # the status word of the kernels travels with the tokens: every step is checked, and the check costs no sync
+        host[self.status_slot:].copy_(self.ops.status[:1], non_blocking=True)
         done = torch.cuda.Event(enable_timing=timed)
         done.record()
         self.h2d_bytes += sb.nbytes
-        self.d2h_bytes += n * 4
+        self.d2h_bytes += n * 4 + 4
         self.num_steps += 1
-        check = sb.is_prefill or (self.num_steps & 127) == 0
-        return ("cuda", host, n, e0, done, check)
+        return ("cuda", host, n, e0, done, (sb.is_prefill, sb.num_seqs, sb.num_tokens))
 
     @staticmethod
     def feed_rows(sb: StepBatch) -> bool:
@@ -241,12 +245,15 @@ class Worker:
         """Wait for a launched step; returns the sampled token of each of its sequences."""
         if ticket[0] == "cpu":
             return ticket[1]
-        _, host, n, e0, done, check = ticket
+        _, host, n, e0, done, shape = ticket
         done.synchronize()
         if e0 is not None:
-            self.device_ms += e0.elapsed_time(done)
-        if check:
-            self.ops.check_status()
+            ms = e0.elapsed_time(done)
+            self.device_ms += ms
+            self.step_times.append((shape[0], shape[1], shape[2], ms))
+        word = int(host[self.status_slot])
+        if word:
+            self.ops.raise_status(word)
         return host[:n].tolist() if self.rank == 0 else []
 
     def run(self, sb: StepBatch) -> list[int]:

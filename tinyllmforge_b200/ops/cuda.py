@@ -60,13 +60,12 @@ def decode_group_slice(group: int) -> int:
 class CudaOps:
     name = "cuda"
 
-    def __init__(self, config: Config | None = None, tp: TPGroup | None = None, device=None, use_cublas_gemm: bool = False):
+    def __init__(self, config: Config | None = None, tp: TPGroup | None = None, device=None):
         self.C = require_ext()
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.tp = tp or TPGroup()
         self.max_model_len = config.max_model_len if config is not None else 4096
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
-        self.use_cublas_gemm = use_cublas_gemm     # bring-up switch for tests; never set by the engine
         self.launches = 0                          # kernels of this library launched so far
         self.fused = None                          # FusedTPComm once enable_fused_comm() ran
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
@@ -83,9 +82,13 @@ class CudaOps:
         """Raise if any kernel since the last check recorded an error (costs a device sync)."""
         word = int(self.status[0].item())
         if word:
-            self.status.zero_()
-            what = [txt for bit, txt in STATUS_BITS.items() if word & bit]
-            raise RuntimeError(f"a CUDA kernel reported: {', '.join(what) or hex(word)}")
+            self.raise_status(word)
+
+    def raise_status(self, word: int) -> None:
+        """Turn a non-zero status word (already read back) into an exception and clear the device copy."""
+        self.status.zero_()
+        what = [txt for bit, txt in STATUS_BITS.items() if word & bit]
+        raise RuntimeError(f"a CUDA kernel reported: {', '.join(what) or hex(word)}")
 
     # ------------------------------------------------------------------ GEMMs
     def linear(self, x: torch.Tensor, w: torch.Tensor, force_mode: int = 0, force_splits: int = 0,
@@ -95,8 +98,6 @@ class CudaOps:
         if isinstance(w, Fp8BlockWeight):
             return self.linear_fp8(x, w)
         out = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
-        if self.use_cublas_gemm:
-            return torch.matmul(x, w.t(), out=out)
         self.C.gemm(x, w, out, 0, force_mode, force_splits | (force_block_c << 8) | (force_deep << 16), self.status)
         self.launches += 1
         return out
@@ -106,10 +107,6 @@ class CudaOps:
         if isinstance(w_gate_up, Fp8BlockWeight):
             return self.silu_mul(self.linear_fp8(x, w_gate_up))
         out = torch.empty(x.shape[0], w_gate_up.shape[0] // 2, dtype=x.dtype, device=x.device)
-        if self.use_cublas_gemm:
-            tmp = torch.matmul(x, w_gate_up.t())
-            self.C.silu_mul(tmp, out)
-            return out
         self.C.gemm(x, w_gate_up, out, 1, force_mode, force_splits | (force_block_c << 8) | (force_deep << 16), self.status)
         self.launches += 1
         return out
@@ -231,33 +228,51 @@ class CudaOps:
 
     # ------------------------------------------------------------------ tensor-parallel exchange
     def tp_all_reduce(self, y, tp):
-        """Library collective (NCCL): the baseline path and the path of steps too large for the push buffers."""
+        """Library collective (NCCL): the baseline path (``comm="nccl"``)."""
         return tp.all_reduce(y)
 
-    def enable_fused_comm(self, hidden_size: int, max_tokens: int) -> None:
+    def enable_fused_comm(self, hidden_size: int, max_tokens: int, timeout_s: float = 10.0) -> None:
         """Allocate the symmetric region; afterwards row-parallel layers, the embedding and the sampler exchange
         data from inside their kernels."""
         from ..parallel.symm import FusedTPComm
-        self.fused = FusedTPComm(self.tp, hidden_size, max_tokens, self.device)
+        self.fused = FusedTPComm(self.tp, hidden_size, max_tokens, self.device, timeout_s)
+
+    def _reduce_norm(self, st, rows, H, residual_in, residual_out, norm_weight, eps):
+        """Consumer half of a row-parallel exchange whose partial sums sit in site ``st``'s buffers: one-shot (every rank
+        pulls the sum of all rows) or two-shot (reduce-scatter, norm on this rank's rows, all-gather).  Returns the
+        normalised rows; in the two-shot form they live in the broadcast buffer and ``residual_out`` holds only this
+        rank's rows (rows r, r + tp, ...), which is all the next exchange of the same step reads."""
+        f, tp = self.fused, self.tp
+        self.launches += 1
+        if norm_weight is not None and f.two_shot(rows, H):
+            from ..parallel.symm import SITE_GATHER
+            ag = f.sites[SITE_GATHER]
+            self.C.tp_rs_norm_ag(tp.rank, st.buf_ptrs, st.mc_buf, st.local_signal, st.epoch, ag.buf_ptrs, ag.mc_buf, ag.signal_ptrs,
+                                 ag.arrive, ag.epoch, ag.local_signal, f.timeout_ns, f.local_only, residual_in, residual_out,
+                                 norm_weight, eps, self.status)
+            return f.y_view(rows, H)
+        y = torch.empty(rows, H, dtype=torch.bfloat16, device=self.device) if norm_weight is not None else None
+        self.C.tp_reduce_rms_norm(tp.size, tp.rank, st.buf_ptrs, st.mc_buf, 0, st.local_signal, st.epoch, f.timeout_ns, f.local_only,
+                                  residual_in, residual_out, norm_weight, y, eps, self.status)
+        return y
 
     def fused_all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         """Sum over the ranks of a bf16 tensor of at most 256 x hidden elements (last dimension a multiple of 8) through
-        the symmetric region: one kernel pushes this rank's rows into every rank's slot, one kernel waits for all ranks
-        and adds the slots in rank order (fp32), so every rank gets the same bits.  Larger tensors: library collective."""
-        from ..parallel.symm import MAX_PUSH_ROWS, SITE_ALLREDUCE
+        the symmetric region: one kernel copies this rank's rows into its partial buffer and signals, one kernel waits for
+        all ranks and pulls the sum (in the switch, or with peer loads in rank order).  Larger tensors: library collective."""
+        from ..parallel.symm import MAX_ALLREDUCE_ROWS, SITE_ALLREDUCE
         tp = self.tp
         if tp.size == 1:
             return x
         H = x.shape[-1]
-        if (self.fused is None or x.dtype != torch.bfloat16 or H % 8 or H > 8192 or x.numel() > MAX_PUSH_ROWS * self.fused.hidden):
+        if (self.fused is None or x.dtype != torch.bfloat16 or H % 8 or H > 8192 or x.numel() > MAX_ALLREDUCE_ROWS * self.fused.hidden):
             return tp.all_reduce(x)
         st = self.fused.sites[SITE_ALLREDUCE]
         x = x.contiguous()
         out = torch.empty_like(x)
-        self.C.tp_rows_push(x, tp.rank, st.slot_ptrs, st.signal_ptrs, st.arrive, st.epoch)
-        self.C.tp_reduce_rms_norm(tp.size, tp.size, st.local_slots, st.slot_stride, st.local_signal, st.epoch, self.fused.timeout_ns,
-                                  None, out, None, None, 0.0, self.status)
-        self.launches += 2
+        self.C.tp_rows_publish(x, st.local_buf, tp.rank, st.signal_ptrs, st.arrive, st.epoch)
+        self.launches += 1
+        self._reduce_norm(st, x.numel() // H, H, None, out, None, 0.0)
         return out
 
     def fused_barrier(self) -> None:
@@ -276,11 +291,11 @@ class CudaOps:
             h = tp.all_reduce(self.embedding(ids, embed.weight, embed.vocab_start))
             return self.add_rms_norm(h, None, norm_weight, eps)
         from ..parallel.symm import SITE_EMBED
-        st = self.fused.sites[SITE_EMBED]
-        self.C.tp_embedding_push(ids, embed.weight, embed.vocab_start, tp.rank, st.slot_ptrs, st.signal_ptrs, st.arrive, st.epoch)
+        f, st = self.fused, self.fused.sites[SITE_EMBED]
+        self.C.tp_embedding_push(ids, embed.weight, embed.vocab_start, tp.rank, st.buf_ptrs, st.signal_ptrs, st.arrive, st.epoch)
         residual = torch.empty(T, H, dtype=embed.weight.dtype, device=ids.device)
         y = torch.empty_like(residual)
-        self.C.tp_reduce_rms_norm(tp.size, 1, st.local_slots, st.slot_stride, st.local_signal, st.epoch, self.fused.timeout_ns,
+        self.C.tp_reduce_rms_norm(tp.size, tp.rank, [], 0, st.local_buf, st.local_signal, st.epoch, f.timeout_ns, f.local_only,
                                   None, residual, norm_weight, y, eps, self.status)
         self.launches += 2
         return y, residual
@@ -288,23 +303,24 @@ class CudaOps:
     def row_linear_add_rms_norm(self, x, layer, residual, norm_weight, eps, site):
         """Row-parallel GEMM + sum over ranks + residual add + RMSNorm -> (normed, residual).
 
-        Fused path (decode-sized batches): the GEMM epilogue pushes its partial sums into every rank's slot
-        buffer over NVLink; one consumer kernel waits for all ranks, adds the slots in rank order, adds the
-        residual and normalises.  Larger batches: GEMM, NCCL all-reduce, add + RMSNorm."""
+        Fused path: the GEMM stores its partial sums into this rank's buffer of the symmetric region and its last CTA
+        signals every rank; one consumer kernel waits for all ranks, pulls the sum over NVLink (one-shot for few bytes,
+        reduce-scatter + all-gather for many, see ``_reduce_norm``), adds the residual and normalises.  No library
+        collective is involved at any batch size."""
         tp = layer.tp
         if tp.size == 1:
             return self.add_rms_norm(self.linear(x, layer.weight), residual, norm_weight, eps)
-        M = x.shape[0]
-        from ..parallel.symm import MAX_PUSH_ROWS
-        if self.fused is None or M > MAX_PUSH_ROWS or isinstance(layer.weight, Fp8BlockWeight):
+        M, H = x.shape[0], layer.weight.shape[0]
+        if self.fused is None or M > self.fused.max_tokens or H != self.fused.hidden:
             return self.add_rms_norm(tp.all_reduce(self.linear(x, layer.weight)), residual, norm_weight, eps)
         st = self.fused.sites[site]
-        self.C.gemm_tp_push(x, layer.weight, 0, tp.rank, st.slot_ptrs, st.signal_ptrs, st.arrive, st.epoch, st.mc_slot, self.status)
-        y = torch.empty(M, layer.weight.shape[0], dtype=x.dtype, device=x.device)
-        self.C.tp_reduce_rms_norm(tp.size, tp.size, st.local_slots, st.slot_stride, st.local_signal, st.epoch, self.fused.timeout_ns,
-                                  residual, residual, norm_weight, y, eps, self.status)
-        self.launches += 2
-        return y, residual
+        if isinstance(layer.weight, Fp8BlockWeight):
+            # the block-scaled GEMM has no signalling epilogue: publish its output with a copy kernel
+            self.C.tp_rows_publish(self.linear_fp8(x, layer.weight), st.local_buf, tp.rank, st.signal_ptrs, st.arrive, st.epoch)
+        else:
+            self.C.gemm_tp(x, layer.weight, st.local_buf, 0, tp.rank, st.signal_ptrs, st.arrive, st.epoch, self.status)
+        self.launches += 1
+        return self._reduce_norm(st, M, H, residual, residual, norm_weight, eps), residual
 
     # ------------------------------------------------------------------ sampling
     def sample_shard(self, logits, temperatures, header, vocab_start):
@@ -327,8 +343,8 @@ class CudaOps:
             from ..parallel.symm import SITE_SAMPLE
             st = self.fused.sites[SITE_SAMPLE]
             out = torch.empty_like(ids)
-            self.C.tp_sample_pairs(best, ids, tp.rank, st.slot_ptrs, st.signal_ptrs, st.arrive, st.epoch, st.local_slots,
-                                   st.slot_stride, st.local_signal, self.fused.timeout_ns, out, self.status)
+            self.C.tp_sample_pairs(best, ids, tp.rank, st.slot_ptrs, st.signal_ptrs, st.arrive, st.epoch, st.local_buf,
+                                   st.slot_stride, st.local_signal, self.fused.timeout_ns, self.fused.local_only, out, self.status)
             self.launches += 2
             return out
         all_best = tp.all_gather_stack(best)

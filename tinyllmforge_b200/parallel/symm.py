@@ -1,30 +1,32 @@
 """Symmetric memory for the in-kernel tensor-parallel exchange.
 
 Every rank allocates the same region through ``torch.distributed._symmetric_memory`` (which exchanges the
-handles between the processes and maps every peer's copy into this process); the kernels of this package then
-read and write peers' memory directly over NVLink.  Only allocation and handle exchange are delegated; no
-collective of that module is used.
+handles between the processes, maps every peer's copy into this process and, where the driver supports it,
+binds all copies to one NVSwitch multicast address); the kernels of this package then read and write peers'
+memory directly over NVLink, or all copies at once through the multicast address (``multimem.ld_reduce`` /
+``multimem.st``).  Only allocation and handle exchange are delegated; no collective of that module is used.
 
 Region layout (identical on every rank, byte offsets):
-    signals   NUM_SITES x 8 words        word [site][r] = pushes rank r has completed at that site
+    signals   NUM_SITES x 8 words        word [site][r] = productions rank r has completed at that site
     pairs     tp x 512 x {float, int}    sampler candidates, slot r written by rank r
     embed     max_tokens x H bf16        embedding rows, each written by the rank that owns the token id
-    slots_o   tp x 256 x H bf16          o_proj partial sums, slot r written by rank r
-    slots_d   tp x 256 x H bf16          down_proj partial sums
-    slots_ar  tp x 256 x H bf16          operands of the standalone all-reduce / barrier
+    part_o    max_tokens x H bf16        THIS rank's o_proj partial sums (peers pull the sum of all ranks' copies)
+    part_d    max_tokens x H bf16        the same for down_proj
+    part_ar   256 x H bf16               operand of the standalone all-reduce / barrier
+    y         max_tokens x H bf16        normalised rows, each broadcast by the rank that reduced it (two-shot exchange)
 
 Replaces the NCCL calls at tinyvllm/layers/linear.py:183 and tinyvllm/layers/embed_head.py:41,66-67.
 """
 from __future__ import annotations
 
 import os
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 
 import torch
 
-SITE_EMBED, SITE_O, SITE_DOWN, SITE_SAMPLE, SITE_ALLREDUCE = 0, 1, 2, 3, 4
+SITE_EMBED, SITE_O, SITE_DOWN, SITE_SAMPLE, SITE_ALLREDUCE, SITE_GATHER = 0, 1, 2, 3, 4, 5
 NUM_SITES = 8
-MAX_PUSH_ROWS = 256          # rows the decode GEMM can push (its token limit)
+MAX_ALLREDUCE_ROWS = 256     # rows of `hidden` elements the standalone all-reduce accepts
 MAX_PAIR_ROWS = 512
 
 
@@ -36,30 +38,35 @@ def _align(n: int, a: int = 256) -> int:
 class Site:
     """Addresses one rank needs to take part in the exchange at one site."""
     index: int
-    slot_ptrs: list[int]       # peer p -> where this rank writes its data in p's memory
     signal_ptrs: list[int]     # peer p -> this rank's signal word in p's memory
-    local_slots: int           # where this rank reads
-    slot_stride: int           # distance between slots, in bf16 elements
-    num_slots: int             # slots to combine when reading
-    local_signal: int
-    arrive: int
+    local_signal: int          # this rank's signal words (one per rank)
+    arrive: int                # private counters
     epoch: int
-    mc_slot: int = 0           # NVLS multicast address of this rank's slot (0: no multicast support)
+    buf_ptrs: list[int] = field(default_factory=list)    # every rank's copy of the site's buffer, rank order
+    local_buf: int = 0         # this rank's copy
+    mc_buf: int = 0            # NVSwitch multicast address of the buffer (0: no multicast support)
+    slot_ptrs: list[int] = field(default_factory=list)   # per-rank slots (pairs): peer p -> slot [rank] in p's buffer
+    slot_stride: int = 0       # distance between slots, in bf16 elements
 
 
 class FusedTPComm:
-    def __init__(self, tp, hidden_size: int, max_tokens: int, device: torch.device, timeout_s: float = 2.0):
+    def __init__(self, tp, hidden_size: int, max_tokens: int, device: torch.device, timeout_s: float = 10.0):
         import torch.distributed._symmetric_memory as symm_mem
 
         self.tp, self.rank, self.size = tp, tp.rank, tp.size
         self.hidden = hidden_size
+        self.max_tokens = max_tokens
         self.timeout_ns = int(timeout_s * 1e9)
+        # one-shot (every rank pulls every row) moves tp x the tensor per direction, two-shot ~1x plus a second flag
+        # round: switch over when the extra bytes cost more than that round
+        self.two_shot_bytes = int(os.environ.get("FORGE_TP_TWO_SHOT_BYTES", str(2 << 20)))
         H = hidden_size
+        rows_bytes = max_tokens * H * 2
         off = {}
         cur = 0
-        for name, nbytes in (("signals", NUM_SITES * 8 * 4), ("pairs", self.size * MAX_PAIR_ROWS * 8),
-                             ("embed", max_tokens * H * 2), ("slots_o", self.size * MAX_PUSH_ROWS * H * 2),
-                             ("slots_d", self.size * MAX_PUSH_ROWS * H * 2), ("slots_ar", self.size * MAX_PUSH_ROWS * H * 2)):
+        for name, nbytes in (("signals", NUM_SITES * 8 * 4), ("pairs", self.size * MAX_PAIR_ROWS * 8), ("embed", rows_bytes),
+                             ("part_o", rows_bytes), ("part_d", rows_bytes), ("part_ar", MAX_ALLREDUCE_ROWS * H * 2),
+                             ("y", rows_bytes)):
             off[name] = cur
             cur = _align(cur + nbytes)
         self.offsets, self.nbytes = off, cur
@@ -70,31 +77,54 @@ class FusedTPComm:
         self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         if os.environ.get("FORGE_NVLS", "1") == "0":
             self.multicast_ptr = 0
-        self.counters = torch.zeros(2 * NUM_SITES, dtype=torch.int32, device=device)     # private: arrive, epoch per site
+        # private words: arrive, epoch per site, then the measurement-mode switch
+        self.counters = torch.zeros(2 * NUM_SITES + 2, dtype=torch.int32, device=device)
         torch.cuda.synchronize()
-        tp.barrier()                       # nobody pushes before every region is zeroed
+        tp.barrier()                       # nobody produces before every region is zeroed
 
         me = self.bases[self.rank]
         cbase = self.counters.data_ptr()
+        self.local_only = cbase + 2 * NUM_SITES * 4
+        mc = self.multicast_ptr
 
-        def site(index, name, slot_bytes, shared_slot=False):
-            return Site(
-                index=index,
-                slot_ptrs=[b + off[name] + (0 if shared_slot else self.rank * slot_bytes) for b in self.bases],
-                signal_ptrs=[b + off["signals"] + (index * 8 + self.rank) * 4 for b in self.bases],
-                local_slots=me + off[name], slot_stride=slot_bytes // 2, num_slots=1 if shared_slot else self.size,
-                local_signal=me + off["signals"] + index * 8 * 4,
-                arrive=cbase + (2 * index) * 4, epoch=cbase + (2 * index + 1) * 4,
-                mc_slot=(self.multicast_ptr + off[name] + (0 if shared_slot else self.rank * slot_bytes)) if self.multicast_ptr else 0)
+        def site(index, name=None, slot_bytes=0):
+            s = Site(index=index,
+                     signal_ptrs=[b + off["signals"] + (index * 8 + self.rank) * 4 for b in self.bases],
+                     local_signal=me + off["signals"] + index * 8 * 4,
+                     arrive=cbase + (2 * index) * 4, epoch=cbase + (2 * index + 1) * 4)
+            if name is not None:
+                s.buf_ptrs = [b + off[name] for b in self.bases]
+                s.local_buf = me + off[name]
+                s.mc_buf = mc + off[name] if mc else 0
+                if slot_bytes:
+                    s.slot_ptrs = [b + off[name] + self.rank * slot_bytes for b in self.bases]
+                    s.slot_stride = slot_bytes // 2
+            return s
 
         self.sites = {
-            SITE_EMBED: site(SITE_EMBED, "embed", max_tokens * H * 2, shared_slot=True),
-            SITE_O: site(SITE_O, "slots_o", MAX_PUSH_ROWS * H * 2),
-            SITE_DOWN: site(SITE_DOWN, "slots_d", MAX_PUSH_ROWS * H * 2),
+            SITE_EMBED: site(SITE_EMBED, "embed"),
+            SITE_O: site(SITE_O, "part_o"),
+            SITE_DOWN: site(SITE_DOWN, "part_d"),
             SITE_SAMPLE: site(SITE_SAMPLE, "pairs", MAX_PAIR_ROWS * 8),
-            SITE_ALLREDUCE: site(SITE_ALLREDUCE, "slots_ar", MAX_PUSH_ROWS * H * 2),
+            SITE_ALLREDUCE: site(SITE_ALLREDUCE, "part_ar"),
+            SITE_GATHER: site(SITE_GATHER, "y"),
         }
-        self.max_tokens = max_tokens
+
+    def two_shot(self, rows: int, width: int) -> bool:
+        """Reduce-scatter + all-gather instead of every rank pulling every row?  Depends only on the shape, so all
+        ranks decide alike."""
+        return (self.size - 1) * rows * width * 2 > self.two_shot_bytes
+
+    def y_view(self, rows: int, width: int) -> torch.Tensor:
+        """The first ``rows x width`` bf16 elements of this rank's broadcast buffer as a tensor."""
+        o = self.offsets["y"]
+        return self.region[o:o + rows * width * 2].view(torch.bfloat16).view(rows, width)
+
+    def set_local_only(self, on: bool) -> None:
+        """Measurement mode (stream-ordered): the exchange kernels skip their waits and peer traffic and work on this
+        rank's own data only.  Results are wrong on purpose; the time difference to a normal run is the exposed
+        communication.  Callers synchronise all ranks (device and host) before switching either way."""
+        self.counters[2 * NUM_SITES] = 1 if on else 0
 
     def close(self):
         self.handle = None
