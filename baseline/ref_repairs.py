@@ -103,8 +103,29 @@ def apply() -> list[str]:
             "B14 QKV parameter size"]
 
 
+def apply_dummy_load() -> str:
+    """Replace the reference's checkpoint loader (tinyvllm/utils/loader.py:11-30) by a random initialisation on the
+    device, for architectures whose safetensors files would be tens of GB (Qwen3-32B: 64 GB, read in full by every
+    rank).  Weight values do not change what the timed region does; loading is outside it."""
+    import torch
+    from tinyvllm.engine import model_runner
+
+    def dummy_load(model, path):
+        g = torch.Generator(device="cuda").manual_seed(0)
+        for _, p in model.named_parameters():
+            if p.dim() >= 2:
+                p.data.normal_(0.0, 0.02, generator=g)
+            else:
+                p.data.fill_(1.0)
+    model_runner.load_model = dummy_load
+    return "checkpoint loader replaced by on-device random init N(0, 0.02)"
+
+
 def worker_entry(config, rank, event):
     """Spawn target of ranks 1..tp-1: repair this interpreter, then run the reference's worker as it would."""
+    import os
     apply()
+    if os.environ.get("FORGE_REF_DUMMY_LOAD") == "1":
+        apply_dummy_load()
     from tinyvllm.engine.model_runner import ModelRunner
     ModelRunner(config, rank, event)

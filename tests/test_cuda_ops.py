@@ -249,6 +249,28 @@ def test_decode_attention(ops, k_lens, nq, nkv, bs, mode, monkeypatch):
 
 
 @pytest.mark.parametrize("mode", ["flat", "chunked"])
+def test_decode_attention_reports_a_length_the_block_table_cannot_describe(ops, mode, monkeypatch):
+    """A context length written too large on the host (one block more than the table has) is clamped on the device: the
+    status word gets the bad-index bit, every access stays inside the table and the scratch, the other rows are right."""
+    monkeypatch.setattr(ops, "decode_attention_mode", mode)
+    k_lens = [300, 100, 520]
+    q, kc, vc, b = _paged_case([1] * 3, k_lens, 16, 8, 256)
+    b.is_prefill = False
+    want = ref.attention(q, kc, vc, b.cu_seqlens_q, b.context_lens, b.block_tables, 128 ** -0.5, 3)
+    b.context_lens = b.context_lens.clone()
+    b.context_lens[1] = (b.table_width + 1) * 256
+    b.block_tables = b.block_tables.clone()
+    b.block_tables[1, 1:] = b.block_tables[1, 0]        # the clamped row reads valid blocks; its result is not checked
+    ops.check_status()
+    got = ops.attention(q, kc, vc, b, 128 ** -0.5)
+    torch.cuda.synchronize()
+    word = int(ops.status[0].item())
+    assert word & 4, word
+    ops.status.zero_()
+    _close(got[[0, 2]], want[[0, 2]], 2e-2, 2e-2)
+
+
+@pytest.mark.parametrize("mode", ["flat", "chunked"])
 def test_decode_attention_padding_rows(ops, mode, monkeypatch):
     monkeypatch.setattr(ops, "decode_attention_mode", mode)
     q, kc, vc, b = _paged_case([1, 1, 1], [100, 0, 7], 16, 8, 256)

@@ -91,6 +91,28 @@ def test_two_calls_in_a_row_match_the_regular_entry_point():
         assert torch.equal(got, want)            # same kernels, same order of operations
 
 
+def test_a_length_beyond_the_slices_is_clamped_and_reported():
+    """context_lens one slice longer than max_chunks * chunk covers: the call succeeds, `status` gets the bad-index bit,
+    and the merge reads only partials of this call (the other rows equal the regular entry point's)."""
+    lib = _lib()
+    lens, nq, nkv, bs, chunk = [500, 260, 90], 16, 8, 256, 256
+    q, kc, vc, bt, cl = _case(lens, nq, nkv, bs, 3)
+    max_chunks = 2
+    want = _regular(q, kc, vc, bt, cl, chunk, max_chunks)
+    bad = cl.clone()
+    bad[1] = max_chunks * chunk + chunk
+    B, _, D = q.shape
+    out = torch.empty(B, nq * D, dtype=BF, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    rc = lib.forge_decode_attention_noalloc(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), bad.data_ptr(), out.data_ptr(),
+                                            B, nq, nkv, D, bs, bt.shape[1], kc.shape[0], chunk, max_chunks, D ** -0.5,
+                                            status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(status[0]) & 4
+    assert torch.equal(out[[0, 2]], want[[0, 2]])
+
+
 def test_oversized_request_is_refused():
     lib = _lib()
     cap = lib.forge_decode_attention_noalloc_capacity_floats()

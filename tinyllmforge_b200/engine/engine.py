@@ -185,6 +185,7 @@ class LLMEngine:
         t3 = time.perf_counter()
         self._mark("postprocess")
         self.step_index += 1
+        st.add_device_time(is_prefill, getattr(self.worker, "last_step_ms", None))
         finished = self.scheduler.postprocess(reqs, token_ids)
         t4 = time.perf_counter()
         self._mark(None)
@@ -258,42 +259,58 @@ class LLMEngine:
 
     # ------------------------------------------------------------------ pipelined loop
     def _can_pipeline(self) -> bool:
-        """The host may run one step ahead of the tokens it reads back when no request can end on a token VALUE:
-        every queued request ignores EOS (or there is no EOS id).  Lengths, finish-by-max_tokens, block growth and
-        slots do not depend on token values; the values themselves travel device-to-device."""
-        if not self.config.extra.get("pipeline", True):
-            return False
-        sch = self.scheduler
-        return all(r.ignore_eos or self.config.eos < 0 for q in (sch.waiting, sch.running) for r in q)
+        """The host runs one step ahead of the tokens it reads back.  Lengths, finish-by-max_tokens, block growth and
+        slots do not depend on token values, and the values themselves travel device-to-device.  A request that may
+        stop on EOS is scheduled one step ahead on the assumption that it does not stop; when its token turns out to
+        be EOS the surplus token of the step already in flight is dropped (see ``_run_pipelined``)."""
+        return bool(self.config.extra.get("pipeline", True))
 
     def _run_pipelined(self, outputs: dict, pbar) -> None:
         """schedule/build/launch step t+1, THEN read step t's tokens: scheduling, building, publishing and output
         handling overlap with the GPU.  Prefill steps are launched only when nothing is in flight (a preempted
-        request must have all its real tokens before it is prefilled again)."""
+        request must have all its real tokens before it is prefilled again).
+
+        EOS: step t+1 is launched before step t's tokens are known, so a request whose step-t token is EOS also sits
+        in step t+1.  When the EOS is read, the request is retired with the tokens up to the EOS, its blocks are
+        freed (later steps run after the one in flight, and blocks are sealed for the prefix cache only with tokens
+        that were read back), and the token step t+1 computes for it is ignored."""
         sch, st, bs = self.scheduler, self.stats, self.config.kvcache_block_size
+        eos = self.config.eos
         inflight = None             # (reqs, ticket, finished requests) of the step not yet read back
 
         def drain():
             nonlocal inflight
             if inflight is None:
                 return
-            reqs, ticket, finished = inflight
+            reqs, ticket, finished, was_prefill = inflight
             inflight = None
             try:
                 toks = self.worker.collect(ticket)
             except RuntimeError as e:
                 raise EngineDeadError(str(e)) from e
+            st.add_device_time(was_prefill, getattr(self.worker, "last_step_ms", None))
+            early = 0
             for (r, idx), tok in zip(reqs, toks):
-                if idx >= 0:
-                    r.token_ids[idx] = tok
+                if idx < 0 or idx >= len(r.token_ids):   # no token expected (chunk of a long prompt), or retired before this step was read
+                    continue
+                r.token_ids[idx] = tok
+                if tok == eos and not r.ignore_eos and idx + 1 - r.num_prompt_tokens < r.max_tokens:
+                    # stops here, one step (or, preempted in between, no step) after the host moved on
+                    del r.token_ids[idx + 1:]
+                    sch.finish_early(r)
+                    outputs[r.req_id] = r.completion_token_ids
+                    early += 1
             for r in finished:
                 outputs[r.req_id] = r.completion_token_ids
+            st.finished_requests += early
             if pbar is not None:
-                pbar.update(len(finished))
+                pbar.update(len(finished) + early)
 
         while not sch.is_finished():
             if sch.has_waiting() and inflight is not None:
                 drain()                                  # the next step may be a prefill: needs real token ids
+                if sch.is_finished():                    # the tokens just read ended the last requests (EOS)
+                    break
             t0 = time.perf_counter()
             self._mark("schedule")
             reqs, is_prefill = sch.schedule(defer_seal=True)
@@ -325,8 +342,10 @@ class LLMEngine:
             self.step_index += 1
             drain()                                      # read the PREVIOUS step while this one runs
             partial = sch.partial                        # a long prompt in the middle of its prefill receives no token
+            # a request the drain above retired (EOS in the previous step) is still part of this step: its token is dropped
+            retired = {id(r) for r in reqs if r.is_finished}
             finished = sch.postprocess(reqs, [PLACEHOLDER] * len(reqs))
-            inflight = ([(r, len(r.token_ids) - 1 if r is not partial else -1) for r in reqs], ticket, finished)
+            inflight = ([(r, -1 if (r is partial or id(r) in retired) else len(r.token_ids) - 1) for r in reqs], ticket, finished, is_prefill)
             t4 = time.perf_counter()
             self._mark(None)
             st.schedule_s += t1 - t0

@@ -133,6 +133,23 @@ class Scheduler:
         self.pool.release(req)
         self.waiting.appendleft(req)
 
+    def finish_early(self, req: Request) -> None:
+        """Retire a request whose newest KNOWN token ended it (EOS) although a later step that still contains it has
+        been scheduled already (the pipelined engine loop schedules one step ahead of the tokens it has read back).
+        Its blocks go back to the pool at once: the step in flight may still write the surplus token's KV entry into
+        the request's last block, but every later step runs after it on the same stream, and a partly filled or
+        unsealed block is never found through the prefix cache."""
+        if req.status is RequestStatus.FINISHED:
+            return
+        was_running = req.status is RequestStatus.RUNNING
+        req.status = RequestStatus.FINISHED
+        if req.block_table:
+            self.pool.release(req)
+        if was_running:
+            self.running = deque(r for r in self.running if r is not req)
+        else:                                              # preempted in the meantime: it waits for a prefill it no longer needs
+            self.waiting = deque(r for r in self.waiting if r is not req)
+
     def has_waiting(self) -> bool:
         """True if the next step may be a prefill."""
         return bool(self.waiting) or self.partial is not None
@@ -142,6 +159,8 @@ class Scheduler:
         The pipelined engine loop passes ``PLACEHOLDER`` ids and patches the real ones in later."""
         finished = []
         for req, tok in zip(batch, token_ids):
+            if req.status is RequestStatus.FINISHED:       # retired by finish_early() while this step was in flight
+                continue
             if req is self.partial:                        # a chunk in the middle of a long prompt: no token yet
                 req.num_computed_tokens = req.prefill_end
                 continue

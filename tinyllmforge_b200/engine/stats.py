@@ -19,10 +19,22 @@ class EngineStats:
     build_s: float = 0.0
     run_s: float = 0.0
     postprocess_s: float = 0.0
+    # device time of the steps (CUDA events around each step on this rank; filled when extra={"device_timing": True})
+    prefill_device_ms: float = 0.0
+    decode_device_ms: float = 0.0
     decode_batch_hist: Counter = field(default_factory=Counter)
+
+    def add_device_time(self, is_prefill: bool, ms: float | None) -> None:
+        if ms is not None:
+            if is_prefill:
+                self.prefill_device_ms += ms
+            else:
+                self.decode_device_ms += ms
 
     def to_dict(self) -> dict:
         d = {k: v for k, v in self.__dict__.items() if k != "decode_batch_hist"}
+        d["decode_step_device_ms"] = self.decode_device_ms / self.decode_steps if self.decode_steps and self.decode_device_ms else None
+        d["prefill_step_device_ms"] = self.prefill_device_ms / self.prefill_steps if self.prefill_steps and self.prefill_device_ms else None
         d["decode_batch_hist"] = {int(k): int(v) for k, v in sorted(self.decode_batch_hist.items())}
         return d
 

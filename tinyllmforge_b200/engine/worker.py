@@ -72,6 +72,7 @@ class Worker:
         self.time_steps = bool(config.extra.get("device_timing", False))
         self.prev_tokens_host = np.zeros(0, dtype=np.int64)
         self.num_steps = 0
+        self.last_step_ms: float | None = None      # device time of the step collected last (with extra={"device_timing": True})
         self.reset_counters()
 
         if self.is_cuda:
@@ -247,9 +248,11 @@ class Worker:
             return ticket[1]
         _, host, n, e0, done, shape = ticket
         done.synchronize()
+        self.last_step_ms = None
         if e0 is not None:
             ms = e0.elapsed_time(done)
             self.device_ms += ms
+            self.last_step_ms = ms
             self.step_times.append((shape[0], shape[1], shape[2], ms))
         word = int(host[self.status_slot])
         if word:

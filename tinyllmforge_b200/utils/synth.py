@@ -52,10 +52,19 @@ def write_tokenizer(path: str, vocab_size: int) -> None:
         json.dump({"unk_token": "<unk>", "eos_token": "<eos>", "pad_token": "<pad>"}, f)
 
 
+def checkpoint_bytes(cfg: ModelConfig) -> int:
+    """Size of the safetensors data ``write_checkpoint`` produces for ``cfg``."""
+    itemsize = torch.finfo(cfg.dtype).bits // 8
+    return sum(itemsize * int(torch.Size(shape).numel()) for shape in hf_tensor_shapes(cfg).values())
+
+
 def write_checkpoint(path: str, cfg: ModelConfig, seed: int = 0, std: float = 0.02, tokenizer: bool = True,
-                     shard_bytes: int = 4 << 30, norm_std: float = 0.0) -> str:
+                     shard_bytes: int = 4 << 30, norm_std: float = 0.0, device: str = "cpu", weights: bool = True) -> str:
     """Write ``config.json`` and seeded random weights under HF names; returns ``path``.
-    Matrices are N(0, std); norm weights are 1 (+ N(0, norm_std) when asked, which makes tests sharper)."""
+    Matrices are N(0, std); norm weights are 1 (+ N(0, norm_std) when asked, which makes tests sharper).
+    ``device="cuda"`` draws the numbers on the GPU (a multi-GB checkpoint then takes seconds instead of minutes; the
+    values differ from the CPU generator's for the same seed).  ``weights=False`` writes only ``config.json`` and the
+    tokenizer (for engines that initialise their weights on the device)."""
     from safetensors.torch import save_file
 
     os.makedirs(path, exist_ok=True)
@@ -64,7 +73,11 @@ def write_checkpoint(path: str, cfg: ModelConfig, seed: int = 0, std: float = 0.
         d["eos_token_id"] = 1
     with open(os.path.join(path, "config.json"), "w") as f:
         json.dump(d, f, indent=1)
-    gen = torch.Generator().manual_seed(seed)
+    if not weights:
+        if tokenizer:
+            write_tokenizer(path, cfg.vocab_size)
+        return path
+    gen = torch.Generator(device=device).manual_seed(seed)
     dtype = cfg.dtype
     itemsize = torch.finfo(dtype).bits // 8
     # plan the shards first so the files can carry the "-i-of-n" names transformers expects
@@ -85,9 +98,9 @@ def write_checkpoint(path: str, cfg: ModelConfig, seed: int = 0, std: float = 0.
             if len(shape) == 1:
                 t = torch.ones(shape, dtype=dtype)
                 if norm_std > 0:
-                    t = (t.float() + torch.empty(shape).normal_(0.0, norm_std, generator=gen)).to(dtype)
+                    t = (t.float() + torch.empty(shape, device=device).normal_(0.0, norm_std, generator=gen).cpu()).to(dtype)
             else:
-                t = torch.empty(shape, dtype=torch.float32).normal_(0.0, std, generator=gen).to(dtype)
+                t = torch.empty(shape, dtype=torch.float32, device=device).normal_(0.0, std, generator=gen).to(dtype).cpu()
             shard[name] = t
             weight_map[name] = fname
         save_file(shard, os.path.join(path, fname), metadata={"format": "pt"})
