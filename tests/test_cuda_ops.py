@@ -407,15 +407,16 @@ def test_peer_flag_wait_runs_out_and_reports_status(ops):
     never written), gives up after its time limit, sets the status bit, and the context stays usable."""
     import time
     H, rows = 1024, 4
-    slots = torch.zeros(2, rows, H, dtype=BF, device="cuda")
+    parts = torch.zeros(2, rows, H, dtype=BF, device="cuda")             # both "ranks'" partial buffers live on this GPU
     signal = torch.zeros(8, dtype=torch.int32, device="cuda")
-    epoch = torch.ones(1, dtype=torch.int32, device="cuda")            # this rank claims one completed push ...
+    epoch = torch.ones(1, dtype=torch.int32, device="cuda")            # this rank claims one completed production ...
     signal[0] = 1                                                       # ... rank 0's flag is there, rank 1's never arrives
+    normal_mode = torch.zeros(1, dtype=torch.int32, device="cuda")      # the measurement-mode switch stays off
     out = torch.empty(rows, H, dtype=BF, device="cuda")
     torch.cuda.synchronize()
     t0 = time.monotonic()
-    ops.C.tp_reduce_rms_norm(2, 2, slots.data_ptr(), rows * H, signal.data_ptr(), epoch.data_ptr(), int(0.2e9), None, out,
-                             None, None, 1e-6, ops.status)
+    ops.C.tp_reduce_rms_norm(2, 0, [parts[0].data_ptr(), parts[1].data_ptr()], 0, 0, signal.data_ptr(), epoch.data_ptr(), int(0.2e9),
+                             normal_mode.data_ptr(), None, out, None, None, 1e-6, ops.status)
     torch.cuda.synchronize()
     assert 0.15 < time.monotonic() - t0 < 5.0
     with pytest.raises(RuntimeError, match="peer flag wait ran out"):
