@@ -166,20 +166,19 @@ extern "C" int forge_tp_reduce_rms_norm(int tp_size, int tp_rank, const long lon
 // Two-shot exchange.  CTA i handles row i * size + rank: this rank's share of the reduce-scatter.  `residual` is a
 // full-size local tensor of which only this rank's rows are read and written (the residual stream stays sharded by
 // rows from one exchange to the next); the normalised row goes to every rank's broadcast buffer.  After its own
-// stores a CTA reports to the grid's arrival counter; the last one publishes this rank's epoch at the all-gather
-// site to every rank, and every CTA then waits until all ranks have published theirs, so that when the kernel
-// completes the whole broadcast buffer is valid on this rank.
+// stores a CTA reports to the grid's arrival counter.  The LAST CTA to arrive publishes this rank's epoch at the
+// all-gather site to every rank and then waits until all ranks have published theirs, so that when the kernel
+// completes the whole broadcast buffer is valid on this rank.  Only that one CTA waits: a CTA that waited while later
+// CTAs of the same grid still queue for a free SM would wait for a signal its own grid cannot send.
 __global__ void __launch_bounds__(256) tp_rs_norm_ag_kernel(TpPull wait_parts, TpReduceSrc src, const __nv_bfloat16* residual_in,
                                                             __nv_bfloat16* residual_out, const __nv_bfloat16* __restrict__ w,
                                                             TpBcastDst dst, TpPush done, TpPull wait_rows, int rows, int H, float eps,
                                                             unsigned* status) {
   __shared__ float red[32];
-  __shared__ unsigned want_rows;
+  __shared__ unsigned last_cta, my_epoch;
   pdl_launch_dependents();
   pdl_wait();
-  // The all-gather epoch is advanced by this kernel's last CTA, after every CTA (this one included) has arrived:
-  // reading it here, before arriving, gives the value before the advance on every CTA.
-  if (threadIdx.x == 0) want_rows = *wait_rows.epoch + 1u;
+  if (threadIdx.x == 0) last_cta = 0u;
   tp_pull_wait(wait_parts, status);
   const bool local = tp_local_only(src.local_only);
   const size_t row = static_cast<size_t>(blockIdx.x) * src.size + src.rank;
@@ -218,8 +217,22 @@ __global__ void __launch_bounds__(256) tp_rs_norm_ag_kernel(TpPull wait_parts, T
       }
     }
   }
-  tp_push_done(done, gridDim.x);                        // contains a CTA barrier: want_rows is visible to all threads after it
-  tp_wait_epoch(wait_rows, want_rows, status);
+  __threadfence_system();                               // this thread's (remote) stores are ordered before what follows
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(done.arrive, 1u);
+    if (prev == gridDim.x - 1) {
+      atomicExch(done.arrive, 0u);
+      __threadfence_system();                           // cumulative: every CTA's stores are ordered before the signal
+      const unsigned e = *done.epoch + 1;
+      *done.epoch = e;
+      for (int p = 0; p < done.size; ++p) st_release_sys(done.signal[p], e);
+      my_epoch = e;
+      last_cta = 1u;
+    }
+  }
+  __syncthreads();
+  if (last_cta != 0u) tp_wait_epoch(wait_rows, my_epoch, status);      // uniform for the CTA
 }
 
 TpPush make_tp_push(int tp_size, int tp_rank, const long long* slot_ptrs, const long long* signal_ptrs, unsigned* arrive,
