@@ -263,6 +263,116 @@ extern "C" int forge_tp_rs_norm_ag(int tp_size, int tp_rank, const long long* pa
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// Tagged-word exchange (decode-sized batches): see "tagged words" in include/tp_comm.cuh
+// ---------------------------------------------------------------------------------------------------------
+// One CTA per row.  Row b belongs to rank b % size.  Its owner polls the sources' tagged partial words (the GEMM
+// epilogues of all ranks stored them there), adds them, adds its shard of the residual, normalises, stores the row
+// into its own `y` and sends it as tagged words to every other rank.  A CTA of a row that belongs to another rank
+// polls the tagged words that row's owner sends and stores the plain row into `y`.  When the kernel completes, `y`
+// holds all rows on every rank.  At most 256 CTAs, all resident at once, so a CTA that polls never keeps one that
+// sends from running.
+__global__ void __launch_bounds__(256) tp_tagged_reduce_norm_kernel(TpTagged tp, const __nv_bfloat16* residual_in,
+                                                                    __nv_bfloat16* residual_out, const __nv_bfloat16* __restrict__ w,
+                                                                    __nv_bfloat16* __restrict__ y, int rows, int H, float eps,
+                                                                    unsigned* status) {
+  __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const unsigned tag_part = *tp.part_epoch;            // advanced by this rank's GEMM, which has completed
+  const unsigned tag_rows = *tp.epoch + 1u;            // read before this CTA reports its arrival (see tp_tagged_done)
+  const bool local = tp_local_only(tp.local_only);
+  const int row = blockIdx.x;
+  const int owner = row % tp.size, j = row / tp.size;
+  const int nvec = H >> 3;
+  if (owner == tp.rank) {
+    float vals[kTpNormChunks][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < kTpNormChunks; ++c) {
+      const int i = threadIdx.x + c * blockDim.x;
+      if (i < nvec) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        const int first = local ? tp.rank : 0, last = local ? tp.rank + 1 : tp.size;
+        for (int s = first; s < last; ++s) {            // rank order: the same sum whichever rank owns the row
+          const uint32_t* p = tp.part + (static_cast<size_t>(s) * tp.rows_per_rank + j) * H + i * 8;
+          const uint4 a = tp_poll_tagged(p, tag_part, tp.timeout_ns, status);
+          const uint4 b = tp_poll_tagged(p + 4, tag_part, tp.timeout_ns, status);
+          acc[0] += bf16_lo(a.x); acc[1] += bf16_hi(a.x); acc[2] += bf16_lo(a.z); acc[3] += bf16_hi(a.z);
+          acc[4] += bf16_lo(b.x); acc[5] += bf16_hi(b.x); acc[6] += bf16_lo(b.z); acc[7] += bf16_hi(b.z);
+        }
+        reinterpret_cast<uint4*>(residual_out + static_cast<size_t>(row) * H)[i] =
+            tp_add_residual8(acc, residual_in != nullptr ? residual_in + static_cast<size_t>(row) * H : nullptr, i);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          vals[c][k] = acc[k];
+          ss += acc[k] * acc[k];
+        }
+      }
+    }
+    const float inv = rsqrtf(cta_sum_c(ss, red) / static_cast<float>(H) + eps);
+#pragma unroll
+    for (int c = 0; c < kTpNormChunks; ++c) {
+      const int i = threadIdx.x + c * blockDim.x;
+      if (i < nvec) {
+        const uint4 o = tp_normed8(vals[c], inv, w, i);
+        reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * H)[i] = o;
+        if (!local) {
+          const size_t off = static_cast<size_t>(row) * H + i * 8;
+          for (int p = 0; p < tp.size; ++p) {
+            if (p == tp.rank) continue;
+            st_volatile_v4(tp.y[p] + off, make_uint4(o.x, tag_rows, o.y, tag_rows));
+            st_volatile_v4(tp.y[p] + off + 4, make_uint4(o.z, tag_rows, o.w, tag_rows));
+          }
+        }
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      uint4 o = make_uint4(0u, 0u, 0u, 0u);             // measurement mode: rows of other ranks are not exchanged
+      if (!local) {
+        const uint32_t* p = tp.y[tp.rank] + static_cast<size_t>(row) * H + i * 8;
+        const uint4 a = tp_poll_tagged(p, tag_rows, tp.timeout_ns, status);
+        const uint4 b = tp_poll_tagged(p + 4, tag_rows, tp.timeout_ns, status);
+        o = make_uint4(a.x, a.z, b.x, b.z);
+      }
+      reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * H)[i] = o;
+    }
+  }
+  TpPush done = {};
+  done.arrive = tp.arrive;
+  done.epoch = tp.epoch;
+  tp_tagged_done(done, gridDim.x);
+}
+
+// part: this rank's buffer of the GEMM site ([tp_size][rows_per_rank][H] words); y_ptrs: every rank's buffer of
+// normalised rows ([256][H] words) in rank order; arrive / epoch: private counters of the normalised-rows site;
+// part_epoch: this rank's epoch at the GEMM site.  `residual` is updated on this rank's rows only.
+extern "C" int forge_tp_tagged_reduce_norm(int tp_size, int tp_rank, const void* part, int rows_per_rank, const unsigned* part_epoch,
+                                           const long long* y_ptrs, unsigned* arrive, unsigned* epoch, long long timeout_ns,
+                                           const unsigned* local_only, const void* residual_in, void* residual_out, const void* w,
+                                           void* y, int rows, int H, float eps, unsigned* status, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if ((H & 7) || H > kTpNormChunks * 256 * 8 || tp_size < 2 || tp_size > kMaxTp || tp_rank < 0 || tp_rank >= tp_size) return -1;
+  if (rows > 256 || (rows + tp_size - 1) / tp_size > rows_per_rank || part == nullptr || y_ptrs == nullptr || w == nullptr ||
+      y == nullptr || residual_out == nullptr)
+    return -1;
+  TpTagged tp = {};
+  tp.size = tp_size;
+  tp.rank = tp_rank;
+  tp.rows_per_rank = rows_per_rank;
+  tp.part = static_cast<const uint32_t*>(part);
+  for (int p = 0; p < tp_size; ++p) tp.y[p] = reinterpret_cast<uint32_t*>(y_ptrs[p]);
+  tp.arrive = arrive;
+  tp.epoch = epoch;
+  tp.part_epoch = part_epoch;
+  tp.timeout_ns = timeout_ns;
+  tp.local_only = local_only;
+  return launch_kernel(tp_tagged_reduce_norm_kernel, dim3(rows), dim3(norm_threads(H)), 0, stream, 0, tp,
+                       static_cast<const __nv_bfloat16*>(residual_in), static_cast<__nv_bfloat16*>(residual_out),
+                       static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), rows, H, eps, status) == cudaSuccess ? 0 : -2;
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // Row pushes
 // ---------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128) embedding_push_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ w,

@@ -399,8 +399,12 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const int cpc = BLOCK_C / static_cast<int>(nsplit);            // columns per owner
   const uint32_t slot_bytes = static_cast<uint32_t>(cpc) * kBlockR * 4;
   bool acc_ok = true;
+  unsigned ll_tag = 0;
   if (is_epi) {
     pdl_wait();                                                  // `out` may still be read by a predecessor
+    // tagged-word push: the tag is this exchange's epoch.  Read before this CTA reports its arrival, i.e. before the
+    // grid's last CTA can advance the counter.
+    if (push.size > 1 && push.ll) ll_tag = *push.epoch + 1u;
     acc_ok = mbar_wait(acc_bar, 0, status);                      // this CTA's ring is idle from here on
     tcgen05_fence_after();
     if (et == 0) trace_point(cta_id, 3);                         // accumulators complete
@@ -488,8 +492,17 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             const int c = tok0 + static_cast<int>(split) * cpc + lc;
             const int n = r0 + lane * 4;
             if (c < m_total && n < n_total) {
-              // Row-parallel layer under tensor parallelism: `out` is this rank's partial buffer in symmetric memory;
-              // the stores are local, the consumer kernels of all ranks pull the sum over NVLink (tp_comm.cuh).
+              if (push.size > 1 && push.ll) {
+                // decode-sized exchange: the row goes, as tagged words, straight to the rank that owns it (a peer store
+                // over NVLink, or a local one), while other CTAs still compute (tp_comm.cuh, "tagged words")
+                const int owner = c % push.size, j = c / push.size;
+                uint32_t* d = reinterpret_cast<uint32_t*>(push.slot[owner]) +
+                              (static_cast<size_t>(push.rank) * push.rows_per_rank + j) * ldo + n;
+                st_volatile_v4(d, make_uint4(pack_bf16x2(v.x, v.y), ll_tag, pack_bf16x2(v.z, v.w), ll_tag));
+                continue;
+              }
+              // Row-parallel layer under tensor parallelism, many rows: `out` is this rank's partial buffer in symmetric
+              // memory; the stores are local, the consumer kernels of all ranks pull the sum over NVLink (tp_comm.cuh).
               __nv_bfloat16* dst = out + static_cast<size_t>(c) * ldo + n;
               if (n + 4 <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0)) {
                 uint2 pk;
@@ -512,7 +525,10 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     cluster_sync();
   }
   if (threadIdx.x == 0) trace_point(cta_id, 7);                  // after the final cluster barrier
-  if (push.size > 1) tp_push_done(push, gridDim.x * gridDim.y * gridDim.z);   // last CTA of the grid signals every rank
+  if (push.size > 1) {
+    if (push.ll) tp_tagged_done(push, gridDim.x * gridDim.y * gridDim.z);      // the data carries its tag: only the epoch advances
+    else tp_push_done(push, gridDim.x * gridDim.y * gridDim.z);                // last CTA of the grid signals every rank
+  }
 
   tcgen05_fence_before();
   __syncthreads();
@@ -724,6 +740,24 @@ extern "C" int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, v
 // Row-parallel GEMM under tensor parallelism: `out` is this rank's partial buffer in symmetric memory (row stride ldo);
 // the kernel's last CTA announces completion to every rank through signal_ptrs (tp_size addresses in peer order).
 // Up to 256 rows run on the weight-tile (decode) kernel, more on the persistent token-tile kernel.
+// Row-parallel GEMM under tensor parallelism, at most 256 rows: every output row is stored as tagged words into the
+// buffer of the rank that owns it (ll_ptrs[p] = rank p's buffer of [tp_size][rows_per_rank][n_out] 32-bit words).
+// n_out must be a multiple of 4.
+extern "C" int forge_gemm_bf16_tp_tagged(const void* x, int ldx, const void* w, int ldw, int M, int n_out, int K, int tune, int tp_size,
+                                         int tp_rank, const long long* ll_ptrs, int rows_per_rank, unsigned* arrive, unsigned* epoch,
+                                         unsigned* status, cudaStream_t stream) {
+  if (tp_size < 2 || tp_size > kMaxTp || M <= 0 || M > 256 || (n_out & 3) || (M + tp_size - 1) / tp_size > rows_per_rank) return -7;
+  TpPush push = {};
+  push.size = tp_size;
+  push.rank = tp_rank;
+  push.ll = 1;
+  push.rows_per_rank = rows_per_rank;
+  for (int p = 0; p < tp_size; ++p) push.slot[p] = reinterpret_cast<__nv_bfloat16*>(ll_ptrs[p]);
+  push.arrive = arrive;
+  push.epoch = epoch;
+  return gemm_dispatch(x, ldx, w, ldw, nullptr, n_out, M, n_out, K, kEpiStore, 2, tune, status, stream, push);
+}
+
 extern "C" int forge_gemm_bf16_tp(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K,
                                   int tune, int tp_size, int tp_rank, const long long* signal_ptrs, unsigned* arrive,
                                   unsigned* epoch, unsigned* status, cudaStream_t stream) {

@@ -18,6 +18,13 @@ int forge_gemm_fp8_block(const void* xq, const float* xs, int xs_ld, const void*
 int forge_gemm_bf16_tp(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K, int tune,
                        int tp_size, int tp_rank, const long long* signal_ptrs, unsigned* arrive, unsigned* epoch, unsigned* status,
                        cudaStream_t stream);
+int forge_gemm_bf16_tp_tagged(const void* x, int ldx, const void* w, int ldw, int M, int n_out, int K, int tune, int tp_size,
+                              int tp_rank, const long long* ll_ptrs, int rows_per_rank, unsigned* arrive, unsigned* epoch,
+                              unsigned* status, cudaStream_t stream);
+int forge_tp_tagged_reduce_norm(int tp_size, int tp_rank, const void* part, int rows_per_rank, const unsigned* part_epoch,
+                                const long long* y_ptrs, unsigned* arrive, unsigned* epoch, long long timeout_ns,
+                                const unsigned* local_only, const void* residual_in, void* residual_out, const void* w, void* y,
+                                int rows, int H, float eps, unsigned* status, cudaStream_t stream);
 int forge_tp_reduce_rms_norm(int tp_size, int tp_rank, const long long* part_ptrs, long long mc_part, const void* slots,
                              const unsigned* signal, const unsigned* epoch, long long timeout_ns, const unsigned* local_only,
                              const void* residual_in, void* sum_out, const void* w, void* y, int rows, int H, float eps,
@@ -414,6 +421,41 @@ void gemm_tp(const Tensor& x, const Tensor& w, int64_t part, int64_t tune, int64
         "forge_gemm_bf16_tp");
 }
 
+// Row-parallel GEMM of at most 256 rows whose epilogue stores every output row as tagged words into the buffer of the rank
+// that owns the row (ll_ptrs[p]: rank p's buffer, [ranks][rows_per_rank][features] 32-bit words).
+void gemm_tp_tagged(const Tensor& x, const Tensor& w, int64_t tune, int64_t tp_rank, const PtrList& ll_ptrs, int64_t rows_per_rank,
+                    int64_t arrive, int64_t epoch, const Tensor& status) {
+  CHECK_BF16(x); CHECK_BF16(w);
+  TORCH_CHECK(x.is_cuda() && w.is_cuda() && x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1, "gemm_tp_tagged: operands");
+  TORCH_CHECK(w.size(1) == x.size(1) && ll_ptrs.size() >= 2, "gemm_tp_tagged: shapes");
+  const c10::cuda::CUDAGuard guard(x.device());
+  check(forge_gemm_bf16_tp_tagged(x.data_ptr(), static_cast<int>(x.stride(0)), w.data_ptr(), static_cast<int>(w.stride(0)),
+                                  static_cast<int>(x.size(0)), static_cast<int>(w.size(0)), static_cast<int>(x.size(1)),
+                                  static_cast<int>(tune), static_cast<int>(ll_ptrs.size()), static_cast<int>(tp_rank), ptrs(ll_ptrs),
+                                  static_cast<int>(rows_per_rank), word(arrive), word(epoch), status_ptr(status), stream_of(x)),
+        "forge_gemm_bf16_tp_tagged");
+}
+
+// Consumer of gemm_tp_tagged: reduce this rank's rows, residual add + RMSNorm, exchange of the normalised rows; y gets
+// all rows, `residual` is updated on this rank's rows (row % ranks == rank) only.
+void tp_tagged_reduce_norm(int64_t tp_rank, int64_t part, int64_t rows_per_rank, int64_t part_epoch, const PtrList& y_ptrs,
+                           int64_t arrive, int64_t epoch, int64_t timeout_ns, int64_t local_only,
+                           const c10::optional<Tensor>& residual_in, Tensor& residual_out, const Tensor& w, Tensor& y, double eps,
+                           const Tensor& status) {
+  CHECK_CUDA_CONTIG(residual_out); CHECK_BF16(residual_out); CHECK_CUDA_CONTIG(w); CHECK_BF16(w); CHECK_CUDA_CONTIG(y); CHECK_BF16(y);
+  const int64_t H = residual_out.size(-1), rows = residual_out.numel() / H;
+  TORCH_CHECK(y_ptrs.size() >= 2 && w.numel() == H && y.numel() == residual_out.numel() && part != 0, "tp_tagged_reduce_norm: shapes");
+  const void* res = nullptr;
+  if (residual_in.has_value()) { CHECK_CUDA_CONTIG(*residual_in); CHECK_BF16(*residual_in); TORCH_CHECK(residual_in->numel() == residual_out.numel()); res = residual_in->data_ptr(); }
+  const c10::cuda::CUDAGuard guard(residual_out.device());
+  check(forge_tp_tagged_reduce_norm(static_cast<int>(y_ptrs.size()), static_cast<int>(tp_rank), reinterpret_cast<const void*>(part),
+                                    static_cast<int>(rows_per_rank), word(part_epoch), ptrs(y_ptrs), word(arrive), word(epoch),
+                                    timeout_ns, word(local_only), res, residual_out.data_ptr(), w.data_ptr(), y.data_ptr(),
+                                    static_cast<int>(rows), static_cast<int>(H), static_cast<float>(eps), status_ptr(status),
+                                    stream_of(residual_out)),
+        "forge_tp_tagged_reduce_norm");
+}
+
 // sum_out = sum over ranks of the partial rows (+ residual_in); y = rms_norm(sum_out) * w when y is given.
 // part_ptrs empty: the rows were written into `slots` (a local address) by their owners and are only copied.
 void tp_reduce_rms_norm(int64_t tp_size, int64_t tp_rank, const PtrList& part_ptrs, int64_t mc_part, int64_t slots,
@@ -503,6 +545,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_fp8_block", &gemm_fp8_block);
   m.def("gemm_fp8_splits", &gemm_fp8_splits);
   m.def("gemm_tp", &gemm_tp);
+  m.def("gemm_tp_tagged", &gemm_tp_tagged);
+  m.def("tp_tagged_reduce_norm", &tp_tagged_reduce_norm);
   m.def("tp_reduce_rms_norm", &tp_reduce_rms_norm);
   m.def("tp_embedding_push", &tp_embedding_push);
   m.def("tp_rows_publish", &tp_rows_publish);

@@ -42,11 +42,13 @@ namespace forge {
 
 constexpr int kMaxTp = 8;
 
-// What a producer needs to announce completion to all ranks and, for owner-writes pushes, where to store.
+// What a producer needs to announce completion to all ranks and, for pushes, where to store.
 struct TpPush {
   int size;                              // <= 1: not tensor-parallel, fields below unused
   int rank;
-  __nv_bfloat16* slot[kMaxTp];           // owner-writes pushes: peer p's copy of the destination buffer (slot [rank] for pairs)
+  int ll;                                // 1: tagged-word push of a row-parallel GEMM (see "tagged words" below); signal[] unused
+  int rows_per_rank;                     // ll: rows of one source rank's area in an owner's buffer
+  __nv_bfloat16* slot[kMaxTp];           // pushes: peer p's copy of the destination buffer (slot [rank] for pairs)
   unsigned* signal[kMaxTp];              // peer p: address of word [rank] in p's signal array of this site
   unsigned* arrive;                      // local: CTAs finished in the current launch
   unsigned* epoch;                       // local: completed productions of this rank at this site
@@ -73,6 +75,24 @@ struct TpReduceSrc {
   // Measurement mode: when the word is non-zero the kernels skip every wait, read only this rank's own partial and
   // store only locally, i.e. they do the same arithmetic and local memory traffic without the exchange.  The
   // results are wrong on purpose; step time minus the time measured this way is the exposed communication.
+  const unsigned* local_only;
+};
+
+// Tagged words (decode-sized exchanges, where latency decides).  Every pair of bf16 values travels as one 8-byte word
+// {payload, tag}; the tag is the exchange's epoch, which sender and receiver both derive from their own counters.  An
+// aligned 8-byte store arrives whole, so a receiver that polls the word until the tag matches has the payload: no
+// fence, no completion flag and no second round trip.  The GEMM epilogue stores each output row straight into the
+// buffer of the rank that owns the row (row % size); that rank adds the sources' words, applies residual + RMSNorm and
+// sends the normalised row, again as tagged words, to every other rank.  Traffic per direction: ~2 x the tensor.
+// A buffer row holds `width` 32-bit words for `width` features: word 2k = features 2k and 2k + 1, word 2k + 1 = tag.
+struct TpTagged {
+  int size, rank, rows_per_rank;
+  const uint32_t* part;                  // local: [size sources][rows_per_rank][width] words, written by the sources' GEMMs
+  uint32_t* y[kMaxTp];                   // every rank's [rows][width] words for normalised rows (y[rank] is local)
+  unsigned* arrive;                      // private counters of the normalised-rows site
+  unsigned* epoch;
+  const unsigned* part_epoch;            // this rank's epoch at the GEMM's site (advanced by its own GEMM)
+  long long timeout_ns;
   const unsigned* local_only;
 };
 
@@ -110,6 +130,14 @@ __device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
   asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ void st_volatile_v4(void* p, uint4 v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -134,6 +162,34 @@ __device__ __forceinline__ void tp_push_done(const TpPush& tp, unsigned total_ct
 }
 
 __device__ __forceinline__ bool tp_local_only(const unsigned* flag) { return flag != nullptr && *flag != 0u; }
+
+// Two tagged words (four bf16 values) at `p`: polls until both tags equal `tag` or the time limit passes.
+__device__ __forceinline__ uint4 tp_poll_tagged(const uint32_t* p, unsigned tag, long long timeout_ns, unsigned* status) {
+  uint4 v = ld_volatile_v4(p);
+  if (v.y == tag && v.w == tag) return v;
+  const unsigned long long t0 = global_timer_ns();
+  for (;;) {
+    v = ld_volatile_v4(p);
+    if (v.y == tag && v.w == tag) return v;
+    if (global_timer_ns() - t0 > static_cast<unsigned long long>(timeout_ns)) {
+      set_status(status, kStatusFlagTimeout);
+      return v;
+    }
+  }
+}
+
+// Producer tail of the tagged-word push: nothing to announce (the data carries its tag); the last CTA of the grid
+// advances this rank's epoch for the consumer kernel that follows in the stream.
+__device__ __forceinline__ void tp_tagged_done(const TpPush& tp, unsigned total_ctas) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(tp.arrive, 1u);
+    if (prev == total_ctas - 1) {
+      atomicExch(tp.arrive, 0u);
+      *tp.epoch = *tp.epoch + 1;
+    }
+  }
+}
 
 // Returns once every rank's signal word reached `want`, or after the time limit.  Call with all threads of the
 // CTA; contains __syncthreads().

@@ -67,14 +67,16 @@ class _Layer:
 
 def _row_linear_rounds(ops, tp, rank, world, g, sizes, mode):
     """Row-parallel layer + exchange + residual add + RMSNorm for every M of ``sizes`` (sites alternate, epochs advance,
-    buffers are reused).  mode: "one" forces the one-shot consumer, "two" the reduce-scatter + all-gather one, "auto"
-    leaves the byte threshold alone.  Returns the worst error relative to the largest expected magnitude."""
+    buffers are reused).  mode: "auto" = what the engine does (tagged words up to 256 rows, pulls above); "one" / "two"
+    switch the tagged path off and force the one-shot / the reduce-scatter + all-gather pull consumer.  Returns the worst
+    error relative to the largest expected magnitude."""
     from tinyllmforge_b200.ops import ref
     from tinyllmforge_b200.parallel.symm import SITE_DOWN, SITE_O
     H, Kfull = 1024, 2048
     f = ops.fused
-    keep = f.two_shot_bytes
-    f.two_shot_bytes = {"one": 1 << 60, "two": -1, "auto": keep}[mode]
+    keep = (f.two_shot_bytes, f.tagged)
+    f.two_shot_bytes = {"one": 1 << 60, "two": -1, "auto": keep[0]}[mode]
+    f.tagged = keep[1] and mode == "auto"
     w_full = (torch.randn(H, Kfull, device="cuda", generator=g) * 0.05).bfloat16()
     norm_w = (1 + 0.1 * torch.randn(H, device="cuda", generator=g)).bfloat16()
     kshard = Kfull // world
@@ -85,7 +87,8 @@ def _row_linear_rounds(ops, tp, rank, world, g, sizes, mode):
         res = torch.randn(M, H, device="cuda", generator=g).bfloat16()
         x = x_full[:, rank * kshard:(rank + 1) * kshard].contiguous()
         res_in = res.clone()
-        two = f.two_shot(M, H)
+        tagged = f.use_tagged(M, H)
+        two = tagged or f.two_shot(M, H)
         y, res_out = ops.row_linear_add_rms_norm(x, layer, res_in, norm_w, 1e-6, SITE_O if it % 2 == 0 else SITE_DOWN)
         y = y.clone()                                  # two-shot: y is the broadcast buffer, reused by the next exchange
         h = x_full.float() @ w_full.float().t()
@@ -95,11 +98,11 @@ def _row_linear_rounds(ops, tp, rank, world, g, sizes, mode):
         e2 = ((y.float() - want_y.float()).abs().max() / want_y.float().abs().max()).item()
         worst = max(worst, e1, e2)
         assert e1 <= 3e-2 and e2 <= 3e-2, (mode, M, two, e1, e2)
-        if f.multicast_ptr == 0:
-            # plain peer loads add in rank order: every rank must hold bit-identical rows
+        if f.multicast_ptr == 0 or tagged:
+            # plain peer loads add in rank order, and a tagged row is computed by one rank: bit-identical rows everywhere
             both = tp.all_gather_stack(y)
             assert all(torch.equal(both[0], both[r]) for r in range(world)), (mode, M)
-    f.two_shot_bytes = keep
+    f.two_shot_bytes, f.tagged = keep
     return worst
 
 
@@ -118,7 +121,7 @@ def case_row_linear(rank, world):
             ops.close()
             continue                                     # no multicast support: the second round covers the only path there is
         g = torch.Generator(device="cuda").manual_seed(1)           # same stream of numbers on every rank
-        worst = max(worst, _row_linear_rounds(ops, tp, rank, world, g, [1, 7, 64, 200, 256, 33, 300, 4096, 256], "auto"))
+        worst = max(worst, _row_linear_rounds(ops, tp, rank, world, g, [1, 7, 64, 200, 256, 33, 300, 4096, 256] + list(range(2, 257, 23)), "auto"))
         worst = max(worst, _row_linear_rounds(ops, tp, rank, world, g, [1, 2, 3, 5, 8, 16, 31, 64, 100, 128, 255, 256, 300, 1000], "two"))
         worst = max(worst, _row_linear_rounds(ops, tp, rank, world, g, list(range(1, 257, 17)) + [300, 4096], "one"))
         # standalone all-reduce and barrier through the same region
@@ -199,8 +202,10 @@ def case_engine(rank, world):
     for name, comm, two_shot_bytes in (("fused", "fused", None), ("fused-two-shot", "fused", "-1"), ("nccl", "nccl", None)):
         if two_shot_bytes is None:
             os.environ.pop("FORGE_TP_TWO_SHOT_BYTES", None)
+            os.environ.pop("FORGE_TP_TAGGED", None)
         else:
-            os.environ["FORGE_TP_TWO_SHOT_BYTES"] = two_shot_bytes      # every exchange as reduce-scatter + all-gather
+            os.environ["FORGE_TP_TWO_SHOT_BYTES"] = two_shot_bytes      # every exchange as reduce-scatter + all-gather pulls
+            os.environ["FORGE_TP_TAGGED"] = "0"
         llm = LLM("tp-test", hf_config=cfg, load_format="dummy", skip_tokenizer_init=True, max_model_len=1024,
                   max_num_batched_tokens=4096, max_num_seqs=32, num_kvcache_blocks=64, tensor_parallel_size=world, comm=comm)
         res = llm.generate(prompts, sp, use_tqdm=False)
@@ -208,6 +213,7 @@ def case_engine(rank, world):
         llm.worker.ops.check_status()
         llm.exit()
     os.environ.pop("FORGE_TP_TWO_SHOT_BYTES", None)
+    os.environ.pop("FORGE_TP_TAGGED", None)
     if rank == 0:
         agree = {}
         for name in ("fused", "fused-two-shot"):

@@ -303,10 +303,14 @@ class CudaOps:
     def row_linear_add_rms_norm(self, x, layer, residual, norm_weight, eps, site):
         """Row-parallel GEMM + sum over ranks + residual add + RMSNorm -> (normed, residual).
 
-        Fused path: the GEMM stores its partial sums into this rank's buffer of the symmetric region and its last CTA
+        Fused path, up to 256 rows (decode): the GEMM epilogue stores every output row, as tagged words, into the memory
+        of the rank that owns the row; the consumer kernel adds the ranks' rows it owns, applies residual + norm and sends
+        the normalised rows to the other ranks the same way: no flags, no fences, two one-way NVLink trips.  More rows
+        (prefill): the GEMM stores its partial sums into this rank's buffer of the symmetric region and its last CTA
         signals every rank; one consumer kernel waits for all ranks, pulls the sum over NVLink (one-shot for few bytes,
         reduce-scatter + all-gather for many, see ``_reduce_norm``), adds the residual and normalises.  No library
-        collective is involved at any batch size."""
+        collective is involved at any batch size.  In the tagged and the two-shot forms ``residual`` holds only this
+        rank's rows (row % tp == rank) afterwards, which is all the next exchange of the same step reads."""
         tp = layer.tp
         if tp.size == 1:
             return self.add_rms_norm(self.linear(x, layer.weight), residual, norm_weight, eps)
@@ -314,6 +318,16 @@ class CudaOps:
         if self.fused is None or M > self.fused.max_tokens or H != self.fused.hidden:
             return self.add_rms_norm(tp.all_reduce(self.linear(x, layer.weight)), residual, norm_weight, eps)
         st = self.fused.sites[site]
+        if self.fused.use_tagged(M, H) and not isinstance(layer.weight, Fp8BlockWeight):
+            # decode-sized: rows travel as tagged words from the GEMM epilogue to their owners and back normalised
+            from ..parallel.symm import SITE_GATHER
+            f, ag = self.fused, self.fused.sites[SITE_GATHER]
+            self.C.gemm_tp_tagged(x, layer.weight, 0, tp.rank, st.ll_ptrs, f.tagged_rows_per_rank, st.arrive, st.epoch, self.status)
+            y = torch.empty(M, H, dtype=x.dtype, device=x.device)
+            self.C.tp_tagged_reduce_norm(tp.rank, st.ll_local, f.tagged_rows_per_rank, st.epoch, ag.ll_ptrs, ag.arrive, ag.epoch,
+                                         f.timeout_ns, f.local_only, residual, residual, norm_weight, y, eps, self.status)
+            self.launches += 2
+            return y, residual
         if isinstance(layer.weight, Fp8BlockWeight):
             # the block-scaled GEMM has no signalling epilogue: publish its output with a copy kernel
             self.C.tp_rows_publish(self.linear_fp8(x, layer.weight), st.local_buf, tp.rank, st.signal_ptrs, st.arrive, st.epoch)

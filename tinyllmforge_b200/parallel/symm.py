@@ -14,6 +14,9 @@ Region layout (identical on every rank, byte offsets):
     part_d    max_tokens x H bf16        the same for down_proj
     part_ar   256 x H bf16               operand of the standalone all-reduce / barrier
     y         max_tokens x H bf16        normalised rows, each broadcast by the rank that reduced it (two-shot exchange)
+    ll_o      tp x ceil(256/tp) x H words   decode-sized o_proj exchange: tagged partial rows this rank owns, one area per
+    ll_d                                    source rank (every bf16 pair travels as {payload, tag}); the same for down_proj
+    ll_y      256 x H words              tagged normalised rows sent by their owners
 
 Replaces the NCCL calls at tinyvllm/layers/linear.py:183 and tinyvllm/layers/embed_head.py:41,66-67.
 """
@@ -28,6 +31,7 @@ SITE_EMBED, SITE_O, SITE_DOWN, SITE_SAMPLE, SITE_ALLREDUCE, SITE_GATHER = 0, 1, 
 NUM_SITES = 8
 MAX_ALLREDUCE_ROWS = 256     # rows of `hidden` elements the standalone all-reduce accepts
 MAX_PAIR_ROWS = 512
+MAX_TAGGED_ROWS = 256        # rows of a decode-sized exchange (the weight-tile GEMM's limit)
 
 
 def _align(n: int, a: int = 256) -> int:
@@ -47,6 +51,8 @@ class Site:
     mc_buf: int = 0            # NVSwitch multicast address of the buffer (0: no multicast support)
     slot_ptrs: list[int] = field(default_factory=list)   # per-rank slots (pairs): peer p -> slot [rank] in p's buffer
     slot_stride: int = 0       # distance between slots, in bf16 elements
+    ll_ptrs: list[int] = field(default_factory=list)     # every rank's tagged-word buffer of the site, rank order
+    ll_local: int = 0
 
 
 class FusedTPComm:
@@ -61,12 +67,15 @@ class FusedTPComm:
         # round: switch over when the extra bytes cost more than that round
         self.two_shot_bytes = int(os.environ.get("FORGE_TP_TWO_SHOT_BYTES", str(2 << 20)))
         H = hidden_size
+        self.tagged = os.environ.get("FORGE_TP_TAGGED", "1") != "0"      # decode-sized exchanges as tagged words (else: pulls)
+        self.tagged_rows_per_rank = (MAX_TAGGED_ROWS + self.size - 1) // self.size
+        ll_bytes = self.size * self.tagged_rows_per_rank * H * 4
         rows_bytes = max_tokens * H * 2
         off = {}
         cur = 0
         for name, nbytes in (("signals", NUM_SITES * 8 * 4), ("pairs", self.size * MAX_PAIR_ROWS * 8), ("embed", rows_bytes),
                              ("part_o", rows_bytes), ("part_d", rows_bytes), ("part_ar", MAX_ALLREDUCE_ROWS * H * 2),
-                             ("y", rows_bytes)):
+                             ("y", rows_bytes), ("ll_o", ll_bytes), ("ll_d", ll_bytes), ("ll_y", MAX_TAGGED_ROWS * H * 4)):
             off[name] = cur
             cur = _align(cur + nbytes)
         self.offsets, self.nbytes = off, cur
@@ -99,6 +108,10 @@ class FusedTPComm:
                 if slot_bytes:
                     s.slot_ptrs = [b + off[name] + self.rank * slot_bytes for b in self.bases]
                     s.slot_stride = slot_bytes // 2
+            if index in (SITE_O, SITE_DOWN, SITE_GATHER):
+                ll = {SITE_O: "ll_o", SITE_DOWN: "ll_d", SITE_GATHER: "ll_y"}[index]
+                s.ll_ptrs = [b + off[ll] for b in self.bases]
+                s.ll_local = me + off[ll]
             return s
 
         self.sites = {
@@ -109,6 +122,10 @@ class FusedTPComm:
             SITE_ALLREDUCE: site(SITE_ALLREDUCE, "part_ar"),
             SITE_GATHER: site(SITE_GATHER, "y"),
         }
+
+    def use_tagged(self, rows: int, width: int) -> bool:
+        """Decode-sized exchange of the model's hidden width: tagged words pushed from the GEMM epilogue."""
+        return self.tagged and rows <= MAX_TAGGED_ROWS and width == self.hidden and width % 8 == 0
 
     def two_shot(self, rows: int, width: int) -> bool:
         """Reduce-scatter + all-gather instead of every rank pulling every row?  Depends only on the shape, so all
@@ -124,7 +141,8 @@ class FusedTPComm:
         """Measurement mode (stream-ordered): the exchange kernels skip their waits and peer traffic and work on this
         rank's own data only.  Results are wrong on purpose; the time difference to a normal run is the exposed
         communication.  Callers synchronise all ranks (device and host) before switching either way."""
-        self.counters[2 * NUM_SITES] = 1 if on else 0
+        with torch.inference_mode():           # the counters may have been created under inference mode (the worker's constructor)
+            self.counters[2 * NUM_SITES] = 1 if on else 0
 
     def close(self):
         self.handle = None
