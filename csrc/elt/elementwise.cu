@@ -406,8 +406,12 @@ extern "C" int forge_silu_mul(const void* x, void* out, long long rows, int I, c
 // ---------------------------------------------------------------------------------------------------------
 // Row gathers.  embedding: out[t] = id in [start, start + n) ? W[id - start] : 0.  gather_rows: out[s] = x[idx[s]].
 // ---------------------------------------------------------------------------------------------------------
+// ssq (optional): fp32 [num_ssq][T].  ssq[0][t] = sum of squares of the row written (so the first linear layer can apply
+// the first RMSNorm as a row scale); ssq[1..][t] = 0 (the accumulators the residual-adding GEMMs of this step add into).
 __global__ void __launch_bounds__(128) embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ w,
-                                                        __nv_bfloat16* __restrict__ out, int H, int vocab_start, int vocab_n) {
+                                                        __nv_bfloat16* __restrict__ out, int H, int vocab_start, int vocab_n,
+                                                        float* __restrict__ ssq, int num_ssq, int T) {
+  __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -415,15 +419,27 @@ __global__ void __launch_bounds__(128) embedding_kernel(const int* __restrict__ 
   const bool ok = local >= 0 && local < vocab_n;
   const uint4* src = reinterpret_cast<const uint4*>(w + static_cast<size_t>(ok ? local : 0) * H);
   uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H);
-  for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) dst[i] = ok ? src[i] : make_uint4(0, 0, 0, 0);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < (H >> 3); i += blockDim.x) {
+    const uint4 v = ok ? src[i] : make_uint4(0, 0, 0, 0);
+    dst[i] = v;
+    const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) ss += bf16_lo(vw[j]) * bf16_lo(vw[j]) + bf16_hi(vw[j]) * bf16_hi(vw[j]);
+  }
+  if (ssq != nullptr) {
+    ss = block_sum(ss, red);
+    if (threadIdx.x == 0) ssq[t] = ss;
+    for (int s = 1 + threadIdx.x; s < num_ssq; s += blockDim.x) ssq[static_cast<size_t>(s) * T + t] = 0.f;
+  }
 }
 
-extern "C" int forge_embedding(const int* ids, const void* w, void* out, int T, int H, int vocab_start, int vocab_n,
-                               cudaStream_t stream) {
+extern "C" int forge_embedding(const int* ids, const void* w, void* out, int T, int H, int vocab_start, int vocab_n, float* ssq,
+                               int num_ssq, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H & 7) return -1;
   return launch_kernel(embedding_kernel, dim3(T), dim3(128), 0, stream, 0, ids, static_cast<const __nv_bfloat16*>(w),
-                       static_cast<__nv_bfloat16*>(out), H, vocab_start, vocab_n) == cudaSuccess ? 0 : -2;
+                       static_cast<__nv_bfloat16*>(out), H, vocab_start, vocab_n, ssq, num_ssq, T) == cudaSuccess ? 0 : -2;
 }
 
 __global__ void __launch_bounds__(128) gather_rows_kernel(const int* __restrict__ idx, const __nv_bfloat16* __restrict__ x,

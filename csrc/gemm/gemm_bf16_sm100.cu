@@ -44,6 +44,30 @@ __device__ __forceinline__ void trace_point(int cta, int k) {
   }
 }
 
+// Optional fusion of the RMSNorm that precedes / the residual add that follows a linear layer (both null: plain GEMM).
+//
+//   in_ssq   the activation rows are NOT normalised: x is the residual stream itself, the norm's weight vector was
+//            folded into the columns of W when the model was loaded, and in_ssq[row] holds the sum of squares of the
+//            activation row.  The epilogue scales output row r by rsqrt(in_ssq[r] / K + eps), which is exactly what
+//            normalising the input row first would give (the reference normalises in a kernel of its own:
+//            tinyvllm/layers/layernorm.py:21-45).
+//   residual out[r][c] = bf16(bf16(acc) + out[r][c]): `out` is the residual stream, updated in place, and
+//            out_ssq[r] += sum of the squares of the new values (fp32 atomics; the caller zeroes it), so that the
+//            NEXT linear layer can apply its norm as a row scale.  Replaces the add half of add_rms_forward.
+struct GemmFuse {
+  const float* in_ssq;
+  float in_width_inv;
+  float eps;
+  int add_residual;
+  float* out_ssq;
+};
+
+__device__ __forceinline__ float fuse_row_scale(const GemmFuse& f, int row, int rows) {
+  if (f.in_ssq == nullptr) return 1.f;
+  return row < rows ? rsqrtf(f.in_ssq[row] * f.in_width_inv + f.eps) : 0.f;
+}
+__device__ __forceinline__ float bf16_round_g(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
 constexpr int tmem_cols_for(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
 
 // =========================================================================================================
@@ -72,7 +96,7 @@ template <int BLOCK_C, int kEpi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                    __nv_bfloat16* __restrict__ out, int ldo, int m_total, int n_total, int K, int dual_off, unsigned* status,
-                   const TpPush push) {
+                   const TpPush push, const GemmFuse fuse) {
   using Cfg = TokCfg<BLOCK_C, kEpi>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -187,6 +211,8 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       tcgen05_fence_after();
       if (ok) {
         constexpr int kChunk = BLOCK_C >= 32 ? 32 : 16;
+        const float row_scale = fuse_row_scale(fuse, r, m_total);          // 1 unless the input norm is folded in
+        float ssq = 0.f;                                                   // of the new residual values of this row (this tile)
 #pragma unroll 1
         for (int cc = 0; cc < BLOCK_C; cc += kChunk) {
           uint32_t v[kChunk];
@@ -200,8 +226,8 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           float f[kChunk];
 #pragma unroll
           for (int j = 0; j < kChunk; ++j) {
-            f[j] = __uint_as_float(v[j]);
-            if constexpr (kEpi == kEpiSiluMul) f[j] = silu(f[j]) * __uint_as_float(u[j]);
+            f[j] = __uint_as_float(v[j]) * row_scale;
+            if constexpr (kEpi == kEpiSiluMul) f[j] = silu(f[j]) * (__uint_as_float(u[j]) * row_scale);
           }
           const int c = c0 + cc;
           if (r < m_total) {
@@ -209,6 +235,16 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             if (c + kChunk <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
               for (int j = 0; j < kChunk; j += 8) {
+                if (fuse.add_residual) {
+                  const uint4 old = *reinterpret_cast<const uint4*>(dst + j);
+                  const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+                  for (int k = 0; k < 4; ++k) {
+                    f[j + 2 * k] = bf16_round_g(bf16_round_g(f[j + 2 * k]) + bf16_lo(ow[k]));
+                    f[j + 2 * k + 1] = bf16_round_g(bf16_round_g(f[j + 2 * k + 1]) + bf16_hi(ow[k]));
+                    ssq += f[j + 2 * k] * f[j + 2 * k] + f[j + 2 * k + 1] * f[j + 2 * k + 1];
+                  }
+                }
                 uint4 pk;
                 pk.x = pack_bf16x2(f[j], f[j + 1]);
                 pk.y = pack_bf16x2(f[j + 2], f[j + 3]);
@@ -219,10 +255,18 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             } else {
 #pragma unroll
               for (int j = 0; j < kChunk; ++j)
-                if (c + j < n_total) dst[j] = __float2bfloat16_rn(f[j]);
+                if (c + j < n_total) {
+                  float val = f[j];
+                  if (fuse.add_residual) {
+                    val = bf16_round_g(bf16_round_g(val) + __bfloat162float(dst[j]));
+                    ssq += val * val;
+                  }
+                  dst[j] = __float2bfloat16_rn(val);
+                }
             }
           }
         }
+        if (fuse.out_ssq != nullptr && r < m_total) atomicAdd(fuse.out_ssq + r, ssq);
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -289,7 +333,7 @@ template <int BLOCK_C, int kEpi, bool kDeep>
 __global__ void __launch_bounds__(kGemmThreads, kDeep ? 1 : 2)
 gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                     __nv_bfloat16* __restrict__ out, int ldo, int n_total, int m_total, int K, int kb_per_split,
-                    int dual_off, unsigned* status, const TpPush push) {
+                    int dual_off, unsigned* status, const TpPush push, const GemmFuse fuse_io) {
   using Cfg = WgtCfg<BLOCK_C, kEpi, kDeep>;
   extern __shared__ uint8_t smem_raw[];
   // The dynamic shared window starts at the same offset in every CTA of the cluster, so equal local
@@ -428,7 +472,10 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
               if constexpr (kChunk == 32) tmem_ld_x32(taddr + BLOCK_C, u); else tmem_ld_x16(taddr + BLOCK_C, u);
               tmem_ld_wait();
 #pragma unroll
-              for (int j = 0; j < kChunk; ++j) v[j] = __float_as_uint(silu(__uint_as_float(v[j])) * __uint_as_float(u[j]));
+              for (int j = 0; j < kChunk; ++j) {
+                const float sc = fuse_row_scale(fuse_io, tok0 + cc + j, m_total);      // column = token; same address for the whole warp
+                v[j] = __float_as_uint(silu(__uint_as_float(v[j]) * sc) * (__uint_as_float(u[j]) * sc));
+              }
             }
           }
           tmem_ld_wait();
@@ -476,8 +523,12 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
           for (int u = 0; u < 2; ++u) {
             const int lc = lc0 + 4 * u;
-            if (lc >= cpc) continue;
+            if (lc >= cpc) continue;                       // uniform for the warp
             float4 v = a[u];
+            const int c = tok0 + static_cast<int>(split) * cpc + lc;
+            const int n = r0 + lane * 4;
+            // the input norm folded in: scale this token's column (the single-split SiLU path scaled on the way out of tensor memory)
+            const float sc = (kEpi == kEpiSiluMul && fuse) ? 1.f : fuse_row_scale(fuse_io, c, m_total);
             if constexpr (kEpi == kEpiSiluMul) {
               if (!fuse) {
                 float4* g = reinterpret_cast<float4*>(gate_red + lc * kBlockR + lane * 4);   // same thread in both rounds
@@ -486,11 +537,13 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                   continue;
                 }
                 const float4 gv = *g;
-                v.x = silu(gv.x) * v.x; v.y = silu(gv.y) * v.y; v.z = silu(gv.z) * v.z; v.w = silu(gv.w) * v.w;
+                v.x = silu(gv.x * sc) * (v.x * sc); v.y = silu(gv.y * sc) * (v.y * sc);
+                v.z = silu(gv.z * sc) * (v.z * sc); v.w = silu(gv.w * sc) * (v.w * sc);
               }
+            } else {
+              v.x *= sc; v.y *= sc; v.z *= sc; v.w *= sc;
             }
-            const int c = tok0 + static_cast<int>(split) * cpc + lc;
-            const int n = r0 + lane * 4;
+            float ssq = 0.f;
             if (c < m_total && n < n_total) {
               if (push.size > 1 && push.ll) {
                 // decode-sized exchange: the row goes, as tagged words, straight to the rank that owns it (a peer store
@@ -499,20 +552,38 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                 uint32_t* d = reinterpret_cast<uint32_t*>(push.slot[owner]) +
                               (static_cast<size_t>(push.rank) * push.rows_per_rank + j) * ldo + n;
                 st_volatile_v4(d, make_uint4(pack_bf16x2(v.x, v.y), ll_tag, pack_bf16x2(v.z, v.w), ll_tag));
-                continue;
-              }
-              // Row-parallel layer under tensor parallelism, many rows: `out` is this rank's partial buffer in symmetric
-              // memory; the stores are local, the consumer kernels of all ranks pull the sum over NVLink (tp_comm.cuh).
-              __nv_bfloat16* dst = out + static_cast<size_t>(c) * ldo + n;
-              if (n + 4 <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0)) {
-                uint2 pk;
-                pk.x = pack_bf16x2(v.x, v.y);
-                pk.y = pack_bf16x2(v.z, v.w);
-                *reinterpret_cast<uint2*>(dst) = pk;
               } else {
-                const float f[4] = {v.x, v.y, v.z, v.w};
-                for (int j = 0; j < 4 && n + j < n_total; ++j) dst[j] = __float2bfloat16_rn(f[j]);
+                // Row-parallel layer under tensor parallelism, many rows: `out` is this rank's partial buffer in symmetric
+                // memory; the stores are local, the consumer kernels of all ranks pull the sum over NVLink (tp_comm.cuh).
+                __nv_bfloat16* dst = out + static_cast<size_t>(c) * ldo + n;
+                if (n + 4 <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0)) {
+                  if (fuse_io.add_residual) {               // `out` is the residual stream: add in place
+                    const uint2 old = *reinterpret_cast<const uint2*>(dst);
+                    v.x = bf16_round_g(bf16_round_g(v.x) + bf16_lo(old.x)); v.y = bf16_round_g(bf16_round_g(v.y) + bf16_hi(old.x));
+                    v.z = bf16_round_g(bf16_round_g(v.z) + bf16_lo(old.y)); v.w = bf16_round_g(bf16_round_g(v.w) + bf16_hi(old.y));
+                    ssq = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                  }
+                  uint2 pk;
+                  pk.x = pack_bf16x2(v.x, v.y);
+                  pk.y = pack_bf16x2(v.z, v.w);
+                  *reinterpret_cast<uint2*>(dst) = pk;
+                } else {
+                  const float f[4] = {v.x, v.y, v.z, v.w};
+                  for (int j = 0; j < 4 && n + j < n_total; ++j) {
+                    float val = f[j];
+                    if (fuse_io.add_residual) {
+                      val = bf16_round_g(bf16_round_g(val) + __bfloat162float(dst[j]));
+                      ssq += val * val;
+                    }
+                    dst[j] = __float2bfloat16_rn(val);
+                  }
+                }
               }
+            }
+            if (fuse_io.out_ssq != nullptr) {              // uniform for the warp: all 32 lanes hold features of token c
+#pragma unroll
+              for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+              if (lane == 0 && c < m_total) atomicAdd(fuse_io.out_ssq + c, ssq);
             }
           }
         }
@@ -579,7 +650,7 @@ extern "C" int forge_gemm_set_trace(unsigned long long* buf) {
 
 template <int BLOCK_C, int kEpi>
 static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int ldw, __nv_bfloat16* out, int ldo, int M,
-                         int n_out, int K, unsigned* status, cudaStream_t stream, const TpPush& push) {
+                         int n_out, int K, unsigned* status, cudaStream_t stream, const TpPush& push, const GemmFuse& fuse) {
   using Cfg = TokCfg<BLOCK_C, kEpi>;
   CUtensorMap tm_x, tm_w;
   if (forge_make_tmap_2d(&tm_x, x, M, K, ldx, kBlockR, 2) != 0) return -2;
@@ -595,7 +666,7 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
   }
   dim3 grid(tiles < num_sms ? tiles : num_sms);
   return launch_kernel(kern, grid, dim3(kGemmThreads), Cfg::kSmemBytes, stream, 0, tm_x, tm_w, out, ldo, M, n_out, K, n_out,
-                       status, push) == cudaSuccess ? 0 : -5;
+                       status, push, fuse) == cudaSuccess ? 0 : -5;
 }
 
 // Cluster size (K splits) of the decode kernel.  Measured on B200 (sweeps over token tile x splits x ring depth for
@@ -620,7 +691,7 @@ static int deep_threshold() {
 
 template <int BLOCK_C, int kEpi, bool kDeep>
 static int launch_weights(const void* x, int ldx, const void* w, int w_rows, int ldw, __nv_bfloat16* out, int ldo, int M,
-                          int n_out, int K, int splits, unsigned* status, cudaStream_t stream, const TpPush& push) {
+                          int n_out, int K, int splits, unsigned* status, cudaStream_t stream, const TpPush& push, const GemmFuse& fuse) {
   using Cfg = WgtCfg<BLOCK_C, kEpi, kDeep>;
   CUtensorMap tm_x, tm_w;
   if (forge_make_tmap_2d(&tm_w, w, w_rows, K, ldw, kBlockR, 2) != 0) return -2;
@@ -632,7 +703,7 @@ static int launch_weights(const void* x, int ldx, const void* w, int w_rows, int
   const int num_kb = (K + kBlockK - 1) / kBlockK;
   const int kb_per_split = (num_kb + splits - 1) / splits;
   return launch_kernel(kern, dim3(tiles, splits, tok_tiles), dim3(kGemmThreads), Cfg::kSmemBytes, stream, splits, tm_w, tm_x,
-                       out, ldo, n_out, M, K, kb_per_split, n_out, status, push) == cudaSuccess ? 0 : -5;
+                       out, ldo, n_out, M, K, kb_per_split, n_out, status, push, fuse) == cudaSuccess ? 0 : -5;
 }
 
 // out[M, n_out] = epilogue(X[M, K] * W[*, K]^T).  epi = 0: W has n_out rows.  epi = 1: W is [2 * n_out, K]
@@ -644,7 +715,8 @@ TpPush make_tp_push(int tp_size, int tp_rank, const long long* slot_ptrs, const 
                     unsigned* epoch);
 
 static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K, int epi,
-                         int force_mode, int tune, unsigned* status, cudaStream_t stream, const TpPush& push) {
+                         int force_mode, int tune, unsigned* status, cudaStream_t stream, const TpPush& push,
+                         const GemmFuse& fuse = GemmFuse{}) {
   const int force_splits = tune & 0xff, force_deep = (tune >> 16) & 0xff;
   int force_bc = (tune >> 8) & 0xff;
   if (M <= 0 || n_out <= 0 || K <= 0) return 0;
@@ -699,8 +771,8 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
     if (force_deep == 1) deep = false;
     if (force_deep == 2) deep = true;
 #define FORGE_W2(BC, EPI)                                                                                                   \
-  (deep ? launch_weights<BC, EPI, true>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, splits, status, stream, push)          \
-        : launch_weights<BC, EPI, false>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, splits, status, stream, push))
+  (deep ? launch_weights<BC, EPI, true>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, splits, status, stream, push, fuse)    \
+        : launch_weights<BC, EPI, false>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, splits, status, stream, push, fuse))
 #define FORGE_W(BC) \
   case BC:          \
     return epi == kEpiSiluMul ? FORGE_W2(BC, kEpiSiluMul) : FORGE_W2(BC, kEpiStore);
@@ -717,8 +789,8 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
   if (force_mode == 1 && (force_bc == 16 || force_bc == 32 || force_bc == 64)) {       // narrow feature tiles: many tokens of a decode step
 #define FORGE_T(BC)                                                                                                           \
   case BC:                                                                                                                    \
-    return epi == kEpiSiluMul ? launch_tokens<BC, kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push)   \
-                              : launch_tokens<BC, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push);
+    return epi == kEpiSiluMul ? launch_tokens<BC, kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse)   \
+                              : launch_tokens<BC, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse);
     switch (force_bc) {
       FORGE_T(16)
       FORGE_T(32)
@@ -726,9 +798,9 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
     }
 #undef FORGE_T
   }
-  if (epi == kEpiSiluMul) return launch_tokens<128, kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push);
-  if (n_out % 256 == 0 || n_out >= 1024) return launch_tokens<256, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push);
-  return launch_tokens<128, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push);
+  if (epi == kEpiSiluMul) return launch_tokens<128, kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse);
+  if (n_out % 256 == 0 || n_out >= 1024) return launch_tokens<256, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse);
+  return launch_tokens<128, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse);
 }
 
 extern "C" int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out,
@@ -740,6 +812,23 @@ extern "C" int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, v
 // Row-parallel GEMM under tensor parallelism: `out` is this rank's partial buffer in symmetric memory (row stride ldo);
 // the kernel's last CTA announces completion to every rank through signal_ptrs (tp_size addresses in peer order).
 // Up to 256 rows run on the weight-tile (decode) kernel, more on the persistent token-tile kernel.
+// The same with the neighbouring norm / residual add fused in (see GemmFuse).  in_ssq: fp32 [M] sums of squares of the
+// rows of x (null: rows are not scaled).  add_residual: out += result in place, out_ssq (fp32 [M], zeroed by the caller,
+// may be null) accumulates the sums of squares of the new rows.
+extern "C" int forge_gemm_bf16_fused(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K,
+                                     int epi, int force_mode, int tune, const float* in_ssq, float eps, int add_residual,
+                                     float* out_ssq, unsigned* status, cudaStream_t stream) {
+  if (add_residual && epi != kEpiStore) return -9;
+  TpPush none = {};
+  GemmFuse fuse = {};
+  fuse.in_ssq = in_ssq;
+  fuse.in_width_inv = 1.0f / static_cast<float>(K);
+  fuse.eps = eps;
+  fuse.add_residual = add_residual;
+  fuse.out_ssq = add_residual ? out_ssq : nullptr;
+  return gemm_dispatch(x, ldx, w, ldw, out, ldo, M, n_out, K, epi, force_mode, tune, status, stream, none, fuse);
+}
+
 // Row-parallel GEMM under tensor parallelism, at most 256 rows: every output row is stored as tagged words into the
 // buffer of the rank that owns it (ll_ptrs[p] = rank p's buffer of [tp_size][rows_per_rank][n_out] 32-bit words).
 // n_out must be a multiple of 4.

@@ -142,6 +142,58 @@ def test_gemm_fp8_block_scaled(ops, M, N, K):
     ops.check_status()
 
 
+# ----------------------------------------------------------------------------- GEMMs with norm / residual fused in
+@pytest.mark.parametrize("M,N,K,mode,silu", [
+    (1, 4096, 1024, 0, False), (8, 4096, 1024, 2, False), (64, 4096, 1024, 0, False), (200, 4096, 1024, 0, False), (256, 6144, 4096, 0, False),
+    (700, 4096, 1024, 0, False), (4096, 2048, 1024, 0, False), (5, 3072, 1024, 0, True), (16, 3072, 1024, 2, True), (100, 3072, 1024, 0, True),
+    (256, 1536, 1024, 2, True), (700, 3072, 1024, 0, True), (130, 12288, 4096, 0, True), (33, 1024, 2048, 2, False),
+])
+def test_gemm_with_folded_input_norm(ops, M, N, K, mode, silu):
+    """(x @ W'.T) * rsqrt(mean(x^2) + eps) per row, W' = W * gamma, against rms_norm(x) * gamma @ W.T in fp32; x is a residual
+    stream with rows of very different magnitudes."""
+    torch.manual_seed(M + N + K)
+    x = (_rand(M, K).float() * torch.logspace(-1, 1.5, M, device="cuda")[:, None]).to(BF)
+    gamma = (1 + 0.2 * torch.randn(K, device="cuda")).to(BF)
+    w = _rand(2 * N if silu else N, K, scale=0.05)
+    w_folded = (w.float() * gamma.float()[None, :]).to(BF)
+    ssq = (x.float() ** 2).sum(-1)
+    got = ops.linear_scaled(x, w_folded, ssq, 1e-6, silu_mul=silu, force_mode=mode)
+    xn = x.float() * torch.rsqrt((x.float() ** 2).mean(-1, keepdim=True) + 1e-6)
+    want = xn @ w_folded.float().t()
+    if silu:
+        want = torch.nn.functional.silu(want[:, :N]) * want[:, N:]
+    _close(got, want, atol=3e-2, rtol=3e-2)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("M,N,K,mode,tune", [
+    (1, 1024, 2048, 0, 0), (7, 1024, 3072, 0, 0), (64, 1024, 2048, 0, 0), (200, 1024, 3072, 0, 0), (256, 1024, 2048, 2, 8), (256, 4096, 12288, 0, 0),
+    (33, 1024, 1024, 2, 1), (300, 1024, 2048, 0, 0), (4096, 1024, 3072, 0, 0), (1000, 4096, 4096, 0, 0), (130, 200, 72, 1, 0), (19, 136, 200, 2, 0),
+])
+def test_gemm_with_residual_add_and_sum_of_squares(ops, M, N, K, mode, tune):
+    """residual += x @ W.T in the epilogue (rounded like a bf16 GEMM followed by a bf16 add) plus the per-row sums of squares."""
+    torch.manual_seed(M * 3 + N + K)
+    x, w = _rand(M, K), _rand(N, K, scale=0.05)
+    residual = _rand(M, N, scale=2.0)
+    want = ((x.float() @ w.float().t()).to(BF).float() + residual.float()).to(BF)
+    ssq = torch.zeros(M, dtype=torch.float32, device="cuda")
+    res = residual.clone()
+    ops.linear_residual(x, w, res, ssq, force_mode=mode, tune=tune)
+    _close(res, want, atol=3e-2, rtol=2e-2)
+    assert torch.allclose(ssq, (res.float() ** 2).sum(-1), rtol=1e-3, atol=1e-3)       # of the values actually stored
+    ops.check_status()
+
+
+def test_embedding_sum_of_squares(ops):
+    V, H, T = 512, 1024, 37
+    table = _rand(V, H)
+    ids = torch.randint(0, V, (T,), device="cuda", dtype=torch.int32)
+    out, ssq = ops.embedding_ssq(ids, table, 0, 5)
+    assert torch.equal(out, table[ids.long()])
+    assert torch.allclose(ssq[0], (out.float() ** 2).sum(-1), rtol=1e-4)
+    assert torch.count_nonzero(ssq[1:]) == 0
+
+
 def test_gemm_strided_input(ops):
     big = _rand(64, 3 * 256)
     x = big[:, 256:512]          # row stride 768, 16-byte aligned start

@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 BS = 256
 
 
-def _models():
+def _models(fold):
     from tinyllmforge_b200 import preset
     from tinyllmforge_b200.models.qwen3 import Qwen3ForCausalLM
     from tinyllmforge_b200.ops.cuda import CudaOps
@@ -35,6 +35,8 @@ def _models():
     with torch.no_grad():
         for (_, a, _, _), (_, b, _, _) in zip(ref.named_parameters(), gpu.named_parameters()):
             b.copy_(a.to(torch.bfloat16))
+    if fold:                 # add + RMSNorm folded into the GEMM epilogues: what the engine runs on one GPU
+        gpu.fold_norm_weights()
     kvh = cfg.num_key_value_heads
     ref.bind_kv_cache(torch.zeros(cfg.num_hidden_layers, 2, 16, kvh, BS, cfg.head_dim))
     gpu.bind_kv_cache(torch.zeros(cfg.num_hidden_layers, 2, 16, kvh, BS, cfg.head_dim, dtype=torch.bfloat16, device=dev))
@@ -60,11 +62,12 @@ def _check(ref, gpu, sb, what):
     return want, agree
 
 
-def test_cuda_model_logits_match_the_fp32_model():
+@pytest.mark.parametrize("fold", [True, False])
+def test_cuda_model_logits_match_the_fp32_model(fold):
     from tinyllmforge_b200 import SamplingParams
     from tinyllmforge_b200.engine.request import Request
     from tinyllmforge_b200.engine.step_batch import build_decode, build_prefill
-    cfg, ref, gpu, ops = _models()
+    cfg, ref, gpu, ops = _models(fold)
     rng = np.random.default_rng(0)
     reqs, nblk = [], 0
     for n in (5, 300, 257, 700):

@@ -87,6 +87,9 @@ class Worker:
                 init_dummy_weights(self.model, config.seed)
             else:
                 load_weights(self.model, config.model)
+            if (self.is_cuda and tp.size == 1 and config.quantization is None and config.dtype == torch.bfloat16
+                    and config.extra.get("fold_norms", True) and not hf.attention_bias):
+                self.model.fold_norm_weights()      # add + RMSNorm become GEMM epilogues (models/qwen3.py)
             if config.quantization == "fp8_block":
                 from ..ops.quant import Fp8BlockWeight
                 for l in self.model.layers:          # the four projections of every block; embeddings and LM head stay bf16

@@ -16,6 +16,8 @@ tinyvllm/utils/context.py), and each block issues a handful of fused ops:
 
     add_rms_norm -> qkv GEMM -> [q/k norm + RoPE + KV store] -> attention -> o GEMM (+ all-reduce)
     add_rms_norm -> gate_up GEMM with SiLU*mul epilogue -> down GEMM (+ all-reduce)
+
+On one GPU with the CUDA op set the add + RMSNorm pairs are folded into the GEMMs around them (``fold_norm_weights``).
 """
 from __future__ import annotations
 
@@ -74,6 +76,7 @@ class Qwen3ForCausalLM:
         self.rope = ref_ops.rope_table(max_positions or cfg.max_position_embeddings, cfg.head_dim, cfg.rope_theta,
                                        self.device)
         self.kv_cache: torch.Tensor | None = None      # [L, 2, blocks, kv_heads, block_size, d]
+        self.norms_folded = False                      # see fold_norm_weights()
 
     # ------------------------------------------------------------------ parameters by Hugging Face name
     def named_parameters(self):
@@ -108,6 +111,43 @@ class Qwen3ForCausalLM:
         assert kv_cache.shape[0] == len(self.layers) and kv_cache.shape[1] == 2
         self.kv_cache = kv_cache
 
+    # ------------------------------------------------------------------ norm folding (single GPU, CUDA op set)
+    def fold_norm_weights(self) -> None:
+        """Fold the weight vectors of ``input_layernorm`` / ``post_attention_layernorm`` into the columns of the linear
+        layer that follows each (qkv_proj, gate_up_proj).  Afterwards rms_norm(r) * gamma @ W.T == (r @ W'.T) * rsqrt(mean(r^2)
+        + eps): the norm becomes a per-row scale in the GEMM epilogue, the residual add moves into the epilogue of the
+        GEMM before it, and the two add + RMSNorm launches per block disappear (``_forward_folded``).  Call once, after
+        the weights are loaded and before any quantisation."""
+        assert not self.norms_folded and self.tp.size == 1
+        with torch.no_grad():
+            for l in self.layers:
+                for lin, gamma in ((l.qkv_proj, l.input_layernorm), (l.gate_up_proj, l.post_attention_layernorm)):
+                    lin.weight.copy_((lin.weight.float() * gamma.float()[None, :]).to(lin.weight.dtype))
+        self.norms_folded = True
+
+    def _forward_folded(self, batch) -> torch.Tensor:
+        """The block loop with the norms folded into the GEMMs (see ``fold_norm_weights``): per block
+        qkv GEMM (row scale) -> q/k-norm + RoPE + KV store -> attention -> o GEMM (residual add) ->
+        gate_up GEMM (row scale, SiLU*mul) -> down GEMM (residual add).  ``ssq[k]`` carries the rows' sums of squares
+        from the GEMM that updates the residual stream to the GEMM that reads it."""
+        ops, layers = self.ops, self.layers
+        L = len(layers)
+        residual, ssq = ops.embedding_ssq(batch.input_ids, self.embed_tokens.weight, self.embed_tokens.vocab_start, 2 * L + 1)
+        fused_decode = (not batch.is_prefill and self.head_dim == 128 and batch.padded_seqs <= ops.fused_qkv_max_batch)
+        for i, l in enumerate(layers):
+            qkv = ops.linear_scaled(residual, l.qkv_proj.weight, ssq[2 * i], self.eps)
+            kc, vc = self.kv_cache[i, 0], self.kv_cache[i, 1]
+            if fused_decode:
+                a = ops.decode_attention_qkv(qkv, l.q_norm, l.k_norm, self.eps, self.rope, kc, vc, batch, self.num_heads, self.scale)
+            else:
+                q = ops.qk_norm_rope_store(qkv, l.q_norm, l.k_norm, self.eps, self.rope, batch.positions,
+                                           batch.slot_mapping, kc, vc, self.num_heads, self.num_kv_heads, self.head_dim)
+                a = ops.attention(q, kc, vc, batch, self.scale)
+            ops.linear_residual(a, l.o_proj.weight, residual, ssq[2 * i + 1])
+            g = ops.linear_scaled(residual, l.gate_up_proj.weight, ssq[2 * i + 1], self.eps, silu_mul=True)
+            ops.linear_residual(g, l.down_proj.weight, residual, ssq[2 * i + 2])
+        return ops.rms_norm(residual, self.norm, self.eps)
+
     # ------------------------------------------------------------------ forward
     def forward(self, batch) -> torch.Tensor:
         """Hidden states ``[tokens, hidden]`` after the final norm.
@@ -116,6 +156,8 @@ class Qwen3ForCausalLM:
         projection is issued together with the cross-rank sum, the residual add and the norm that follows it,
         so that an op set can fuse the three (``row_linear_add_rms_norm``)."""
         from ..parallel.symm import SITE_DOWN, SITE_O
+        if self.norms_folded:
+            return self._forward_folded(batch)
         ops = self.ops
         layers = self.layers
         x, residual = ops.embed_norm(batch.input_ids, self.embed_tokens, layers[0].input_layernorm, self.eps)

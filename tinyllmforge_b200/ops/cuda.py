@@ -111,6 +111,33 @@ class CudaOps:
         self.launches += 1
         return out
 
+    # --- GEMMs with the neighbouring RMSNorm / residual add fused in (single GPU, bf16 weights; see models/qwen3.py)
+    def embedding_ssq(self, ids, weight, vocab_start, num_ssq: int):
+        """(rows, ssq): embedding rows plus a fp32 [num_ssq, tokens] array whose row 0 holds each row's sum of squares and
+        whose other rows are zeroed (accumulators for ``linear_residual``)."""
+        out = torch.empty(ids.shape[0], weight.shape[1], dtype=weight.dtype, device=weight.device)
+        ssq = torch.empty(num_ssq, ids.shape[0], dtype=torch.float32, device=weight.device)
+        self.C.embedding(ids, weight, out, vocab_start, ssq)
+        self.launches += 1
+        return out, ssq
+
+    def linear_scaled(self, x: torch.Tensor, w: torch.Tensor, ssq_row: torch.Tensor, eps: float, silu_mul: bool = False,
+                      force_mode: int = 0, tune: int = 0) -> torch.Tensor:
+        """rms_norm(x) @ w0.T computed as (x @ w.T) * rsqrt(ssq / K + eps) per row, where w = w0 with the norm weight
+        folded into its columns and ssq_row holds the rows' sums of squares.  silu_mul: w is [2I, K] (gate rows, up rows)."""
+        n_out = w.shape[0] // 2 if silu_mul else w.shape[0]
+        out = torch.empty(x.shape[0], n_out, dtype=x.dtype, device=x.device)
+        self.C.gemm_fused(x, w, out, 1 if silu_mul else 0, force_mode, tune, ssq_row, eps, False, None, self.status)
+        self.launches += 1
+        return out
+
+    def linear_residual(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, ssq_out: torch.Tensor,
+                        force_mode: int = 0, tune: int = 0) -> None:
+        """residual += x @ w.T in place (rounded like a bf16 GEMM output followed by a bf16 add); ssq_out (zeroed, fp32
+        [tokens]) receives the sums of squares of the new residual rows."""
+        self.C.gemm_fused(x, w, residual, 0, force_mode, tune, None, 0.0, True, ssq_out, self.status)
+        self.launches += 1
+
     def linear_fp8(self, x: torch.Tensor, w: "Fp8BlockWeight") -> torch.Tensor:
         """Block-scaled fp8 GEMM: quantise activations per token and 128 features, multiply on the e4m3 tensor-core
         path, apply the scales per K block while accumulating."""
@@ -151,7 +178,7 @@ class CudaOps:
 
     def embedding(self, ids, weight, vocab_start=0):
         out = torch.empty(ids.shape[0], weight.shape[1], dtype=weight.dtype, device=weight.device)
-        self.C.embedding(ids, weight, out, vocab_start)
+        self.C.embedding(ids, weight, out, vocab_start, None)
         self.launches += 1
         return out
 
