@@ -406,11 +406,11 @@ extern "C" int forge_silu_mul(const void* x, void* out, long long rows, int I, c
 // ---------------------------------------------------------------------------------------------------------
 // Row gathers.  embedding: out[t] = id in [start, start + n) ? W[id - start] : 0.  gather_rows: out[s] = x[idx[s]].
 // ---------------------------------------------------------------------------------------------------------
-// ssq (optional): fp32 [num_ssq][T].  ssq[0][t] = sum of squares of the row written (so the first linear layer can apply
-// the first RMSNorm as a row scale); ssq[1..][t] = 0 (the accumulators the residual-adding GEMMs of this step add into).
+// ssq (optional): fp32 [T][parts].  ssq[t][0] = sum of squares of the row written, ssq[t][1..] = 0, so that the first linear
+// layer can apply the first RMSNorm as a row scale (it sums the parts; see GemmFuse in gemm_bf16_sm100.cu).
 __global__ void __launch_bounds__(128) embedding_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ w,
                                                         __nv_bfloat16* __restrict__ out, int H, int vocab_start, int vocab_n,
-                                                        float* __restrict__ ssq, int num_ssq, int T) {
+                                                        float* __restrict__ ssq, int parts) {
   __shared__ float red[32];
   pdl_launch_dependents();
   pdl_wait();
@@ -429,17 +429,16 @@ __global__ void __launch_bounds__(128) embedding_kernel(const int* __restrict__ 
   }
   if (ssq != nullptr) {
     ss = block_sum(ss, red);
-    if (threadIdx.x == 0) ssq[t] = ss;
-    for (int s = 1 + threadIdx.x; s < num_ssq; s += blockDim.x) ssq[static_cast<size_t>(s) * T + t] = 0.f;
+    for (int s = threadIdx.x; s < parts; s += blockDim.x) ssq[static_cast<size_t>(t) * parts + s] = s == 0 ? ss : 0.f;
   }
 }
 
 extern "C" int forge_embedding(const int* ids, const void* w, void* out, int T, int H, int vocab_start, int vocab_n, float* ssq,
-                               int num_ssq, cudaStream_t stream) {
+                               int parts, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H & 7) return -1;
   return launch_kernel(embedding_kernel, dim3(T), dim3(128), 0, stream, 0, ids, static_cast<const __nv_bfloat16*>(w),
-                       static_cast<__nv_bfloat16*>(out), H, vocab_start, vocab_n, ssq, num_ssq, T) == cudaSuccess ? 0 : -2;
+                       static_cast<__nv_bfloat16*>(out), H, vocab_start, vocab_n, ssq, parts) == cudaSuccess ? 0 : -2;
 }
 
 __global__ void __launch_bounds__(128) gather_rows_kernel(const int* __restrict__ idx, const __nv_bfloat16* __restrict__ x,

@@ -47,24 +47,32 @@ __device__ __forceinline__ void trace_point(int cta, int k) {
 // Optional fusion of the RMSNorm that precedes / the residual add that follows a linear layer (both null: plain GEMM).
 //
 //   in_ssq   the activation rows are NOT normalised: x is the residual stream itself, the norm's weight vector was
-//            folded into the columns of W when the model was loaded, and in_ssq[row] holds the sum of squares of the
-//            activation row.  The epilogue scales output row r by rsqrt(in_ssq[r] / K + eps), which is exactly what
-//            normalising the input row first would give (the reference normalises in a kernel of its own:
+//            folded into the columns of W when the model was loaded, and in_ssq[row][0 .. in_parts) holds partial sums
+//            of squares of the activation row (one per 128 features, written by the GEMM that produced the row).  The
+//            epilogue scales output row r by rsqrt(sum(in_ssq[r]) / K + eps), which is exactly what normalising the
+//            input row first would give (the reference normalises in a kernel of its own:
 //            tinyvllm/layers/layernorm.py:21-45).
 //   residual out[r][c] = bf16(bf16(acc) + out[r][c]): `out` is the residual stream, updated in place, and
-//            out_ssq[r] += sum of the squares of the new values (fp32 atomics; the caller zeroes it), so that the
-//            NEXT linear layer can apply its norm as a row scale.  Replaces the add half of add_rms_forward.
+//            out_ssq[r][p] = sum of the squares of the new values of features [128 p, 128 p + 128), so that the NEXT
+//            linear layer can apply its norm as a row scale.  Every (row, part) is written by exactly one thread and
+//            summed in a fixed order: results do not depend on scheduling.  Replaces the add half of add_rms_forward.
 struct GemmFuse {
   const float* in_ssq;
+  int in_parts;
   float in_width_inv;
   float eps;
   int add_residual;
   float* out_ssq;
+  int out_parts;
 };
 
 __device__ __forceinline__ float fuse_row_scale(const GemmFuse& f, int row, int rows) {
   if (f.in_ssq == nullptr) return 1.f;
-  return row < rows ? rsqrtf(f.in_ssq[row] * f.in_width_inv + f.eps) : 0.f;
+  if (row >= rows) return 0.f;
+  const float* p = f.in_ssq + static_cast<size_t>(row) * f.in_parts;
+  float s = 0.f;
+  for (int i = 0; i < f.in_parts; ++i) s += p[i];
+  return rsqrtf(s * f.in_width_inv + f.eps);
 }
 __device__ __forceinline__ float bf16_round_g(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
@@ -212,7 +220,7 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       if (ok) {
         constexpr int kChunk = BLOCK_C >= 32 ? 32 : 16;
         const float row_scale = fuse_row_scale(fuse, r, m_total);          // 1 unless the input norm is folded in
-        float ssq = 0.f;                                                   // of the new residual values of this row (this tile)
+        float ssq = 0.f;                                                   // of the new residual values of this row, current 128 columns
 #pragma unroll 1
         for (int cc = 0; cc < BLOCK_C; cc += kChunk) {
           uint32_t v[kChunk];
@@ -265,8 +273,12 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 }
             }
           }
+          if (fuse.out_ssq != nullptr && ((cc + kChunk) & 127) == 0) {      // a group of 128 columns is complete (tiles are 128 or 256 wide)
+            const int g0 = c + kChunk - 128;
+            if (r < m_total && g0 < n_total) fuse.out_ssq[static_cast<size_t>(r) * fuse.out_parts + (g0 >> 7)] = ssq;
+            ssq = 0.f;
+          }
         }
-        if (fuse.out_ssq != nullptr && r < m_total) atomicAdd(fuse.out_ssq + r, ssq);
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -311,7 +323,7 @@ struct WgtCfg {
   static constexpr int kRingBytes = kStages * kStageBytes > kEpilogueBytes ? kStages * kStageBytes : kEpilogueBytes;
   static constexpr bool kCanSplit = BLOCK_C <= 64;                // wider tiles have no room for receive slots
   static constexpr int kTmemCols = tmem_cols_for(BLOCK_C * kNumR);
-  static constexpr int kSmemBytes = kRingBytes + 1024 + 256;
+  static constexpr int kSmemBytes = kRingBytes + 1024 + 512 + 512;          // alignment slack, barriers, column scales
   static_assert(BLOCK_C % 16 == 0 && BLOCK_C >= 16 && BLOCK_C <= 128, "token tile of the decode kernel");
   static_assert(kStages >= 2, "need at least a double buffer");
   static_assert(kSmemBytes <= (kDeep ? 227 : 113) * 1024, "two CTAs per SM (one for the deep ring)");
@@ -347,6 +359,7 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   uint64_t* acc_bar = empty_bar + Cfg::kStages;
   uint64_t* recv_bar = acc_bar + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(recv_bar + 1);
+  float* col_scale = reinterpret_cast<float*>(smem + Cfg::kRingBytes + 512);   // [BLOCK_C] row scales of this CTA's tokens (folded norm)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t split = cluster_ctarank(), nsplit = cluster_nctarank();
@@ -449,6 +462,11 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // tagged-word push: the tag is this exchange's epoch.  Read before this CTA reports its arrival, i.e. before the
     // grid's last CTA can advance the counter.
     if (push.size > 1 && push.ll) ll_tag = *push.epoch + 1u;
+    // folded input norm: the scale of every token column of this CTA, once
+    if (fuse_io.in_ssq != nullptr) {
+      if (et < BLOCK_C) col_scale[et] = fuse_row_scale(fuse_io, tok0 + et, m_total);
+      named_barrier_sync(1, 128);
+    }
     acc_ok = mbar_wait(acc_bar, 0, status);                      // this CTA's ring is idle from here on
     tcgen05_fence_after();
     if (et == 0) trace_point(cta_id, 3);                         // accumulators complete
@@ -473,7 +491,7 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
               tmem_ld_wait();
 #pragma unroll
               for (int j = 0; j < kChunk; ++j) {
-                const float sc = fuse_row_scale(fuse_io, tok0 + cc + j, m_total);      // column = token; same address for the whole warp
+                const float sc = fuse_io.in_ssq != nullptr ? col_scale[cc + j] : 1.f;     // column = token
                 v[j] = __float_as_uint(silu(__uint_as_float(v[j]) * sc) * (__uint_as_float(u[j]) * sc));
               }
             }
@@ -528,7 +546,7 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             const int c = tok0 + static_cast<int>(split) * cpc + lc;
             const int n = r0 + lane * 4;
             // the input norm folded in: scale this token's column (the single-split SiLU path scaled on the way out of tensor memory)
-            const float sc = (kEpi == kEpiSiluMul && fuse) ? 1.f : fuse_row_scale(fuse_io, c, m_total);
+            const float sc = ((kEpi == kEpiSiluMul && fuse) || fuse_io.in_ssq == nullptr) ? 1.f : col_scale[c - tok0];
             if constexpr (kEpi == kEpiSiluMul) {
               if (!fuse) {
                 float4* g = reinterpret_cast<float4*>(gate_red + lc * kBlockR + lane * 4);   // same thread in both rounds
@@ -583,7 +601,7 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             if (fuse_io.out_ssq != nullptr) {              // uniform for the warp: all 32 lanes hold features of token c
 #pragma unroll
               for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
-              if (lane == 0 && c < m_total) atomicAdd(fuse_io.out_ssq + c, ssq);
+              if (lane == 0 && c < m_total) fuse_io.out_ssq[static_cast<size_t>(c) * fuse_io.out_parts + blockIdx.x] = ssq;   // this CTA's 128 features
             }
           }
         }
@@ -740,6 +758,7 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
     else if (t32 <= 148) narrow = 32;
     else if (t64 <= 148) narrow = 64;
   }
+  if (fuse.add_residual) narrow = 0;              // the sums of squares are kept per 128 features: tiles of 128 or 256
   if (narrow) {
     force_mode = 1;
     force_bc = narrow;
@@ -812,20 +831,24 @@ extern "C" int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, v
 // Row-parallel GEMM under tensor parallelism: `out` is this rank's partial buffer in symmetric memory (row stride ldo);
 // the kernel's last CTA announces completion to every rank through signal_ptrs (tp_size addresses in peer order).
 // Up to 256 rows run on the weight-tile (decode) kernel, more on the persistent token-tile kernel.
-// The same with the neighbouring norm / residual add fused in (see GemmFuse).  in_ssq: fp32 [M] sums of squares of the
-// rows of x (null: rows are not scaled).  add_residual: out += result in place, out_ssq (fp32 [M], zeroed by the caller,
-// may be null) accumulates the sums of squares of the new rows.
+// The same with the neighbouring norm / residual add fused in (see GemmFuse).  in_ssq: fp32 [M][in_parts] partial sums of
+// squares of the rows of x (null: rows are not scaled).  add_residual: out += result in place and out_ssq (fp32
+// [M][ceil(n_out / 128)], may be null) receives the sums of squares of the new rows per 128 features.
 extern "C" int forge_gemm_bf16_fused(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K,
-                                     int epi, int force_mode, int tune, const float* in_ssq, float eps, int add_residual,
-                                     float* out_ssq, unsigned* status, cudaStream_t stream) {
+                                     int epi, int force_mode, int tune, const float* in_ssq, int in_parts, float eps,
+                                     int add_residual, float* out_ssq, unsigned* status, cudaStream_t stream) {
   if (add_residual && epi != kEpiStore) return -9;
+  if (in_ssq != nullptr && in_parts < 1) return -9;
+  if (add_residual && force_mode == 1 && ((tune >> 8) & 0xff) != 0) return -9;      // no narrow tiles with the residual epilogue
   TpPush none = {};
   GemmFuse fuse = {};
   fuse.in_ssq = in_ssq;
+  fuse.in_parts = in_parts;
   fuse.in_width_inv = 1.0f / static_cast<float>(K);
   fuse.eps = eps;
   fuse.add_residual = add_residual;
   fuse.out_ssq = add_residual ? out_ssq : nullptr;
+  fuse.out_parts = (n_out + 127) / 128;
   return gemm_dispatch(x, ldx, w, ldw, out, ldo, M, n_out, K, epi, force_mode, tune, status, stream, none, fuse);
 }
 

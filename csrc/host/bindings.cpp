@@ -11,7 +11,7 @@ extern "C" {
 int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K, int epi,
                     int force_mode, int force_splits, unsigned* status, cudaStream_t stream);
 int forge_gemm_bf16_fused(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K, int epi,
-                          int force_mode, int tune, const float* in_ssq, float eps, int add_residual, float* out_ssq,
+                          int force_mode, int tune, const float* in_ssq, int in_parts, float eps, int add_residual, float* out_ssq,
                           unsigned* status, cudaStream_t stream);
 int forge_gemm_set_trace(unsigned long long* buf);
 int forge_quant_fp8_1x128(const void* x, void* xq, float* scale, int M, int K, int scale_ld, cudaStream_t stream);
@@ -52,7 +52,7 @@ int forge_qk_norm_rope_store(const void* qkv, int ld_qkv, const void* qw, const 
                              int T, int nq, int nkv, int D, int block_size, long long num_slots, int do_rope, unsigned* status,
                              cudaStream_t stream);
 int forge_silu_mul(const void* x, void* out, long long rows, int I, cudaStream_t stream);
-int forge_embedding(const int* ids, const void* w, void* out, int T, int H, int vocab_start, int vocab_n, float* ssq, int num_ssq,
+int forge_embedding(const int* ids, const void* w, void* out, int T, int H, int vocab_start, int vocab_n, float* ssq, int parts,
                     cudaStream_t stream);
 int forge_gather_rows(const int* idx, const void* x, void* out, int S, int H, int x_rows, cudaStream_t stream);
 int forge_feed_tokens(int* ids, const int* src_rows, const int* prev_tokens, int n, int prev_n, cudaStream_t stream);
@@ -114,10 +114,10 @@ void gemm(const Tensor& x, const Tensor& w, Tensor& out, int64_t epi, int64_t fo
         "forge_gemm_bf16");
 }
 
-// The GEMM with the neighbouring RMSNorm / residual add fused in.  in_ssq (fp32, >= M): the rows of x are un-normalised, the
-// norm weight is folded into w, and output row r is scaled by rsqrt(in_ssq[r] / K + eps).  add_residual: out is the residual
-// stream, updated in place (out += x @ w.T, rounded as the separate kernels would); out_ssq (fp32, >= M, zeroed by the caller)
-// accumulates the sums of squares of the new rows.
+// The GEMM with the neighbouring RMSNorm / residual add fused in.  in_ssq (fp32 [M, parts]): the rows of x are un-normalised,
+// the norm weight is folded into w, and output row r is scaled by rsqrt(sum(in_ssq[r]) / K + eps).  add_residual: out is the
+// residual stream, updated in place (out += x @ w.T, rounded as the separate kernels would); out_ssq (fp32
+// [M, ceil(n_out / 128)]) receives the sums of squares of the new rows per 128 features.
 void gemm_fused(const Tensor& x, const Tensor& w, Tensor& out, int64_t epi, int64_t force_mode, int64_t tune,
                 const c10::optional<Tensor>& in_ssq, double eps, bool add_residual, const c10::optional<Tensor>& out_ssq,
                 const Tensor& status) {
@@ -132,12 +132,22 @@ void gemm_fused(const Tensor& x, const Tensor& w, Tensor& out, int64_t epi, int6
   TORCH_CHECK(!(add_residual && epi != 0), "gemm_fused: the residual add goes with the plain epilogue");
   const float* in_p = nullptr;
   float* out_p = nullptr;
-  if (in_ssq.has_value()) { CHECK_CUDA_CONTIG(*in_ssq); CHECK_F32(*in_ssq); TORCH_CHECK(in_ssq->numel() >= M, "gemm_fused: in_ssq too short"); in_p = in_ssq->data_ptr<float>(); }
-  if (out_ssq.has_value()) { CHECK_CUDA_CONTIG(*out_ssq); CHECK_F32(*out_ssq); TORCH_CHECK(out_ssq->numel() >= M, "gemm_fused: out_ssq too short"); out_p = out_ssq->data_ptr<float>(); }
+  int in_parts = 0;
+  if (in_ssq.has_value()) {
+    CHECK_CUDA_CONTIG(*in_ssq); CHECK_F32(*in_ssq);
+    TORCH_CHECK(in_ssq->dim() == 2 && in_ssq->size(0) >= M && in_ssq->size(1) >= 1, "gemm_fused: in_ssq must be [>= M, parts]");
+    in_p = in_ssq->data_ptr<float>();
+    in_parts = static_cast<int>(in_ssq->size(1));
+  }
+  if (out_ssq.has_value()) {
+    CHECK_CUDA_CONTIG(*out_ssq); CHECK_F32(*out_ssq);
+    TORCH_CHECK(out_ssq->dim() == 2 && out_ssq->size(0) >= M && out_ssq->size(1) == (n_out + 127) / 128, "gemm_fused: out_ssq must be [>= M, ceil(n_out / 128)]");
+    out_p = out_ssq->data_ptr<float>();
+  }
   const c10::cuda::CUDAGuard guard(x.device());
   check(forge_gemm_bf16_fused(x.data_ptr(), static_cast<int>(x.stride(0)), w.data_ptr(), static_cast<int>(w.stride(0)), out.data_ptr(),
                               static_cast<int>(out.stride(0)), static_cast<int>(M), static_cast<int>(n_out), static_cast<int>(K),
-                              static_cast<int>(epi), static_cast<int>(force_mode), static_cast<int>(tune), in_p,
+                              static_cast<int>(epi), static_cast<int>(force_mode), static_cast<int>(tune), in_p, in_parts,
                               static_cast<float>(eps), add_residual ? 1 : 0, out_p, status_ptr(status), stream_of(x)),
         "forge_gemm_bf16_fused");
 }
@@ -204,22 +214,22 @@ void silu_mul(const Tensor& x, Tensor& out) {
   check(forge_silu_mul(x.data_ptr(), out.data_ptr(), rows, static_cast<int>(I), stream_of(x)), "forge_silu_mul");
 }
 
-// ssq (optional, fp32 [n, T]): row 0 receives the sums of squares of the rows written, rows 1.. are zeroed.
+// ssq (optional, fp32 [T, parts]): column 0 receives the sums of squares of the rows written, the other columns zero.
 void embedding(const Tensor& ids, const Tensor& w, Tensor& out, int64_t vocab_start, const c10::optional<Tensor>& ssq) {
   CHECK_CUDA_CONTIG(ids); CHECK_I32(ids); CHECK_CUDA_CONTIG(w); CHECK_BF16(w); CHECK_CUDA_CONTIG(out); CHECK_BF16(out);
   const int64_t T = ids.numel(), H = w.size(1);
   TORCH_CHECK(out.numel() == T * H, "embedding: bad output shape");
   float* sp = nullptr;
-  int num_ssq = 0;
+  int parts = 0;
   if (ssq.has_value()) {
     CHECK_CUDA_CONTIG(*ssq); CHECK_F32(*ssq);
-    TORCH_CHECK(ssq->dim() == 2 && ssq->size(1) == T, "embedding: ssq must be [n, tokens]");
+    TORCH_CHECK(ssq->dim() == 2 && ssq->size(0) == T && ssq->size(1) >= 1, "embedding: ssq must be [tokens, parts]");
     sp = ssq->data_ptr<float>();
-    num_ssq = static_cast<int>(ssq->size(0));
+    parts = static_cast<int>(ssq->size(1));
   }
   const c10::cuda::CUDAGuard guard(w.device());
   check(forge_embedding(ids.data_ptr<int>(), w.data_ptr(), out.data_ptr(), static_cast<int>(T), static_cast<int>(H),
-                        static_cast<int>(vocab_start), static_cast<int>(w.size(0)), sp, num_ssq, stream_of(w)),
+                        static_cast<int>(vocab_start), static_cast<int>(w.size(0)), sp, parts, stream_of(w)),
         "forge_embedding");
 }
 

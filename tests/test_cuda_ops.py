@@ -156,7 +156,8 @@ def test_gemm_with_folded_input_norm(ops, M, N, K, mode, silu):
     gamma = (1 + 0.2 * torch.randn(K, device="cuda")).to(BF)
     w = _rand(2 * N if silu else N, K, scale=0.05)
     w_folded = (w.float() * gamma.float()[None, :]).to(BF)
-    ssq = (x.float() ** 2).sum(-1)
+    parts = (K + 127) // 128          # the sums of squares arrive in pieces of 128 features, as the producing GEMM writes them
+    ssq = (x.float() ** 2).view(M, parts, -1).sum(-1).contiguous()
     got = ops.linear_scaled(x, w_folded, ssq, 1e-6, silu_mul=silu, force_mode=mode)
     xn = x.float() * torch.rsqrt((x.float() ** 2).mean(-1, keepdim=True) + 1e-6)
     want = xn @ w_folded.float().t()
@@ -169,6 +170,7 @@ def test_gemm_with_folded_input_norm(ops, M, N, K, mode, silu):
 @pytest.mark.parametrize("M,N,K,mode,tune", [
     (1, 1024, 2048, 0, 0), (7, 1024, 3072, 0, 0), (64, 1024, 2048, 0, 0), (200, 1024, 3072, 0, 0), (256, 1024, 2048, 2, 8), (256, 4096, 12288, 0, 0),
     (33, 1024, 1024, 2, 1), (300, 1024, 2048, 0, 0), (4096, 1024, 3072, 0, 0), (1000, 4096, 4096, 0, 0), (130, 200, 72, 1, 0), (19, 136, 200, 2, 0),
+    (700, 1100, 256, 1, 0), (40, 5120, 3200, 0, 0),
 ])
 def test_gemm_with_residual_add_and_sum_of_squares(ops, M, N, K, mode, tune):
     """residual += x @ W.T in the epilogue (rounded like a bf16 GEMM followed by a bf16 add) plus the per-row sums of squares."""
@@ -176,11 +178,17 @@ def test_gemm_with_residual_add_and_sum_of_squares(ops, M, N, K, mode, tune):
     x, w = _rand(M, K), _rand(N, K, scale=0.05)
     residual = _rand(M, N, scale=2.0)
     want = ((x.float() @ w.float().t()).to(BF).float() + residual.float()).to(BF)
-    ssq = torch.zeros(M, dtype=torch.float32, device="cuda")
+    parts = (N + 127) // 128
+    ssq = torch.full((M, parts), float("nan"), dtype=torch.float32, device="cuda")     # every entry must be written
     res = residual.clone()
     ops.linear_residual(x, w, res, ssq, force_mode=mode, tune=tune)
-    _close(res, want, atol=3e-2, rtol=2e-2)
-    assert torch.allclose(ssq, (res.float() ** 2).sum(-1), rtol=1e-3, atol=1e-3)       # of the values actually stored
+    _close(res, want, atol=6e-2, rtol=2e-2)
+    sq = torch.nn.functional.pad(res.float() ** 2, (0, parts * 128 - N)).view(M, parts, 128).sum(-1)
+    assert torch.allclose(ssq, sq, rtol=1e-3, atol=1e-3)                               # of the values actually stored
+    ssq2 = torch.empty_like(ssq)
+    res2 = residual.clone()
+    ops.linear_residual(x, w, res2, ssq2, force_mode=mode, tune=tune)
+    assert torch.equal(res2, res) and torch.equal(ssq2, ssq)                           # no dependence on scheduling
     ops.check_status()
 
 
@@ -188,10 +196,11 @@ def test_embedding_sum_of_squares(ops):
     V, H, T = 512, 1024, 37
     table = _rand(V, H)
     ids = torch.randint(0, V, (T,), device="cuda", dtype=torch.int32)
-    out, ssq = ops.embedding_ssq(ids, table, 0, 5)
+    out, ssq, scratch = ops.embedding_ssq(ids, table, 0)
     assert torch.equal(out, table[ids.long()])
-    assert torch.allclose(ssq[0], (out.float() ** 2).sum(-1), rtol=1e-4)
-    assert torch.count_nonzero(ssq[1:]) == 0
+    assert ssq.shape == (T, H // 128) == scratch.shape
+    assert torch.allclose(ssq.sum(-1), (out.float() ** 2).sum(-1), rtol=1e-4)
+    assert torch.count_nonzero(ssq[:, 1:]) == 0
 
 
 def test_gemm_strided_input(ops):

@@ -128,14 +128,13 @@ class Qwen3ForCausalLM:
     def _forward_folded(self, batch) -> torch.Tensor:
         """The block loop with the norms folded into the GEMMs (see ``fold_norm_weights``): per block
         qkv GEMM (row scale) -> q/k-norm + RoPE + KV store -> attention -> o GEMM (residual add) ->
-        gate_up GEMM (row scale, SiLU*mul) -> down GEMM (residual add).  ``ssq[k]`` carries the rows' sums of squares
-        from the GEMM that updates the residual stream to the GEMM that reads it."""
+        gate_up GEMM (row scale, SiLU*mul) -> down GEMM (residual add).  ``ssq_a`` / ``ssq_b`` carry the rows' sums of
+        squares from the GEMM that updates the residual stream to the GEMM that reads it."""
         ops, layers = self.ops, self.layers
-        L = len(layers)
-        residual, ssq = ops.embedding_ssq(batch.input_ids, self.embed_tokens.weight, self.embed_tokens.vocab_start, 2 * L + 1)
+        residual, ssq_a, ssq_b = ops.embedding_ssq(batch.input_ids, self.embed_tokens.weight, self.embed_tokens.vocab_start)
         fused_decode = (not batch.is_prefill and self.head_dim == 128 and batch.padded_seqs <= ops.fused_qkv_max_batch)
         for i, l in enumerate(layers):
-            qkv = ops.linear_scaled(residual, l.qkv_proj.weight, ssq[2 * i], self.eps)
+            qkv = ops.linear_scaled(residual, l.qkv_proj.weight, ssq_a, self.eps)
             kc, vc = self.kv_cache[i, 0], self.kv_cache[i, 1]
             if fused_decode:
                 a = ops.decode_attention_qkv(qkv, l.q_norm, l.k_norm, self.eps, self.rope, kc, vc, batch, self.num_heads, self.scale)
@@ -143,9 +142,9 @@ class Qwen3ForCausalLM:
                 q = ops.qk_norm_rope_store(qkv, l.q_norm, l.k_norm, self.eps, self.rope, batch.positions,
                                            batch.slot_mapping, kc, vc, self.num_heads, self.num_kv_heads, self.head_dim)
                 a = ops.attention(q, kc, vc, batch, self.scale)
-            ops.linear_residual(a, l.o_proj.weight, residual, ssq[2 * i + 1])
-            g = ops.linear_scaled(residual, l.gate_up_proj.weight, ssq[2 * i + 1], self.eps, silu_mul=True)
-            ops.linear_residual(g, l.down_proj.weight, residual, ssq[2 * i + 2])
+            ops.linear_residual(a, l.o_proj.weight, residual, ssq_b)
+            g = ops.linear_scaled(residual, l.gate_up_proj.weight, ssq_b, self.eps, silu_mul=True)
+            ops.linear_residual(g, l.down_proj.weight, residual, ssq_a)
         return ops.rms_norm(residual, self.norm, self.eps)
 
     # ------------------------------------------------------------------ forward

@@ -112,19 +112,22 @@ class CudaOps:
         return out
 
     # --- GEMMs with the neighbouring RMSNorm / residual add fused in (single GPU, bf16 weights; see models/qwen3.py)
-    def embedding_ssq(self, ids, weight, vocab_start, num_ssq: int):
-        """(rows, ssq): embedding rows plus a fp32 [num_ssq, tokens] array whose row 0 holds each row's sum of squares and
-        whose other rows are zeroed (accumulators for ``linear_residual``)."""
-        out = torch.empty(ids.shape[0], weight.shape[1], dtype=weight.dtype, device=weight.device)
-        ssq = torch.empty(num_ssq, ids.shape[0], dtype=torch.float32, device=weight.device)
-        self.C.embedding(ids, weight, out, vocab_start, ssq)
+    def embedding_ssq(self, ids, weight, vocab_start):
+        """(rows, ssq_a, ssq_b): embedding rows and two fp32 [tokens, ceil(H / 128)] arrays of per-row partial sums of squares.
+        ssq_a describes the rows returned (their sum of squares in column 0); ssq_b is scratch for ``linear_residual``:
+        the block loop alternates between the two (the o GEMM writes one, the down GEMM the other)."""
+        T, H = ids.shape[0], weight.shape[1]
+        out = torch.empty(T, H, dtype=weight.dtype, device=weight.device)
+        ssq = torch.empty(2, T, (H + 127) // 128, dtype=torch.float32, device=weight.device)
+        self.C.embedding(ids, weight, out, vocab_start, ssq[0])
         self.launches += 1
-        return out, ssq
+        return out, ssq[0], ssq[1]
 
     def linear_scaled(self, x: torch.Tensor, w: torch.Tensor, ssq_row: torch.Tensor, eps: float, silu_mul: bool = False,
                       force_mode: int = 0, tune: int = 0) -> torch.Tensor:
         """rms_norm(x) @ w0.T computed as (x @ w.T) * rsqrt(ssq / K + eps) per row, where w = w0 with the norm weight
-        folded into its columns and ssq_row holds the rows' sums of squares.  silu_mul: w is [2I, K] (gate rows, up rows)."""
+        folded into its columns and ssq_row [tokens, parts] holds partial sums of squares of the rows.  silu_mul: w is
+        [2I, K] (gate rows, up rows)."""
         n_out = w.shape[0] // 2 if silu_mul else w.shape[0]
         out = torch.empty(x.shape[0], n_out, dtype=x.dtype, device=x.device)
         self.C.gemm_fused(x, w, out, 1 if silu_mul else 0, force_mode, tune, ssq_row, eps, False, None, self.status)
@@ -133,8 +136,8 @@ class CudaOps:
 
     def linear_residual(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, ssq_out: torch.Tensor,
                         force_mode: int = 0, tune: int = 0) -> None:
-        """residual += x @ w.T in place (rounded like a bf16 GEMM output followed by a bf16 add); ssq_out (zeroed, fp32
-        [tokens]) receives the sums of squares of the new residual rows."""
+        """residual += x @ w.T in place (rounded like a bf16 GEMM output followed by a bf16 add); ssq_out (fp32
+        [tokens, ceil(H / 128)]) receives the sums of squares of the new residual rows, one per 128 features."""
         self.C.gemm_fused(x, w, residual, 0, force_mode, tune, None, 0.0, True, ssq_out, self.status)
         self.launches += 1
 
