@@ -21,6 +21,7 @@
 // (TMEM lane quadrant = warp % 4).  All mbarrier waits are bounded (see ptx.cuh).
 #include "../include/launch.cuh"
 #include "../include/ptx.cuh"
+#include "../include/sampling.cuh"
 #include "../include/tp_comm.cuh"
 
 namespace forge {
@@ -30,7 +31,7 @@ constexpr int kBlockK = 64;    // 64 bf16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
 constexpr int kGemmThreads = 192;
 
-enum GemmEpilogue { kEpiStore = 0, kEpiSiluMul = 1 };
+enum GemmEpilogue { kEpiStore = 0, kEpiSiluMul = 1, kEpiSample = 2 };
 
 // Optional phase timeline of the decode kernel: when set (forge_gemm_set_trace), CTA b writes %globaltimer
 // (ns) at eight points into trace[b * 8 ..].  Null in normal operation.
@@ -76,6 +77,20 @@ __device__ __forceinline__ float fuse_row_scale(const GemmFuse& f, int row, int 
 }
 __device__ __forceinline__ float bf16_round_g(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
+// Sampling epilogue of the LM-head GEMM (kEpiSample): the logits never reach memory.  Each epilogue thread owns one
+// token row of the tile; it rounds every accumulator to bf16 (what the materialised logits would hold), scales by 1 / T,
+// adds the Gumbel noise of that (row, GLOBAL token id) and keeps the best (score, id) of the tile's columns; one pair per
+// (row, vocabulary tile) is written and a small kernel merges them.  Same numbers, hence the same tokens, as
+// sample_partial_kernel on materialised logits (tinyvllm/layers/embed_head.py:58-70 + tinyvllm/layers/sampler.py:13-21).
+struct GemmSample {
+  const float* temps;        // [rows]
+  const int* header;         // packed step header: [9] step index, [10], [11] seed
+  int vocab_start;           // global id of column 0 (a multiple of 4)
+  float* part_v;             // [rows][n_tiles]
+  int* part_i;
+  int n_tiles;
+};
+
 constexpr int tmem_cols_for(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
 
 // =========================================================================================================
@@ -104,7 +119,7 @@ template <int BLOCK_C, int kEpi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                    __nv_bfloat16* __restrict__ out, int ldo, int m_total, int n_total, int K, int dual_off, unsigned* status,
-                   const TpPush push, const GemmFuse fuse) {
+                   const TpPush push, const GemmFuse fuse, const GemmSample samp) {
   using Cfg = TokCfg<BLOCK_C, kEpi>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -217,6 +232,45 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
       const int c0 = (t / m_tiles) * BLOCK_C;
       const bool ok = mbar_wait(&acc_full[buf], (n >> 1) & 1, status);
       tcgen05_fence_after();
+      if constexpr (kEpi == kEpiSample) {
+        if (ok) {
+          const bool live = r < m_total;                                   // padding rows of the token tile: nothing to sample
+          const float T = live ? samp.temps[r] : 0.f;
+          const bool greedy = !(T > 0.f);
+          const float inv_t = greedy ? 1.f : 1.f / T;
+          const uint32_t step = static_cast<uint32_t>(samp.header[9]);
+          const uint32_t k0 = static_cast<uint32_t>(samp.header[10]), k1 = static_cast<uint32_t>(samp.header[11]);
+          Best best{-INFINITY, 0x7fffffff};
+#pragma unroll 1
+          for (int cc = 0; cc < BLOCK_C; cc += 32) {
+            uint32_t v[32];
+            tmem_ld_x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * Cfg::kAccCols + cc, v);
+            tmem_ld_wait();
+            if (live) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                const int c = c0 + cc + j;                                 // local vocabulary index; n_total is a multiple of 4
+                if (c < n_total) {
+                  const int gid = samp.vocab_start + c;
+                  uint32_t rnd[4] = {0, 0, 0, 0};
+                  if (!greedy) philox4x32_10(static_cast<uint32_t>(gid >> 2), static_cast<uint32_t>(r), step, 0u, k0, k1, rnd);
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) {
+                    float sc = bf16_round_g(__uint_as_float(v[j + q])) * inv_t;
+                    if (!greedy) sc += gumbel_from_bits(rnd[q]);
+                    best = better(best, Best{sc, gid + q});
+                  }
+                }
+              }
+            }
+          }
+          if (live) {
+            const size_t slot = static_cast<size_t>(r) * samp.n_tiles + t / m_tiles;
+            samp.part_v[slot] = best.v;
+            samp.part_i[slot] = best.i;
+          }
+        }
+      } else
       if (ok) {
         constexpr int kChunk = BLOCK_C >= 32 ? 32 : 16;
         const float row_scale = fuse_row_scale(fuse, r, m_total);          // 1 unless the input norm is folded in
@@ -668,7 +722,8 @@ extern "C" int forge_gemm_set_trace(unsigned long long* buf) {
 
 template <int BLOCK_C, int kEpi>
 static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int ldw, __nv_bfloat16* out, int ldo, int M,
-                         int n_out, int K, unsigned* status, cudaStream_t stream, const TpPush& push, const GemmFuse& fuse) {
+                         int n_out, int K, unsigned* status, cudaStream_t stream, const TpPush& push, const GemmFuse& fuse,
+                         const GemmSample& samp = GemmSample{}) {
   using Cfg = TokCfg<BLOCK_C, kEpi>;
   CUtensorMap tm_x, tm_w;
   if (forge_make_tmap_2d(&tm_x, x, M, K, ldx, kBlockR, 2) != 0) return -2;
@@ -684,7 +739,7 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
   }
   dim3 grid(tiles < num_sms ? tiles : num_sms);
   return launch_kernel(kern, grid, dim3(kGemmThreads), Cfg::kSmemBytes, stream, 0, tm_x, tm_w, out, ldo, M, n_out, K, n_out,
-                       status, push, fuse) == cudaSuccess ? 0 : -5;
+                       status, push, fuse, samp) == cudaSuccess ? 0 : -5;
 }
 
 // Cluster size (K splits) of the decode kernel.  Measured on B200 (sweeps over token tile x splits x ring depth for
@@ -831,6 +886,32 @@ extern "C" int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, v
 // Row-parallel GEMM under tensor parallelism: `out` is this rank's partial buffer in symmetric memory (row stride ldo);
 // the kernel's last CTA announces completion to every rank through signal_ptrs (tp_size addresses in peer order).
 // Up to 256 rows run on the weight-tile (decode) kernel, more on the persistent token-tile kernel.
+extern "C" int forge_sample_merge(const float* part_v, const int* part_i, int n, int rows, int* out_i, float* out_v, cudaStream_t stream);
+
+// LM head + sampling in one pass over the weights: out_i[r] = the sampled (T > 0) or arg-max (T == 0) GLOBAL token id of
+// row r among this rank's `vocab` columns, out_v[r] its score (for the cross-rank merge).  The logits are never written.
+// part_v / part_i: scratch of M * ceil(vocab / 256) entries.  vocab and vocab_start must be multiples of 4.
+extern "C" int forge_gemm_bf16_sample(const void* x, int ldx, const void* w, int ldw, int M, int vocab, int K, int vocab_start,
+                                      const float* temps, const int* header, float* part_v, int* part_i, int* out_i, float* out_v,
+                                      unsigned* status, cudaStream_t stream) {
+  if (M <= 0 || vocab <= 0) return 0;
+  if ((K & 7) || (ldx & 7) || (ldw & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
+      (vocab & 3) || (vocab_start & 3))
+    return -1;
+  GemmSample samp;
+  samp.temps = temps;
+  samp.header = header;
+  samp.vocab_start = vocab_start;
+  samp.part_v = part_v;
+  samp.part_i = part_i;
+  samp.n_tiles = (vocab + 255) / 256;
+  TpPush none = {};
+  GemmFuse plain = {};
+  const int rc = launch_tokens<256, kEpiSample>(x, ldx, w, vocab, ldw, nullptr, 0, M, vocab, K, status, stream, none, plain, samp);
+  if (rc != 0) return rc;
+  return forge_sample_merge(part_v, part_i, samp.n_tiles, M, out_i, out_v, stream);
+}
+
 // The same with the neighbouring norm / residual add fused in (see GemmFuse).  in_ssq: fp32 [M][in_parts] partial sums of
 // squares of the rows of x (null: rows are not scaled).  add_residual: out += result in place and out_ssq (fp32
 // [M][ceil(n_out / 128)], may be null) receives the sums of squares of the new rows per 128 features.

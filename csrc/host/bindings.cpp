@@ -13,6 +13,9 @@ int forge_gemm_bf16(const void* x, int ldx, const void* w, int ldw, void* out, i
 int forge_gemm_bf16_fused(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K, int epi,
                           int force_mode, int tune, const float* in_ssq, int in_parts, float eps, int add_residual, float* out_ssq,
                           unsigned* status, cudaStream_t stream);
+int forge_gemm_bf16_sample(const void* x, int ldx, const void* w, int ldw, int M, int vocab, int K, int vocab_start, const float* temps,
+                           const int* header, float* part_v, int* part_i, int* out_i, float* out_v, unsigned* status,
+                           cudaStream_t stream);
 int forge_gemm_set_trace(unsigned long long* buf);
 int forge_quant_fp8_1x128(const void* x, void* xq, float* scale, int M, int K, int scale_ld, cudaStream_t stream);
 int forge_gemm_fp8_splits(int M, int N, int K);
@@ -150,6 +153,28 @@ void gemm_fused(const Tensor& x, const Tensor& w, Tensor& out, int64_t epi, int6
                               static_cast<int>(epi), static_cast<int>(force_mode), static_cast<int>(tune), in_p, in_parts,
                               static_cast<float>(eps), add_residual ? 1 : 0, out_p, status_ptr(status), stream_of(x)),
         "forge_gemm_bf16_fused");
+}
+
+// LM head + sampling: x [rows, K] @ w [vocab, K]^T, sampled per row without writing the logits.  part_v / part_i: scratch of
+// rows * ceil(vocab / 256) entries; out_i / out_v: the winning global id and its score per row.
+void gemm_sample(const Tensor& x, const Tensor& w, int64_t vocab_start, const Tensor& temps, const Tensor& header, Tensor& part_v,
+                 Tensor& part_i, Tensor& out_i, Tensor& out_v, const Tensor& status) {
+  CHECK_BF16(x); CHECK_BF16(w); CHECK_CUDA_CONTIG(temps); CHECK_F32(temps); CHECK_CUDA_CONTIG(header); CHECK_I32(header);
+  CHECK_CUDA_CONTIG(part_v); CHECK_F32(part_v); CHECK_CUDA_CONTIG(part_i); CHECK_I32(part_i);
+  CHECK_CUDA_CONTIG(out_i); CHECK_I32(out_i); CHECK_CUDA_CONTIG(out_v); CHECK_F32(out_v);
+  TORCH_CHECK(x.is_cuda() && w.is_cuda() && x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && w.size(1) == x.size(1),
+              "gemm_sample: operands");
+  const int64_t rows = x.size(0), vocab = w.size(0), tiles = (vocab + 255) / 256;
+  TORCH_CHECK(temps.numel() >= rows && header.numel() >= 12 && out_i.numel() >= rows && out_v.numel() >= rows &&
+                  part_v.numel() >= rows * tiles && part_i.numel() >= rows * tiles,
+              "gemm_sample: lengths");
+  TORCH_CHECK(vocab % 4 == 0 && vocab_start % 4 == 0, "gemm_sample: the vocabulary shard must start and end on a multiple of 4");
+  const c10::cuda::CUDAGuard guard(x.device());
+  check(forge_gemm_bf16_sample(x.data_ptr(), static_cast<int>(x.stride(0)), w.data_ptr(), static_cast<int>(w.stride(0)),
+                               static_cast<int>(rows), static_cast<int>(vocab), static_cast<int>(x.size(1)),
+                               static_cast<int>(vocab_start), temps.data_ptr<float>(), header.data_ptr<int>(), part_v.data_ptr<float>(),
+                               part_i.data_ptr<int>(), out_i.data_ptr<int>(), out_v.data_ptr<float>(), status_ptr(status), stream_of(x)),
+        "forge_gemm_bf16_sample");
 }
 
 // Phase timeline of the decode GEMM (profiling aid): int64 CUDA tensor of >= 8 * CTAs entries, or None to switch off.
@@ -592,6 +617,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "tinyllmforge_b200 sm_100a kernels";
   m.def("gemm", &gemm);
   m.def("gemm_fused", &gemm_fused);
+  m.def("gemm_sample", &gemm_sample);
   m.def("gemm_set_trace", &gemm_set_trace);
   m.def("quant_fp8", &quant_fp8);
   m.def("gemm_fp8_block", &gemm_fp8_block);

@@ -462,6 +462,28 @@ def test_sampler_distribution(ops):
     assert (freq - want).abs().max() < 0.03
 
 
+@pytest.mark.parametrize("rows,vocab,start", [(8, 151936, 0), (64, 75968, 75968), (200, 40000, 4), (256, 151936, 0)])
+def test_lm_head_gemm_samples_in_its_epilogue_like_the_two_kernel_path(ops, rows, vocab, start):
+    """LM head + sampling in one kernel (logits never written) picks exactly the tokens of GEMM -> logits -> sampler:
+    the same bf16-rounded logits, the same noise per (row, global token id); greedy rows (T = 0) are the arg-max."""
+    torch.manual_seed(rows + vocab)
+    K = 1024
+    hidden, w = _rand(rows, K), _rand(vocab, K, scale=0.05)
+    temps = torch.full((rows,), 0.6, device="cuda")
+    temps[::3] = 0.0
+    temps[1::5] = 1.3
+    hdr = _header(step=11, seed=5)
+    assert ops.can_sample_in_lm_head(rows, w)
+    ids, best = ops.lm_head_sample_shard(hidden, w, temps, hdr, start)
+    logits = ops.linear(hidden, w)
+    want_ids, want_best = ops.sample_shard(logits, temps, hdr, start)
+    assert torch.equal(ids, want_ids)
+    assert torch.equal(best, want_best)
+    greedy = (temps == 0).nonzero().flatten()
+    assert torch.equal(ids[greedy].long() - start, logits[greedy].float().argmax(-1))
+    ops.check_status()
+
+
 # ----------------------------------------------------------------------------- bounded waits
 def test_peer_flag_wait_runs_out_and_reports_status(ops):
     """Failure detection on the device: a consumer waits for a peer that never signals (the flag word is simply

@@ -188,5 +188,14 @@ class Qwen3ForCausalLM:
         return self.ops.sample(logits, batch, self.lm_head.vocab_start, self.tp)
 
     def step(self, batch) -> torch.Tensor:
-        """forward + logits + sampling: token ids for the first ``batch.num_seqs`` rows."""
-        return self.sample(self.compute_logits(self.forward(batch), batch), batch)
+        """forward + logits + sampling: token ids for the first ``batch.num_seqs`` rows.  Where the op set can sample in
+        the epilogue of the LM-head GEMM, the logits are never materialised (the reference writes them, gathers them to
+        rank 0 and samples there: tinyvllm/layers/embed_head.py:58-70, tinyvllm/layers/sampler.py:13-21)."""
+        hidden = self.forward(batch)
+        ops, head = self.ops, self.lm_head
+        rows = batch.last_index.shape[0]
+        if hasattr(ops, "can_sample_in_lm_head") and head.bias is None and ops.can_sample_in_lm_head(rows, head.weight):
+            last = ops.select_rows(hidden, batch.last_index)
+            ids, best = ops.lm_head_sample_shard(last, head.weight, batch.temperatures, batch.header, head.vocab_start)
+            return ops.merge_ranks(ids, best, self.tp)
+        return self.sample(self.compute_logits(hidden, batch), batch)

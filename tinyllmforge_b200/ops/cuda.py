@@ -75,6 +75,7 @@ class CudaOps:
         # Scratch of the flat kernel, sized for any head grouping (~1.2 MB).
         self.decode_attention_mode = os.environ.get("FORGE_DECODE_ATTN", "auto")
         self.fused_qkv_max_batch = int(os.environ.get("FORGE_FUSED_QKV_MAX", "32"))   # see models/qwen3.py
+        self.sample_in_lm_head = os.environ.get("FORGE_LM_HEAD_SAMPLE", "1") != "0"
         self._flat_scratch = torch.empty(2 * self.num_sms * (2 * 4 * 130 + 2) + 64, dtype=torch.float32, device=self.device)
 
     # ------------------------------------------------------------------ status word
@@ -379,8 +380,30 @@ class CudaOps:
         self.launches += 2
         return ids, best
 
+    def can_sample_in_lm_head(self, rows: int, weight) -> bool:
+        """The LM-head GEMM can sample in its epilogue when it runs on the persistent token-tile kernel (many vocabulary
+        tiles, at least 8 rows) over a bf16 shard whose bounds are multiples of 4 (one Philox call serves 4 token ids)."""
+        return (self.sample_in_lm_head and not isinstance(weight, Fp8BlockWeight) and rows >= 8 and weight.shape[0] % 4 == 0
+                and (weight.shape[0] + 127) // 128 >= 296)
+
+    def lm_head_sample_shard(self, hidden, weight, temperatures, header, vocab_start):
+        """(ids int32 [rows], scores fp32 [rows]) of this vocab shard, sampled in the epilogue of the LM-head GEMM: the
+        ``[rows, vocab / tp]`` logits are never written.  Same tokens as ``linear`` + ``sample_shard``."""
+        rows, tiles = hidden.shape[0], (weight.shape[0] + 255) // 256
+        part_v = torch.empty(rows * tiles, dtype=torch.float32, device=hidden.device)
+        part_i = torch.empty(rows * tiles, dtype=torch.int32, device=hidden.device)
+        ids = torch.empty(rows, dtype=torch.int32, device=hidden.device)
+        best = torch.empty(rows, dtype=torch.float32, device=hidden.device)
+        self.C.gemm_sample(hidden, weight, vocab_start, temperatures, header, part_v, part_i, ids, best, self.status)
+        self.launches += 2
+        return ids, best
+
     def sample(self, logits, batch, vocab_start, tp):
         ids, best = self.sample_shard(logits, batch.temperatures, batch.header, vocab_start)
+        return self.merge_ranks(ids, best, tp)
+
+    def merge_ranks(self, ids, best, tp):
+        """The winner among the ranks' (id, score) pairs of every row; every rank gets the same ids."""
         if tp.size == 1:
             return ids
         if self.fused is not None and ids.shape[0] <= 512:
