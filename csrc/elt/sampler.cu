@@ -1,18 +1,13 @@
-// Temperature sampling without a softmax and without materialising probabilities.
+// Temperature sampling without a softmax, without materialising probabilities, and with one random number per GROUP of
+// 16 token ids instead of one per token id (the two-level procedure is described in include/sampling.cuh).
 //
 // The reference computes softmax(logits / T), divides by Exp(1) noise and takes the argmax
-// (tinyvllm/layers/sampler.py:13-21): eight ATen kernels over [rows, vocab] fp32.  Dividing by an
-// exponential and taking the argmax is the Gumbel-max trick, and the softmax normaliser is constant
-// per row, so   token = argmax_i ( logit_i / T  -  log(-log u_i) )   draws from the same distribution.
-// T == 0 selects plain argmax.
+// (tinyvllm/layers/sampler.py:13-21): eight ATen kernels over [rows, vocab] fp32.
 //
-// u_i comes from Philox-4x32-10 keyed by the engine seed with counter (global vocab id / 4, row, step, 0),
-// lane = id % 4: a pure function of (seed, step, row, GLOBAL vocab id).  A vocabulary sharded over
-// tensor-parallel ranks therefore samples the same token as an unsharded one: each rank reduces its shard to
-// one (score, id) pair per row and only those pairs are merged (ops/ref.py gumbel_noise is the same function
-// on the CPU).
+// A vocabulary sharded over tensor-parallel ranks samples the same token as an unsharded one: each rank reduces its shard to
+// one (group score, token id) pair per row and only those pairs are merged.
 //
-// Two kernels: partial argmax per (row, vocab slice), then a merge per row that can also fold in the pairs
+// Two kernels: the best group per (row, vocab slice) and its token, then a merge per row that can also fold in the pairs
 // of other ranks.
 #include "../include/launch.cuh"
 #include "../include/ptx.cuh"
@@ -21,6 +16,24 @@
 namespace forge {
 
 constexpr int kSampleThreads = 256;
+
+// The 16 logits of group g of a row (global ids 16 g ..), -INFINITY outside the shard [vocab_start, vocab_start + vocab).
+__device__ __forceinline__ void load_group(const __nv_bfloat16* lrow, int g, int vocab_start, int vocab, bool aligned, float lv[kSampleGroup]) {
+  const int local0 = g * kSampleGroup - vocab_start;
+  if (aligned && local0 >= 0 && local0 + kSampleGroup <= vocab) {
+    const uint4 a = *reinterpret_cast<const uint4*>(lrow + local0), b = *reinterpret_cast<const uint4*>(lrow + local0 + 8);
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      lv[2 * j] = bf16_lo(w[j]);
+      lv[2 * j + 1] = bf16_hi(w[j]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < kSampleGroup; ++j)
+      lv[j] = (local0 + j >= 0 && local0 + j < vocab) ? __bfloat162float(lrow[local0 + j]) : -INFINITY;
+  }
+}
 
 // header: the packed step buffer's first words; [9] = step index, [10], [11] = seed low / high.
 __global__ void __launch_bounds__(kSampleThreads) sample_partial_kernel(
@@ -36,36 +49,22 @@ __global__ void __launch_bounds__(kSampleThreads) sample_partial_kernel(
   const float inv_t = greedy ? 1.f : 1.f / T;
   const uint32_t step = static_cast<uint32_t>(header[9]);
   const uint32_t k0 = static_cast<uint32_t>(header[10]), k1 = static_cast<uint32_t>(header[11]);
-  // slice boundaries in groups of four ids, aligned on the GLOBAL id so one Philox call serves four ids
-  const int g_first = vocab_start >> 2, g_last = (vocab_start + vocab - 1) >> 2;
+  // slice boundaries in groups of 16 ids, aligned on the GLOBAL id
+  const int g_first = vocab_start / kSampleGroup, g_last = (vocab_start + vocab - 1) / kSampleGroup;
   const int ngroups = g_last - g_first + 1;
   const int per = (ngroups + nsplit - 1) / nsplit;
   const int gb = g_first + split * per;
   const int ge = min(gb + per, g_last + 1);
   const __nv_bfloat16* lrow = logits + static_cast<size_t>(row) * ld;
+  const bool aligned = (reinterpret_cast<uintptr_t>(lrow) & 15) == 0 && (vocab_start & 7) == 0;   // groups start on 16-byte boundaries
+  // level 1: every thread scores the groups it visits; `i` of the pair is the group index here
   Best best{-INFINITY, 0x7fffffff};
-  const bool row_aligned = ((reinterpret_cast<uintptr_t>(lrow) - 2 * static_cast<uintptr_t>(vocab_start & 3)) & 7) == 0;
   for (int g = gb + threadIdx.x; g < ge; g += kSampleThreads) {
+    float lv[kSampleGroup];
+    load_group(lrow, g, vocab_start, vocab, aligned, lv);
     uint32_t rnd[4] = {0, 0, 0, 0};
-    if (!greedy) philox4x32_10(static_cast<uint32_t>(g), static_cast<uint32_t>(row), step, 0u, k0, k1, rnd);
-    const int local0 = g * 4 - vocab_start;
-    float lv[4];
-    if (row_aligned && local0 >= 0 && local0 + 4 <= vocab) {        // one 8-byte load for the four logits of the group
-      const uint2 raw = *reinterpret_cast<const uint2*>(lrow + local0);
-      lv[0] = bf16_lo(raw.x); lv[1] = bf16_hi(raw.x); lv[2] = bf16_lo(raw.y); lv[3] = bf16_hi(raw.y);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) lv[j] = (local0 + j >= 0 && local0 + j < vocab) ? __bfloat162float(lrow[local0 + j]) : -INFINITY;
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int local = local0 + j;
-      if (local >= 0 && local < vocab) {
-        float s = lv[j] * inv_t;
-        if (!greedy) s += gumbel_from_bits(rnd[j]);
-        best = better(best, Best{s, g * 4 + j});
-      }
-    }
+    if (!greedy) philox4x32_10(static_cast<uint32_t>(g >> 2), static_cast<uint32_t>(row), step, 1u, k0, k1, rnd);
+    best = better(best, Best{sample_group_score(lv, inv_t, greedy, rnd[g & 3]), g});
   }
   best = warp_best(best);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -75,8 +74,15 @@ __global__ void __launch_bounds__(kSampleThreads) sample_partial_kernel(
     Best b = lane < kSampleThreads / 32 ? Best{sv[lane], si[lane]} : Best{-INFINITY, 0x7fffffff};
     b = warp_best(b);
     if (lane == 0) {
+      // level 2: the token inside the slice's winning group
+      int token = 0x7fffffff;
+      if (b.i != 0x7fffffff) {
+        float lv[kSampleGroup];
+        load_group(lrow, b.i, vocab_start, vocab, aligned, lv);
+        token = sample_group_token(lv, b.i, inv_t, greedy, static_cast<uint32_t>(row), step, k0, k1);
+      }
       part_v[static_cast<size_t>(row) * nsplit + split] = b.v;
-      part_i[static_cast<size_t>(row) * nsplit + split] = b.i;
+      part_i[static_cast<size_t>(row) * nsplit + split] = token;
     }
   }
 }

@@ -78,10 +78,11 @@ __device__ __forceinline__ float fuse_row_scale(const GemmFuse& f, int row, int 
 __device__ __forceinline__ float bf16_round_g(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
 // Sampling epilogue of the LM-head GEMM (kEpiSample): the logits never reach memory.  Each epilogue thread owns one
-// token row of the tile; it rounds every accumulator to bf16 (what the materialised logits would hold), scales by 1 / T,
-// adds the Gumbel noise of that (row, GLOBAL token id) and keeps the best (score, id) of the tile's columns; one pair per
-// (row, vocabulary tile) is written and a small kernel merges them.  Same numbers, hence the same tokens, as
-// sample_partial_kernel on materialised logits (tinyvllm/layers/embed_head.py:58-70 + tinyvllm/layers/sampler.py:13-21).
+// token row of the tile; it rounds every accumulator to bf16 (what the materialised logits would hold) and runs the
+// two-level sampler of include/sampling.cuh over the tile's 16 groups of 16 columns: the best group's score, and the token
+// drawn inside that group, are written as one pair per (row, vocabulary tile); a small kernel merges the pairs.  Same
+// numbers, hence the same tokens, as sample_partial_kernel on materialised logits (tinyvllm/layers/embed_head.py:58-70 +
+// tinyvllm/layers/sampler.py:13-21).
 struct GemmSample {
   const float* temps;        // [rows]
   const int* header;         // packed step header: [9] step index, [10], [11] seed
@@ -240,34 +241,41 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           const float inv_t = greedy ? 1.f : 1.f / T;
           const uint32_t step = static_cast<uint32_t>(samp.header[9]);
           const uint32_t k0 = static_cast<uint32_t>(samp.header[10]), k1 = static_cast<uint32_t>(samp.header[11]);
-          Best best{-INFINITY, 0x7fffffff};
+          Best best{-INFINITY, 0x7fffffff};              // best group of this tile: (score, group index)
+          float bestv[kSampleGroup];                     // its logits, kept for level 2
+#pragma unroll
+          for (int i = 0; i < kSampleGroup; ++i) bestv[i] = -INFINITY;
+          uint32_t rnd[4] = {0, 0, 0, 0};                // group noise: one Philox call per four groups (two chunks)
 #pragma unroll 1
           for (int cc = 0; cc < BLOCK_C; cc += 32) {
             uint32_t v[32];
             tmem_ld_x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * Cfg::kAccCols + cc, v);
             tmem_ld_wait();
-            if (live) {
+            if (live && c0 + cc < n_total) {
+              const int g0 = (samp.vocab_start + c0 + cc) / kSampleGroup;      // even: tiles and chunks start on multiples of 32 ids
+              if (!greedy && (g0 & 3) == 0)
+                philox4x32_10(static_cast<uint32_t>(g0 >> 2), static_cast<uint32_t>(r), step, 1u, k0, k1, rnd);
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                const int c = c0 + cc + j;                                 // local vocabulary index; n_total is a multiple of 4
-                if (c < n_total) {
-                  const int gid = samp.vocab_start + c;
-                  uint32_t rnd[4] = {0, 0, 0, 0};
-                  if (!greedy) philox4x32_10(static_cast<uint32_t>(gid >> 2), static_cast<uint32_t>(r), step, 0u, k0, k1, rnd);
+              for (int h = 0; h < 2; ++h) {
+                float lv[kSampleGroup];
 #pragma unroll
-                  for (int q = 0; q < 4; ++q) {
-                    float sc = bf16_round_g(__uint_as_float(v[j + q])) * inv_t;
-                    if (!greedy) sc += gumbel_from_bits(rnd[q]);
-                    best = better(best, Best{sc, gid + q});
-                  }
+                for (int i = 0; i < kSampleGroup; ++i)
+                  lv[i] = c0 + cc + h * kSampleGroup + i < n_total ? bf16_round_g(__uint_as_float(v[h * kSampleGroup + i])) : -INFINITY;
+                const float sg = sample_group_score(lv, inv_t, greedy, rnd[(g0 + h) & 3]);
+                if (sg > best.v) {                         // groups are visited in ascending order: ties keep the earlier one
+                  best = Best{sg, g0 + h};
+#pragma unroll
+                  for (int i = 0; i < kSampleGroup; ++i) bestv[i] = lv[i];
                 }
               }
             }
           }
+          int token = 0x7fffffff;
+          if (live && best.i != 0x7fffffff) token = sample_group_token(bestv, best.i, inv_t, greedy, static_cast<uint32_t>(r), step, k0, k1);
           if (live) {
             const size_t slot = static_cast<size_t>(r) * samp.n_tiles + t / m_tiles;
             samp.part_v[slot] = best.v;
-            samp.part_i[slot] = best.i;
+            samp.part_i[slot] = token;
           }
         }
       } else
@@ -890,13 +898,14 @@ extern "C" int forge_sample_merge(const float* part_v, const int* part_i, int n,
 
 // LM head + sampling in one pass over the weights: out_i[r] = the sampled (T > 0) or arg-max (T == 0) GLOBAL token id of
 // row r among this rank's `vocab` columns, out_v[r] its score (for the cross-rank merge).  The logits are never written.
-// part_v / part_i: scratch of M * ceil(vocab / 256) entries.  vocab and vocab_start must be multiples of 4.
+// part_v / part_i: scratch of M * ceil(vocab / 256) entries.  vocab_start must be a multiple of 32 (sampling groups of 16
+// ids; a 32-column chunk of the accumulator holds two whole groups).
 extern "C" int forge_gemm_bf16_sample(const void* x, int ldx, const void* w, int ldw, int M, int vocab, int K, int vocab_start,
                                       const float* temps, const int* header, float* part_v, int* part_i, int* out_i, float* out_v,
                                       unsigned* status, cudaStream_t stream) {
   if (M <= 0 || vocab <= 0) return 0;
   if ((K & 7) || (ldx & 7) || (ldw & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
-      (vocab & 3) || (vocab_start & 3))
+      (vocab_start & 31))
     return -1;
   GemmSample samp;
   samp.temps = temps;

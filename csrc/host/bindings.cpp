@@ -168,7 +168,7 @@ void gemm_sample(const Tensor& x, const Tensor& w, int64_t vocab_start, const Te
   TORCH_CHECK(temps.numel() >= rows && header.numel() >= 12 && out_i.numel() >= rows && out_v.numel() >= rows &&
                   part_v.numel() >= rows * tiles && part_i.numel() >= rows * tiles,
               "gemm_sample: lengths");
-  TORCH_CHECK(vocab % 4 == 0 && vocab_start % 4 == 0, "gemm_sample: the vocabulary shard must start and end on a multiple of 4");
+  TORCH_CHECK(vocab_start % 32 == 0, "gemm_sample: the vocabulary shard must start on a multiple of 32");
   const c10::cuda::CUDAGuard guard(x.device());
   check(forge_gemm_bf16_sample(x.data_ptr(), static_cast<int>(x.stride(0)), w.data_ptr(), static_cast<int>(w.stride(0)),
                                static_cast<int>(rows), static_cast<int>(vocab), static_cast<int>(x.size(1)),

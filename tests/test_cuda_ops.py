@@ -451,18 +451,21 @@ def test_sampler_is_invariant_to_vocab_sharding(ops):
     assert torch.equal(out, full_ids)
 
 
-def test_sampler_distribution(ops):
-    """Empirical frequencies over many steps follow softmax(logits / T)."""
-    vocab, T, n = 16, 0.7, 4000
-    logits = torch.linspace(-2, 2, vocab, device="cuda").to(BF)[None].repeat(n, 1).contiguous()
+@pytest.mark.parametrize("vocab,start", [(16, 0), (80, 0), (72, 16)])
+def test_sampler_distribution(ops, vocab, start):
+    """Empirical frequencies over many rows follow softmax(logits / T): one group (level 2 alone), several groups (level 1
+    picks the group, level 2 the token), and a shard whose last group is partial."""
+    T, n = 0.7, 6000
+    base = torch.linspace(-2, 2, vocab, device="cuda")[torch.randperm(vocab, device="cuda", generator=torch.Generator(device="cuda").manual_seed(vocab))]
+    logits = base.to(BF)[None].repeat(n, 1).contiguous()
     temps = torch.full((n,), T, device="cuda")
-    ids, _ = ops.sample_shard(logits, temps, _header(1, 7), 0)
-    freq = torch.bincount(ids.long().cpu(), minlength=vocab).float() / n
+    ids, _ = ops.sample_shard(logits, temps, _header(1, 7), start)
+    freq = torch.bincount(ids.long().cpu() - start, minlength=vocab).float() / n
     want = torch.softmax(logits[0].float().cpu() / T, -1)
-    assert (freq - want).abs().max() < 0.03
+    assert (freq - want).abs().max() < 0.025
 
 
-@pytest.mark.parametrize("rows,vocab,start", [(8, 151936, 0), (64, 75968, 75968), (200, 40000, 4), (256, 151936, 0)])
+@pytest.mark.parametrize("rows,vocab,start", [(8, 151936, 0), (64, 75968, 75968), (200, 40000, 40000), (256, 151936, 0)])
 def test_lm_head_gemm_samples_in_its_epilogue_like_the_two_kernel_path(ops, rows, vocab, start):
     """LM head + sampling in one kernel (logits never written) picks exactly the tokens of GEMM -> logits -> sampler:
     the same bf16-rounded logits, the same noise per (row, global token id); greedy rows (T = 0) are the arg-max."""

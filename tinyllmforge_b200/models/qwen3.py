@@ -194,7 +194,8 @@ class Qwen3ForCausalLM:
         hidden = self.forward(batch)
         ops, head = self.ops, self.lm_head
         rows = batch.last_index.shape[0]
-        if hasattr(ops, "can_sample_in_lm_head") and head.bias is None and ops.can_sample_in_lm_head(rows, head.weight):
+        if (hasattr(ops, "can_sample_in_lm_head") and getattr(head, "bias", None) is None and head.vocab_start % 32 == 0
+                and ops.can_sample_in_lm_head(rows, head.weight)):
             last = ops.select_rows(hidden, batch.last_index)
             ids, best = ops.lm_head_sample_shard(last, head.weight, batch.temperatures, batch.header, head.vocab_start)
             return ops.merge_ranks(ids, best, self.tp)

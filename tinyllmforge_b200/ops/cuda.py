@@ -382,8 +382,9 @@ class CudaOps:
 
     def can_sample_in_lm_head(self, rows: int, weight) -> bool:
         """The LM-head GEMM can sample in its epilogue when it runs on the persistent token-tile kernel (many vocabulary
-        tiles, at least 8 rows) over a bf16 shard whose bounds are multiples of 4 (one Philox call serves 4 token ids)."""
-        return (self.sample_in_lm_head and not isinstance(weight, Fp8BlockWeight) and rows >= 8 and weight.shape[0] % 4 == 0
+        tiles, at least 8 rows) over a bf16 shard; the shard must start on a multiple of 32 token ids (checked by the
+        caller that knows the start)."""
+        return (self.sample_in_lm_head and not isinstance(weight, Fp8BlockWeight) and rows >= 8
                 and (weight.shape[0] + 127) // 128 >= 296)
 
     def lm_head_sample_shard(self, hidden, weight, temperatures, header, vocab_start):

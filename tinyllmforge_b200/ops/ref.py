@@ -197,27 +197,59 @@ def gumbel_noise(rows: int, vocab: int, seed: int, step: int, vocab_start: int =
     bits = np.choose(np.broadcast_to(lane, outs[0].shape), outs)
     # u = (k + 0.5) / 2^24 with k the top 24 bits.  The winners of the arg-max have u close to 1, where fp32 cannot
     # resolve 1 - u; work from w = 1 - u = (2^24 - k - 0.5) / 2^24 in fp64: E = -log(u) = -log1p(-w), noise = -log(E).
+    return _gumbel_from_bits(bits)
+
+
+SAMPLE_GROUP = 16
+
+
+def _gumbel_from_bits(bits: np.ndarray) -> np.ndarray:
     k = (bits >> np.uint32(8)).astype(np.float64)
     w = (16777216.0 - k - 0.5) / 16777216.0
     return (-np.log(-np.log1p(-w))).astype(np.float32)
 
 
+def group_gumbel_noise(rows: int, g_first: int, ngroups: int, seed: int, step: int) -> np.ndarray:
+    """Gumbel noise per (row, group of 16 global vocab ids): Philox counter (g // 4, row, step, 1), lane g % 4."""
+    g = np.arange(g_first, g_first + ngroups, dtype=np.int64)
+    r = np.arange(rows, dtype=np.uint32)[:, None]
+    outs = philox4x32((g // 4).astype(np.uint32)[None, :], r, np.uint32(step & 0xFFFFFFFF), np.uint32(1),
+                      seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF)
+    bits = np.choose(np.broadcast_to((g % 4)[None, :], outs[0].shape), outs)
+    return _gumbel_from_bits(bits)
+
+
 def sample(logits: torch.Tensor, temperatures: torch.Tensor, seed: int, step: int, vocab_start: int = 0):
     """Returns (token ids int64 [rows], winning scores fp32 [rows]) over this vocab shard.
 
-    T == 0 -> argmax(logits).  T > 0 -> argmax(logits / T + Gumbel noise), which draws from
-    softmax(logits / T) exactly as the reference's ``probs / Exp(1)`` race does, without the softmax.
-    The score is returned so that vocab shards can be merged by taking the row-wise maximum.
+    T == 0 -> argmax(logits), score = the maximum.  T > 0 -> a draw from softmax(logits / T), as the reference's
+    ``probs / Exp(1)`` race is (tinyvllm/layers/sampler.py:13-21), in two levels so that only one random number per GROUP
+    of 16 consecutive global token ids is needed: (1) the winning group is argmax_g (logsumexp_{i in g}(logit_i / T) +
+    Gumbel(row, g)), which is distributed as the group holding the arg-max of per-token Gumbel-max sampling; (2) inside it
+    the token is argmax_i (logit_i / T + Gumbel(row, i)).  The score returned is the winning group's, so that vocab shards
+    (which start on multiples of 16) can be merged by taking the row-wise maximum.  Same procedure as csrc/include/sampling.cuh.
     """
     lf = logits.float()
     rows, vocab = lf.shape
     t = temperatures.float().to(lf.device)
     greedy = t <= 0
-    noise = torch.from_numpy(gumbel_noise(rows, vocab, seed, step, vocab_start)).to(lf.device)
     inv_t = torch.where(greedy, torch.ones_like(t), 1.0 / torch.where(greedy, torch.ones_like(t), t))
-    score = lf * inv_t[:, None] + torch.where(greedy[:, None], torch.zeros_like(noise), noise)
-    best, idx = score.max(dim=-1)
-    return idx + vocab_start, best
+    x = lf * inv_t[:, None]
+    G = SAMPLE_GROUP
+    g_first, g_last = vocab_start // G, (vocab_start + vocab - 1) // G
+    ngroups = g_last - g_first + 1
+    lead = vocab_start - g_first * G                      # ids of the first group that lie before the shard
+    padded = torch.full((rows, ngroups * G), float("-inf"), device=lf.device)
+    padded[:, lead:lead + vocab] = x
+    grp = padded.view(rows, ngroups, G)
+    gscore = torch.logsumexp(grp, dim=-1)
+    gnoise = torch.from_numpy(group_gumbel_noise(rows, g_first, ngroups, seed, step)).to(lf.device)
+    gscore = torch.where(greedy[:, None], grp.max(dim=-1).values, gscore + gnoise)
+    best, gwin = gscore.max(dim=-1)                        # ties -> the first (lowest) group
+    noise = torch.from_numpy(gumbel_noise(rows, ngroups * G, seed, step, g_first * G)).to(lf.device).view(rows, ngroups, G)
+    inner = grp + torch.where(greedy[:, None, None], torch.zeros_like(noise), noise)
+    pick = inner[torch.arange(rows, device=lf.device), gwin].argmax(dim=-1)
+    return (g_first + gwin) * G + pick, best
 
 
 # ----------------------------------------------------------------------------- op set
