@@ -293,12 +293,25 @@ __global__ void __launch_bounds__(256) tp_tagged_reduce_norm_kernel(TpTagged tp,
       if (i < nvec) {
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         const int first = local ? tp.rank : 0, last = local ? tp.rank + 1 : tp.size;
-        for (int s = first; s < last; ++s) {            // rank order: the same sum whichever rank owns the row
-          const uint32_t* p = tp.part + (static_cast<size_t>(s) * tp.rows_per_rank + j) * H + i * 8;
-          const uint4 a = tp_poll_tagged(p, tag_part, tp.timeout_ns, status);
-          const uint4 b = tp_poll_tagged(p + 4, tag_part, tp.timeout_ns, status);
-          acc[0] += bf16_lo(a.x); acc[1] += bf16_hi(a.x); acc[2] += bf16_lo(a.z); acc[3] += bf16_hi(a.z);
-          acc[4] += bf16_lo(b.x); acc[5] += bf16_hi(b.x); acc[6] += bf16_lo(b.z); acc[7] += bf16_hi(b.z);
+        const uint32_t* base = tp.part + static_cast<size_t>(j) * H + i * 8;
+        const size_t src_stride = static_cast<size_t>(tp.rows_per_rank) * H;
+        // all sources' words are requested before any is examined: the loads overlap instead of paying one trip to L2 each
+        uint4 a[kMaxTp], b[kMaxTp];
+#pragma unroll
+        for (int s = 0; s < kMaxTp; ++s) {
+          if (s >= first && s < last) {
+            a[s] = ld_volatile_v4(base + s * src_stride);
+            b[s] = ld_volatile_v4(base + s * src_stride + 4);
+          }
+        }
+#pragma unroll
+        for (int s = 0; s < kMaxTp; ++s) {              // rank order: the same sum whichever rank owns the row
+          if (s >= first && s < last) {
+            const uint4 wa = tp_poll_tagged(base + s * src_stride, a[s], tag_part, tp.timeout_ns, status);
+            const uint4 wb = tp_poll_tagged(base + s * src_stride + 4, b[s], tag_part, tp.timeout_ns, status);
+            acc[0] += bf16_lo(wa.x); acc[1] += bf16_hi(wa.x); acc[2] += bf16_lo(wa.z); acc[3] += bf16_hi(wa.z);
+            acc[4] += bf16_lo(wb.x); acc[5] += bf16_hi(wb.x); acc[6] += bf16_lo(wb.z); acc[7] += bf16_hi(wb.z);
+          }
         }
         reinterpret_cast<uint4*>(residual_out + static_cast<size_t>(row) * H)[i] =
             tp_add_residual8(acc, residual_in != nullptr ? residual_in + static_cast<size_t>(row) * H : nullptr, i);
@@ -331,8 +344,9 @@ __global__ void __launch_bounds__(256) tp_tagged_reduce_norm_kernel(TpTagged tp,
       uint4 o = make_uint4(0u, 0u, 0u, 0u);             // measurement mode: rows of other ranks are not exchanged
       if (!local) {
         const uint32_t* p = tp.y[tp.rank] + static_cast<size_t>(row) * H + i * 8;
-        const uint4 a = tp_poll_tagged(p, tag_rows, tp.timeout_ns, status);
-        const uint4 b = tp_poll_tagged(p + 4, tag_rows, tp.timeout_ns, status);
+        const uint4 a0 = ld_volatile_v4(p), b0 = ld_volatile_v4(p + 4);
+        const uint4 a = tp_poll_tagged(p, a0, tag_rows, tp.timeout_ns, status);
+        const uint4 b = tp_poll_tagged(p + 4, b0, tag_rows, tp.timeout_ns, status);
         o = make_uint4(a.x, a.z, b.x, b.z);
       }
       reinterpret_cast<uint4*>(y + static_cast<size_t>(row) * H)[i] = o;

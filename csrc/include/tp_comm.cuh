@@ -163,11 +163,12 @@ __device__ __forceinline__ void tp_push_done(const TpPush& tp, unsigned total_ct
 
 __device__ __forceinline__ bool tp_local_only(const unsigned* flag) { return flag != nullptr && *flag != 0u; }
 
-// Two tagged words (four bf16 values) at `p`: polls until both tags equal `tag` or the time limit passes.
-__device__ __forceinline__ uint4 tp_poll_tagged(const uint32_t* p, unsigned tag, long long timeout_ns, unsigned* status) {
-  uint4 v = ld_volatile_v4(p);
+// Two tagged words (four bf16 values) at `p`, first try already in `v`: polls until both tags equal `tag` or the time limit
+// passes.  Polling backs off (the words sit in this GPU's L2, where the peers' stores have to land too).
+__device__ __forceinline__ uint4 tp_poll_tagged(const uint32_t* p, uint4 v, unsigned tag, long long timeout_ns, unsigned* status) {
   if (v.y == tag && v.w == tag) return v;
   const unsigned long long t0 = global_timer_ns();
+  unsigned pause = 32;
   for (;;) {
     v = ld_volatile_v4(p);
     if (v.y == tag && v.w == tag) return v;
@@ -175,6 +176,8 @@ __device__ __forceinline__ uint4 tp_poll_tagged(const uint32_t* p, unsigned tag,
       set_status(status, kStatusFlagTimeout);
       return v;
     }
+    __nanosleep(pause);
+    if (pause < 256) pause <<= 1;
   }
 }
 
