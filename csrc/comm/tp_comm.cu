@@ -271,7 +271,7 @@ extern "C" int forge_tp_rs_norm_ag(int tp_size, int tp_rank, const long long* pa
 // polls the tagged words that row's owner sends and stores the plain row into `y`.  When the kernel completes, `y`
 // holds all rows on every rank.  At most 256 CTAs, all resident at once, so a CTA that polls never keeps one that
 // sends from running.
-__global__ void __launch_bounds__(256) tp_tagged_reduce_norm_kernel(TpTagged tp, const __nv_bfloat16* residual_in,
+__global__ void __launch_bounds__(256, 2) tp_tagged_reduce_norm_kernel(TpTagged tp, const __nv_bfloat16* residual_in,
                                                                     __nv_bfloat16* residual_out, const __nv_bfloat16* __restrict__ w,
                                                                     __nv_bfloat16* __restrict__ y, int rows, int H, float eps,
                                                                     unsigned* status) {
@@ -295,22 +295,26 @@ __global__ void __launch_bounds__(256) tp_tagged_reduce_norm_kernel(TpTagged tp,
         const int first = local ? tp.rank : 0, last = local ? tp.rank + 1 : tp.size;
         const uint32_t* base = tp.part + static_cast<size_t>(j) * H + i * 8;
         const size_t src_stride = static_cast<size_t>(tp.rows_per_rank) * H;
-        // all sources' words are requested before any is examined: the loads overlap instead of paying one trip to L2 each
-        uint4 a[kMaxTp], b[kMaxTp];
+        // four sources at a time: their words are requested before any is examined, so the loads overlap instead of
+        // paying one trip to L2 each (and the code stays small: this kernel runs dozens of times per step)
+#pragma unroll 1
+        for (int s0 = first; s0 < last; s0 += 4) {
+          uint4 a[4], b[4];
 #pragma unroll
-        for (int s = 0; s < kMaxTp; ++s) {
-          if (s >= first && s < last) {
-            a[s] = ld_volatile_v4(base + s * src_stride);
-            b[s] = ld_volatile_v4(base + s * src_stride + 4);
+          for (int k = 0; k < 4; ++k) {
+            if (s0 + k < last) {
+              a[k] = ld_volatile_v4(base + (s0 + k) * src_stride);
+              b[k] = ld_volatile_v4(base + (s0 + k) * src_stride + 4);
+            }
           }
-        }
 #pragma unroll
-        for (int s = 0; s < kMaxTp; ++s) {              // rank order: the same sum whichever rank owns the row
-          if (s >= first && s < last) {
-            const uint4 wa = tp_poll_tagged(base + s * src_stride, a[s], tag_part, tp.timeout_ns, status);
-            const uint4 wb = tp_poll_tagged(base + s * src_stride + 4, b[s], tag_part, tp.timeout_ns, status);
-            acc[0] += bf16_lo(wa.x); acc[1] += bf16_hi(wa.x); acc[2] += bf16_lo(wa.z); acc[3] += bf16_hi(wa.z);
-            acc[4] += bf16_lo(wb.x); acc[5] += bf16_hi(wb.x); acc[6] += bf16_lo(wb.z); acc[7] += bf16_hi(wb.z);
+          for (int k = 0; k < 4; ++k) {                 // rank order: the same sum whichever rank owns the row
+            if (s0 + k < last) {
+              const uint4 wa = tp_poll_tagged(base + (s0 + k) * src_stride, a[k], tag_part, tp.timeout_ns, status);
+              const uint4 wb = tp_poll_tagged(base + (s0 + k) * src_stride + 4, b[k], tag_part, tp.timeout_ns, status);
+              acc[0] += bf16_lo(wa.x); acc[1] += bf16_hi(wa.x); acc[2] += bf16_lo(wa.z); acc[3] += bf16_hi(wa.z);
+              acc[4] += bf16_lo(wb.x); acc[5] += bf16_hi(wb.x); acc[6] += bf16_lo(wb.z); acc[7] += bf16_hi(wb.z);
+            }
           }
         }
         reinterpret_cast<uint4*>(residual_out + static_cast<size_t>(row) * H)[i] =

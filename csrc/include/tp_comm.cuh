@@ -165,8 +165,10 @@ __device__ __forceinline__ bool tp_local_only(const unsigned* flag) { return fla
 
 // Two tagged words (four bf16 values) at `p`, first try already in `v`: polls until both tags equal `tag` or the time limit
 // passes.  Polling backs off (the words sit in this GPU's L2, where the peers' stores have to land too).
-__device__ __forceinline__ uint4 tp_poll_tagged(const uint32_t* p, uint4 v, unsigned tag, long long timeout_ns, unsigned* status) {
-  if (v.y == tag && v.w == tag) return v;
+// The retry loop is kept out of line: it is the rare path, and the kernels that poll are launched dozens of times per
+// step, where a small instruction footprint matters more than a call.
+static __device__ __noinline__ uint4 tp_poll_tagged_slow(const uint32_t* p, unsigned tag, long long timeout_ns, unsigned* status) {
+  uint4 v;
   const unsigned long long t0 = global_timer_ns();
   unsigned pause = 32;
   for (;;) {
@@ -179,6 +181,10 @@ __device__ __forceinline__ uint4 tp_poll_tagged(const uint32_t* p, uint4 v, unsi
     __nanosleep(pause);
     if (pause < 256) pause <<= 1;
   }
+}
+__device__ __forceinline__ uint4 tp_poll_tagged(const uint32_t* p, uint4 v, unsigned tag, long long timeout_ns, unsigned* status) {
+  if (v.y == tag && v.w == tag) return v;
+  return tp_poll_tagged_slow(p, tag, timeout_ns, status);
 }
 
 // Producer tail of the tagged-word push: nothing to announce (the data carries its tag); the last CTA of the grid
