@@ -16,6 +16,7 @@
 //
 // head_dim is 128 (all Qwen3 sizes).  Scores use exp2 with the scale folded into q.
 #include <algorithm>
+#include <cstdlib>
 
 #include "../include/decode_common.cuh"
 #include "../include/launch.cuh"
@@ -532,10 +533,307 @@ static int launch_decode_flat(const void* q, const void* kc, const void* vc, con
   return 0;
 }
 
+// =========================================================================================================
+// Flat tile partition on the tensor cores, for q-head groups of 4..8 per KV head (Qwen3-4B/8B: 4, 14B: 5, 32B: 8).
+//
+// With G q heads per KV head every cached K and V element takes part in G multiply-adds.  On the CUDA cores that is
+// the bound from G = 4 on (Qwen3-8B: 0.72 of copy bandwidth; a group of 8 had to stream the cache twice); as a matrix
+// product it is nothing: the G query rows are padded to the 16-row side of mma.sync m16n8k16, S = Q K^T and O += P V
+// run on the tensor cores exactly as in a prefill kernel, and the kernel is a pure stream of the cache again.
+// (tcgen05 has no use for 4..8 rows: its smallest tile is 64 rows, and the operand is streamed once, not reused.)
+//
+// Same partition, partial slots and merge kernel as decode_attn_flat_kernel.  Differences: one item = (sequence, KV
+// head) with all G heads; tiles of 64 tokens land in shared memory ROW BY ROW (one 256-byte bulk copy per token, issued
+// by all 32 lanes of the producer warp) with a row pitch of 272 bytes, so that the eight rows an ldmatrix touches fall
+// into different banks; one CTA per SM with a five-stage ring (174 KB in flight).
+// =========================================================================================================
+constexpr int kTcTile = 64;
+constexpr int kTcPitch = kD * 2 + 16;                 // bytes between token rows in shared memory
+constexpr int kTcTileBytes = kTcTile * kTcPitch;
+constexpr int kTcStages = 5;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// D (16 x 8, fp32) += A (16 x 16, bf16, rows 8..15 zero: a1 = a3 = 0) * B (16 x 8, bf16)
+__device__ __forceinline__ void mma_rows8(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+
+template <int G>
+__global__ void __launch_bounds__(kDecThreads, 1) decode_attn_flat_tc_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+    const int* __restrict__ block_tables, const int* __restrict__ context_lens, __nv_bfloat16* __restrict__ out,
+    float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ cta_meta, int B, int nq, int nkv, int block_size,
+    int table_width, int num_blocks, int min_tiles, float scale_log2, unsigned* status) {
+  static_assert(G >= 1 && G <= 8, "the query rows of a group fill the first eight rows of the MMA tile");
+  constexpr int kRing = kTcStages * 2 * kTcTileBytes;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  float* s_acc = reinterpret_cast<float*>(smem + kRing);                      // merge area, separate from the ring
+  int* cum = reinterpret_cast<int*>(s_acc + decode_merge_floats(G));          // [B + 1]
+  int* chunk_tot = cum + kFlatMaxSeqs + 1;                                    // [16]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(chunk_tot + 16) + 15) & ~uintptr_t(15));
+  uint64_t* empty_bar = full_bar + kTcStages;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kTcStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 4);
+    }
+    fence_mbar_init();
+  }
+  pdl_wait();                                           // q, the new K/V entries and the step buffer come from predecessors
+
+  // ---- exclusive prefix sum of tiles per sequence (as in decode_attn_flat_kernel)
+  const int n_chunks32 = (B + 31) >> 5;
+  for (int ch = warp; ch < n_chunks32; ch += kDecThreads / 32) {
+    const int b = ch * 32 + lane;
+    const int len = b < B ? decode_checked_len(context_lens, b, table_width * block_size, status) : 0;
+    int v = (len + kTcTile - 1) / kTcTile;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, v, o);
+      if (lane >= o) v += u;
+    }
+    if (b < B) cum[b + 1] = v;
+    if (lane == 31) chunk_tot[ch] = v;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int v = lane < n_chunks32 ? chunk_tot[lane] : 0;
+    const int own = v;
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) {
+      const int u = __shfl_up_sync(0xffffffffu, v, o);
+      if (lane >= o) v += u;
+    }
+    if (lane < 16) chunk_tot[lane] = v - own;
+    if (lane == 0) cum[0] = 0;
+  }
+  __syncthreads();
+  for (int b = threadIdx.x; b < B; b += kDecThreads) cum[b + 1] += chunk_tot[b >> 5];
+  __syncthreads();
+
+  const int items_per_seq = nkv;                        // one item = all G heads of a KV head
+  const int total = items_per_seq * cum[B];
+  int per_cta = (total + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  if (per_cta < min_tiles) per_cta = min_tiles;
+  const int f0 = blockIdx.x * per_cta;
+  const int f1 = min(f0 + per_cta, total);
+  for (int b = blockIdx.x; b < B; b += gridDim.x)
+    if (cum[b + 1] == cum[b])
+      for (int i = threadIdx.x; i < nq * kD; i += kDecThreads) out[static_cast<size_t>(b) * nq * kD + i] = __float2bfloat16_rn(0.f);
+  if (threadIdx.x == 0) cta_meta[blockIdx.x * 2] = -1;
+  if (f0 >= f1) return;                                 // uniform for the CTA
+  __syncthreads();
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ producer: every lane copies rows lane and lane + 32
+    FlatCursor c = flat_locate(cum, B, items_per_seq, f0);
+    int it = 0;
+    for (int f = f0; f < f1;) {
+      const int seg = min(c.n_b - c.t, f1 - f);
+      const int kvh = c.h;
+      const int* table = block_tables + static_cast<size_t>(c.b) * table_width;
+      for (int i = 0; i < seg; ++i, ++it) {
+        const int s = it % kTcStages;
+        const uint32_t ph = (it / kTcStages) & 1;
+        int ok = 1;
+        if (lane == 0) ok = mbar_wait(&empty_bar[s], ph ^ 1, status) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) { f = f1; break; }
+        const int tok0 = (c.t + i) * kTcTile;
+        int blk = table[tok0 / block_size];
+        if (blk < 0 || blk >= num_blocks) {
+          set_status(status, kStatusBadIndex);
+          blk = 0;
+        }
+        const size_t off = ((static_cast<size_t>(blk) * nkv + kvh) * block_size + (tok0 % block_size)) * kD;
+        uint8_t* stg = smem + s * 2 * kTcTileBytes;
+        if (lane == 0) mbar_expect_tx(&full_bar[s], 2 * kTcTile * kD * 2);
+        __syncwarp();                                   // the expectation is registered before any copy can complete
+#pragma unroll
+        for (int h = 0; h < kTcTile / 32; ++h) {
+          const int row = lane + 32 * h;
+          bulk_load(stg + row * kTcPitch, k_cache + off + static_cast<size_t>(row) * kD, kD * 2, &full_bar[s]);
+          bulk_load(stg + kTcTileBytes + row * kTcPitch, v_cache + off + static_cast<size_t>(row) * kD, kD * 2, &full_bar[s]);
+        }
+      }
+      f += seg;
+      flat_next_item(c, cum, B, items_per_seq);
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------------- consumers (warps 0..3): 16 tokens of every tile each
+  FlatCursor c = flat_locate(cum, B, items_per_seq, f0);
+  const int row = lane >> 2, quad = lane & 3;           // MMA fragment coordinates: query row (head of the group), column pair
+  const int mat = lane >> 3, mrow = lane & 7;           // ldmatrix: this lane supplies row `mrow` of matrix `mat`
+  int it = 0;
+  bool ok = true;
+  for (int f = f0; f < f1 && ok;) {
+    const int seg = min(c.n_b - c.t, f1 - f);
+    const int kvh = c.h;
+    const int qh0 = kvh * G;
+    const int len = decode_checked_len(context_lens, c.b, table_width * block_size, nullptr);
+    // A fragments of Q: rows 0..G-1 = the heads of the group, the rest zero; 8 k-steps of 16 dims
+    uint32_t qa[8][2];
+    {
+      const __nv_bfloat16* qp = q + (static_cast<size_t>(c.b) * nq + qh0 + row) * kD + 2 * quad;
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        qa[kk][0] = row < G ? *reinterpret_cast<const uint32_t*>(qp + kk * 16) : 0u;
+        qa[kk][1] = row < G ? *reinterpret_cast<const uint32_t*>(qp + kk * 16 + 8) : 0u;
+      }
+    }
+    float m_run = -INFINITY, l_run = 0.f;                // of query row `row`; l is this lane's share until the end
+    float o[16][4];
+#pragma unroll
+    for (int nb = 0; nb < 16; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f;
+    for (int i = 0; i < seg; ++i, ++it) {
+      const int s = it % kTcStages;
+      const uint32_t ph = (it / kTcStages) & 1;
+      ok = mbar_wait(&full_bar[s], ph, status);
+      if (!ok) break;
+      const uint32_t Ks = smem_u32(smem + s * 2 * kTcTileBytes) + warp * 16 * kTcPitch;   // this warp's 16 tokens
+      const uint32_t Vs = Ks + kTcTileBytes;
+      // S = Q K^T: two blocks of 8 tokens
+      float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int kk = 0; kk < 8; ++kk) {
+        uint32_t kb[4];
+        ldmatrix_x4(kb, Ks + ((mat >> 1) * 8 + mrow) * kTcPitch + (kk * 16 + (mat & 1) * 8) * 2);
+        mma_rows8(sc[0], qa[kk][0], qa[kk][1], kb[0], kb[1]);
+        mma_rows8(sc[1], qa[kk][0], qa[kk][1], kb[2], kb[3]);
+      }
+      // this lane: row `row`, tokens warp * 16 + j * 8 + 2 * quad + {0, 1} of the tile
+      const int valid = len - (c.t + i) * kTcTile;
+      float mt = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int tok = warp * 16 + j * 8 + 2 * quad + e;
+          sc[j][e] = tok < valid ? sc[j][e] * scale_log2 : -INFINITY;
+          mt = fmaxf(mt, sc[j][e]);
+        }
+      mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 1));
+      mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 2));
+      const float m_new = fmaxf(m_run, mt);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = exp2f(m_run - m_use);
+      float p[2][2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) p[j][e] = exp2f(sc[j][e] - m_use);
+      l_run = l_run * alpha + (p[0][0] + p[0][1] + p[1][0] + p[1][1]);
+      m_run = m_new;
+#pragma unroll
+      for (int nb = 0; nb < 16; ++nb) {
+        o[nb][0] *= alpha;
+        o[nb][1] *= alpha;
+      }
+      // O += P V: P as the A operand (16 tokens = one k-step), V transposed on the way out of shared memory
+      const uint32_t pa0 = pack_bf16x2(p[0][0], p[0][1]), pa2 = pack_bf16x2(p[1][0], p[1][1]);
+#pragma unroll
+      for (int dd = 0; dd < 8; ++dd) {
+        uint32_t vb[4];
+        ldmatrix_x4_trans(vb, Vs + ((mat & 1) * 8 + mrow) * kTcPitch + (dd * 16 + (mat >> 1) * 8) * 2);
+        mma_rows8(o[2 * dd], pa0, pa2, vb[0], vb[1]);
+        mma_rows8(o[2 * dd + 1], pa0, pa2, vb[2], vb[3]);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
+    }
+    if (!ok) break;
+    // ---- end of this CTA's part of the item: publish the warp's state in the layout decode_merged reads, merge, store
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (row < G) {
+      float* dst = s_acc + (warp * G + row) * kD + 2 * quad;
+#pragma unroll
+      for (int nb = 0; nb < 16; ++nb) *reinterpret_cast<float2*>(dst + nb * 8) = make_float2(o[nb][0], o[nb][1]);
+      if (quad == 0) {
+        s_acc[4 * G * kD + warp * G + row] = m_run;
+        s_acc[4 * G * kD + 4 * G + warp * G + row] = l_run;
+      }
+    }
+    named_barrier_sync(1, 128);
+    const bool starts_here = c.t == 0, whole = starts_here && seg == c.n_b;
+    const int d = threadIdx.x;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float M, L;
+      const float ov = decode_merged<G>(s_acc, g, d, M, L);
+      if (whole) {
+        out[(static_cast<size_t>(c.b) * nq + qh0 + g) * kD + d] = __float2bfloat16_rn(ov);
+      } else {
+        const size_t pp = (static_cast<size_t>(blockIdx.x) * 2 + (starts_here ? 1 : 0)) * G + g;
+        part_o[pp * kD + d] = ov;
+        if (d == 0) {
+          part_ml[pp * 2] = M;
+          part_ml[pp * 2 + 1] = L;
+        }
+      }
+    }
+    if (starts_here && !whole && d == 0) {
+      const int item_end = f + c.n_b;
+      cta_meta[blockIdx.x * 2] = c.b * items_per_seq + c.h;
+      cta_meta[blockIdx.x * 2 + 1] = (item_end - 1) / per_cta - static_cast<int>(blockIdx.x) + 1;
+    }
+    named_barrier_sync(1, 128);
+    f += seg;
+    flat_next_item(c, cum, B, items_per_seq);
+  }
+}
+
+// Group sizes the tensor-core variant takes (all heads of the group in one item); cache blocks of at least 64 tokens.
+static bool decode_flat_tc_ok(int group, int block_size) {
+  static const bool enabled = !(std::getenv("FORGE_DECODE_TC") != nullptr && std::getenv("FORGE_DECODE_TC")[0] == '0');
+  return enabled && block_size >= kTcTile && (group == 4 || group == 5 || group == 8);
+}
+
+extern "C" int forge_decode_attention_flat_uses_tensor_cores(int nq, int nkv, int block_size) {
+  return nkv > 0 && nq % nkv == 0 && decode_flat_tc_ok(nq / nkv, block_size) ? 1 : 0;
+}
+
+template <int G>
+static int launch_decode_flat_tc(const void* q, const void* kc, const void* vc, const int* bt, const int* lens, void* out,
+                                 float* scratch, int num_ctas, int B, int nq, int nkv, int block_size, int table_width, int num_blocks,
+                                 float scale_log2, unsigned* status, cudaStream_t stream) {
+  constexpr int smem = kTcStages * 2 * kTcTileBytes + decode_merge_floats(G) * 4 + (kFlatMaxSeqs + 1 + 16) * 4 + 16 + 2 * kTcStages * 8 + 128;
+  static_assert(smem <= 227 * 1024, "one CTA per SM");
+  auto kern = decode_attn_flat_tc_kernel<G>;
+  FORGE_ENSURE_DYN_SMEM(kern, smem);
+  float* part_o = scratch;
+  float* part_ml = part_o + static_cast<size_t>(num_ctas) * 2 * G * kD;
+  int* cta_meta = reinterpret_cast<int*>(part_ml + static_cast<size_t>(num_ctas) * 2 * G * 2);
+  const int min_tiles = 256 / kTcTile;
+  if (launch_kernel(kern, dim3(num_ctas), dim3(kDecThreads), smem, stream, 0, static_cast<const __nv_bfloat16*>(q),
+                    static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc), bt, lens,
+                    static_cast<__nv_bfloat16*>(out), part_o, part_ml, cta_meta, B, nq, nkv, block_size, table_width, num_blocks,
+                    min_tiles, scale_log2, status) != cudaSuccess)
+    return -5;
+  if (launch_kernel(decode_flat_combine_kernel<G>, dim3(num_ctas), dim3(kD), 0, stream, 0, static_cast<const float*>(part_o),
+                    static_cast<const float*>(part_ml), static_cast<const int*>(cta_meta), static_cast<__nv_bfloat16*>(out), nq,
+                    nkv) != cudaSuccess)
+    return -5;
+  return 0;
+}
+
 // Floats of scratch the flat kernel needs for a grid of num_ctas CTAs and up to B sequences.
 extern "C" size_t forge_decode_attention_flat_scratch_floats(int num_ctas, int B, int nq, int nkv) {
   const int group = nkv > 0 ? nq / nkv : 1;
-  const int G = decode_group_slice(group);
+  int G = decode_group_slice(group);
+  if (group <= 8 && group > G) G = group;               // the tensor-core variant keeps all heads of a group in one item
   (void)B;
   return static_cast<size_t>(num_ctas) * 2 * G * (kD + 2) + static_cast<size_t>(num_ctas) * 2 + 64;
 }
@@ -553,6 +851,14 @@ static int decode_flat_impl(const void* q, const void* kc, const void* vc, const
   const int group = nq / nkv;
   const int G = decode_group_slice(group);
   const float sl2 = scale * 1.4426950408889634f;
+  if (fuse.qkv == nullptr && decode_flat_tc_ok(group, block_size)) {
+#define FORGE_TC(GG) \
+  return launch_decode_flat_tc<GG>(q, kc, vc, bt, lens, out, scratch, num_ctas, B, nq, nkv, block_size, table_width, num_blocks, sl2, status, stream)
+    if (group == 4) FORGE_TC(4);
+    if (group == 5) FORGE_TC(5);
+    FORGE_TC(8);
+#undef FORGE_TC
+  }
 #define FORGE_DEC(GG, TT)                                                                                                       \
   return launch_decode_flat<GG, TT>(q, kc, vc, bt, lens, out, scratch, num_ctas, B, nq, nkv, block_size, table_width, num_blocks, \
                                     sl2, status, stream, fuse)

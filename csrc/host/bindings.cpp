@@ -67,6 +67,7 @@ int forge_decode_attention(const void* q, const void* kc, const void* vc, const 
                            float* part_o, float* part_ml, int B, int nq, int nkv, int head_dim, int block_size, int table_width,
                            int num_blocks, int chunk, int max_chunks, float scale, unsigned* status, cudaStream_t stream);
 size_t forge_decode_attention_flat_scratch_floats(int num_ctas, int B, int nq, int nkv);
+int forge_decode_attention_flat_uses_tensor_cores(int nq, int nkv, int block_size);
 int forge_decode_attention_flat(const void* q, const void* kc, const void* vc, const int* bt, const int* lens, void* out,
                                 float* scratch, int num_ctas, int B, int nq, int nkv, int head_dim, int block_size, int table_width,
                                 int num_blocks, float scale, unsigned* status, cudaStream_t stream);
@@ -339,6 +340,11 @@ void decode_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_ca
 int64_t decode_attention_flat_scratch_floats(int64_t num_ctas, int64_t B, int64_t nq, int64_t nkv) {
   return static_cast<int64_t>(forge_decode_attention_flat_scratch_floats(static_cast<int>(num_ctas), static_cast<int>(B),
                                                                          static_cast<int>(nq), static_cast<int>(nkv)));
+}
+
+// True when the flat decode kernel for this head grouping runs on the tensor cores (one CTA per SM is then the grid to use).
+bool decode_attention_flat_uses_tensor_cores(int64_t nq, int64_t nkv, int64_t block_size) {
+  return forge_decode_attention_flat_uses_tensor_cores(static_cast<int>(nq), static_cast<int>(nkv), static_cast<int>(block_size)) != 0;
 }
 
 // Decode attention with the flat tile partition: num_ctas CTAs share all KV tiles equally.  scratch: fp32, at least
@@ -643,5 +649,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("decode_attention_flat", &decode_attention_flat);
   m.def("decode_attention_qkv", &decode_attention_qkv);
   m.def("decode_attention_flat_scratch_floats", &decode_attention_flat_scratch_floats);
+  m.def("decode_attention_flat_uses_tensor_cores", &decode_attention_flat_uses_tensor_cores);
   m.def("prefill_attention", &prefill_attention);
 }

@@ -212,8 +212,10 @@ class CudaOps:
             return out
         B = batch.padded_seqs
         if self.decode_attention_mode == "flat" or (self.decode_attention_mode == "auto" and 48 <= B <= 512):
-            # all KV tiles of the step dealt out equally to two CTAs per SM (one for wide head groups); lengths are read on the device
-            ctas = (1 if decode_group_slice(H // k_cache.shape[1]) > 4 else 2) * self.num_sms
+            # all KV tiles of the step dealt out equally to two CTAs per SM (one for wide head groups and for the tensor-core
+            # variant that takes groups of 4..8 q heads per KV head); lengths are read on the device
+            one = decode_group_slice(H // k_cache.shape[1]) > 4 or self.C.decode_attention_flat_uses_tensor_cores(H, k_cache.shape[1], k_cache.shape[2])
+            ctas = (1 if one else 2) * self.num_sms
             need = self.C.decode_attention_flat_scratch_floats(ctas, B, H, k_cache.shape[1])
             if self._flat_scratch is None or self._flat_scratch.numel() < need:
                 self._flat_scratch = torch.empty(need, dtype=torch.float32, device=q.device)
