@@ -542,15 +542,18 @@ static int launch_decode_flat(const void* q, const void* kc, const void* vc, con
 // run on the tensor cores exactly as in a prefill kernel, and the kernel is a pure stream of the cache again.
 // (tcgen05 has no use for 4..8 rows: its smallest tile is 64 rows, and the operand is streamed once, not reused.)
 //
-// Same partition, partial slots and merge kernel as decode_attn_flat_kernel.  Differences: one item = (sequence, KV
-// head) with all G heads; tiles of 64 tokens land in shared memory ROW BY ROW (one 256-byte bulk copy per token, issued
-// by all 32 lanes of the producer warp) with a row pitch of 272 bytes, so that the eight rows an ldmatrix touches fall
-// into different banks; one CTA per SM with a five-stage ring (174 KB in flight).
+// Same partition, partial slots, merge kernel and bulk-copy ring as decode_attention_flat_kernel (a tile = 64 tokens =
+// one contiguous 16 KB run per operand); one item = (sequence, KV head) with all G heads.  The token rows sit 256 bytes
+// apart in shared memory, so the eight rows an ldmatrix touches share their banks (8 wavefronts instead of 1): at one
+// tile per ~0.7 us and SM that costs about a third of the shared-memory cycles and is cheaper than any layout that
+// needs one copy per row (measured: 256-byte row copies with a padded pitch ran at 0.17 of copy bandwidth).
+// Groups of up to 5 heads leave room for two CTAs per SM (three stages each); 8 heads take one CTA with six stages.
 // =========================================================================================================
 constexpr int kTcTile = 64;
-constexpr int kTcPitch = kD * 2 + 16;                 // bytes between token rows in shared memory
+constexpr int kTcPitch = kD * 2;                      // bytes between token rows in shared memory
 constexpr int kTcTileBytes = kTcTile * kTcPitch;
-constexpr int kTcStages = 5;
+__host__ __device__ constexpr int tc_ctas_per_sm(int G) { return G > 5 ? 1 : 2; }
+__host__ __device__ constexpr int tc_stages(int G) { return G > 5 ? 6 : 3; }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -565,12 +568,13 @@ __device__ __forceinline__ void mma_rows8(float (&c)[4], uint32_t a0, uint32_t a
 }
 
 template <int G>
-__global__ void __launch_bounds__(kDecThreads, 1) decode_attn_flat_tc_kernel(
+__global__ void __launch_bounds__(kDecThreads, tc_ctas_per_sm(G)) decode_attn_flat_tc_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
     const int* __restrict__ block_tables, const int* __restrict__ context_lens, __nv_bfloat16* __restrict__ out,
     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ cta_meta, int B, int nq, int nkv, int block_size,
     int table_width, int num_blocks, int min_tiles, float scale_log2, unsigned* status) {
   static_assert(G >= 1 && G <= 8, "the query rows of a group fill the first eight rows of the MMA tile");
+  constexpr int kTcStages = tc_stages(G);
   constexpr int kRing = kTcStages * 2 * kTcTileBytes;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
@@ -635,39 +639,33 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_attn_flat_tc_kernel(
   __syncthreads();
 
   if (warp == 4) {
-    // ------------------------------------------------------------------ producer: every lane copies rows lane and lane + 32
-    FlatCursor c = flat_locate(cum, B, items_per_seq, f0);
-    int it = 0;
-    for (int f = f0; f < f1;) {
-      const int seg = min(c.n_b - c.t, f1 - f);
-      const int kvh = c.h;
-      const int* table = block_tables + static_cast<size_t>(c.b) * table_width;
-      for (int i = 0; i < seg; ++i, ++it) {
-        const int s = it % kTcStages;
-        const uint32_t ph = (it / kTcStages) & 1;
-        int ok = 1;
-        if (lane == 0) ok = mbar_wait(&empty_bar[s], ph ^ 1, status) ? 1 : 0;
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (!ok) { f = f1; break; }
-        const int tok0 = (c.t + i) * kTcTile;
-        int blk = table[tok0 / block_size];
-        if (blk < 0 || blk >= num_blocks) {
-          set_status(status, kStatusBadIndex);
-          blk = 0;
+    // ------------------------------------------------------------------ producer: one ring across all items
+    if (lane == 0) {
+      FlatCursor c = flat_locate(cum, B, items_per_seq, f0);
+      int it = 0;
+      for (int f = f0; f < f1;) {
+        const int seg = min(c.n_b - c.t, f1 - f);
+        const int kvh = c.h;
+        const int* table = block_tables + static_cast<size_t>(c.b) * table_width;
+        for (int i = 0; i < seg; ++i, ++it) {
+          const int s = it % kTcStages;
+          const uint32_t ph = (it / kTcStages) & 1;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1, status)) { f = f1; break; }
+          const int tok0 = (c.t + i) * kTcTile;
+          int blk = table[tok0 / block_size];
+          if (blk < 0 || blk >= num_blocks) {
+            set_status(status, kStatusBadIndex);
+            blk = 0;
+          }
+          const size_t off = ((static_cast<size_t>(blk) * nkv + kvh) * block_size + (tok0 % block_size)) * kD;
+          uint8_t* stg = smem + s * 2 * kTcTileBytes;
+          mbar_expect_tx(&full_bar[s], 2 * kTcTileBytes);
+          bulk_load(stg, k_cache + off, kTcTileBytes, &full_bar[s]);
+          bulk_load(stg + kTcTileBytes, v_cache + off, kTcTileBytes, &full_bar[s]);
         }
-        const size_t off = ((static_cast<size_t>(blk) * nkv + kvh) * block_size + (tok0 % block_size)) * kD;
-        uint8_t* stg = smem + s * 2 * kTcTileBytes;
-        if (lane == 0) mbar_expect_tx(&full_bar[s], 2 * kTcTile * kD * 2);
-        __syncwarp();                                   // the expectation is registered before any copy can complete
-#pragma unroll
-        for (int h = 0; h < kTcTile / 32; ++h) {
-          const int row = lane + 32 * h;
-          bulk_load(stg + row * kTcPitch, k_cache + off + static_cast<size_t>(row) * kD, kD * 2, &full_bar[s]);
-          bulk_load(stg + kTcTileBytes + row * kTcPitch, v_cache + off + static_cast<size_t>(row) * kD, kD * 2, &full_bar[s]);
-        }
+        f += seg;
+        flat_next_item(c, cum, B, items_per_seq);
       }
-      f += seg;
-      flat_next_item(c, cum, B, items_per_seq);
     }
     return;
   }
@@ -796,21 +794,30 @@ __global__ void __launch_bounds__(kDecThreads, 1) decode_attn_flat_tc_kernel(
 }
 
 // Group sizes the tensor-core variant takes (all heads of the group in one item); cache blocks of at least 64 tokens.
+// Measured on B200 (us per launch, CUDA cores / tensor cores): group 4, 256 sequences x 800 tokens: 186 / 237; group 8,
+// 64 x 2304: 235 / 179.  With the shared-memory bank conflicts of the unpadded rows the tensor-core variant pays from
+// groups of 6; the smallest group it is used for can be changed (tests run it for 4 and 5 as well).
+static int g_tc_min_group = 6;
+extern "C" void forge_decode_attention_set_tc_min_group(int g) { g_tc_min_group = g; }
 static bool decode_flat_tc_ok(int group, int block_size) {
-  static const bool enabled = !(std::getenv("FORGE_DECODE_TC") != nullptr && std::getenv("FORGE_DECODE_TC")[0] == '0');
-  return enabled && block_size >= kTcTile && (group == 4 || group == 5 || group == 8);
+  return block_size >= kTcTile && group >= g_tc_min_group && (group == 4 || group == 5 || group == 8);
 }
 
-extern "C" int forge_decode_attention_flat_uses_tensor_cores(int nq, int nkv, int block_size) {
-  return nkv > 0 && nq % nkv == 0 && decode_flat_tc_ok(nq / nkv, block_size) ? 1 : 0;
+// CTAs per SM the flat decode kernel for this head grouping runs with (the grid to use is this times the SM count).
+extern "C" int forge_decode_attention_flat_ctas_per_sm(int nq, int nkv, int block_size, int from_raw_qkv) {
+  if (nkv <= 0 || nq % nkv != 0) return 2;
+  const int group = nq / nkv;
+  if (!from_raw_qkv && decode_flat_tc_ok(group, block_size)) return tc_ctas_per_sm(group);
+  return decode_ctas_per_sm(decode_group_slice(group));
 }
 
 template <int G>
 static int launch_decode_flat_tc(const void* q, const void* kc, const void* vc, const int* bt, const int* lens, void* out,
                                  float* scratch, int num_ctas, int B, int nq, int nkv, int block_size, int table_width, int num_blocks,
                                  float scale_log2, unsigned* status, cudaStream_t stream) {
+  constexpr int kTcStages = tc_stages(G);
   constexpr int smem = kTcStages * 2 * kTcTileBytes + decode_merge_floats(G) * 4 + (kFlatMaxSeqs + 1 + 16) * 4 + 16 + 2 * kTcStages * 8 + 128;
-  static_assert(smem <= 227 * 1024, "one CTA per SM");
+  static_assert(smem <= (tc_ctas_per_sm(G) == 2 ? 113 : 227) * 1024, "two CTAs per SM up to five heads, one for eight");
   auto kern = decode_attn_flat_tc_kernel<G>;
   FORGE_ENSURE_DYN_SMEM(kern, smem);
   float* part_o = scratch;

@@ -67,7 +67,8 @@ int forge_decode_attention(const void* q, const void* kc, const void* vc, const 
                            float* part_o, float* part_ml, int B, int nq, int nkv, int head_dim, int block_size, int table_width,
                            int num_blocks, int chunk, int max_chunks, float scale, unsigned* status, cudaStream_t stream);
 size_t forge_decode_attention_flat_scratch_floats(int num_ctas, int B, int nq, int nkv);
-int forge_decode_attention_flat_uses_tensor_cores(int nq, int nkv, int block_size);
+int forge_decode_attention_flat_ctas_per_sm(int nq, int nkv, int block_size, int from_raw_qkv);
+void forge_decode_attention_set_tc_min_group(int g);
 int forge_decode_attention_flat(const void* q, const void* kc, const void* vc, const int* bt, const int* lens, void* out,
                                 float* scratch, int num_ctas, int B, int nq, int nkv, int head_dim, int block_size, int table_width,
                                 int num_blocks, float scale, unsigned* status, cudaStream_t stream);
@@ -342,9 +343,9 @@ int64_t decode_attention_flat_scratch_floats(int64_t num_ctas, int64_t B, int64_
                                                                          static_cast<int>(nq), static_cast<int>(nkv)));
 }
 
-// True when the flat decode kernel for this head grouping runs on the tensor cores (one CTA per SM is then the grid to use).
-bool decode_attention_flat_uses_tensor_cores(int64_t nq, int64_t nkv, int64_t block_size) {
-  return forge_decode_attention_flat_uses_tensor_cores(static_cast<int>(nq), static_cast<int>(nkv), static_cast<int>(block_size)) != 0;
+// CTAs per SM the flat decode kernel runs with for this head grouping (grid = this x the SM count).
+int64_t decode_attention_flat_ctas_per_sm(int64_t nq, int64_t nkv, int64_t block_size, bool from_raw_qkv) {
+  return forge_decode_attention_flat_ctas_per_sm(static_cast<int>(nq), static_cast<int>(nkv), static_cast<int>(block_size), from_raw_qkv ? 1 : 0);
 }
 
 // Decode attention with the flat tile partition: num_ctas CTAs share all KV tiles equally.  scratch: fp32, at least
@@ -649,6 +650,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("decode_attention_flat", &decode_attention_flat);
   m.def("decode_attention_qkv", &decode_attention_qkv);
   m.def("decode_attention_flat_scratch_floats", &decode_attention_flat_scratch_floats);
-  m.def("decode_attention_flat_uses_tensor_cores", &decode_attention_flat_uses_tensor_cores);
+  m.def("decode_attention_flat_ctas_per_sm", &decode_attention_flat_ctas_per_sm);
+  m.def("decode_attention_set_tc_min_group", [](int64_t g) { forge_decode_attention_set_tc_min_group(static_cast<int>(g)); });
   m.def("prefill_attention", &prefill_attention);
 }

@@ -378,7 +378,25 @@ def test_decode_attention_from_raw_qkv(ops, k_lens, nq, nkv, bs, mode, monkeypat
     ops.check_status()
 
 
-@pytest.mark.parametrize("batch,lo,hi,nq,nkv", [(64, 100, 1500, 16, 8), (200, 1, 700, 16, 8), (300, 3000, 3100, 8, 2), (7, 1, 4000, 32, 8)])
+@pytest.mark.parametrize("k_lens,nq,nkv", [([300, 1000, 70, 2], 32, 8), ([129, 640, 33, 2011], 40, 8), ([50, 400, 900], 8, 2)])
+def test_decode_attention_tensor_core_variant_for_small_groups(ops, k_lens, nq, nkv, monkeypatch):
+    """The tensor-core flat kernel is used from groups of 6 q heads per KV head by default; here it also runs groups of 4 and 5."""
+    monkeypatch.setattr(ops, "decode_attention_mode", "flat")
+    q, kc, vc, b = _paged_case([1] * len(k_lens), k_lens, nq, nkv, 256)
+    b.is_prefill = False
+    want = ref.attention(q, kc, vc, b.cu_seqlens_q, b.context_lens, b.block_tables, 128 ** -0.5, b.num_seqs)
+    ops.C.decode_attention_set_tc_min_group(4)
+    try:
+        got = ops.attention(q, kc, vc, b, 128 ** -0.5)
+        torch.cuda.synchronize()
+    finally:
+        ops.C.decode_attention_set_tc_min_group(6)
+    _close(got, want, 2e-2, 2e-2)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("batch,lo,hi,nq,nkv", [(64, 100, 1500, 16, 8), (200, 1, 700, 16, 8), (300, 3000, 3100, 8, 2), (7, 1, 4000, 32, 8),
+                                                (70, 100, 2500, 64, 8)])
 def test_decode_attention_flat_partition_many_sequences(ops, batch, lo, hi, nq, nkv, monkeypatch):
     """Enough tiles that every CTA's range spans several (sequence, head) items and most items are cut at most once;
     lengths from 1 token to several thousand, zero-length rows in between; both kernels against the fp32 statement,

@@ -212,13 +212,8 @@ class CudaOps:
             return out
         B = batch.padded_seqs
         if self.decode_attention_mode == "flat" or (self.decode_attention_mode == "auto" and 48 <= B <= 512):
-            # all KV tiles of the step dealt out equally to two CTAs per SM (one for wide head groups and for the tensor-core
-            # variant that takes groups of 4..8 q heads per KV head); lengths are read on the device
-            one = decode_group_slice(H // k_cache.shape[1]) > 4 or self.C.decode_attention_flat_uses_tensor_cores(H, k_cache.shape[1], k_cache.shape[2])
-            ctas = (1 if one else 2) * self.num_sms
-            need = self.C.decode_attention_flat_scratch_floats(ctas, B, H, k_cache.shape[1])
-            if self._flat_scratch is None or self._flat_scratch.numel() < need:
-                self._flat_scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+            # all KV tiles of the step dealt out equally to two CTAs per SM (one for wide head groups); lengths are read on the device
+            ctas = self._flat_ctas(H, k_cache, False)
             self.C.decode_attention_flat(q, k_cache, v_cache, batch.block_tables, batch.context_lens, out, self._flat_scratch,
                                          ctas, scale, self.status)
             self.launches += 2
@@ -235,6 +230,15 @@ class CudaOps:
         self.launches += 2 if max_chunks > 1 else 1
         return out
 
+    def _flat_ctas(self, num_heads, k_cache, from_raw_qkv: bool) -> int:
+        """Grid of the flat decode kernel for this head grouping; also makes sure the scratch is large enough."""
+        nkv, bs = k_cache.shape[1], k_cache.shape[2]
+        ctas = self.C.decode_attention_flat_ctas_per_sm(num_heads, nkv, bs, from_raw_qkv) * self.num_sms
+        need = self.C.decode_attention_flat_scratch_floats(ctas, 512, num_heads, nkv)
+        if self._flat_scratch is None or self._flat_scratch.numel() < need:
+            self._flat_scratch = torch.empty(need, dtype=torch.float32, device=k_cache.device)
+        return ctas
+
     def decode_attention_qkv(self, qkv, q_weight, k_weight, eps, table, k_cache, v_cache, batch, num_heads, scale, do_rope=True):
         """Decode step: attention straight from the raw qkv projection.  q/k-norm, rotation at position len - 1 and the
         KV-cache store of the step's token happen inside the attention kernel (one launch less per layer than
@@ -243,9 +247,9 @@ class CudaOps:
         out = torch.empty(B, num_heads * D, dtype=qkv.dtype, device=qkv.device)
         rope = table if do_rope else None
         if self.decode_attention_mode == "flat" or (self.decode_attention_mode == "auto" and 48 <= B <= 512):
+            ctas = self._flat_ctas(num_heads, k_cache, True)          # may grow the scratch: before it is passed on
             self.C.decode_attention_qkv(qkv, q_weight, k_weight, eps, rope, k_cache, v_cache, batch.block_tables, batch.context_lens,
-                                        out, self._flat_scratch, (1 if decode_group_slice(num_heads // k_cache.shape[1]) > 4 else 2) * self.num_sms,
-                                        None, None, 0, 0, num_heads, scale, self.status)
+                                        out, self._flat_scratch, ctas, None, None, 0, 0, num_heads, scale, self.status)
             self.launches += 2
             return out
         max_len = batch.table_width * k_cache.shape[2]
