@@ -4,7 +4,7 @@
 
 Cases: decode_attention (64 sequences x 2048 tokens, 16 / 8 heads), decode_attention_g4 (256 x 800, 32 / 8 heads: Qwen3-8B),
 decode_attention_g8 (64 x 2304, 64 / 8 heads: Qwen3-32B), prefill_attention, gemm_decode, gemm_decode_split, gemm_prefill,
-gemm_prefill_8b (8192 x 6144 x 4096), gemm_silu, gemm_residual (o_proj-like GEMM with the residual add + sums of squares
+gemm_prefill_8b (8192 x 6144 x 4096), gemm_silu, gemm_fp8 (256 x 6144 x 4096, block-scaled e4m3 weights), gemm_residual (o_proj-like GEMM with the residual add + sums of squares
 epilogue), gemm_scaled (qkv-like GEMM with the folded-norm row scale), lm_head_sample (LM head + sampling in one kernel),
 rms_norm, qk_norm_rope_store, sampler.
 ``--lib`` runs the library kernel the reference would use on the same case instead (cuBLAS through torch.matmul for the
@@ -113,6 +113,19 @@ def build(case: str, ops, lib: bool = False):
                 return ops.linear_residual(x, w, res, ssq_out)
             return ops.linear_scaled(x, w, ssq_in, 1e-6)
         return run, (N * K + M * K + 2 * M * N) * 2, 2 * M * N * K
+    if case == "gemm_fp8":
+        from ..ops.quant import Fp8BlockWeight
+        M, N, K = 256, 6144, 4096                          # Qwen3-8B qkv projection at a decode batch of 256
+        ws = [Fp8BlockWeight.quantize(torch.randn(N, K, device="cuda", dtype=BF) * 0.02) for _ in range(8)]
+        wb = [torch.randn(N, K, device="cuda", dtype=BF) * 0.02 for _ in range(8)]
+        x = torch.randn(M, K, device="cuda", dtype=BF)
+        state = {"i": 0}
+
+        def run():
+            i = state["i"] % 8
+            state["i"] += 1
+            return torch.matmul(x, wb[i].t()) if lib else ops.linear_fp8(x, ws[i])
+        return run, (N * K * (2 if lib else 1) + M * K * 2 + M * N * 2), 2 * M * N * K
     if case == "lm_head_sample":
         rows, V, K = 256, 151936, 1024
         w = torch.randn(V, K, device="cuda", dtype=BF) * 0.02
