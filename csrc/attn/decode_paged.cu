@@ -542,16 +542,23 @@ static int launch_decode_flat(const void* q, const void* kc, const void* vc, con
 // run on the tensor cores exactly as in a prefill kernel, and the kernel is a pure stream of the cache again.
 // (tcgen05 has no use for 4..8 rows: its smallest tile is 64 rows, and the operand is streamed once, not reused.)
 //
-// Same partition, partial slots, merge kernel and bulk-copy ring as decode_attention_flat_kernel (a tile = 64 tokens =
-// one contiguous 16 KB run per operand); one item = (sequence, KV head) with all G heads.  The token rows sit 256 bytes
-// apart in shared memory, so the eight rows an ldmatrix touches share their banks (8 wavefronts instead of 1): at one
-// tile per ~0.7 us and SM that costs about a third of the shared-memory cycles and is cheaper than any layout that
-// needs one copy per row (measured: 256-byte row copies with a padded pitch ran at 0.17 of copy bandwidth).
+// Same partition, partial slots and merge kernel as decode_attention_flat_kernel; one item = (sequence, KV head) with
+// all G heads.  A tile = 64 tokens of K and of V, each loaded as two TMA boxes of 64 rows x 64 dims (128 bytes) with the
+// 128-byte swizzle from a 2-D view [all token rows of the cache, 128] of the paged cache: inside a box the 16-byte chunk c
+// of row r sits at chunk c ^ (r % 8), so the eight rows an ldmatrix touches fall into different banks.  (Contiguous 16 KB
+// bulk copies leave the rows 256 bytes apart: every ldmatrix then takes eight shared-memory wavefronts, which bounded the
+// kernel at 0.55 of copy bandwidth; one 256-byte bulk copy per row with a padded pitch ran at 0.17.)
 // Groups of up to 5 heads leave room for two CTAs per SM (three stages each); 8 heads take one CTA with six stages.
 // =========================================================================================================
 constexpr int kTcTile = 64;
-constexpr int kTcPitch = kD * 2;                      // bytes between token rows in shared memory
-constexpr int kTcTileBytes = kTcTile * kTcPitch;
+constexpr int kTcBoxBytes = kTcTile * 128;            // one TMA box: 64 token rows x 64 dims
+constexpr int kTcTileBytes = 2 * kTcBoxBytes;         // K (or V) of a tile: dims 0..63, then dims 64..127
+extern "C" int forge_make_tmap_2d(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows,
+                                  int elem_bytes);
+// Shared-memory address of the 16-byte chunk `chunk` (0..15: eight dims each) of token row `r` of a swizzled tile.
+__device__ __forceinline__ uint32_t tc_chunk_addr(uint32_t tile, int r, int chunk) {
+  return tile + (chunk >> 3) * kTcBoxBytes + r * 128 + (((chunk & 7) ^ (r & 7)) << 4);
+}
 __host__ __device__ constexpr int tc_ctas_per_sm(int G) { return G > 5 ? 1 : 2; }
 __host__ __device__ constexpr int tc_stages(int G) { return G > 5 ? 6 : 3; }
 
@@ -569,7 +576,7 @@ __device__ __forceinline__ void mma_rows8(float (&c)[4], uint32_t a0, uint32_t a
 
 template <int G>
 __global__ void __launch_bounds__(kDecThreads, tc_ctas_per_sm(G)) decode_attn_flat_tc_kernel(
-    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache, const __nv_bfloat16* __restrict__ v_cache,
+    const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const __nv_bfloat16* __restrict__ q,
     const int* __restrict__ block_tables, const int* __restrict__ context_lens, __nv_bfloat16* __restrict__ out,
     float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ cta_meta, int B, int nq, int nkv, int block_size,
     int table_width, int num_blocks, int min_tiles, float scale_log2, unsigned* status) {
@@ -577,7 +584,7 @@ __global__ void __launch_bounds__(kDecThreads, tc_ctas_per_sm(G)) decode_attn_fl
   constexpr int kTcStages = tc_stages(G);
   constexpr int kRing = kTcStages * 2 * kTcTileBytes;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));   // swizzled boxes
   float* s_acc = reinterpret_cast<float*>(smem + kRing);                      // merge area, separate from the ring
   int* cum = reinterpret_cast<int*>(s_acc + decode_merge_floats(G));          // [B + 1]
   int* chunk_tot = cum + kFlatMaxSeqs + 1;                                    // [16]
@@ -587,6 +594,8 @@ __global__ void __launch_bounds__(kDecThreads, tc_ctas_per_sm(G)) decode_attn_fl
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
+    prefetch_tensormap(&tm_k);
+    prefetch_tensormap(&tm_v);
     for (int s = 0; s < kTcStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 4);
@@ -657,11 +666,13 @@ __global__ void __launch_bounds__(kDecThreads, tc_ctas_per_sm(G)) decode_attn_fl
             set_status(status, kStatusBadIndex);
             blk = 0;
           }
-          const size_t off = ((static_cast<size_t>(blk) * nkv + kvh) * block_size + (tok0 % block_size)) * kD;
+          const int row0 = (blk * nkv + kvh) * block_size + (tok0 % block_size);     // token row in the 2-D view of the cache
           uint8_t* stg = smem + s * 2 * kTcTileBytes;
           mbar_expect_tx(&full_bar[s], 2 * kTcTileBytes);
-          bulk_load(stg, k_cache + off, kTcTileBytes, &full_bar[s]);
-          bulk_load(stg + kTcTileBytes, v_cache + off, kTcTileBytes, &full_bar[s]);
+          tma_load_2d(stg, &tm_k, &full_bar[s], 0, row0);
+          tma_load_2d(stg + kTcBoxBytes, &tm_k, &full_bar[s], 64, row0);
+          tma_load_2d(stg + kTcTileBytes, &tm_v, &full_bar[s], 0, row0);
+          tma_load_2d(stg + kTcTileBytes + kTcBoxBytes, &tm_v, &full_bar[s], 64, row0);
         }
         f += seg;
         flat_next_item(c, cum, B, items_per_seq);
@@ -700,14 +711,15 @@ __global__ void __launch_bounds__(kDecThreads, tc_ctas_per_sm(G)) decode_attn_fl
       const uint32_t ph = (it / kTcStages) & 1;
       ok = mbar_wait(&full_bar[s], ph, status);
       if (!ok) break;
-      const uint32_t Ks = smem_u32(smem + s * 2 * kTcTileBytes) + warp * 16 * kTcPitch;   // this warp's 16 tokens
+      const uint32_t Ks = smem_u32(smem + s * 2 * kTcTileBytes);
       const uint32_t Vs = Ks + kTcTileBytes;
+      const int r0 = warp * 16;                                                           // this warp's 16 tokens of the tile
       // S = Q K^T: two blocks of 8 tokens
       float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
       for (int kk = 0; kk < 8; ++kk) {
         uint32_t kb[4];
-        ldmatrix_x4(kb, Ks + ((mat >> 1) * 8 + mrow) * kTcPitch + (kk * 16 + (mat & 1) * 8) * 2);
+        ldmatrix_x4(kb, tc_chunk_addr(Ks, r0 + (mat >> 1) * 8 + mrow, 2 * kk + (mat & 1)));
         mma_rows8(sc[0], qa[kk][0], qa[kk][1], kb[0], kb[1]);
         mma_rows8(sc[1], qa[kk][0], qa[kk][1], kb[2], kb[3]);
       }
@@ -744,7 +756,7 @@ __global__ void __launch_bounds__(kDecThreads, tc_ctas_per_sm(G)) decode_attn_fl
 #pragma unroll
       for (int dd = 0; dd < 8; ++dd) {
         uint32_t vb[4];
-        ldmatrix_x4_trans(vb, Vs + ((mat & 1) * 8 + mrow) * kTcPitch + (dd * 16 + (mat >> 1) * 8) * 2);
+        ldmatrix_x4_trans(vb, tc_chunk_addr(Vs, r0 + (mat & 1) * 8 + mrow, 2 * dd + (mat >> 1)));
         mma_rows8(o[2 * dd], pa0, pa2, vb[0], vb[1]);
         mma_rows8(o[2 * dd + 1], pa0, pa2, vb[2], vb[3]);
       }
@@ -816,16 +828,20 @@ static int launch_decode_flat_tc(const void* q, const void* kc, const void* vc, 
                                  float* scratch, int num_ctas, int B, int nq, int nkv, int block_size, int table_width, int num_blocks,
                                  float scale_log2, unsigned* status, cudaStream_t stream) {
   constexpr int kTcStages = tc_stages(G);
-  constexpr int smem = kTcStages * 2 * kTcTileBytes + decode_merge_floats(G) * 4 + (kFlatMaxSeqs + 1 + 16) * 4 + 16 + 2 * kTcStages * 8 + 128;
+  constexpr int smem = kTcStages * 2 * kTcTileBytes + decode_merge_floats(G) * 4 + (kFlatMaxSeqs + 1 + 16) * 4 + 16 + 2 * kTcStages * 8 + 1024;
   static_assert(smem <= (tc_ctas_per_sm(G) == 2 ? 113 : 227) * 1024, "two CTAs per SM up to five heads, one for eight");
   auto kern = decode_attn_flat_tc_kernel<G>;
   FORGE_ENSURE_DYN_SMEM(kern, smem);
+  // the paged cache as a 2-D tensor [every token row of every block and KV head, 128]; box = 64 rows x 64 dims, 128-byte swizzle
+  CUtensorMap tm_k, tm_v;
+  const uint64_t rows = static_cast<uint64_t>(num_blocks) * nkv * block_size;
+  if ((reinterpret_cast<uintptr_t>(kc) & 15) || (reinterpret_cast<uintptr_t>(vc) & 15)) return -1;
+  if (forge_make_tmap_2d(&tm_k, kc, rows, kD, kD, kTcTile, 2) != 0 || forge_make_tmap_2d(&tm_v, vc, rows, kD, kD, kTcTile, 2) != 0) return -2;
   float* part_o = scratch;
   float* part_ml = part_o + static_cast<size_t>(num_ctas) * 2 * G * kD;
   int* cta_meta = reinterpret_cast<int*>(part_ml + static_cast<size_t>(num_ctas) * 2 * G * 2);
   const int min_tiles = 256 / kTcTile;
-  if (launch_kernel(kern, dim3(num_ctas), dim3(kDecThreads), smem, stream, 0, static_cast<const __nv_bfloat16*>(q),
-                    static_cast<const __nv_bfloat16*>(kc), static_cast<const __nv_bfloat16*>(vc), bt, lens,
+  if (launch_kernel(kern, dim3(num_ctas), dim3(kDecThreads), smem, stream, 0, tm_k, tm_v, static_cast<const __nv_bfloat16*>(q), bt, lens,
                     static_cast<__nv_bfloat16*>(out), part_o, part_ml, cta_meta, B, nq, nkv, block_size, table_width, num_blocks,
                     min_tiles, scale_log2, status) != cudaSuccess)
     return -5;
