@@ -537,7 +537,7 @@ static int launch_decode_flat(const void* q, const void* kc, const void* vc, con
 // Flat tile partition on the tensor cores, for q-head groups of 4..8 per KV head (Qwen3-4B/8B: 4, 14B: 5, 32B: 8).
 //
 // With G q heads per KV head every cached K and V element takes part in G multiply-adds.  On the CUDA cores that is
-// the bound from G = 4 on (Qwen3-8B: 0.72 of copy bandwidth; a group of 8 had to stream the cache twice); as a matrix
+// the bound from G = 4 on (Qwen3-8B: 0.69 of copy bandwidth; a group of 8 had to stream the cache twice); as a matrix
 // product it is nothing: the G query rows are padded to the 16-row side of mma.sync m16n8k16, S = Q K^T and O += P V
 // run on the tensor cores exactly as in a prefill kernel, and the kernel is a pure stream of the cache again.
 // (tcgen05 has no use for 4..8 rows: its smallest tile is 64 rows, and the operand is streamed once, not reused.)
@@ -806,10 +806,10 @@ __global__ void __launch_bounds__(kDecThreads, tc_ctas_per_sm(G)) decode_attn_fl
 }
 
 // Group sizes the tensor-core variant takes (all heads of the group in one item); cache blocks of at least 64 tokens.
-// Measured on B200 (us per launch, CUDA cores / tensor cores): group 4, 256 sequences x 800 tokens: 186 / 237; group 8,
-// 64 x 2304: 235 / 179.  With the shared-memory bank conflicts of the unpadded rows the tensor-core variant pays from
-// groups of 6; the smallest group it is used for can be changed (tests run it for 4 and 5 as well).
-static int g_tc_min_group = 6;
+// Measured on B200 (us per launch incl. the merge kernel; CUDA cores / tensor cores / flash-attn 2 on the same case):
+// group 4, 256 sequences x 800 tokens: 188 / 151 / 189; group 8, 64 x 2304: 235 / 111 / 139.  The smallest group the
+// tensor-core variant is used for can be changed (tests also run groups 4 and 5 on the CUDA cores).
+static int g_tc_min_group = 4;
 extern "C" void forge_decode_attention_set_tc_min_group(int g) { g_tc_min_group = g; }
 static bool decode_flat_tc_ok(int group, int block_size) {
   return block_size >= kTcTile && group >= g_tc_min_group && (group == 4 || group == 5 || group == 8);
