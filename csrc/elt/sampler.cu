@@ -115,7 +115,7 @@ extern "C" int forge_sample_nsplit(int rows, int vocab) {
   // Five CTAs of 256 threads fit an SM (registers).  A grid of about ONE wave is the worst case (256 rows x 3 slices = 768
   // CTAs for 740 places: the last 28 ran alone and the kernel took twice as long): aim for ~8 waves of equal CTAs, so the
   // ragged last wave costs < 10 %; never fewer than ~2K ids per CTA.
-  int want = (148 * 5 * 8 + rows - 1) / rows;
+  int want = (device_sm_count() * 5 * 8 + rows - 1) / rows;
   int cap = (vocab + 2047) / 2048;
   int n = want < cap ? want : cap;
   return n < 1 ? 1 : (n > 64 ? 64 : n);

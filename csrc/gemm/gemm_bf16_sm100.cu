@@ -739,12 +739,7 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
   auto kern = gemm_tokens_kernel<BLOCK_C, kEpi>;
   FORGE_ENSURE_DYN_SMEM(kern, Cfg::kSmemBytes);
   const int tiles = ((M + kBlockR - 1) / kBlockR) * ((n_out + BLOCK_C - 1) / BLOCK_C);
-  static int num_sms = 0;
-  if (num_sms == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || num_sms <= 0) num_sms = 148;
-  }
+  const int num_sms = device_sm_count();
   dim3 grid(tiles < num_sms ? tiles : num_sms);
   return launch_kernel(kern, grid, dim3(kGemmThreads), Cfg::kSmemBytes, stream, 0, tm_x, tm_w, out, ldo, M, n_out, K, n_out,
                        status, push, fuse, samp) == cudaSuccess ? 0 : -5;
@@ -756,9 +751,11 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
 // that keeps the grid within two CTAs per SM, leaves each split >= 2 K blocks and each CTA >= 4 columns to reduce.
 static int choose_splits(int ctas_unsplit, int num_kb, int block_c, bool silu) {
   // fewer K blocks per CTA also means the whole K slice is prefetched into the ring before the predecessor kernel ends
-  static const int small_limit = std::getenv("FORGE_SPLIT_LIMIT") ? std::atoi(std::getenv("FORGE_SPLIT_LIMIT")) : 296;
-  // SiLU needs the complete gate sum before the nonlinearity, i.e. two exchange rounds: split less eagerly
-  const int limit = silu ? 200 : small_limit;
+  static const int split_limit_env = std::getenv("FORGE_SPLIT_LIMIT") ? std::atoi(std::getenv("FORGE_SPLIT_LIMIT")) : 0;
+  const int sms = device_sm_count();
+  const int small_limit = split_limit_env > 0 ? split_limit_env : 2 * sms;      // two CTAs per SM
+  // SiLU needs the complete gate sum before the nonlinearity, i.e. two exchange rounds: split less eagerly (~1.35 CTAs per SM)
+  const int limit = silu ? (sms * 200) / 148 : small_limit;
   int s = 1;
   while (s < 8 && ctas_unsplit * s * 2 <= limit && num_kb / (s * 2) >= 2 && s * 2 <= block_c / 4) s *= 2;
   return s;
@@ -808,7 +805,8 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
   // Few tokens -> the weight-tile (decode) kernel, except for very wide layers (the LM head: ~1200 feature tiles), where the
   // persistent token-tile kernel streams weights best: its ring never drains between tiles and its epilogue overlaps
   // the next tile (measured 58-91 us vs 60-182 us for 8..256 tokens x 151936 x 1024; cuBLAS 55-83 us).
-  const bool wide = (n_out + kBlockR - 1) / kBlockR >= 296 && epi == kEpiStore && push.size <= 1 && M >= 8;
+  const int sms = device_sm_count();
+  const bool wide = (n_out + kBlockR - 1) / kBlockR >= 2 * sms && epi == kEpiStore && push.size <= 1 && M >= 8;
   // Many tokens of a decode step (64..256) on a layer with enough output features and a short K: the token-tile
   // kernel with narrow feature tiles (32 or 64) gives ~100-128 CTAs without splitting K, and its epilogue goes
   // straight from tensor memory to global rows (no exchange through shared memory).  Measured on the Qwen3-0.6B
@@ -818,8 +816,8 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
     const int m_tiles = (M + kBlockR - 1) / kBlockR;
     const int t32 = ((n_out + 31) / 32) * m_tiles, t64 = ((n_out + 63) / 64) * m_tiles;
     if (n_out < 2048) {}                           // few features (o, down): K must be split, the weight-tile kernel does it
-    else if (t32 <= 148) narrow = 32;
-    else if (t64 <= 148) narrow = 64;
+    else if (t32 <= sms) narrow = 32;
+    else if (t64 <= sms) narrow = 64;
   }
   if (fuse.add_residual) narrow = 0;              // the sums of squares are kept per 128 features: tiles of 128 or 256
   if (narrow) {
@@ -838,7 +836,7 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
     if (M > 16) {
       const int cap = M <= 32 ? 32 : M <= 64 ? 64 : 128;
       bc = (K >= 4096 && M > 64) ? 64 : 32;
-      while (bc < cap && feature_tiles * ((M + bc - 1) / bc) > 148) bc *= 2;
+      while (bc < cap && feature_tiles * ((M + bc - 1) / bc) > sms) bc *= 2;
     }
     if (force_bc == 16 || force_bc == 32 || force_bc == 64 || force_bc == 128) bc = force_bc;
     const int num_kb = (K + kBlockK - 1) / kBlockK;
@@ -849,7 +847,7 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
     if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return -6;
     // ring depth: the deep ring when the grid is at most one CTA per SM and every CTA has many K blocks to stream
     const int kb_per_cta = (num_kb + splits - 1) / splits;
-    bool deep = ctas_unsplit * splits <= 148 && kb_per_cta * (bc + (epi == kEpiSiluMul ? 256 : 128)) >= deep_threshold();
+    bool deep = ctas_unsplit * splits <= sms && kb_per_cta * (bc + (epi == kEpiSiluMul ? 256 : 128)) >= deep_threshold();
     if (force_deep == 1) deep = false;
     if (force_deep == 2) deep = true;
 #define FORGE_W2(BC, EPI)                                                                                                   \

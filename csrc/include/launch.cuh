@@ -40,6 +40,20 @@ inline bool pdl_enabled() {
     }                                                                                                                   \
   } while (0)
 
+// Streaming multiprocessors of the current device (queried once per device; grid and tile heuristics are stated in
+// multiples of it instead of a fixed 148).
+inline int device_sm_count() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                  int cluster_y, Args... args) {

@@ -113,6 +113,34 @@ def test_a_length_beyond_the_slices_is_clamped_and_reported():
     assert torch.equal(out[[0, 2]], want[[0, 2]])
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs a second GPU")
+def test_second_device_in_the_same_process():
+    """The scratch address and the kernels' shared-memory limit are per device: a process that drives two GPUs gets the
+    right ones on each (plain kernels only, no peer memory)."""
+    lib = _lib()
+    prev = torch.cuda.current_device()
+    try:
+        torch.cuda.set_device(1)
+        with torch.cuda.device(1):
+            lens, nq, nkv, bs, chunk = [700, 300, 1200], 16, 8, 256, 256
+            q, kc, vc, bt, cl = [t.to("cuda:1") for t in _case(lens, nq, nkv, bs, 5)]
+            max_chunks = -(-max(lens) // chunk)
+            B, _, D = q.shape
+            out = torch.empty(B, nq * D, dtype=BF, device="cuda:1")
+            status = torch.zeros(4, dtype=torch.int32, device="cuda:1")
+            rc = lib.forge_decode_attention_noalloc(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), cl.data_ptr(), out.data_ptr(),
+                                                    B, nq, nkv, D, bs, bt.shape[1], kc.shape[0], chunk, max_chunks, D ** -0.5,
+                                                    status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+            assert rc == 0, lib.forge_decode_attention_noalloc_strerror(rc).decode()
+            torch.cuda.synchronize()
+            assert int(status[0]) == 0
+    finally:
+        torch.cuda.set_device(prev)
+    q0, kc0, vc0, bt0, cl0 = _case(lens, nq, nkv, bs, 5)
+    want = _regular(q0, kc0, vc0, bt0, cl0, chunk, max_chunks)
+    assert torch.equal(out.cpu(), want.cpu())
+
+
 def test_oversized_request_is_refused():
     lib = _lib()
     cap = lib.forge_decode_attention_noalloc_capacity_floats()

@@ -39,7 +39,7 @@ def require_ext():
 def decode_chunking(batch: int, num_kv_heads: int, block_size: int, max_len: int) -> tuple[int, int]:
     """(tokens per context chunk, number of chunks) for the split-KV decode kernel.
 
-    Small batches split the context finely so that all 148 SMs get work; large batches keep chunks long so
+    Small batches split the context finely so that every SM gets work; large batches keep chunks long so
     that the partial-merge traffic stays negligible.  Depends only on shapes known at graph-capture time."""
     tile = min(block_size, 64)
     ctas = batch * num_kv_heads
@@ -391,7 +391,7 @@ class CudaOps:
         tiles, at least 8 rows) over a bf16 shard; the shard must start on a multiple of 32 token ids (checked by the
         caller that knows the start)."""
         return (self.sample_in_lm_head and not isinstance(weight, Fp8BlockWeight) and rows >= 8
-                and (weight.shape[0] + 127) // 128 >= 296)
+                and (weight.shape[0] + 127) // 128 >= 2 * self.num_sms)
 
     def lm_head_sample_shard(self, hidden, weight, temperatures, header, vocab_start):
         """(ids int32 [rows], scores fp32 [rows]) of this vocab shard, sampled in the epilogue of the LM-head GEMM: the
