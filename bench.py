@@ -26,6 +26,7 @@ import argparse
 import json
 import os
 import shutil
+import signal
 import statistics
 import subprocess
 import sys
@@ -38,6 +39,8 @@ sys.path.insert(0, ROOT)
 
 NUM_SEQS, MAX_IN, MAX_OUT = 256, 1024, 1024
 HEADLINE_MODEL = "qwen3-0.6b"
+T_START = time.monotonic()          # the run's time budget counts from here
+MIN_CHILD_S = 45.0                   # an extra workload with less time left than this is skipped
 
 
 def make_workload():
@@ -417,47 +420,64 @@ def child_env(n: int, port_offset: int, for_reference: bool) -> dict:
 
 
 def run_child(cmd: list[str], env: dict, timeout_s: float) -> dict | None:
-    """Runs a benchmark script, returns the last JSON line it printed (None if it printed none: a non-zero rank)."""
+    """Runs a benchmark script in a process group of its own, returns the last JSON line it printed (None if it printed
+    none: a non-zero rank).  At the time limit the whole group is ended (the reference starts worker processes)."""
+    if timeout_s < MIN_CHILD_S:
+        return {"unavailable": f"skipped: {timeout_s:.0f} s left of the run's time budget"}
+    p = subprocess.Popen([sys.executable] + cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, cwd=ROOT,
+                         start_new_session=True)
     try:
-        r = subprocess.run([sys.executable] + cmd, env=env, capture_output=True, text=True, timeout=timeout_s, cwd=ROOT,
-                           start_new_session=True)
+        stdout, stderr = p.communicate(timeout=timeout_s)
     except subprocess.TimeoutExpired:
+        try:
+            os.killpg(p.pid, signal.SIGKILL)          # the group this call created, nothing else
+        except ProcessLookupError:
+            pass
+        p.communicate()
         return {"unavailable": f"did not finish within {timeout_s:.0f} s"}
-    for line in reversed(r.stdout.strip().splitlines()):
+    for line in reversed(stdout.strip().splitlines()):
         if line.startswith("{"):
             try:
                 return json.loads(line)
             except ValueError:
                 continue
-    if r.returncode != 0:
-        return {"unavailable": f"exit code {r.returncode}: {r.stderr.strip()[-300:]}"}
+    if p.returncode != 0:
+        return {"unavailable": f"exit code {p.returncode}: {stderr.strip()[-300:]}"}
     return None
 
 
 def run_extras(args) -> dict:
     """BASELINE configs beyond the headline, measured with the same engine arm at the same N.  Each runs in a child
     process BEFORE the headline engine is built (a fresh process frees every byte and the fixed rendezvous port of the
-    reference); a failure or a timeout becomes an ``unavailable`` entry and never touches the headline number."""
+    reference); a failure or a timeout becomes an ``unavailable`` entry and never touches the headline number.
+    All of them together get what ``--time-budget`` leaves after the headline's own estimated time: a workload that
+    would not fit is skipped, not cut short in the middle of the headline."""
     n, ref = args.gpus, args.impl == "reference"
     rank = int(os.environ.get("RANK", "0")) if n > 1 else 0
     if ref and rank != 0:
         return {}
+    per_pass = (6.5 if ref else 4.5)                       # seconds, the slowest N measured (N=1)
+    headline_s = (150.0 if ref else 75.0) + (args.steps + args.warmup + 1) * per_pass * 1.15
+    deadline = T_START + args.time_budget - headline_s
+
+    def left() -> float:
+        return min(args.extras_timeout, deadline - time.monotonic())
     common = ["--gpus", str(n), "--impl", args.impl, "--comm", args.comm]
     keep = ("metric", "value", "unit", "ms_per_step", "steps", "warmup", "e2e", "decode_step_ms", "prefill_ms", "exposed_comm_pct",
             "gpu_launches", "unavailable", "shims")
     out = {}
     r = run_child(["bench.py", "--model", "qwen3-8b", "--steps", "2", "--warmup", "1", "--no-extras"] + common +
-                  ([] if ref else ["--load", "dummy"]), child_env(n, 101, ref), args.extras_timeout)
+                  ([] if ref else ["--load", "dummy"]), child_env(n, 101, ref), left())
     if r is not None:
         out[f"config3_qwen3_8b_tp{n}"] = {k: r[k] for k in keep if k in r}
     if n == 8:
-        r = run_child(["bench_prefix_cache.py"] + common, child_env(n, 102, ref), args.extras_timeout)
+        r = run_child(["bench_prefix_cache.py"] + common, child_env(n, 102, ref), left())
         if r is not None:
             out["config5_prefix_cache_qwen3_8b_tp8"] = r
         for q in ("none", "fp8_block"):
             if ref and q != "none":
                 continue                  # the reference has no fp8 path
-            r = run_child(["bench_decode.py", "--quantization", q] + common, child_env(n, 103 + (q != "none"), ref), args.extras_timeout)
+            r = run_child(["bench_decode.py", "--quantization", q] + common, child_env(n, 103 + (q != "none"), ref), left())
             if r is not None:
                 out["config4_qwen3_32b_tp8_" + ("bf16" if q == "none" else "fp8_block")] = r
     return out
@@ -479,7 +499,9 @@ def main():
     ap.add_argument("--load", default="auto", choices=["auto", "dummy"],
                     help="auto: write and load a safetensors checkpoint; dummy: random-init on the device (large models)")
     ap.add_argument("--no-extras", action="store_true", help="only the named model's workload (what the child runs use)")
-    ap.add_argument("--extras-timeout", type=float, default=900.0, help="seconds each extra workload's child process gets")
+    ap.add_argument("--extras-timeout", type=float, default=600.0, help="most seconds one extra workload's child process gets")
+    ap.add_argument("--time-budget", type=float, default=800.0,
+                    help="seconds the whole run should fit in: the extra workloads get what the headline's estimated time leaves")
     args = ap.parse_args()
     extras = None
     if not args.no_extras and args.model == HEADLINE_MODEL and args.quantization == "none" and os.environ.get("FORGE_BENCH_EXTRAS", "1") != "0":

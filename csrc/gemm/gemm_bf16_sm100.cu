@@ -94,6 +94,233 @@ struct GemmSample {
 
 constexpr int tmem_cols_for(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
 
+// Stream-K for the token-tile kernel (ws == nullptr: off, every CTA computes whole output tiles).
+//
+// A decode-sized GEMM on a large layer (few hundred tokens x 4096..12288 features x 4096..12288 K) has fewer output tiles
+// than the GPU has SMs, or a number of tiles that divides badly by it, while every tile streams megabytes of weights.  The
+// (tile, group of K blocks) units are therefore numbered tile-major and dealt out evenly: CTA c of G takes units
+// [U c / G, U (c + 1) / G).  Its range may begin in the middle of one tile and end in the middle of another; for such a
+// partial tile the CTA writes its fp32 partial sums into a slot of its own in `ws` and counts itself in counters[tile].
+// The CTA that arrives LAST adds up all the tile's partial sums, always in the order of the K ranges (the result does not
+// depend on which CTA that is), and runs the epilogue.  Nobody waits for anybody.  The last CTA puts the counter back to
+// zero, so the buffers serve the next launch on the same stream as they are.
+struct GemmStreamK {
+  float* ws;          // [gridDim.x][2][kSkSlotFloats]: slot 0 = the partial tile at the start of the CTA's range, 1 = at its end
+  int* counters;      // [tiles]
+  int kgroup;         // K blocks per unit
+};
+constexpr int kSkSlotFloats = 128 * 256;       // one accumulator set: 128 rows x up to 256 columns
+// Element (row, col) of a slot lives at (col / 4) * 512 + row * 4 + col % 4: the 32 rows x 4 columns of a warp's vector
+// access are 512 contiguous bytes.
+constexpr int kSkBatch = 4;                    // partial tiles whose loads are in flight together when summing
+
+struct TokSched {
+  int num_kb, kgroup, num_kg;
+  long long u, u_begin, u_end;     // stream-K: next unit, range of this CTA
+  int t_next, t_end, stride;       // whole tiles
+  bool stream;
+  // worker `w` of `workers` (a CTA of the grid, or a CTA pair)
+  __device__ TokSched(int num_tiles, int num_kb_, const GemmStreamK& sk) : TokSched(num_tiles, num_kb_, sk, blockIdx.x, gridDim.x) {}
+  __device__ TokSched(int num_tiles, int num_kb_, const GemmStreamK& sk, int w, int workers) {
+    num_kb = num_kb_;
+    stream = sk.ws != nullptr;
+    kgroup = stream ? sk.kgroup : num_kb_;
+    num_kg = (num_kb + kgroup - 1) / kgroup;
+    const long long U = static_cast<long long>(num_tiles) * num_kg;
+    u_begin = stream ? U * w / workers : 0;
+    u_end = stream ? U * (w + 1) / workers : 0;
+    u = u_begin;
+    t_next = w;
+    t_end = num_tiles;
+    stride = workers;
+  }
+  // next piece of work: K blocks [kb0, kb1) of tile t
+  __device__ bool next(int& t, int& kb0, int& kb1) {
+    if (!stream) {
+      if (t_next >= t_end) return false;
+      t = t_next;
+      t_next += stride;
+      kb0 = 0;
+      kb1 = num_kb;
+      return true;
+    }
+    if (u >= u_end) return false;
+    t = static_cast<int>(u / num_kg);
+    const long long tile_a = static_cast<long long>(t) * num_kg;
+    const long long e = u_end < tile_a + num_kg ? u_end : tile_a + num_kg;
+    kb0 = static_cast<int>(u - tile_a) * kgroup;
+    kb1 = static_cast<int>(e - tile_a) * kgroup;
+    if (kb1 > num_kb) kb1 = num_kb;
+    u = e;
+    return true;
+  }
+};
+
+// ---- epilogue pieces shared by the token-tile kernels ----------------------------------------------------------------
+// Stream-K bookkeeping of one partial tile, as one epilogue thread sees it.
+struct SkTile {
+  long long U, a;        // units in all; first unit of this tile
+  int workers;           // CTAs (or CTA pairs) the units are dealt to
+  int first, n;          // the tile's K ranges belong to workers first .. first + n - 1; n == 0: another CTA adds them up
+  int cta_mul, cta_add;  // worker w's scratch slots are those of CTA w * cta_mul + cta_add
+};
+
+// One thread's row of an accumulator set (kAccCols fp32 columns at TMEM address tacc) -> scratch slot `slot`.
+template <int kAccCols>
+__device__ __forceinline__ void sk_dump(uint32_t tacc, float* slot, int row_in_tile, bool live) {
+  float* mine = slot + row_in_tile * 4;
+#pragma unroll 1
+  for (int cc = 0; cc < kAccCols; cc += 32) {
+    uint32_t v[32];
+    tmem_ld_x32(tacc + cc, v);
+    tmem_ld_wait();
+    if (live) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        *reinterpret_cast<uint4*>(mine + ((cc >> 2) + q) * 512) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+    }
+  }
+}
+
+// Called by the 128 epilogue threads of a CTA after sk_dump: counts the CTA in for tile t (counter `counter`) and tells
+// whether it is the last of the tile's contributors, i.e. the one that adds the partial sums up (n > 0).
+__device__ __forceinline__ SkTile sk_arrive(const GemmStreamK& sk, int counter, int* flag, bool first_thread, int t, int num_tiles,
+                                            int num_kg, int workers, int cta_mul, int cta_add) {
+  __threadfence();
+  named_barrier_sync(1, 128);
+  if (first_thread) *flag = atomicAdd(&sk.counters[counter], 1);
+  named_barrier_sync(1, 128);
+  const int arrived = *flag;
+  SkTile tile;
+  tile.U = static_cast<long long>(num_tiles) * num_kg;
+  tile.a = static_cast<long long>(t) * num_kg;
+  tile.workers = workers;
+  tile.cta_mul = cta_mul;
+  tile.cta_add = cta_add;
+  const long long G = workers;
+  tile.first = static_cast<int>(((tile.a + 1) * G + tile.U - 1) / tile.U) - 1;
+  tile.n = static_cast<int>(((tile.a + num_kg) * G + tile.U - 1) / tile.U) - tile.first;
+  if (arrived != tile.n - 1) {
+    tile.n = 0;
+  } else {
+    __threadfence();
+    if (first_thread) sk.counters[counter] = 0;
+  }
+  return tile;
+}
+
+// One thread's row of an output tile: accumulators (whole tile: from tensor memory at tacc; else the sum of the partial
+// tiles described by `tile`) -> row scale / SiLU * up / residual add and sums of squares -> bf16 row `r` of `out`,
+// columns c0 .. c0 + BLOCK_C.
+template <int BLOCK_C, int kEpi>
+__device__ __forceinline__ void tile_epilogue(uint32_t tacc, bool whole, const SkTile& tile, const float* ws, int row_in_tile, int r,
+                                              int c0, int m_total, int n_total, __nv_bfloat16* __restrict__ out, int ldo,
+                                              const GemmFuse& fuse) {
+  constexpr int kChunk = BLOCK_C >= 32 ? 32 : 16;
+  constexpr int kNumC = kEpi == kEpiSiluMul ? 2 : 1;
+  const float row_scale = fuse_row_scale(fuse, r, m_total);          // 1 unless the input norm is folded in
+  float ssq = 0.f;                                                   // of the new residual values of this row, current 128 columns
+#pragma unroll 1
+  for (int cc = 0; cc < BLOCK_C; cc += kChunk) {
+    uint32_t v[kChunk];
+    uint32_t u[kEpi == kEpiSiluMul ? kChunk : 1];
+    const uint32_t taddr = tacc + cc;
+    if (whole) {
+      if constexpr (kChunk == 32) tmem_ld_x32(taddr, v); else tmem_ld_x16(taddr, v);
+      if constexpr (kEpi == kEpiSiluMul) {
+        if constexpr (kChunk == 32) tmem_ld_x32(taddr + BLOCK_C, u); else tmem_ld_x16(taddr + BLOCK_C, u);
+      }
+      tmem_ld_wait();
+    } else if constexpr (kChunk == 32) {
+      // sum of the partial tiles, in the order of their K ranges
+#pragma unroll
+      for (int half = 0; half < kNumC; ++half) {
+        float a[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) a[j] = 0.f;
+        const int col = cc + half * BLOCK_C;
+        for (int s0 = 0; s0 < tile.n; s0 += kSkBatch) {
+          uint4 pb[kSkBatch][8];
+#pragma unroll
+          for (int i = 0; i < kSkBatch; ++i) {
+            if (s0 + i < tile.n && r < m_total) {
+              const int w = tile.first + s0 + i;
+              const long long u0 = tile.U * w / tile.workers;
+              const float* src = ws + (static_cast<size_t>(w * tile.cta_mul + tile.cta_add) * 2 + (u0 >= tile.a ? 0 : 1)) * kSkSlotFloats + row_in_tile * 4;
+#pragma unroll
+              for (int q = 0; q < 8; ++q) pb[i][q] = __ldcg(reinterpret_cast<const uint4*>(src + ((col >> 2) + q) * 512));
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < kSkBatch; ++i) {
+            if (s0 + i < tile.n && r < m_total) {
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                a[4 * q] += __uint_as_float(pb[i][q].x);
+                a[4 * q + 1] += __uint_as_float(pb[i][q].y);
+                a[4 * q + 2] += __uint_as_float(pb[i][q].z);
+                a[4 * q + 3] += __uint_as_float(pb[i][q].w);
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (half == 0) v[j] = __float_as_uint(a[j]);
+          else u[kEpi == kEpiSiluMul ? j : 0] = __float_as_uint(a[j]);
+        }
+      }
+    }
+    float f[kChunk];
+#pragma unroll
+    for (int j = 0; j < kChunk; ++j) {
+      f[j] = __uint_as_float(v[j]) * row_scale;
+      if constexpr (kEpi == kEpiSiluMul) f[j] = silu(f[j]) * (__uint_as_float(u[j]) * row_scale);
+    }
+    const int c = c0 + cc;
+    if (r < m_total) {
+      __nv_bfloat16* dst = out + static_cast<size_t>(r) * ldo + c;
+      if (c + kChunk <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+        for (int j = 0; j < kChunk; j += 8) {
+          if (fuse.add_residual) {
+            const uint4 old = *reinterpret_cast<const uint4*>(dst + j);
+            const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              f[j + 2 * k] = bf16_round_g(bf16_round_g(f[j + 2 * k]) + bf16_lo(ow[k]));
+              f[j + 2 * k + 1] = bf16_round_g(bf16_round_g(f[j + 2 * k + 1]) + bf16_hi(ow[k]));
+              ssq += f[j + 2 * k] * f[j + 2 * k] + f[j + 2 * k + 1] * f[j + 2 * k + 1];
+            }
+          }
+          uint4 pk;
+          pk.x = pack_bf16x2(f[j], f[j + 1]);
+          pk.y = pack_bf16x2(f[j + 2], f[j + 3]);
+          pk.z = pack_bf16x2(f[j + 4], f[j + 5]);
+          pk.w = pack_bf16x2(f[j + 6], f[j + 7]);
+          *reinterpret_cast<uint4*>(dst + j) = pk;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < kChunk; ++j)
+          if (c + j < n_total) {
+            float val = f[j];
+            if (fuse.add_residual) {
+              val = bf16_round_g(bf16_round_g(val) + __bfloat162float(dst[j]));
+              ssq += val * val;
+            }
+            dst[j] = __float2bfloat16_rn(val);
+          }
+      }
+    }
+    if (fuse.out_ssq != nullptr && ((cc + kChunk) & 127) == 0) {      // a group of 128 columns is complete (tiles are 128 or 256 wide)
+      const int g0 = c + kChunk - 128;
+      if (r < m_total && g0 < n_total) fuse.out_ssq[static_cast<size_t>(r) * fuse.out_parts + (g0 >> 7)] = ssq;
+      ssq = 0.f;
+    }
+  }
+}
+
 // =========================================================================================================
 // prefill: R = X tile (128 tokens), C = W tile (BLOCK_C features; two tiles for SiLU).  Persistent CTAs.
 // =========================================================================================================
@@ -120,7 +347,7 @@ template <int BLOCK_C, int kEpi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                    __nv_bfloat16* __restrict__ out, int ldo, int m_total, int n_total, int K, int dual_off, unsigned* status,
-                   const TpPush push, const GemmFuse fuse, const GemmSample samp) {
+                   const TpPush push, const GemmFuse fuse, const GemmSample samp, const GemmStreamK sk) {
   using Cfg = TokCfg<BLOCK_C, kEpi>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -129,6 +356,7 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   uint64_t* acc_full = empty_bar + Cfg::kStages;       // [2]
   uint64_t* acc_empty = acc_full + 2;                  // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  int* sk_flag = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m_tiles = (m_total + kBlockR - 1) / kBlockR;
@@ -162,32 +390,36 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   if (warp == 0 && lane == 0) {
     // Weights never depend on a predecessor kernel: the weight halves of the first ring stages are requested
     // before waiting for it, the activation halves after (the stage's barrier counts the bytes of both).
-    const int pre = blockIdx.x < num_tiles ? min(num_kb, Cfg::kStages) : 0;
-    const int c_first = (blockIdx.x / m_tiles) * BLOCK_C;
+    TokSched sched(num_tiles, num_kb, sk);
+    int t = 0, kb0 = 0, kb1 = 0;
+    bool have = sched.next(t, kb0, kb1);
+    const int pre = have ? min(kb1 - kb0, Cfg::kStages) : 0;
+    const int c_first = (t / m_tiles) * BLOCK_C;
     for (int i = 0; i < pre; ++i) {
       uint8_t* st = smem + i * Cfg::kStageBytes;
       mbar_expect_tx(&full_bar[i], Cfg::kStageBytes);
       for (int j = 0; j < Cfg::kNumC; ++j)
-        tma_load_2d(st + Cfg::kRBytes + j * Cfg::kCBytes, &tm_w, &full_bar[i], i * kBlockK, c_first + j * dual_off);
+        tma_load_2d(st + Cfg::kRBytes + j * Cfg::kCBytes, &tm_w, &full_bar[i], (kb0 + i) * kBlockK, c_first + j * dual_off);
     }
     pdl_wait();                                 // x and out belong to predecessors
     int it = 0;                                 // running K-block counter across tiles: the ring never drains
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    while (have) {
       const int r0 = (t % m_tiles) * kBlockR, c0 = (t / m_tiles) * BLOCK_C;
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % Cfg::kStages;
         uint8_t* st = smem + s * Cfg::kStageBytes;
-        if (it < pre) {                         // first tile, stage already armed and its weights under way
+        if (it < pre) {                         // first piece, stage already armed and its weights under way
           tma_load_2d(st, &tm_x, &full_bar[s], kb * kBlockK, r0);
           continue;
         }
         const uint32_t ph = (it / Cfg::kStages) & 1;
-        if (!mbar_wait_parked(&empty_bar[s], ph ^ 1, status)) { t = num_tiles; break; }
+        if (!mbar_wait_parked(&empty_bar[s], ph ^ 1, status)) { have = false; break; }
         mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
         tma_load_2d(st, &tm_x, &full_bar[s], kb * kBlockK, r0);
         for (int i = 0; i < Cfg::kNumC; ++i)
           tma_load_2d(st + Cfg::kRBytes + i * Cfg::kCBytes, &tm_w, &full_bar[s], kb * kBlockK, c0 + i * dual_off);
       }
+      if (have) have = sched.next(t, kb0, kb1);
     }
   } else {
     pdl_wait();
@@ -196,14 +428,15 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc(kBlockR, BLOCK_C, 1, 1);
-      int it = 0, n = 0;
-      for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++n) {
+      TokSched sched(num_tiles, num_kb, sk);
+      int it = 0, t = 0, kb0 = 0, kb1 = 0;
+      for (int n = 0; sched.next(t, kb0, kb1); ++n) {
         const int buf = n & 1;
         if (!mbar_wait_parked(&acc_empty[buf], ((n >> 1) & 1) ^ 1, status)) break;      // the epilogue has drained this set
         tcgen05_fence_after();
         const uint32_t acc_addr = tmem_base + buf * Cfg::kAccCols;
         bool ok = true;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % Cfg::kStages;
           const uint32_t ph = (it / Cfg::kStages) & 1;
           if (!mbar_wait_parked(&full_bar[s], ph, status)) { ok = false; break; }
@@ -212,7 +445,7 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
             const uint32_t koff = k * kUmmaK * 2;
-            const uint32_t acc = (kb | k) != 0;
+            const uint32_t acc = (kb != kb0) || (k != 0);
             const uint64_t dx = umma_desc_k_sw128(st + koff);
             umma_f16(acc_addr, dx, umma_desc_k_sw128(st + Cfg::kRBytes + koff), idesc, acc);
             if constexpr (kEpi == kEpiSiluMul)
@@ -226,13 +459,16 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     }
   } else if (warp >= 2) {
     const int quad = warp & 3;
-    int n = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++n) {
+    TokSched sched(num_tiles, num_kb, sk);
+    int t = 0, kb0 = 0, kb1 = 0;
+    for (int n = 0; sched.next(t, kb0, kb1); ++n) {
       const int buf = n & 1;
       const int r = (t % m_tiles) * kBlockR + quad * 32 + lane;
       const int c0 = (t / m_tiles) * BLOCK_C;
       const bool ok = mbar_wait(&acc_full[buf], (n >> 1) & 1, status);
       tcgen05_fence_after();
+      const bool whole = kb0 == 0 && kb1 == num_kb;       // false only under stream-K
+      bool released = false;                                // accumulator set already handed back
       if constexpr (kEpi == kEpiSample) {
         if (ok) {
           const bool live = r < m_total;                                   // padding rows of the token tile: nothing to sample
@@ -278,73 +514,30 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             samp.part_i[slot] = token;
           }
         }
-      } else
-      if (ok) {
-        constexpr int kChunk = BLOCK_C >= 32 ? 32 : 16;
-        const float row_scale = fuse_row_scale(fuse, r, m_total);          // 1 unless the input norm is folded in
-        float ssq = 0.f;                                                   // of the new residual values of this row, current 128 columns
-#pragma unroll 1
-        for (int cc = 0; cc < BLOCK_C; cc += kChunk) {
-          uint32_t v[kChunk];
-          uint32_t u[kEpi == kEpiSiluMul ? kChunk : 1];
-          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * Cfg::kAccCols + cc;
-          if constexpr (kChunk == 32) tmem_ld_x32(taddr, v); else tmem_ld_x16(taddr, v);
-          if constexpr (kEpi == kEpiSiluMul) {
-            if constexpr (kChunk == 32) tmem_ld_x32(taddr + BLOCK_C, u); else tmem_ld_x16(taddr + BLOCK_C, u);
-          }
-          tmem_ld_wait();
-          float f[kChunk];
-#pragma unroll
-          for (int j = 0; j < kChunk; ++j) {
-            f[j] = __uint_as_float(v[j]) * row_scale;
-            if constexpr (kEpi == kEpiSiluMul) f[j] = silu(f[j]) * (__uint_as_float(u[j]) * row_scale);
-          }
-          const int c = c0 + cc;
-          if (r < m_total) {
-            __nv_bfloat16* dst = out + static_cast<size_t>(r) * ldo + c;
-            if (c + kChunk <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-              for (int j = 0; j < kChunk; j += 8) {
-                if (fuse.add_residual) {
-                  const uint4 old = *reinterpret_cast<const uint4*>(dst + j);
-                  const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
-#pragma unroll
-                  for (int k = 0; k < 4; ++k) {
-                    f[j + 2 * k] = bf16_round_g(bf16_round_g(f[j + 2 * k]) + bf16_lo(ow[k]));
-                    f[j + 2 * k + 1] = bf16_round_g(bf16_round_g(f[j + 2 * k + 1]) + bf16_hi(ow[k]));
-                    ssq += f[j + 2 * k] * f[j + 2 * k] + f[j + 2 * k + 1] * f[j + 2 * k + 1];
-                  }
-                }
-                uint4 pk;
-                pk.x = pack_bf16x2(f[j], f[j + 1]);
-                pk.y = pack_bf16x2(f[j + 2], f[j + 3]);
-                pk.z = pack_bf16x2(f[j + 4], f[j + 5]);
-                pk.w = pack_bf16x2(f[j + 6], f[j + 7]);
-                *reinterpret_cast<uint4*>(dst + j) = pk;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < kChunk; ++j)
-                if (c + j < n_total) {
-                  float val = f[j];
-                  if (fuse.add_residual) {
-                    val = bf16_round_g(bf16_round_g(val) + __bfloat162float(dst[j]));
-                    ssq += val * val;
-                  }
-                  dst[j] = __float2bfloat16_rn(val);
-                }
-            }
-          }
-          if (fuse.out_ssq != nullptr && ((cc + kChunk) & 127) == 0) {      // a group of 128 columns is complete (tiles are 128 or 256 wide)
-            const int g0 = c + kChunk - 128;
-            if (r < m_total && g0 < n_total) fuse.out_ssq[static_cast<size_t>(r) * fuse.out_parts + (g0 >> 7)] = ssq;
-            ssq = 0.f;
+      } else {
+        const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * Cfg::kAccCols;
+        SkTile tile = {};
+        if (ok && !whole) {
+          if constexpr (BLOCK_C >= 32) {
+            // this CTA's partial sums -> its slot; hand the accumulator set back; count this CTA in
+            const long long u_seg = static_cast<long long>(t) * sched.num_kg + kb0 / sched.kgroup;
+            sk_dump<Cfg::kAccCols>(tacc, sk.ws + (static_cast<size_t>(blockIdx.x) * 2 + (u_seg == sched.u_begin ? 0 : 1)) * kSkSlotFloats,
+                                   quad * 32 + lane, r < m_total);
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            released = true;
+            tile = sk_arrive(sk, t, sk_flag, warp == 2 && lane == 0, t, num_tiles, sched.num_kg, gridDim.x, 1, 0);
           }
         }
+        if (ok && (whole || tile.n > 0))
+          tile_epilogue<BLOCK_C, kEpi>(tacc, whole, tile, sk.ws, quad * 32 + lane, r, c0, m_total, n_total, out, ldo, fuse);
       }
-      tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[buf]);     // this accumulator set may be overwritten
+      if (!released) {
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);     // this accumulator set may be overwritten
+      }
       if (!ok) break;
     }
   }
@@ -358,6 +551,189 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
   if (warp == 1) {
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// =========================================================================================================
+// many tokens, CTA pairs: one UMMA of M = 256 tokens x N = 256 features per pair of SMs (cta_group::2)
+// =========================================================================================================
+// The token-tile kernel above is bound by what one SM can load: 48 KB of operands per 128 x 256 x 64 block of
+// multiply-adds.  Here the two CTAs of a cluster share one instruction of twice the height: each loads its own 128 tokens
+// of X and only HALF of the 256 weight rows (the tensor core reads the other half from the partner's shared memory), i.e.
+// 32 KB for the same block.  Plain GEMM: CTA rank r loads weight rows c0 + 128 r.  SiLU: the 256 columns of the
+// accumulator are 128 gate + 128 up features, rank 0 loads the gate rows, rank 1 the up rows.  Each CTA drains its own
+// 128 x 256 accumulator block.  Persistent over the pairs, two accumulator sets, optional stream-K exactly as above (a
+// worker is a pair; every CTA keeps partial tiles and counters of its own rows).
+//
+// Barriers: full[s] lives in the leader (rank 0): its producer arrives once with the byte count of BOTH CTAs' loads, and
+// both CTAs' TMA loads credit it.  empty[s] and acc_full[b] exist in both CTAs and are signalled in both at once by the
+// leader's tcgen05.commit.  acc_empty[b] lives in the leader and counts the epilogue warps of both CTAs.
+template <int kEpi>
+struct PairCfg {
+  static constexpr int kBlockN = kEpi == kEpiSiluMul ? 128 : 256;       // output features per tile
+  static constexpr int kHalfBytes = kBlockR * kBlockK * 2;              // 128 rows x 64 bf16
+  static constexpr int kStageBytes = 2 * kHalfBytes;                    // this CTA's X rows + its half of the weight rows
+  static constexpr int kStages = 6;
+  static constexpr int kAccCols = 256;
+  static constexpr int kTmemCols = 512;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+template <int kEpi>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+                 __nv_bfloat16* __restrict__ out, int ldo, int m_total, int n_total, int K, int dual_off, unsigned* status,
+                 const TpPush push, const GemmFuse fuse, const GemmStreamK sk) {
+  using Cfg = PairCfg<kEpi>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint64_t* empty_bar = full_bar + Cfg::kStages;
+  uint64_t* acc_full = empty_bar + Cfg::kStages;       // [2]
+  uint64_t* acc_empty = acc_full + 2;                  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  int* sk_flag = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(cluster_ctarank());          // 0 = leader
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int m_tiles = (m_total + 2 * kBlockR - 1) / (2 * kBlockR);
+  const int n_tiles = (n_total + Cfg::kBlockN - 1) / Cfg::kBlockN;
+  const int num_tiles = m_tiles * n_tiles;
+  const int num_kb = (K + kBlockK - 1) / kBlockK;
+  const int w_row_rank = rank * (kEpi == kEpiSiluMul ? dual_off : kBlockR);   // this CTA's half of a tile's weight rows
+
+  if (warp == 0 && lane == 0) {
+    prefetch_tensormap(&tm_x);
+    prefetch_tensormap(&tm_w);
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 8);                     // one arrival per epilogue warp of both CTAs
+    }
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  pdl_launch_dependents();
+  tcgen05_fence_before();
+  cluster_sync();                                      // both CTAs' barriers and tensor memory exist before anyone signals
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 && lane == 0) {
+    TokSched sched(num_tiles, num_kb, sk, pair, pairs);
+    int t = 0, kb0 = 0, kb1 = 0;
+    bool have = sched.next(t, kb0, kb1);
+    const int pre = have ? min(kb1 - kb0, Cfg::kStages) : 0;
+    const int c_first = (t / m_tiles) * Cfg::kBlockN + w_row_rank;
+    for (int i = 0; i < pre; ++i) {                    // weights do not depend on the predecessor kernel
+      if (rank == 0) mbar_expect_tx(&full_bar[i], 2 * Cfg::kStageBytes);
+      tma_load_2d_pair(smem + i * Cfg::kStageBytes + Cfg::kHalfBytes, &tm_w, dsmem_addr(smem_u32(&full_bar[i]), 0), (kb0 + i) * kBlockK, c_first);
+    }
+    pdl_wait();
+    int it = 0;
+    while (have) {
+      const int r0 = (t % m_tiles) * 2 * kBlockR + rank * kBlockR, c0 = (t / m_tiles) * Cfg::kBlockN + w_row_rank;
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int s = it % Cfg::kStages;
+        uint8_t* st = smem + s * Cfg::kStageBytes;
+        const uint32_t lbar = dsmem_addr(smem_u32(&full_bar[s]), 0);
+        if (it < pre) {
+          tma_load_2d_pair(st, &tm_x, lbar, kb * kBlockK, r0);
+          continue;
+        }
+        const uint32_t ph = (it / Cfg::kStages) & 1;
+        if (!mbar_wait_parked(&empty_bar[s], ph ^ 1, status)) { have = false; break; }
+        if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * Cfg::kStageBytes);
+        tma_load_2d_pair(st, &tm_x, lbar, kb * kBlockK, r0);
+        tma_load_2d_pair(st + Cfg::kHalfBytes, &tm_w, lbar, kb * kBlockK, c0);
+      }
+      if (have) have = sched.next(t, kb0, kb1);
+    }
+  } else {
+    pdl_wait();
+  }
+
+  if (warp == 1 && rank == 0) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(2 * kBlockR, 256, 1, 1);
+      TokSched sched(num_tiles, num_kb, sk, pair, pairs);
+      int it = 0, t = 0, kb0 = 0, kb1 = 0;
+      for (int n = 0; sched.next(t, kb0, kb1); ++n) {
+        const int buf = n & 1;
+        if (!mbar_wait_parked(&acc_empty[buf], ((n >> 1) & 1) ^ 1, status)) break;      // both epilogues have drained this set
+        tcgen05_fence_after();
+        const uint32_t acc_addr = tmem_base + buf * Cfg::kAccCols;
+        bool ok = true;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+          const int s = it % Cfg::kStages;
+          const uint32_t ph = (it / Cfg::kStages) & 1;
+          if (!mbar_wait_parked(&full_bar[s], ph, status)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t st = smem_u32(smem + s * Cfg::kStageBytes);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            const uint32_t koff = k * kUmmaK * 2;
+            umma_f16_pair(acc_addr, umma_desc_k_sw128(st + koff), umma_desc_k_sw128(st + Cfg::kHalfBytes + koff), idesc,
+                          (kb != kb0) || (k != 0));
+          }
+          umma_commit_pair(&empty_bar[s], 3);
+        }
+        umma_commit_pair(&acc_full[buf], 3);
+        if (!ok) break;
+      }
+    }
+  } else if (warp >= 2) {
+    const int quad = warp & 3;
+    TokSched sched(num_tiles, num_kb, sk, pair, pairs);
+    int t = 0, kb0 = 0, kb1 = 0;
+    for (int n = 0; sched.next(t, kb0, kb1); ++n) {
+      const int buf = n & 1;
+      const int r = (t % m_tiles) * 2 * kBlockR + rank * kBlockR + quad * 32 + lane;
+      const int c0 = (t / m_tiles) * Cfg::kBlockN;
+      const bool ok = mbar_wait(&acc_full[buf], (n >> 1) & 1, status);
+      tcgen05_fence_after();
+      const bool whole = kb0 == 0 && kb1 == num_kb;
+      const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * Cfg::kAccCols;
+      const uint32_t leader_empty = dsmem_addr(smem_u32(&acc_empty[buf]), 0);
+      bool released = false;
+      SkTile tile = {};
+      if (ok && !whole) {
+        const long long u_seg = static_cast<long long>(t) * sched.num_kg + kb0 / sched.kgroup;
+        sk_dump<Cfg::kAccCols>(tacc, sk.ws + (static_cast<size_t>(blockIdx.x) * 2 + (u_seg == sched.u_begin ? 0 : 1)) * kSkSlotFloats,
+                               quad * 32 + lane, r < m_total);
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(leader_empty);
+        released = true;
+        tile = sk_arrive(sk, t * 2 + rank, sk_flag, warp == 2 && lane == 0, t, num_tiles, sched.num_kg, pairs, 2, rank);
+      }
+      if (ok && (whole || tile.n > 0))
+        tile_epilogue<Cfg::kBlockN, kEpi>(tacc, whole, tile, sk.ws, quad * 32 + lane, r, c0, m_total, n_total, out, ldo, fuse);
+      if (!released) {
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(leader_empty);
+      }
+      if (!ok) break;
+    }
+  }
+
+  if (push.size > 1) tp_push_done(push, gridDim.x);
+
+  // Neither CTA may leave while its partner can still signal its barriers or read its shared memory.
+  tcgen05_fence_before();
+  __syncwarp();
+  cluster_sync();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
   }
 }
 
@@ -728,10 +1104,35 @@ extern "C" int forge_gemm_set_trace(unsigned long long* buf) {
   return cudaMemcpyToSymbol(g_gemm_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : -1;
 }
 
+// Stream-K scratch of each device: set once per process and device by the host library (forge_gemm_set_streamk_workspace),
+// shared by every GEMM launched on that device, which must therefore be ordered on one stream.
+struct StreamKWorkspace {
+  float* ws;
+  int* counters;
+  int ctas, tiles;
+};
+static StreamKWorkspace g_sk_workspace[16];
+
+extern "C" int forge_gemm_set_streamk_workspace(float* ws, int* counters, int ctas, int tiles) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return -1;
+  g_sk_workspace[dev] = StreamKWorkspace{ws, counters, ctas, tiles};
+  return 0;
+}
+// floats a workspace for `ctas` CTAs needs
+extern "C" long long forge_gemm_streamk_workspace_floats(int ctas) { return static_cast<long long>(ctas) * 2 * kSkSlotFloats; }
+
+static const StreamKWorkspace* streamk_workspace() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
+  return g_sk_workspace[dev].ws != nullptr ? &g_sk_workspace[dev] : nullptr;
+}
+
+// kgroup > 0: stream-K with units of `kgroup` K blocks (needs the device's workspace; falls back to whole tiles without it)
 template <int BLOCK_C, int kEpi>
 static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int ldw, __nv_bfloat16* out, int ldo, int M,
                          int n_out, int K, unsigned* status, cudaStream_t stream, const TpPush& push, const GemmFuse& fuse,
-                         const GemmSample& samp = GemmSample{}) {
+                         const GemmSample& samp = GemmSample{}, int kgroup = 0) {
   using Cfg = TokCfg<BLOCK_C, kEpi>;
   CUtensorMap tm_x, tm_w;
   if (forge_make_tmap_2d(&tm_x, x, M, K, ldx, kBlockR, 2) != 0) return -2;
@@ -740,9 +1141,50 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
   FORGE_ENSURE_DYN_SMEM(kern, Cfg::kSmemBytes);
   const int tiles = ((M + kBlockR - 1) / kBlockR) * ((n_out + BLOCK_C - 1) / BLOCK_C);
   const int num_sms = device_sm_count();
-  dim3 grid(tiles < num_sms ? tiles : num_sms);
-  return launch_kernel(kern, grid, dim3(kGemmThreads), Cfg::kSmemBytes, stream, 0, tm_x, tm_w, out, ldo, M, n_out, K, n_out,
-                       status, push, fuse, samp) == cudaSuccess ? 0 : -5;
+  int ctas = tiles < num_sms ? tiles : num_sms;
+  GemmStreamK sk = {nullptr, nullptr, 0};
+  if (kgroup > 0 && BLOCK_C >= 32 && kEpi != kEpiSample) {
+    const StreamKWorkspace* wsp = streamk_workspace();
+    const int num_kb = (K + kBlockK - 1) / kBlockK;
+    if (kgroup > num_kb) kgroup = num_kb;
+    const long long units = static_cast<long long>(tiles) * ((num_kb + kgroup - 1) / kgroup);
+    const int want = units < num_sms ? static_cast<int>(units) : num_sms;
+    if (wsp != nullptr && want <= wsp->ctas && tiles <= wsp->tiles && units > tiles) {
+      sk = GemmStreamK{wsp->ws, wsp->counters, kgroup};
+      ctas = want;
+    }
+  }
+  return launch_kernel(kern, dim3(ctas), dim3(kGemmThreads), Cfg::kSmemBytes, stream, 0, tm_x, tm_w, out, ldo, M, n_out, K, n_out,
+                       status, push, fuse, samp, sk) == cudaSuccess ? 0 : -5;
+}
+
+// CTA-pair kernel: grid = 2 x pairs, clusters of 2 along x.  kgroup > 0: stream-K over the pairs.
+template <int kEpi>
+static int launch_pair(const void* x, int ldx, const void* w, int w_rows, int ldw, __nv_bfloat16* out, int ldo, int M, int n_out,
+                       int K, unsigned* status, cudaStream_t stream, const TpPush& push, const GemmFuse& fuse, int kgroup) {
+  using Cfg = PairCfg<kEpi>;
+  CUtensorMap tm_x, tm_w;
+  if (forge_make_tmap_2d(&tm_x, x, M, K, ldx, kBlockR, 2) != 0) return -2;
+  if (forge_make_tmap_2d(&tm_w, w, w_rows, K, ldw, kBlockR, 2) != 0) return -3;
+  auto kern = gemm_pair_kernel<kEpi>;
+  FORGE_ENSURE_DYN_SMEM(kern, Cfg::kSmemBytes);
+  const int tiles = ((M + 2 * kBlockR - 1) / (2 * kBlockR)) * ((n_out + Cfg::kBlockN - 1) / Cfg::kBlockN);
+  const int max_pairs = device_sm_count() / 2;
+  int pairs = tiles < max_pairs ? tiles : max_pairs;
+  GemmStreamK sk = {nullptr, nullptr, 0};
+  if (kgroup > 0) {
+    const StreamKWorkspace* wsp = streamk_workspace();
+    const int num_kb = (K + kBlockK - 1) / kBlockK;
+    if (kgroup > num_kb) kgroup = num_kb;
+    const long long units = static_cast<long long>(tiles) * ((num_kb + kgroup - 1) / kgroup);
+    const int want = units < max_pairs ? static_cast<int>(units) : max_pairs;
+    if (wsp != nullptr && 2 * want <= wsp->ctas && 2 * tiles <= wsp->tiles && units > tiles) {
+      sk = GemmStreamK{wsp->ws, wsp->counters, kgroup};
+      pairs = want;
+    }
+  }
+  return launch_kernel_cluster_x(kern, dim3(2 * pairs), dim3(kGemmThreads), Cfg::kSmemBytes, stream, 2, tm_x, tm_w, out, ldo, M, n_out,
+                                 K, n_out, status, push, fuse, sk) == cudaSuccess ? 0 : -5;
 }
 
 // Cluster size (K splits) of the decode kernel.  Measured on B200 (sweeps over token tile x splits x ring depth for
@@ -825,6 +1267,22 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
     force_bc = narrow;
   } else if (force_mode == 0 && epi == kEpiSiluMul && K >= 4096 && M > 64 && M <= 256 && push.size <= 1) {
     force_mode = 1;     // a large gated MLP (8B and up) is compute-heavy already at ~100 tokens: full 128 x (128 + 128) tiles
+  }
+  if (force_mode == 3) {            // token-tile kernel with stream-K: tune bits 0..7 = K blocks per unit, bits 8..15 = feature tile
+    const int kg = force_splits > 0 ? force_splits : 4;
+    const GemmSample none{};
+    if (force_bc == 64 && fuse.add_residual) return -6;       // the sums of squares are kept per 128 features
+    if (epi == kEpiSiluMul) {
+      if (force_bc == 64) return launch_tokens<64, kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, none, kg);
+      return launch_tokens<128, kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, none, kg);
+    }
+    if (force_bc == 64) return launch_tokens<64, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, none, kg);
+    if (force_bc == 128) return launch_tokens<128, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, none, kg);
+    return launch_tokens<256, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, none, kg);
+  }
+  if (force_mode == 4) {            // CTA-pair kernel (256-token x 256-feature tiles); tune bits 0..7 = K blocks per stream-K unit (0: whole tiles)
+    if (epi == kEpiSiluMul) return launch_pair<kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, force_splits);
+    return launch_pair<kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, force_splits);
   }
   const bool decode = force_mode == 2 || (force_mode == 0 && M <= 256 && !wide);
   if (decode) {

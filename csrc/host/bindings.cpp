@@ -17,6 +17,8 @@ int forge_gemm_bf16_sample(const void* x, int ldx, const void* w, int ldw, int M
                            const int* header, float* part_v, int* part_i, int* out_i, float* out_v, unsigned* status,
                            cudaStream_t stream);
 int forge_gemm_set_trace(unsigned long long* buf);
+int forge_gemm_set_streamk_workspace(float* ws, int* counters, int ctas, int tiles);
+long long forge_gemm_streamk_workspace_floats(int ctas);
 int forge_quant_fp8_1x128(const void* x, void* xq, float* scale, int M, int K, int scale_ld, cudaStream_t stream);
 int forge_gemm_fp8_splits(int M, int N, int K);
 int forge_gemm_fp8_block(const void* xq, const float* xs, int xs_ld, const void* wq, const float* ws, void* out, int ldo, int M,
@@ -651,6 +653,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("decode_attention_qkv", &decode_attention_qkv);
   m.def("decode_attention_flat_scratch_floats", &decode_attention_flat_scratch_floats);
   m.def("decode_attention_flat_ctas_per_sm", &decode_attention_flat_ctas_per_sm);
+  m.def("gemm_set_streamk_workspace", [](torch::Tensor ws, torch::Tensor counters, int64_t ctas) {
+    // scratch of the stream-K GEMM for the current device: fp32 partial tiles and zeroed per-tile arrival counters
+    TORCH_CHECK(ws.is_cuda() && ws.scalar_type() == torch::kFloat32 && ws.is_contiguous(), "ws: contiguous fp32 CUDA tensor");
+    TORCH_CHECK(counters.is_cuda() && counters.scalar_type() == torch::kInt32 && counters.is_contiguous(), "counters: contiguous int32 CUDA tensor");
+    TORCH_CHECK(ws.numel() >= forge_gemm_streamk_workspace_floats(static_cast<int>(ctas)), "ws too small for ", ctas, " CTAs");
+    check(forge_gemm_set_streamk_workspace(ws.data_ptr<float>(), counters.data_ptr<int>(), static_cast<int>(ctas), static_cast<int>(counters.numel())),
+          "forge_gemm_set_streamk_workspace");
+  });
+  m.def("gemm_streamk_workspace_floats", [](int64_t ctas) { return static_cast<int64_t>(forge_gemm_streamk_workspace_floats(static_cast<int>(ctas))); });
   m.def("decode_attention_set_tc_min_group", [](int64_t g) { forge_decode_attention_set_tc_min_group(static_cast<int>(g)); });
   m.def("prefill_attention", &prefill_attention);
 }

@@ -201,6 +201,50 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// ---- CTA pairs (cta_group::2) ----------------------------------------------------------------------------
+// Two CTAs of a cluster (ranks 2i, 2i + 1) on the two SMs of a pair work on one UMMA: M = 256 rows (128 per CTA), each
+// CTA keeps its own half of A and its own half of the N rows of B in its shared memory, at the same offsets, and gets the
+// 128 x N accumulator block of its rows in its own tensor memory.  The even CTA (the leader) issues the instruction.
+// Every tcgen05 instruction of such a kernel that takes a cta_group carries cta_group::2; allocation and release of
+// tensor memory are executed by the same warp of BOTH CTAs.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_slot, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  const uint32_t z = 0;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(z)
+      : "memory");
+}
+// One arrival on the mbarrier at this shared-memory offset in every CTA of `cta_mask` (bit = rank in the cluster) when
+// all UMMAs issued so far by this thread have completed.  (A barrier signal, not a data transfer.)
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(cta_mask) : "memory");
+}
+// 2-D tile load into THIS CTA's shared memory whose bytes are credited to an mbarrier of the pair's leader
+// (`leader_bar`: a shared::cluster address, see dsmem_addr).
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* tm, uint32_t leader_bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tm)), "r"(leader_bar), "r"(x), "r"(y)
+      : "memory");
+}
+// Arrival on an mbarrier of another CTA of the cluster (shared::cluster address).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_addr) : "memory");
+}
+
 // ---- TMEM -> registers ---------------------------------------------------------------------------------
 // Warp w of a CTA may touch TMEM lanes 32 * (w % 4) .. +31. Thread t of the warp receives lane
 // (32 * (w % 4) + t), columns col .. col + N - 1, one 32-bit value each.

@@ -35,6 +35,8 @@ def _close(a, b, atol, rtol):
     (1, 128, 64, 0), (16, 256, 128, 0), (7, 1024, 1024, 0), (64, 4096, 1024, 0), (200, 1024, 2048, 0),
     (256, 6144, 1024, 0), (128, 128, 64, 1), (300, 384, 256, 1), (1000, 1024, 1024, 0), (4096, 4096, 1024, 0),
     (130, 200, 72, 1), (33, 136, 200, 2), (256, 1024, 3072, 2),
+    # one rank's shapes of the 32B architecture split 8 ways: qkv, o_proj, down_proj at decode and prefill sizes
+    (64, 1280, 5120, 0), (64, 5120, 1024, 0), (64, 5120, 3200, 0), (2048, 1280, 5120, 0), (2048, 5120, 3200, 0),
 ])
 def test_gemm_matches_fp32(ops, M, N, K, mode):
     torch.manual_seed(M * 7 + N)
@@ -45,7 +47,8 @@ def test_gemm_matches_fp32(ops, M, N, K, mode):
     ops.check_status()
 
 
-@pytest.mark.parametrize("M,I,K,mode", [(8, 256, 128, 0), (100, 3072, 1024, 0), (256, 1536, 1024, 2), (700, 3072, 1024, 0), (384, 512, 256, 1)])
+@pytest.mark.parametrize("M,I,K,mode", [(8, 256, 128, 0), (100, 3072, 1024, 0), (256, 1536, 1024, 2), (700, 3072, 1024, 0), (384, 512, 256, 1),
+                                        (64, 3200, 5120, 0), (2048, 3200, 5120, 0)])
 def test_gemm_silu_mul_epilogue(ops, M, I, K, mode):
     torch.manual_seed(M + I)
     x, w = _rand(M, K), _rand(2 * I, K, scale=0.05)
@@ -192,6 +195,90 @@ def test_gemm_with_residual_add_and_sum_of_squares(ops, M, N, K, mode, tune):
     ops.check_status()
 
 
+@pytest.mark.parametrize("M,N,K,bc,kg,silu", [
+    (256, 6144, 4096, 0, 4, False), (64, 4096, 4096, 0, 4, False), (200, 4096, 12288, 0, 4, False), (16, 1280, 5120, 128, 2, False),
+    (100, 5120, 3200, 0, 3, False), (256, 12288, 4096, 0, 4, True), (50, 3200, 5120, 0, 8, True), (130, 1000, 520, 64, 1, False),
+    (300, 1536, 1024, 64, 2, True), (1, 256, 64, 0, 1, False), (7, 136, 4104, 128, 5, False),
+])
+def test_gemm_stream_k_matches_fp32(ops, M, N, K, bc, kg, silu):
+    """Token-tile kernel with the (tile, K group) units dealt out evenly over the CTAs: partial tiles go through the
+    scratch buffer and are summed by the CTA that arrives last."""
+    torch.manual_seed(M + N + K)
+    x, w = _rand(M, K), _rand(2 * N if silu else N, K, scale=0.05)
+    fn = ops.linear_silu_mul if silu else ops.linear
+    out = fn(x, w, force_mode=3, force_splits=kg, force_block_c=bc)
+    ref_ = x.float() @ w.float().t()
+    want = torch.nn.functional.silu(ref_[:, :N]) * ref_[:, N:] if silu else ref_
+    _close(out, want, atol=2e-2, rtol=2e-2)
+    out2 = fn(x, w, force_mode=3, force_splits=kg, force_block_c=bc)
+    assert torch.equal(out, out2)                      # partial sums are added in the order of their K ranges
+    ops.check_status()
+
+
+@pytest.mark.parametrize("M,N,K,kg", [(256, 4096, 4096, 4), (64, 4096, 12288, 4), (130, 1024, 3072, 2), (40, 5120, 3200, 4)])
+def test_gemm_stream_k_with_the_fused_epilogues(ops, M, N, K, kg):
+    torch.manual_seed(M + K)
+    x, w = _rand(M, K), _rand(N, K, scale=0.05)
+    residual = _rand(M, N, scale=2.0)
+    want = ((x.float() @ w.float().t()).to(BF).float() + residual.float()).to(BF)
+    parts = (N + 127) // 128
+    ssq = torch.full((M, parts), float("nan"), dtype=torch.float32, device="cuda")
+    res = residual.clone()
+    ops.linear_residual(x, w, res, ssq, force_mode=3, tune=kg)
+    _close(res, want, atol=6e-2, rtol=2e-2)
+    sq = torch.nn.functional.pad(res.float() ** 2, (0, parts * 128 - N)).view(M, parts, 128).sum(-1)
+    assert torch.allclose(ssq, sq, rtol=1e-3, atol=1e-3)
+    res2, ssq2 = residual.clone(), torch.empty_like(ssq)
+    ops.linear_residual(x, w, res2, ssq2, force_mode=3, tune=kg)
+    assert torch.equal(res2, res) and torch.equal(ssq2, ssq)
+    # folded input norm as a row scale
+    pk = (K + 127) // 128
+    ssq_in = (x.float() ** 2).view(M, pk, -1).sum(-1).contiguous()
+    got = ops.linear_scaled(x, w, ssq_in, 1e-6, force_mode=3, tune=kg)
+    xn = x.float() * torch.rsqrt((x.float() ** 2).mean(-1, keepdim=True) + 1e-6)
+    _close(got, xn @ w.float().t(), atol=3e-2, rtol=3e-2)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("M,N,K,kg,silu", [
+    (256, 256, 64, 0, False), (512, 512, 256, 0, False), (256, 6144, 4096, 0, False), (256, 6144, 4096, 4, False), (8192, 4096, 1024, 0, False),
+    (200, 4096, 4096, 4, False), (100, 1280, 5120, 2, False), (1000, 1100, 520, 0, False), (700, 1100, 520, 3, False), (4096, 3072, 1024, 0, True),
+    (256, 12288, 4096, 4, True), (130, 1536, 1024, 2, True), (300, 200, 72, 0, True), (1, 128, 64, 0, False),
+])
+def test_gemm_cta_pair_kernel_matches_fp32(ops, M, N, K, kg, silu):
+    """One 256 x 256 UMMA per pair of SMs (cta_group::2): each CTA loads its 128 tokens and half of the weight rows."""
+    torch.manual_seed(M + N + K)
+    x, w = _rand(M, K), _rand(2 * N if silu else N, K, scale=0.05)
+    fn = ops.linear_silu_mul if silu else ops.linear
+    out = fn(x, w, force_mode=4, force_splits=kg)
+    ref_ = x.float() @ w.float().t()
+    want = torch.nn.functional.silu(ref_[:, :N]) * ref_[:, N:] if silu else ref_
+    _close(out, want, atol=2e-2, rtol=2e-2)
+    assert torch.equal(out, fn(x, w, force_mode=4, force_splits=kg))
+    ops.check_status()
+
+
+@pytest.mark.parametrize("M,N,K,kg", [(256, 4096, 4096, 4), (2048, 1024, 3072, 0), (130, 1024, 3072, 2)])
+def test_gemm_cta_pair_kernel_with_the_fused_epilogues(ops, M, N, K, kg):
+    torch.manual_seed(M + K)
+    x, w = _rand(M, K), _rand(N, K, scale=0.05)
+    residual = _rand(M, N, scale=2.0)
+    want = ((x.float() @ w.float().t()).to(BF).float() + residual.float()).to(BF)
+    parts = (N + 127) // 128
+    ssq = torch.full((M, parts), float("nan"), dtype=torch.float32, device="cuda")
+    res = residual.clone()
+    ops.linear_residual(x, w, res, ssq, force_mode=4, tune=kg)
+    _close(res, want, atol=6e-2, rtol=2e-2)
+    sq = torch.nn.functional.pad(res.float() ** 2, (0, parts * 128 - N)).view(M, parts, 128).sum(-1)
+    assert torch.allclose(ssq, sq, rtol=1e-3, atol=1e-3)
+    pk = (K + 127) // 128
+    ssq_in = (x.float() ** 2).view(M, pk, -1).sum(-1).contiguous()
+    got = ops.linear_scaled(x, w, ssq_in, 1e-6, force_mode=4, tune=kg)
+    xn = x.float() * torch.rsqrt((x.float() ** 2).mean(-1, keepdim=True) + 1e-6)
+    _close(got, xn @ w.float().t(), atol=3e-2, rtol=3e-2)
+    ops.check_status()
+
+
 def test_embedding_sum_of_squares(ops):
     V, H, T = 512, 1024, 37
     table = _rand(V, H)
@@ -297,7 +384,7 @@ def _paged_case(q_lens, k_lens, nq, nkv, bs, seed=0):
 @pytest.mark.parametrize("mode", ["flat", "chunked"])
 @pytest.mark.parametrize("k_lens,nq,nkv,bs", [
     ([1], 16, 8, 256), ([5, 300, 64, 1000], 16, 8, 256), ([17, 33, 250], 8, 2, 16), ([700, 2011, 129], 32, 8, 256),
-    ([40, 90], 8, 8, 32), ([513, 77], 8, 1, 64), ([300, 1000, 70, 2], 40, 8, 256), ([129, 640, 33], 64, 8, 256), ([50, 400], 6, 2, 64),
+    ([40, 90], 8, 8, 32), ([513, 77], 8, 1, 64), ([300, 1000, 70, 2], 40, 8, 256), ([129, 640, 33], 64, 8, 256), ([50, 400], 6, 2, 64), ([700, 2011, 129], 8, 1, 256),
 ])
 def test_decode_attention(ops, k_lens, nq, nkv, bs, mode, monkeypatch):
     monkeypatch.setattr(ops, "decode_attention_mode", mode)

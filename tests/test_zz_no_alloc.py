@@ -118,12 +118,13 @@ def test_second_device_in_the_same_process():
     """The scratch address and the kernels' shared-memory limit are per device: a process that drives two GPUs gets the
     right ones on each (plain kernels only, no peer memory)."""
     lib = _lib()
+    lens, nq, nkv, bs, chunk = [700, 300, 1200], 16, 8, 256, 256
+    case0 = _case(lens, nq, nkv, bs, 5)               # built once (the block table comes from the host generator)
     prev = torch.cuda.current_device()
     try:
         torch.cuda.set_device(1)
         with torch.cuda.device(1):
-            lens, nq, nkv, bs, chunk = [700, 300, 1200], 16, 8, 256, 256
-            q, kc, vc, bt, cl = [t.to("cuda:1") for t in _case(lens, nq, nkv, bs, 5)]
+            q, kc, vc, bt, cl = [t.to("cuda:1") for t in case0]
             max_chunks = -(-max(lens) // chunk)
             B, _, D = q.shape
             out = torch.empty(B, nq * D, dtype=BF, device="cuda:1")
@@ -136,8 +137,7 @@ def test_second_device_in_the_same_process():
             assert int(status[0]) == 0
     finally:
         torch.cuda.set_device(prev)
-    q0, kc0, vc0, bt0, cl0 = _case(lens, nq, nkv, bs, 5)
-    want = _regular(q0, kc0, vc0, bt0, cl0, chunk, max_chunks)
+    want = _regular(*case0, chunk, max_chunks)
     assert torch.equal(out.cpu(), want.cpu())
 
 

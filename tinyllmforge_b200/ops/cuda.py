@@ -57,6 +57,23 @@ def decode_group_slice(group: int) -> int:
     return 1
 
 
+_STREAMK_WS: dict = {}
+
+
+def _streamk_workspace(C, device, num_sms: int) -> None:
+    """Scratch of the stream-K GEMM (fp32 partial tiles of CTAs whose share of the work ends inside an output tile, and
+    per-tile arrival counters): one per device and process, never freed, because CUDA graphs captured by any engine of
+    the process keep its address.  All GEMMs of a device share it, so they must be ordered on one stream."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key in _STREAMK_WS:
+        return
+    with torch.cuda.device(key):
+        ws = torch.empty(C.gemm_streamk_workspace_floats(num_sms), dtype=torch.float32, device=device)
+        counters = torch.zeros(8192, dtype=torch.int32, device=device)
+        C.gemm_set_streamk_workspace(ws, counters, num_sms)
+    _STREAMK_WS[key] = (ws, counters)
+
+
 class CudaOps:
     name = "cuda"
 
@@ -77,6 +94,7 @@ class CudaOps:
         self.fused_qkv_max_batch = int(os.environ.get("FORGE_FUSED_QKV_MAX", "32"))   # see models/qwen3.py
         self.sample_in_lm_head = os.environ.get("FORGE_LM_HEAD_SAMPLE", "1") != "0"
         self._flat_scratch = torch.empty(2 * self.num_sms * (2 * 4 * 130 + 2) + 64, dtype=torch.float32, device=self.device)
+        _streamk_workspace(self.C, self.device, self.num_sms)
 
     # ------------------------------------------------------------------ status word
     def check_status(self) -> None:
