@@ -114,6 +114,22 @@ constexpr int kSkSlotFloats = 128 * 256;       // one accumulator set: 128 rows 
 // access are 512 contiguous bytes.
 constexpr int kSkBatch = 4;                    // partial tiles whose loads are in flight together when summing
 
+// Order of the output tiles: groups of `group` token tiles; inside a group the token tile index runs fastest and all
+// feature tiles are visited before the next group starts.  CTAs that run at the same time then work on a compact block
+// of (a few token tiles) x (a few feature tiles) whose operands stay in L2 even where X or W as a whole does not fit
+// (8192 tokens x 12288 features of K).  With at most `group` token tiles this is plain token-tile-fastest order.
+constexpr int kRasterGroupTok = 16;      // 128-token tiles: 2048 tokens
+constexpr int kRasterGroupPair = 8;      // 256-token tiles
+__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int group, int& mt, int& nt) {
+  const int per_group = group * n_tiles;
+  const int g = t / per_group;
+  const int first = g * group;
+  const int gm = m_tiles - first < group ? m_tiles - first : group;
+  const int within = t - g * per_group;
+  mt = first + within % gm;
+  nt = within / gm;
+}
+
 struct TokSched {
   int num_kb, kgroup, num_kg;
   long long u, u_begin, u_end;     // stream-K: next unit, range of this CTA
@@ -394,7 +410,9 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     int t = 0, kb0 = 0, kb1 = 0;
     bool have = sched.next(t, kb0, kb1);
     const int pre = have ? min(kb1 - kb0, Cfg::kStages) : 0;
-    const int c_first = (t / m_tiles) * BLOCK_C;
+    int mt = 0, nt = 0;
+    tile_coords(t, m_tiles, n_tiles, kRasterGroupTok, mt, nt);
+    const int c_first = nt * BLOCK_C;
     for (int i = 0; i < pre; ++i) {
       uint8_t* st = smem + i * Cfg::kStageBytes;
       mbar_expect_tx(&full_bar[i], Cfg::kStageBytes);
@@ -404,7 +422,8 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     pdl_wait();                                 // x and out belong to predecessors
     int it = 0;                                 // running K-block counter across tiles: the ring never drains
     while (have) {
-      const int r0 = (t % m_tiles) * kBlockR, c0 = (t / m_tiles) * BLOCK_C;
+      tile_coords(t, m_tiles, n_tiles, kRasterGroupTok, mt, nt);
+      const int r0 = mt * kBlockR, c0 = nt * BLOCK_C;
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % Cfg::kStages;
         uint8_t* st = smem + s * Cfg::kStageBytes;
@@ -463,8 +482,10 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     int t = 0, kb0 = 0, kb1 = 0;
     for (int n = 0; sched.next(t, kb0, kb1); ++n) {
       const int buf = n & 1;
-      const int r = (t % m_tiles) * kBlockR + quad * 32 + lane;
-      const int c0 = (t / m_tiles) * BLOCK_C;
+      int mt = 0, nt = 0;
+      tile_coords(t, m_tiles, n_tiles, kRasterGroupTok, mt, nt);
+      const int r = mt * kBlockR + quad * 32 + lane;
+      const int c0 = nt * BLOCK_C;
       const bool ok = mbar_wait(&acc_full[buf], (n >> 1) & 1, status);
       tcgen05_fence_after();
       const bool whole = kb0 == 0 && kb1 == num_kb;       // false only under stream-K
@@ -509,7 +530,7 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
           int token = 0x7fffffff;
           if (live && best.i != 0x7fffffff) token = sample_group_token(bestv, best.i, inv_t, greedy, static_cast<uint32_t>(r), step, k0, k1);
           if (live) {
-            const size_t slot = static_cast<size_t>(r) * samp.n_tiles + t / m_tiles;
+            const size_t slot = static_cast<size_t>(r) * samp.n_tiles + nt;
             samp.part_v[slot] = best.v;
             samp.part_i[slot] = token;
           }
@@ -631,7 +652,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     int t = 0, kb0 = 0, kb1 = 0;
     bool have = sched.next(t, kb0, kb1);
     const int pre = have ? min(kb1 - kb0, Cfg::kStages) : 0;
-    const int c_first = (t / m_tiles) * Cfg::kBlockN + w_row_rank;
+    int mt = 0, nt = 0;
+    tile_coords(t, m_tiles, n_tiles, kRasterGroupPair, mt, nt);
+    const int c_first = nt * Cfg::kBlockN + w_row_rank;
     for (int i = 0; i < pre; ++i) {                    // weights do not depend on the predecessor kernel
       if (rank == 0) mbar_expect_tx(&full_bar[i], 2 * Cfg::kStageBytes);
       tma_load_2d_pair(smem + i * Cfg::kStageBytes + Cfg::kHalfBytes, &tm_w, dsmem_addr(smem_u32(&full_bar[i]), 0), (kb0 + i) * kBlockK, c_first);
@@ -639,7 +662,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     pdl_wait();
     int it = 0;
     while (have) {
-      const int r0 = (t % m_tiles) * 2 * kBlockR + rank * kBlockR, c0 = (t / m_tiles) * Cfg::kBlockN + w_row_rank;
+      tile_coords(t, m_tiles, n_tiles, kRasterGroupPair, mt, nt);
+      const int r0 = mt * 2 * kBlockR + rank * kBlockR, c0 = nt * Cfg::kBlockN + w_row_rank;
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % Cfg::kStages;
         uint8_t* st = smem + s * Cfg::kStageBytes;
@@ -695,8 +719,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     int t = 0, kb0 = 0, kb1 = 0;
     for (int n = 0; sched.next(t, kb0, kb1); ++n) {
       const int buf = n & 1;
-      const int r = (t % m_tiles) * 2 * kBlockR + rank * kBlockR + quad * 32 + lane;
-      const int c0 = (t / m_tiles) * Cfg::kBlockN;
+      int mt = 0, nt = 0;
+      tile_coords(t, m_tiles, n_tiles, kRasterGroupPair, mt, nt);
+      const int r = mt * 2 * kBlockR + rank * kBlockR + quad * 32 + lane;
+      const int c0 = nt * Cfg::kBlockN;
       const bool ok = mbar_wait(&acc_full[buf], (n >> 1) & 1, status);
       tcgen05_fence_after();
       const bool whole = kb0 == 0 && kb1 == num_kb;
@@ -1249,6 +1275,15 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
   // the next tile (measured 58-91 us vs 60-182 us for 8..256 tokens x 151936 x 1024; cuBLAS 55-83 us).
   const int sms = device_sm_count();
   const bool wide = (n_out + kBlockR - 1) / kBlockR >= 2 * sms && epi == kEpiStore && push.size <= 1 && M >= 8;
+  // More than 256 tokens (prefill): the CTA-pair kernel, whose SMs load two thirds of the bytes of the single-CTA kernel
+  // per multiply-add (measured 1.23-1.58 PFLOP/s vs 1.15-1.30 on the 0.6B / 8B layer shapes at 8192 tokens).  Also for
+  // 129..256 tokens of a decode step on a layer with at least ~20 tiles of 256 features (qkv and gate_up of 8B, the
+  // per-rank gate_up / down of 32B over 8 ranks: 25-53 us vs 32-62 us), where one pair tile covers all tokens and the
+  // weights are read once.
+  if (force_mode == 0 && push.size <= 1) {
+    const int pair_tiles = (n_out + (epi == kEpiSiluMul ? 127 : 255)) / (epi == kEpiSiluMul ? 128 : 256);
+    if (M > 256 || (M > 128 && K >= 2048 && pair_tiles >= 20 && !wide)) force_mode = 4;
+  }
   // Many tokens of a decode step (64..256) on a layer with enough output features and a short K: the token-tile
   // kernel with narrow feature tiles (32 or 64) gives ~100-128 CTAs without splitting K, and its epilogue goes
   // straight from tensor memory to global rows (no exchange through shared memory).  Measured on the Qwen3-0.6B
@@ -1280,7 +1315,7 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
     if (force_bc == 128) return launch_tokens<128, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, none, kg);
     return launch_tokens<256, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, none, kg);
   }
-  if (force_mode == 4) {            // CTA-pair kernel (256-token x 256-feature tiles); tune bits 0..7 = K blocks per stream-K unit (0: whole tiles)
+  if (force_mode == 4) {
     if (epi == kEpiSiluMul) return launch_pair<kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, force_splits);
     return launch_pair<kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, force_splits);
   }
@@ -1421,7 +1456,7 @@ extern "C" int forge_gemm_bf16_tp(const void* x, int ldx, const void* w, int ldw
                                   unsigned* epoch, unsigned* status, cudaStream_t stream) {
   if (tp_size < 2 || tp_size > kMaxTp || M <= 0) return -7;
   const TpPush push = make_tp_push(tp_size, tp_rank, nullptr, signal_ptrs, arrive, epoch);
-  return gemm_dispatch(x, ldx, w, ldw, out, ldo, M, n_out, K, kEpiStore, M <= 256 ? 2 : 1, tune, status, stream, push);
+  return gemm_dispatch(x, ldx, w, ldw, out, ldo, M, n_out, K, kEpiStore, M <= 256 ? 2 : 4, M <= 256 ? tune : 0, status, stream, push);
 }
 
 }  // namespace forge
