@@ -108,6 +108,7 @@ struct GemmStreamK {
   float* ws;          // [gridDim.x][2][kSkSlotFloats]: slot 0 = the partial tile at the start of the CTA's range, 1 = at its end
   int* counters;      // [tiles]
   int kgroup;         // K blocks per unit
+  int w_dynamic;      // the weights were written by the kernel launched just before (a dequantised copy): no early prefetch
 };
 constexpr int kSkSlotFloats = 128 * 256;       // one accumulator set: 128 rows x up to 256 columns
 // Element (row, col) of a slot lives at (col / 4) * 512 + row * 4 + col % 4: the 32 rows x 4 columns of a warp's vector
@@ -413,6 +414,7 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     int mt = 0, nt = 0;
     tile_coords(t, m_tiles, n_tiles, kRasterGroupTok, mt, nt);
     const int c_first = nt * BLOCK_C;
+    if (sk.w_dynamic) pdl_wait();
     for (int i = 0; i < pre; ++i) {
       uint8_t* st = smem + i * Cfg::kStageBytes;
       mbar_expect_tx(&full_bar[i], Cfg::kStageBytes);
@@ -655,7 +657,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     int mt = 0, nt = 0;
     tile_coords(t, m_tiles, n_tiles, kRasterGroupPair, mt, nt);
     const int c_first = nt * Cfg::kBlockN + w_row_rank;
-    for (int i = 0; i < pre; ++i) {                    // weights do not depend on the predecessor kernel
+    if (sk.w_dynamic) pdl_wait();
+    for (int i = 0; i < pre; ++i) {                    // weights do not depend on the predecessor kernel (unless w_dynamic)
       if (rank == 0) mbar_expect_tx(&full_bar[i], 2 * Cfg::kStageBytes);
       tma_load_2d_pair(smem + i * Cfg::kStageBytes + Cfg::kHalfBytes, &tm_w, dsmem_addr(smem_u32(&full_bar[i]), 0), (kb0 + i) * kBlockK, c_first);
     }
@@ -1158,7 +1161,7 @@ static const StreamKWorkspace* streamk_workspace() {
 template <int BLOCK_C, int kEpi>
 static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int ldw, __nv_bfloat16* out, int ldo, int M,
                          int n_out, int K, unsigned* status, cudaStream_t stream, const TpPush& push, const GemmFuse& fuse,
-                         const GemmSample& samp = GemmSample{}, int kgroup = 0) {
+                         const GemmSample& samp = GemmSample{}, int kgroup = 0, int w_dynamic = 0) {
   using Cfg = TokCfg<BLOCK_C, kEpi>;
   CUtensorMap tm_x, tm_w;
   if (forge_make_tmap_2d(&tm_x, x, M, K, ldx, kBlockR, 2) != 0) return -2;
@@ -1168,7 +1171,7 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
   const int tiles = ((M + kBlockR - 1) / kBlockR) * ((n_out + BLOCK_C - 1) / BLOCK_C);
   const int num_sms = device_sm_count();
   int ctas = tiles < num_sms ? tiles : num_sms;
-  GemmStreamK sk = {nullptr, nullptr, 0};
+  GemmStreamK sk = {nullptr, nullptr, 0, w_dynamic};
   if (kgroup > 0 && BLOCK_C >= 32 && kEpi != kEpiSample) {
     const StreamKWorkspace* wsp = streamk_workspace();
     const int num_kb = (K + kBlockK - 1) / kBlockK;
@@ -1176,7 +1179,7 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
     const long long units = static_cast<long long>(tiles) * ((num_kb + kgroup - 1) / kgroup);
     const int want = units < num_sms ? static_cast<int>(units) : num_sms;
     if (wsp != nullptr && want <= wsp->ctas && tiles <= wsp->tiles && units > tiles) {
-      sk = GemmStreamK{wsp->ws, wsp->counters, kgroup};
+      sk = GemmStreamK{wsp->ws, wsp->counters, kgroup, w_dynamic};
       ctas = want;
     }
   }
@@ -1187,7 +1190,8 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
 // CTA-pair kernel: grid = 2 x pairs, clusters of 2 along x.  kgroup > 0: stream-K over the pairs.
 template <int kEpi>
 static int launch_pair(const void* x, int ldx, const void* w, int w_rows, int ldw, __nv_bfloat16* out, int ldo, int M, int n_out,
-                       int K, unsigned* status, cudaStream_t stream, const TpPush& push, const GemmFuse& fuse, int kgroup) {
+                       int K, unsigned* status, cudaStream_t stream, const TpPush& push, const GemmFuse& fuse, int kgroup,
+                       int w_dynamic = 0) {
   using Cfg = PairCfg<kEpi>;
   CUtensorMap tm_x, tm_w;
   if (forge_make_tmap_2d(&tm_x, x, M, K, ldx, kBlockR, 2) != 0) return -2;
@@ -1197,7 +1201,7 @@ static int launch_pair(const void* x, int ldx, const void* w, int w_rows, int ld
   const int tiles = ((M + 2 * kBlockR - 1) / (2 * kBlockR)) * ((n_out + Cfg::kBlockN - 1) / Cfg::kBlockN);
   const int max_pairs = device_sm_count() / 2;
   int pairs = tiles < max_pairs ? tiles : max_pairs;
-  GemmStreamK sk = {nullptr, nullptr, 0};
+  GemmStreamK sk = {nullptr, nullptr, 0, w_dynamic};
   if (kgroup > 0) {
     const StreamKWorkspace* wsp = streamk_workspace();
     const int num_kb = (K + kBlockK - 1) / kBlockK;
@@ -1205,7 +1209,7 @@ static int launch_pair(const void* x, int ldx, const void* w, int w_rows, int ld
     const long long units = static_cast<long long>(tiles) * ((num_kb + kgroup - 1) / kgroup);
     const int want = units < max_pairs ? static_cast<int>(units) : max_pairs;
     if (wsp != nullptr && 2 * want <= wsp->ctas && 2 * tiles <= wsp->tiles && units > tiles) {
-      sk = GemmStreamK{wsp->ws, wsp->counters, kgroup};
+      sk = GemmStreamK{wsp->ws, wsp->counters, kgroup, w_dynamic};
       pairs = want;
     }
   }
@@ -1256,7 +1260,8 @@ static int launch_weights(const void* x, int ldx, const void* w, int w_rows, int
 // (gate rows then up rows) and out = silu(gate) * up.  Requirements: K % 8 == 0, x/w 16-byte aligned,
 // ldx/ldw % 8 == 0.  force_mode: 0 auto, 1 token-tile kernel, 2 weight-tile (decode) kernel (needs M <= 256).
 // tune: 0 auto; else bits 0..7 = cluster size (K splits), bits 8..15 = token tile (16/32/64/128) of the decode
-// kernel, bits 16..23 = ring depth (1 = two CTAs per SM, 2 = deep ring); each may be 0 = choose.  Returns 0 on success.
+// kernel, bits 16..23 = ring depth (1 = two CTAs per SM, 2 = deep ring); each may be 0 = choose; bit 24 = W was written by
+// the kernel launched just before (more than 256 tokens only).  Returns 0 on success.
 TpPush make_tp_push(int tp_size, int tp_rank, const long long* slot_ptrs, const long long* signal_ptrs, unsigned* arrive,
                     unsigned* epoch);
 
@@ -1264,6 +1269,7 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
                          int force_mode, int tune, unsigned* status, cudaStream_t stream, const TpPush& push,
                          const GemmFuse& fuse = GemmFuse{}) {
   const int force_splits = tune & 0xff, force_deep = (tune >> 16) & 0xff;
+  const int w_dynamic = (tune >> 24) & 1;        // W is the output of the preceding kernel: only the many-token kernels take that
   int force_bc = (tune >> 8) & 0xff;
   if (M <= 0 || n_out <= 0 || K <= 0) return 0;
   if ((K & 7) || (ldx & 7) || (ldw & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
@@ -1280,6 +1286,7 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
   // 129..256 tokens of a decode step on a layer with at least ~20 tiles of 256 features (qkv and gate_up of 8B, the
   // per-rank gate_up / down of 32B over 8 ranks: 25-53 us vs 32-62 us), where one pair tile covers all tokens and the
   // weights are read once.
+  if (w_dynamic && (force_mode == 0 || force_mode == 2)) force_mode = 4;      // the only kernels that wait before reading W
   if (force_mode == 0 && push.size <= 1) {
     const int pair_tiles = (n_out + (epi == kEpiSiluMul ? 127 : 255)) / (epi == kEpiSiluMul ? 128 : 256);
     if (M > 256 || (M > 128 && K >= 2048 && pair_tiles >= 20 && !wide)) force_mode = 4;
@@ -1300,8 +1307,11 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
   if (narrow) {
     force_mode = 1;
     force_bc = narrow;
-  } else if (force_mode == 0 && epi == kEpiSiluMul && K >= 4096 && M > 64 && M <= 256 && push.size <= 1) {
-    force_mode = 1;     // a large gated MLP (8B and up) is compute-heavy already at ~100 tokens: full 128 x (128 + 128) tiles
+  } else if (force_mode == 0 && epi == kEpiSiluMul && K >= 4096 && M <= 256 && push.size <= 1 &&
+             (M > 64 || (M > 24 && (n_out + kBlockR - 1) / kBlockR >= 64))) {
+    // a large gated MLP (8B and up) is compute-heavy already at ~100 tokens: full 128 x (128 + 128) tiles; with 64 or
+    // more such tiles (8B on one GPU: 96) the persistent kernel also streams best from ~32 tokens (39.5 vs 48 us at 64)
+    force_mode = 1;
   }
   if (force_mode == 3) {            // token-tile kernel with stream-K: tune bits 0..7 = K blocks per unit, bits 8..15 = feature tile
     const int kg = force_splits > 0 ? force_splits : 4;
@@ -1316,9 +1326,10 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
     return launch_tokens<256, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, none, kg);
   }
   if (force_mode == 4) {
-    if (epi == kEpiSiluMul) return launch_pair<kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, force_splits);
-    return launch_pair<kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, force_splits);
+    if (epi == kEpiSiluMul) return launch_pair<kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, force_splits, w_dynamic);
+    return launch_pair<kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, force_splits, w_dynamic);
   }
+  if (w_dynamic) return -8;
   const bool decode = force_mode == 2 || (force_mode == 0 && M <= 256 && !wide);
   if (decode) {
     if (M > 256) return -7;
@@ -1456,7 +1467,7 @@ extern "C" int forge_gemm_bf16_tp(const void* x, int ldx, const void* w, int ldw
                                   unsigned* epoch, unsigned* status, cudaStream_t stream) {
   if (tp_size < 2 || tp_size > kMaxTp || M <= 0) return -7;
   const TpPush push = make_tp_push(tp_size, tp_rank, nullptr, signal_ptrs, arrive, epoch);
-  return gemm_dispatch(x, ldx, w, ldw, out, ldo, M, n_out, K, kEpiStore, M <= 256 ? 2 : 4, M <= 256 ? tune : 0, status, stream, push);
+  return gemm_dispatch(x, ldx, w, ldw, out, ldo, M, n_out, K, kEpiStore, M <= 256 ? 2 : 4, M <= 256 ? tune : (tune & (1 << 24)), status, stream, push);
 }
 
 }  // namespace forge

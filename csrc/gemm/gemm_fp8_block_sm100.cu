@@ -225,6 +225,46 @@ extern "C" int forge_quant_fp8_1x128(const void* x, void* xq, float* scale, int 
                        static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(xq), scale, M, K, scale_ld) == cudaSuccess ? 0 : -2;
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Weight dequantiser: e4m3 [N, K] with 128 x 128 block scales -> bf16 [N, K].  With many tokens (prefill) the GEMM is
+// bound by the tensor cores, not by the weight bytes: the layer's weights are expanded once per call into a scratch
+// buffer (3 bytes of traffic per weight, a few per cent of the GEMM's time from ~1000 tokens) and the bf16 CTA-pair
+// kernel does the multiplication with the activations left in bf16.  16 weights per thread.
+// ---------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) dequant_fp8_block_kernel(const uint8_t* __restrict__ wq, const float* __restrict__ scale,
+                                                                __nv_bfloat16* __restrict__ out, int N, int K) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int per_row = K >> 4;
+  const long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  if (i >= static_cast<long long>(N) * per_row) return;
+  const int n = static_cast<int>(i / per_row), k0 = static_cast<int>(i % per_row) << 4;
+  const float s = scale[static_cast<size_t>(n >> 7) * (K >> 7) + (k0 >> 7)];
+  const uint4 raw = *reinterpret_cast<const uint4*>(wq + static_cast<size_t>(n) * K + k0);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint32_t o[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>((w[j] >> (16 * h)) & 0xffffu), __NV_E4M3);
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+      o[2 * j + h] = pack_bf16x2(f.x * s, f.y * s);
+    }
+  }
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(n) * K + k0);
+  dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+  dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+extern "C" int forge_dequant_fp8_block(const void* wq, const float* scale, void* out, int N, int K, cudaStream_t stream) {
+  if (N <= 0) return 0;
+  if (K & 127) return -1;
+  const long long threads = static_cast<long long>(N) * (K >> 4);
+  return launch_kernel(dequant_fp8_block_kernel, dim3(static_cast<unsigned>((threads + 255) / 256)), dim3(256), 0, stream, 0,
+                       static_cast<const uint8_t*>(wq), scale, static_cast<__nv_bfloat16*>(out), N, K) == cudaSuccess ? 0 : -2;
+}
+
 template <int BLOCK_C>
 static int launch_f8(const void* xq, const float* xs, int xs_ld, const void* wq, const float* ws, void* out, int ldo, int M, int N,
                      int K, int splits, float* partial, unsigned* status, cudaStream_t stream) {

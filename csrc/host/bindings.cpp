@@ -20,6 +20,7 @@ int forge_gemm_set_trace(unsigned long long* buf);
 int forge_gemm_set_streamk_workspace(float* ws, int* counters, int ctas, int tiles);
 long long forge_gemm_streamk_workspace_floats(int ctas);
 int forge_quant_fp8_1x128(const void* x, void* xq, float* scale, int M, int K, int scale_ld, cudaStream_t stream);
+int forge_dequant_fp8_block(const void* wq, const float* scale, void* out, int N, int K, cudaStream_t stream);
 int forge_gemm_fp8_splits(int M, int N, int K);
 int forge_gemm_fp8_block(const void* xq, const float* xs, int xs_ld, const void* wq, const float* ws, void* out, int ldo, int M,
                          int N, int K, float* partial, unsigned* status, cudaStream_t stream);
@@ -629,6 +630,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_sample", &gemm_sample);
   m.def("gemm_set_trace", &gemm_set_trace);
   m.def("quant_fp8", &quant_fp8);
+  m.def("dequant_fp8_block", [](const Tensor& wq, const Tensor& scale, Tensor& out) {
+    // e4m3 weights [N, K] with fp32 scales [ceil(N / 128), K / 128] -> bf16 [N, K]
+    TORCH_CHECK(wq.is_cuda() && wq.dim() == 2 && wq.element_size() == 1 && wq.is_contiguous(), "dequant_fp8_block: wq must be a contiguous 1-byte [N, K] CUDA tensor");
+    const int64_t N = wq.size(0), K = wq.size(1);
+    TORCH_CHECK(K % 128 == 0 && scale.scalar_type() == torch::kFloat32 && scale.is_contiguous() && scale.numel() == ((N + 127) / 128) * (K / 128),
+                "dequant_fp8_block: scale must be fp32 [ceil(N / 128), K / 128]");
+    TORCH_CHECK(out.scalar_type() == torch::kBFloat16 && out.is_contiguous() && out.numel() >= N * K, "dequant_fp8_block: out must hold N * K bf16 values");
+    check(forge_dequant_fp8_block(wq.data_ptr(), scale.data_ptr<float>(), out.data_ptr(), static_cast<int>(N), static_cast<int>(K),
+                                  stream_of(wq)), "forge_dequant_fp8_block");
+  });
   m.def("gemm_fp8_block", &gemm_fp8_block);
   m.def("gemm_fp8_splits", &gemm_fp8_splits);
   m.def("gemm_tp", &gemm_tp);

@@ -134,7 +134,7 @@ def test_gemm_fp8_block_scaled(ops, M, N, K):
     q_ref, s_ref = quantize_activations_ref(x)
     assert torch.allclose(xs[:, :M], s_ref, rtol=1e-6)
     assert (xq.view(torch.float8_e4m3fn).float() - q_ref.float()).abs().max() <= 32          # at most one e4m3 step at the top of the range
-    out = ops.linear(x, wq)
+    out = ops.linear_fp8(x, wq)            # the e4m3 kernel itself (ops.linear expands the weight to bf16 for many tokens)
     # the GEMM itself, checked on exactly the operands it saw: the CUDA-quantised activations, dequantised in fp32
     xd = xq.view(torch.float8_e4m3fn).float().view(M, K // 128, 128) * xs[:, :M].t()[..., None]
     _close(out, xd.view(M, K) @ wq.dequantize().t(), atol=2e-2, rtol=2e-2)
@@ -276,6 +276,27 @@ def test_gemm_cta_pair_kernel_with_the_fused_epilogues(ops, M, N, K, kg):
     got = ops.linear_scaled(x, w, ssq_in, 1e-6, force_mode=4, tune=kg)
     xn = x.float() * torch.rsqrt((x.float() ** 2).mean(-1, keepdim=True) + 1e-6)
     _close(got, xn @ w.float().t(), atol=3e-2, rtol=3e-2)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("M,N,K,silu", [(600, 1280, 1024, False), (2048, 3200, 5120, True), (1000, 5120, 3200, False)])
+def test_fp8_weights_with_many_tokens_are_expanded_and_multiplied_in_bf16(ops, M, N, K, silu):
+    """Prefill-sized GEMM on a block-scaled e4m3 weight: the weight is expanded to bf16 (exactly: e4m3 x scale rounded to
+    bf16) right before the bf16 GEMM, which must not read it early; activations are not quantised."""
+    from tinyllmforge_b200.ops.quant import Fp8BlockWeight
+    torch.manual_seed(N + K)
+    w = _rand(2 * N if silu else N, K, scale=0.05)
+    wq = Fp8BlockWeight.quantize(w)
+    wd = wq.dequantize()
+    assert torch.equal(ops._expand_fp8(wq), wd.to(BF))
+    for seed in range(3):                              # the scratch buffer is overwritten between calls
+        x = _rand(M, K)
+        got = (ops.linear_silu_mul if silu else ops.linear)(x, wq)
+        ref_ = x.float() @ wd.to(BF).float().t()
+        want = torch.nn.functional.silu(ref_[:, :N]) * ref_[:, N:] if silu else ref_
+        _close(got, want, atol=2e-2, rtol=2e-2)
+        other = Fp8BlockWeight.quantize(_rand(2 * N if silu else N, K, scale=0.05))
+        ops._expand_fp8(other)
     ops.check_status()
 
 

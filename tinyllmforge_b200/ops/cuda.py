@@ -57,6 +57,8 @@ def decode_group_slice(group: int) -> int:
     return 1
 
 
+W_DYNAMIC = 1 << 8              # in the ring-depth byte of the GEMM's tuning word (bit 24): W comes from the preceding kernel
+FP8_EXPAND_MIN_ROWS = 128       # more rows than this: expand fp8 weights to bf16 and run the bf16 GEMM (see CudaOps._expand_fp8)
 _STREAMK_WS: dict = {}
 
 
@@ -95,6 +97,8 @@ class CudaOps:
         self.sample_in_lm_head = os.environ.get("FORGE_LM_HEAD_SAMPLE", "1") != "0"
         self._flat_scratch = torch.empty(2 * self.num_sms * (2 * 4 * 130 + 2) + 64, dtype=torch.float32, device=self.device)
         _streamk_workspace(self.C, self.device, self.num_sms)
+        self._fp8_scratch = None                   # bf16 expansion of one fp8 weight (see _expand_fp8)
+        self._fp8_retired = []
 
     # ------------------------------------------------------------------ status word
     def check_status(self) -> None:
@@ -115,7 +119,9 @@ class CudaOps:
         """x @ w.T.  ``w`` must not be the output of the kernel launched just before this call: the decode
         kernel starts streaming weights before it waits for its predecessor (weights are static in the engine)."""
         if isinstance(w, Fp8BlockWeight):
-            return self.linear_fp8(x, w)
+            if x.shape[0] <= FP8_EXPAND_MIN_ROWS:
+                return self.linear_fp8(x, w)
+            w, force_deep = self._expand_fp8(w), force_deep | W_DYNAMIC
         out = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
         self.C.gemm(x, w, out, 0, force_mode, force_splits | (force_block_c << 8) | (force_deep << 16), self.status)
         self.launches += 1
@@ -124,7 +130,9 @@ class CudaOps:
     def linear_silu_mul(self, x: torch.Tensor, w_gate_up: torch.Tensor, force_mode: int = 0, force_splits: int = 0,
                         force_block_c: int = 0, force_deep: int = 0) -> torch.Tensor:
         if isinstance(w_gate_up, Fp8BlockWeight):
-            return self.silu_mul(self.linear_fp8(x, w_gate_up))
+            if x.shape[0] <= FP8_EXPAND_MIN_ROWS:
+                return self.silu_mul(self.linear_fp8(x, w_gate_up))
+            w_gate_up, force_deep = self._expand_fp8(w_gate_up), force_deep | W_DYNAMIC
         out = torch.empty(x.shape[0], w_gate_up.shape[0] // 2, dtype=x.dtype, device=x.device)
         self.C.gemm(x, w_gate_up, out, 1, force_mode, force_splits | (force_block_c << 8) | (force_deep << 16), self.status)
         self.launches += 1
@@ -159,6 +167,21 @@ class CudaOps:
         [tokens, ceil(H / 128)]) receives the sums of squares of the new residual rows, one per 128 features."""
         self.C.gemm_fused(x, w, residual, 0, force_mode, tune, None, 0.0, True, ssq_out, self.status)
         self.launches += 1
+
+    def _expand_fp8(self, w: "Fp8BlockWeight") -> torch.Tensor:
+        """bf16 copy of a block-scaled e4m3 weight in a scratch buffer that the next expansion overwrites (stream-ordered:
+        the GEMM that reads it is launched before the next expansion).  For GEMMs with many tokens, whose time is set by
+        the tensor cores: the weights stay e4m3 in memory, the activations stay bf16, and the bf16 CTA-pair kernel with its
+        fused epilogues does the multiplication; the expansion moves 3 bytes per weight."""
+        N, K = w.shape
+        if self._fp8_scratch is None or self._fp8_scratch.numel() < N * K:
+            if self._fp8_scratch is not None:
+                self._fp8_retired.append(self._fp8_scratch)      # CUDA graphs captured so far keep using the smaller buffer
+            self._fp8_scratch = torch.empty(N * K, dtype=torch.bfloat16, device=self.device)
+        out = self._fp8_scratch[:N * K].view(N, K)
+        self.C.dequant_fp8_block(w.q.view(torch.uint8), w.scale, out)
+        self.launches += 1
+        return out
 
     def linear_fp8(self, x: torch.Tensor, w: "Fp8BlockWeight") -> torch.Tensor:
         """Block-scaled fp8 GEMM: quantise activations per token and 128 features, multiply on the e4m3 tensor-core
@@ -383,9 +406,11 @@ class CudaOps:
                                          f.timeout_ns, f.local_only, residual, residual, norm_weight, y, eps, self.status)
             self.launches += 2
             return y, residual
-        if isinstance(layer.weight, Fp8BlockWeight):
+        if isinstance(layer.weight, Fp8BlockWeight) and M <= FP8_EXPAND_MIN_ROWS:
             # the block-scaled GEMM has no signalling epilogue: publish its output with a copy kernel
             self.C.tp_rows_publish(self.linear_fp8(x, layer.weight), st.local_buf, tp.rank, st.signal_ptrs, st.arrive, st.epoch)
+        elif isinstance(layer.weight, Fp8BlockWeight):
+            self.C.gemm_tp(x, self._expand_fp8(layer.weight), st.local_buf, W_DYNAMIC << 16, tp.rank, st.signal_ptrs, st.arrive, st.epoch, self.status)
         else:
             self.C.gemm_tp(x, layer.weight, st.local_buf, 0, tp.rank, st.signal_ptrs, st.arrive, st.epoch, self.status)
         self.launches += 1
