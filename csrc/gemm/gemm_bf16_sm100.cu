@@ -109,6 +109,7 @@ struct GemmStreamK {
   int* counters;      // [tiles]
   int kgroup;         // K blocks per unit
   int w_dynamic;      // the weights were written by the kernel launched just before (a dequantised copy): no early prefetch
+  int defer;          // partial tiles are only written; gemm_splitk_finish_kernel adds them up and runs the epilogue
 };
 constexpr int kSkSlotFloats = 128 * 256;       // one accumulator set: 128 rows x up to 256 columns
 // Element (row, col) of a slot lives at (col / 4) * 512 + row * 4 + col % 4: the 32 rows x 4 columns of a warp's vector
@@ -550,7 +551,7 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
             released = true;
-            tile = sk_arrive(sk, t, sk_flag, warp == 2 && lane == 0, t, num_tiles, sched.num_kg, gridDim.x, 1, 0);
+            if (!sk.defer) tile = sk_arrive(sk, t, sk_flag, warp == 2 && lane == 0, t, num_tiles, sched.num_kg, gridDim.x, 1, 0);
           }
         }
         if (ok && (whole || tile.n > 0))
@@ -741,7 +742,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(leader_empty);
         released = true;
-        tile = sk_arrive(sk, t * 2 + rank, sk_flag, warp == 2 && lane == 0, t, num_tiles, sched.num_kg, pairs, 2, rank);
+        if (!sk.defer) tile = sk_arrive(sk, t * 2 + rank, sk_flag, warp == 2 && lane == 0, t, num_tiles, sched.num_kg, pairs, 2, rank);
       }
       if (ok && (whole || tile.n > 0))
         tile_epilogue<Cfg::kBlockN, kEpi>(tacc, whole, tile, sk.ws, quad * 32 + lane, r, c0, m_total, n_total, out, ldo, fuse);
@@ -763,6 +764,111 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   if (warp == 1) {
     tcgen05_fence_after();
     tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// =========================================================================================================
+// split-K in two kernels: partial tiles from the GEMM, sums + epilogue from all SMs
+// =========================================================================================================
+// With K split S ways and exactly one (tile, K range) per CTA (or CTA pair) the GEMM kernels above only write their fp32
+// partial tiles (GemmStreamK::defer).  This kernel adds the S partial tiles of every output element in the order of the K
+// ranges and applies the same epilogues (row scale, SiLU * up, residual add + sums of squares).  One CTA adding four
+// 128 x 256 partial tiles through its own L2 port takes ~5 us; spread over all SMs the same bytes take ~1 us.
+//
+// Block = 1024 threads = 32 rows (lane) x 32 groups of 4 columns (warp): 32 rows x 128 output columns.  Reads follow the
+// slot layout (a warp reads 512 contiguous bytes per partial tile).  Grid: (tile row blocks of 32 live rows, 128-column
+// parts of the tile, tiles).
+struct SplitKFinish {
+  const float* ws;
+  int num_tiles, m_tiles, n_tiles, num_kg, workers;
+  int pair;             // 1: partial tiles come from CTA pairs (256-row tiles, scratch owner = 2 * worker + row half)
+  int block_n;          // output columns per tile (SiLU: 128 of the 256 accumulator columns are up features)
+  int raster_group;
+};
+
+template <int kEpi>
+__global__ void __launch_bounds__(1024) gemm_splitk_finish_kernel(const SplitKFinish p, __nv_bfloat16* __restrict__ out, int ldo,
+                                                                 int m_total, int n_total, const GemmFuse fuse) {
+  __shared__ float s_ssq[32][33];
+  __shared__ float s_scale[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, cg = threadIdx.x >> 5;
+  const int t = blockIdx.z;
+  int mt = 0, nt = 0;
+  tile_coords(t, p.m_tiles, p.n_tiles, p.raster_group, mt, nt);
+  const int tile_rows = p.pair ? 2 * kBlockR : kBlockR;
+  const int row_in_tile = blockIdx.x * 32 + lane;
+  const int r = mt * tile_rows + row_in_tile;
+  if (mt * tile_rows + blockIdx.x * 32 >= m_total) return;                 // no live row in this block (uniform)
+  const int half = row_in_tile >> 7, row_in_slot = row_in_tile & 127;       // which CTA of a pair owns the row
+  const int col_in_tile = blockIdx.y * 128 + cg * 4;                        // output column of this thread's group of four
+  const int c = nt * p.block_n + col_in_tile;
+  if (cg == 0) s_scale[lane] = fuse_row_scale(fuse, r, m_total);
+  // the tile's K ranges belong to workers first .. first + n - 1 (the arithmetic of TokSched / sk_arrive)
+  const long long U = static_cast<long long>(p.num_tiles) * p.num_kg, G = p.workers;
+  const long long a = static_cast<long long>(t) * p.num_kg;
+  const int first = static_cast<int>(((a + 1) * G + U - 1) / U) - 1;
+  const int n = static_cast<int>(((a + p.num_kg) * G + U - 1) / U) - first;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f}, up[4] = {0.f, 0.f, 0.f, 0.f};
+  const bool live = r < m_total && col_in_tile < p.block_n && c < n_total;
+  if (live) {
+    for (int i = 0; i < n; ++i) {
+      const int w = first + i;
+      const long long u0 = U * w / G;
+      const int owner = p.pair ? 2 * w + half : w;
+      const float* slot = p.ws + (static_cast<size_t>(owner) * 2 + (u0 >= a ? 0 : 1)) * kSkSlotFloats + row_in_slot * 4;
+      const float4 v = __ldcg(reinterpret_cast<const float4*>(slot + (col_in_tile >> 2) * 512));
+      acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+      if constexpr (kEpi == kEpiSiluMul) {
+        const float4 g = __ldcg(reinterpret_cast<const float4*>(slot + ((col_in_tile + p.block_n) >> 2) * 512));
+        up[0] += g.x; up[1] += g.y; up[2] += g.z; up[3] += g.w;
+      }
+    }
+  }
+  __syncthreads();
+  const float row_scale = s_scale[lane];
+  float ssq = 0.f;
+  if (live) {
+    float f[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      f[j] = acc[j] * row_scale;
+      if constexpr (kEpi == kEpiSiluMul) f[j] = silu(f[j]) * (up[j] * row_scale);
+    }
+    __nv_bfloat16* dst = out + static_cast<size_t>(r) * ldo + c;
+    if (c + 4 <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0)) {
+      if (fuse.add_residual) {
+        const uint2 old = *reinterpret_cast<const uint2*>(dst);
+        f[0] = bf16_round_g(bf16_round_g(f[0]) + bf16_lo(old.x));
+        f[1] = bf16_round_g(bf16_round_g(f[1]) + bf16_hi(old.x));
+        f[2] = bf16_round_g(bf16_round_g(f[2]) + bf16_lo(old.y));
+        f[3] = bf16_round_g(bf16_round_g(f[3]) + bf16_hi(old.y));
+        ssq = (f[0] * f[0] + f[1] * f[1]) + (f[2] * f[2] + f[3] * f[3]);
+      }
+      *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (c + j < n_total) {
+          float val = f[j];
+          if (fuse.add_residual) {
+            val = bf16_round_g(bf16_round_g(val) + __bfloat162float(dst[j]));
+            ssq += val * val;
+          }
+          dst[j] = __float2bfloat16_rn(val);
+        }
+    }
+  }
+  if (fuse.out_ssq != nullptr) {            // sums of squares of the 128 columns of this block, added in column order
+    s_ssq[cg][lane] = ssq;
+    __syncthreads();
+    if (cg == 0 && r < m_total && nt * p.block_n + blockIdx.y * 128 < n_total) {
+      float tot = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) tot += s_ssq[i][lane];
+      fuse.out_ssq[static_cast<size_t>(r) * fuse.out_parts + ((nt * p.block_n + blockIdx.y * 128) >> 7)] = tot;
+    }
   }
 }
 
@@ -1157,29 +1263,57 @@ static const StreamKWorkspace* streamk_workspace() {
   return g_sk_workspace[dev].ws != nullptr ? &g_sk_workspace[dev] : nullptr;
 }
 
-// kgroup > 0: stream-K with units of `kgroup` K blocks (needs the device's workspace; falls back to whole tiles without it)
+// Launches the reduce + epilogue kernel behind a GEMM that only wrote partial tiles.
+template <int kEpi>
+static int launch_finish(const GemmStreamK& sk, int tiles, int m_tiles, int n_tiles, int num_kg, int workers, int pair, int block_n,
+                         int raster_group, __nv_bfloat16* out, int ldo, int M, int n_out, const GemmFuse& fuse, cudaStream_t stream) {
+  SplitKFinish p = {sk.ws, tiles, m_tiles, n_tiles, num_kg, workers, pair, block_n, raster_group};
+  const int tile_rows = pair ? 2 * kBlockR : kBlockR;
+  const int live_rows = M < tile_rows ? M : tile_rows;
+  dim3 grid((live_rows + 31) / 32, (block_n + 127) / 128, tiles);
+  return launch_kernel(gemm_splitk_finish_kernel<kEpi>, grid, dim3(1024), 0, stream, 0, p, out, ldo, M, n_out, fuse) == cudaSuccess ? 0 : -5;
+}
+
+// kgroup > 0: stream-K with units of `kgroup` K blocks (needs the device's workspace; falls back to whole tiles without it).
+// defer_splits > 1: K split that many ways, one (tile, K range) per CTA, sums and epilogue by gemm_splitk_finish_kernel.
 template <int BLOCK_C, int kEpi>
 static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int ldw, __nv_bfloat16* out, int ldo, int M,
                          int n_out, int K, unsigned* status, cudaStream_t stream, const TpPush& push, const GemmFuse& fuse,
-                         const GemmSample& samp = GemmSample{}, int kgroup = 0, int w_dynamic = 0) {
+                         const GemmSample& samp = GemmSample{}, int kgroup = 0, int w_dynamic = 0, int defer_splits = 0) {
   using Cfg = TokCfg<BLOCK_C, kEpi>;
   CUtensorMap tm_x, tm_w;
   if (forge_make_tmap_2d(&tm_x, x, M, K, ldx, kBlockR, 2) != 0) return -2;
   if (forge_make_tmap_2d(&tm_w, w, w_rows, K, ldw, BLOCK_C, 2) != 0) return -3;
   auto kern = gemm_tokens_kernel<BLOCK_C, kEpi>;
   FORGE_ENSURE_DYN_SMEM(kern, Cfg::kSmemBytes);
-  const int tiles = ((M + kBlockR - 1) / kBlockR) * ((n_out + BLOCK_C - 1) / BLOCK_C);
+  const int m_tiles = (M + kBlockR - 1) / kBlockR, n_tiles = (n_out + BLOCK_C - 1) / BLOCK_C;
+  const int tiles = m_tiles * n_tiles;
   const int num_sms = device_sm_count();
+  const int num_kb = (K + kBlockK - 1) / kBlockK;
   int ctas = tiles < num_sms ? tiles : num_sms;
-  GemmStreamK sk = {nullptr, nullptr, 0, w_dynamic};
+  GemmStreamK sk = {nullptr, nullptr, 0, w_dynamic, 0};
+  const StreamKWorkspace* wsp = streamk_workspace();
+  if constexpr (kEpi != kEpiSample && (BLOCK_C == 128 || BLOCK_C == 256)) {
+    if (defer_splits > 1 && wsp != nullptr && push.size <= 1) {
+      const int kg = (num_kb + defer_splits - 1) / defer_splits;
+      const int num_kg = (num_kb + kg - 1) / kg;
+      const long long units = static_cast<long long>(tiles) * num_kg;
+      if (num_kg > 1 && units <= num_sms && units <= wsp->ctas) {
+        sk = GemmStreamK{wsp->ws, wsp->counters, kg, w_dynamic, 1};
+        if (launch_kernel(kern, dim3(static_cast<unsigned>(units)), dim3(kGemmThreads), Cfg::kSmemBytes, stream, 0, tm_x, tm_w, out, ldo, M,
+                          n_out, K, n_out, status, push, fuse, samp, sk) != cudaSuccess)
+          return -5;
+        return launch_finish<kEpi>(sk, tiles, m_tiles, n_tiles, num_kg, static_cast<int>(units), 0, BLOCK_C, kRasterGroupTok, out, ldo, M,
+                                   n_out, fuse, stream);
+      }
+    }
+  }
   if (kgroup > 0 && BLOCK_C >= 32 && kEpi != kEpiSample) {
-    const StreamKWorkspace* wsp = streamk_workspace();
-    const int num_kb = (K + kBlockK - 1) / kBlockK;
     if (kgroup > num_kb) kgroup = num_kb;
     const long long units = static_cast<long long>(tiles) * ((num_kb + kgroup - 1) / kgroup);
     const int want = units < num_sms ? static_cast<int>(units) : num_sms;
     if (wsp != nullptr && want <= wsp->ctas && tiles <= wsp->tiles && units > tiles) {
-      sk = GemmStreamK{wsp->ws, wsp->counters, kgroup, w_dynamic};
+      sk = GemmStreamK{wsp->ws, wsp->counters, kgroup, w_dynamic, 0};
       ctas = want;
     }
   }
@@ -1187,29 +1321,44 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
                        status, push, fuse, samp, sk) == cudaSuccess ? 0 : -5;
 }
 
-// CTA-pair kernel: grid = 2 x pairs, clusters of 2 along x.  kgroup > 0: stream-K over the pairs.
+// CTA-pair kernel: grid = 2 x pairs, clusters of 2 along x.  kgroup > 0: stream-K over the pairs.  defer_splits > 1: K split
+// that many ways, one (tile, K range) per pair, sums and epilogue by gemm_splitk_finish_kernel.
 template <int kEpi>
 static int launch_pair(const void* x, int ldx, const void* w, int w_rows, int ldw, __nv_bfloat16* out, int ldo, int M, int n_out,
                        int K, unsigned* status, cudaStream_t stream, const TpPush& push, const GemmFuse& fuse, int kgroup,
-                       int w_dynamic = 0) {
+                       int w_dynamic = 0, int defer_splits = 0) {
   using Cfg = PairCfg<kEpi>;
   CUtensorMap tm_x, tm_w;
   if (forge_make_tmap_2d(&tm_x, x, M, K, ldx, kBlockR, 2) != 0) return -2;
   if (forge_make_tmap_2d(&tm_w, w, w_rows, K, ldw, kBlockR, 2) != 0) return -3;
   auto kern = gemm_pair_kernel<kEpi>;
   FORGE_ENSURE_DYN_SMEM(kern, Cfg::kSmemBytes);
-  const int tiles = ((M + 2 * kBlockR - 1) / (2 * kBlockR)) * ((n_out + Cfg::kBlockN - 1) / Cfg::kBlockN);
+  const int m_tiles = (M + 2 * kBlockR - 1) / (2 * kBlockR), n_tiles = (n_out + Cfg::kBlockN - 1) / Cfg::kBlockN;
+  const int tiles = m_tiles * n_tiles;
   const int max_pairs = device_sm_count() / 2;
+  const int num_kb = (K + kBlockK - 1) / kBlockK;
   int pairs = tiles < max_pairs ? tiles : max_pairs;
-  GemmStreamK sk = {nullptr, nullptr, 0, w_dynamic};
+  GemmStreamK sk = {nullptr, nullptr, 0, w_dynamic, 0};
+  const StreamKWorkspace* wsp = streamk_workspace();
+  if (defer_splits > 1 && wsp != nullptr && push.size <= 1) {
+    const int kg = (num_kb + defer_splits - 1) / defer_splits;
+    const int num_kg = (num_kb + kg - 1) / kg;
+    const long long units = static_cast<long long>(tiles) * num_kg;
+    if (num_kg > 1 && units <= max_pairs && 2 * units <= wsp->ctas) {
+      sk = GemmStreamK{wsp->ws, wsp->counters, kg, w_dynamic, 1};
+      if (launch_kernel_cluster_x(kern, dim3(static_cast<unsigned>(2 * units)), dim3(kGemmThreads), Cfg::kSmemBytes, stream, 2, tm_x, tm_w,
+                                  out, ldo, M, n_out, K, n_out, status, push, fuse, sk) != cudaSuccess)
+        return -5;
+      return launch_finish<kEpi>(sk, tiles, m_tiles, n_tiles, num_kg, static_cast<int>(units), 1, Cfg::kBlockN, kRasterGroupPair, out, ldo,
+                                 M, n_out, fuse, stream);
+    }
+  }
   if (kgroup > 0) {
-    const StreamKWorkspace* wsp = streamk_workspace();
-    const int num_kb = (K + kBlockK - 1) / kBlockK;
     if (kgroup > num_kb) kgroup = num_kb;
     const long long units = static_cast<long long>(tiles) * ((num_kb + kgroup - 1) / kgroup);
     const int want = units < max_pairs ? static_cast<int>(units) : max_pairs;
     if (wsp != nullptr && 2 * want <= wsp->ctas && 2 * tiles <= wsp->tiles && units > tiles) {
-      sk = GemmStreamK{wsp->ws, wsp->counters, kgroup, w_dynamic};
+      sk = GemmStreamK{wsp->ws, wsp->counters, kgroup, w_dynamic, 0};
       pairs = want;
     }
   }
@@ -1287,6 +1436,21 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
   // per-rank gate_up / down of 32B over 8 ranks: 25-53 us vs 32-62 us), where one pair tile covers all tokens and the
   // weights are read once.
   if (w_dynamic && (force_mode == 0 || force_mode == 2)) force_mode = 4;      // the only kernels that wait before reading W
+  // Two shapes where K split over otherwise idle SMs plus the reduce kernel wins (measured in CUDA-graph chains): a layer
+  // with few feature tiles and a very long K at 129..256 tokens (8B down_proj: 34 us vs 43), and a mid-sized gated MLP at
+  // 33..128 tokens (the per-rank gate_up of 32B over 8 ranks, 25 tiles: 20-22 us vs 25-36).
+  int defer_splits = 0;
+  if (force_mode == 0 && push.size <= 1 && !wide && !w_dynamic) {
+    const int max_pairs = sms / 2;
+    const int ptiles = (n_out + 255) / 256, stiles = (n_out + kBlockR - 1) / kBlockR;
+    if (epi == kEpiStore && M > 128 && M <= 256 && K >= 8192 && ptiles <= 18 && max_pairs / ptiles >= 2) {
+      force_mode = 5;
+      defer_splits = max_pairs / ptiles < 4 ? max_pairs / ptiles : 4;
+    } else if (epi == kEpiSiluMul && M > 32 && M <= 128 && K >= 4096 && stiles >= 16 && stiles * 4 <= sms) {
+      force_mode = 6;
+      defer_splits = 4;
+    }
+  }
   if (force_mode == 0 && push.size <= 1) {
     const int pair_tiles = (n_out + (epi == kEpiSiluMul ? 127 : 255)) / (epi == kEpiSiluMul ? 128 : 256);
     if (M > 256 || (M > 128 && K >= 2048 && pair_tiles >= 20 && !wide)) force_mode = 4;
@@ -1312,6 +1476,17 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
     // a large gated MLP (8B and up) is compute-heavy already at ~100 tokens: full 128 x (128 + 128) tiles; with 64 or
     // more such tiles (8B on one GPU: 96) the persistent kernel also streams best from ~32 tokens (39.5 vs 48 us at 64)
     force_mode = 1;
+  }
+  if (force_mode == 5 || force_mode == 6) {      // K split `tune & 0xff` ways + reduce kernel: 5 = CTA pairs, 6 = single CTAs
+    const int S = defer_splits > 1 ? defer_splits : (force_splits > 1 ? force_splits : 2);
+    const GemmSample none{};
+    if (force_mode == 5) {
+      if (epi == kEpiSiluMul) return launch_pair<kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, 0, w_dynamic, S);
+      return launch_pair<kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, 0, w_dynamic, S);
+    }
+    if (epi == kEpiSiluMul) return launch_tokens<128, kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, none, 0, w_dynamic, S);
+    if (force_bc == 128) return launch_tokens<128, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, none, 0, w_dynamic, S);
+    return launch_tokens<256, kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, none, 0, w_dynamic, S);
   }
   if (force_mode == 3) {            // token-tile kernel with stream-K: tune bits 0..7 = K blocks per unit, bits 8..15 = feature tile
     const int kg = force_splits > 0 ? force_splits : 4;

@@ -300,6 +300,49 @@ def test_fp8_weights_with_many_tokens_are_expanded_and_multiplied_in_bf16(ops, M
     ops.check_status()
 
 
+@pytest.mark.parametrize("mode", [5, 6])
+@pytest.mark.parametrize("M,N,K,S,silu", [
+    (256, 4096, 4096, 4, False), (64, 6144, 4096, 6, False), (200, 4096, 12288, 4, False), (16, 1280, 5120, 8, False),
+    (100, 5120, 3200, 3, False), (130, 1536, 4096, 4, True), (50, 3200, 5120, 2, True), (7, 136, 4104, 5, False), (300, 1000, 2048, 2, False),
+])
+def test_gemm_split_k_with_reduce_kernel(ops, M, N, K, S, silu, mode):
+    """K split S ways, one (tile, K range) per CTA or CTA pair; a second kernel adds the partial tiles and runs the epilogue."""
+    torch.manual_seed(M + N + K)
+    x, w = _rand(M, K), _rand(2 * N if silu else N, K, scale=0.05)
+    fn = ops.linear_silu_mul if silu else ops.linear
+    out = fn(x, w, force_mode=mode, force_splits=S)
+    ref_ = x.float() @ w.float().t()
+    want = torch.nn.functional.silu(ref_[:, :N]) * ref_[:, N:] if silu else ref_
+    _close(out, want, atol=2e-2, rtol=2e-2)
+    assert torch.equal(out, fn(x, w, force_mode=mode, force_splits=S))
+    ops.check_status()
+
+
+@pytest.mark.parametrize("mode", [5, 6])
+@pytest.mark.parametrize("M,N,K,S", [(256, 4096, 4096, 4), (64, 4096, 12288, 8), (130, 1024, 3072, 2), (40, 5120, 3200, 4)])
+def test_gemm_split_k_with_reduce_kernel_and_fused_epilogues(ops, M, N, K, S, mode):
+    torch.manual_seed(M + K)
+    x, w = _rand(M, K), _rand(N, K, scale=0.05)
+    residual = _rand(M, N, scale=2.0)
+    want = ((x.float() @ w.float().t()).to(BF).float() + residual.float()).to(BF)
+    parts = (N + 127) // 128
+    ssq = torch.full((M, parts), float("nan"), dtype=torch.float32, device="cuda")
+    res = residual.clone()
+    ops.linear_residual(x, w, res, ssq, force_mode=mode, tune=S)
+    _close(res, want, atol=6e-2, rtol=2e-2)
+    sq = torch.nn.functional.pad(res.float() ** 2, (0, parts * 128 - N)).view(M, parts, 128).sum(-1)
+    assert torch.allclose(ssq, sq, rtol=1e-3, atol=1e-3)
+    res2, ssq2 = residual.clone(), torch.empty_like(ssq)
+    ops.linear_residual(x, w, res2, ssq2, force_mode=mode, tune=S)
+    assert torch.equal(res2, res) and torch.equal(ssq2, ssq)
+    pk = (K + 127) // 128
+    ssq_in = (x.float() ** 2).view(M, pk, -1).sum(-1).contiguous()
+    got = ops.linear_scaled(x, w, ssq_in, 1e-6, force_mode=mode, tune=S)
+    xn = x.float() * torch.rsqrt((x.float() ** 2).mean(-1, keepdim=True) + 1e-6)
+    _close(got, xn @ w.float().t(), atol=3e-2, rtol=3e-2)
+    ops.check_status()
+
+
 def test_embedding_sum_of_squares(ops):
     V, H, T = 512, 1024, 37
     table = _rand(V, H)
