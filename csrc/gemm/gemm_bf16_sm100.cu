@@ -775,9 +775,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 // ranges and applies the same epilogues (row scale, SiLU * up, residual add + sums of squares).  One CTA adding four
 // 128 x 256 partial tiles through its own L2 port takes ~5 us; spread over all SMs the same bytes take ~1 us.
 //
-// Block = 1024 threads = 32 rows (lane) x 32 groups of 4 columns (warp): 32 rows x 128 output columns.  Reads follow the
-// slot layout (a warp reads 512 contiguous bytes per partial tile).  Grid: (tile row blocks of 32 live rows, 128-column
-// parts of the tile, tiles).
+// Block = 256 threads, 32 rows x 128 output columns.  Phase 1 (thread = row x 4 groups of 4 columns): reads follow the slot
+// layout, a warp reads 512 contiguous bytes per partial tile and group; sums, row scale and SiLU * up go to shared memory
+// as fp32.  Phase 2 (warp = 4 rows, lane = 4 consecutive columns): residual add, bf16 rows written 256 bytes at a time,
+// sums of squares by a warp shuffle tree (a fixed order).  Grid: (blocks of 32 rows, 128-column parts of a tile, tiles).
 struct SplitKFinish {
   const float* ws;
   int num_tiles, m_tiles, n_tiles, num_kg, workers;
@@ -785,89 +786,120 @@ struct SplitKFinish {
   int block_n;          // output columns per tile (SiLU: 128 of the 256 accumulator columns are up features)
   int raster_group;
 };
+constexpr int kFinishMaxParts = 16;
 
 template <int kEpi>
-__global__ void __launch_bounds__(1024) gemm_splitk_finish_kernel(const SplitKFinish p, __nv_bfloat16* __restrict__ out, int ldo,
-                                                                 int m_total, int n_total, const GemmFuse fuse) {
-  __shared__ float s_ssq[32][33];
+__global__ void __launch_bounds__(256) gemm_splitk_finish_kernel(const SplitKFinish p, __nv_bfloat16* __restrict__ out, int ldo,
+                                                                int m_total, int n_total, const GemmFuse fuse) {
+  __shared__ __align__(16) float s_val[32][132];
   __shared__ float s_scale[32];
+  __shared__ unsigned s_slot[kFinishMaxParts];        // offset of each partial tile's slot, in units of kSkSlotFloats
+  __shared__ int s_n;
   pdl_launch_dependents();
   pdl_wait();
-  const int lane = threadIdx.x & 31, cg = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.z;
   int mt = 0, nt = 0;
   tile_coords(t, p.m_tiles, p.n_tiles, p.raster_group, mt, nt);
   const int tile_rows = p.pair ? 2 * kBlockR : kBlockR;
-  const int row_in_tile = blockIdx.x * 32 + lane;
-  const int r = mt * tile_rows + row_in_tile;
-  if (mt * tile_rows + blockIdx.x * 32 >= m_total) return;                 // no live row in this block (uniform)
-  const int half = row_in_tile >> 7, row_in_slot = row_in_tile & 127;       // which CTA of a pair owns the row
-  const int col_in_tile = blockIdx.y * 128 + cg * 4;                        // output column of this thread's group of four
-  const int c = nt * p.block_n + col_in_tile;
-  if (cg == 0) s_scale[lane] = fuse_row_scale(fuse, r, m_total);
-  // the tile's K ranges belong to workers first .. first + n - 1 (the arithmetic of TokSched / sk_arrive)
-  const long long U = static_cast<long long>(p.num_tiles) * p.num_kg, G = p.workers;
-  const long long a = static_cast<long long>(t) * p.num_kg;
-  const int first = static_cast<int>(((a + 1) * G + U - 1) / U) - 1;
-  const int n = static_cast<int>(((a + p.num_kg) * G + U - 1) / U) - first;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f}, up[4] = {0.f, 0.f, 0.f, 0.f};
-  const bool live = r < m_total && col_in_tile < p.block_n && c < n_total;
-  if (live) {
+  const int row0_in_tile = blockIdx.x * 32;
+  const int row0 = mt * tile_rows + row0_in_tile;
+  if (row0 >= m_total) return;                                              // no live row in this block (uniform)
+  const int half = row0_in_tile >> 7;                                       // which CTA of a pair owns these rows
+  const int col0_in_tile = blockIdx.y * 128;
+  const int c0 = nt * p.block_n + col0_in_tile;
+  if (threadIdx.x < 32) s_scale[threadIdx.x] = fuse_row_scale(fuse, row0 + threadIdx.x, m_total);
+  if (threadIdx.x == 32) {
+    // the tile's K ranges belong to workers first .. first + n - 1 (the arithmetic of TokSched / sk_arrive)
+    const long long U = static_cast<long long>(p.num_tiles) * p.num_kg, G = p.workers;
+    const long long a = static_cast<long long>(t) * p.num_kg;
+    const int first = static_cast<int>(((a + 1) * G + U - 1) / U) - 1;
+    int n = static_cast<int>(((a + p.num_kg) * G + U - 1) / U) - first;
+    if (n > kFinishMaxParts) n = kFinishMaxParts;                           // the host never splits that far
     for (int i = 0; i < n; ++i) {
       const int w = first + i;
       const long long u0 = U * w / G;
-      const int owner = p.pair ? 2 * w + half : w;
-      const float* slot = p.ws + (static_cast<size_t>(owner) * 2 + (u0 >= a ? 0 : 1)) * kSkSlotFloats + row_in_slot * 4;
-      const float4 v = __ldcg(reinterpret_cast<const float4*>(slot + (col_in_tile >> 2) * 512));
-      acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
-      if constexpr (kEpi == kEpiSiluMul) {
-        const float4 g = __ldcg(reinterpret_cast<const float4*>(slot + ((col_in_tile + p.block_n) >> 2) * 512));
-        up[0] += g.x; up[1] += g.y; up[2] += g.z; up[3] += g.w;
+      s_slot[i] = static_cast<unsigned>((p.pair ? 2 * w + half : w) * 2 + (u0 >= a ? 0 : 1));
+    }
+    s_n = n;
+  }
+  __syncthreads();
+  const int n = s_n;
+  {
+    const int r = row0 + lane;
+    const float row_scale = s_scale[lane];
+    const size_t row_off = static_cast<size_t>((row0_in_tile & 127) + lane) * 4;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int cg = warp * 4 + j;                                          // group of four columns inside the 128
+      const int col = col0_in_tile + cg * 4;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f}, up[4] = {0.f, 0.f, 0.f, 0.f};
+      if (r < m_total && col < p.block_n) {
+        for (int i0 = 0; i0 < n; i0 += 4) {             // four partial tiles' loads in flight; added in order
+          float4 v[4], g[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            if (i0 + k < n) {
+              const float* slot = p.ws + static_cast<size_t>(s_slot[i0 + k]) * kSkSlotFloats + row_off;
+              v[k] = __ldcg(reinterpret_cast<const float4*>(slot + (col >> 2) * 512));
+              if constexpr (kEpi == kEpiSiluMul) g[k] = __ldcg(reinterpret_cast<const float4*>(slot + ((col + p.block_n) >> 2) * 512));
+            }
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            if (i0 + k < n) {
+              acc[0] += v[k].x; acc[1] += v[k].y; acc[2] += v[k].z; acc[3] += v[k].w;
+              if constexpr (kEpi == kEpiSiluMul) { up[0] += g[k].x; up[1] += g[k].y; up[2] += g[k].z; up[3] += g[k].w; }
+            }
+          }
+        }
       }
+      float4 f;
+      f.x = acc[0] * row_scale; f.y = acc[1] * row_scale; f.z = acc[2] * row_scale; f.w = acc[3] * row_scale;
+      if constexpr (kEpi == kEpiSiluMul) {
+        f.x = silu(f.x) * (up[0] * row_scale); f.y = silu(f.y) * (up[1] * row_scale);
+        f.z = silu(f.z) * (up[2] * row_scale); f.w = silu(f.w) * (up[3] * row_scale);
+      }
+      *reinterpret_cast<float4*>(&s_val[lane][cg * 4]) = f;
     }
   }
   __syncthreads();
-  const float row_scale = s_scale[lane];
-  float ssq = 0.f;
-  if (live) {
-    float f[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      f[j] = acc[j] * row_scale;
-      if constexpr (kEpi == kEpiSiluMul) f[j] = silu(f[j]) * (up[j] * row_scale);
-    }
-    __nv_bfloat16* dst = out + static_cast<size_t>(r) * ldo + c;
-    if (c + 4 <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0)) {
-      if (fuse.add_residual) {
-        const uint2 old = *reinterpret_cast<const uint2*>(dst);
-        f[0] = bf16_round_g(bf16_round_g(f[0]) + bf16_lo(old.x));
-        f[1] = bf16_round_g(bf16_round_g(f[1]) + bf16_hi(old.x));
-        f[2] = bf16_round_g(bf16_round_g(f[2]) + bf16_lo(old.y));
-        f[3] = bf16_round_g(bf16_round_g(f[3]) + bf16_hi(old.y));
-        ssq = (f[0] * f[0] + f[1] * f[1]) + (f[2] * f[2] + f[3] * f[3]);
-      }
-      *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]));
-    } else {
-#pragma unroll
-      for (int j = 0; j < 4; ++j)
-        if (c + j < n_total) {
-          float val = f[j];
-          if (fuse.add_residual) {
-            val = bf16_round_g(bf16_round_g(val) + __bfloat162float(dst[j]));
-            ssq += val * val;
-          }
-          dst[j] = __float2bfloat16_rn(val);
+  for (int rr = 0; rr < 4; ++rr) {
+    const int row = warp * 4 + rr, r = row0 + row;
+    const int c = c0 + lane * 4;
+    const float4 v = *reinterpret_cast<const float4*>(&s_val[row][lane * 4]);
+    float f[4] = {v.x, v.y, v.z, v.w};
+    float ssq = 0.f;
+    if (r < m_total && col0_in_tile + lane * 4 < p.block_n && c < n_total) {
+      __nv_bfloat16* dst = out + static_cast<size_t>(r) * ldo + c;
+      if (c + 4 <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0)) {
+        if (fuse.add_residual) {
+          const uint2 old = *reinterpret_cast<const uint2*>(dst);
+          f[0] = bf16_round_g(bf16_round_g(f[0]) + bf16_lo(old.x));
+          f[1] = bf16_round_g(bf16_round_g(f[1]) + bf16_hi(old.x));
+          f[2] = bf16_round_g(bf16_round_g(f[2]) + bf16_lo(old.y));
+          f[3] = bf16_round_g(bf16_round_g(f[3]) + bf16_hi(old.y));
+          ssq = (f[0] * f[0] + f[1] * f[1]) + (f[2] * f[2] + f[3] * f[3]);
         }
-    }
-  }
-  if (fuse.out_ssq != nullptr) {            // sums of squares of the 128 columns of this block, added in column order
-    s_ssq[cg][lane] = ssq;
-    __syncthreads();
-    if (cg == 0 && r < m_total && nt * p.block_n + blockIdx.y * 128 < n_total) {
-      float tot = 0.f;
+        *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]));
+      } else {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) tot += s_ssq[i][lane];
-      fuse.out_ssq[static_cast<size_t>(r) * fuse.out_parts + ((nt * p.block_n + blockIdx.y * 128) >> 7)] = tot;
+        for (int j = 0; j < 4; ++j)
+          if (c + j < n_total) {
+            float val = f[j];
+            if (fuse.add_residual) {
+              val = bf16_round_g(bf16_round_g(val) + __bfloat162float(dst[j]));
+              ssq += val * val;
+            }
+            dst[j] = __float2bfloat16_rn(val);
+          }
+      }
+    }
+    if (fuse.out_ssq != nullptr) {            // sum of squares of the row's 128 columns: a shuffle tree, the same order every time
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ssq += __shfl_xor_sync(0xffffffffu, ssq, o);
+      if (lane == 0 && r < m_total && c0 < n_total) fuse.out_ssq[static_cast<size_t>(r) * fuse.out_parts + (c0 >> 7)] = ssq;
     }
   }
 }
@@ -1271,7 +1303,7 @@ static int launch_finish(const GemmStreamK& sk, int tiles, int m_tiles, int n_ti
   const int tile_rows = pair ? 2 * kBlockR : kBlockR;
   const int live_rows = M < tile_rows ? M : tile_rows;
   dim3 grid((live_rows + 31) / 32, (block_n + 127) / 128, tiles);
-  return launch_kernel(gemm_splitk_finish_kernel<kEpi>, grid, dim3(1024), 0, stream, 0, p, out, ldo, M, n_out, fuse) == cudaSuccess ? 0 : -5;
+  return launch_kernel(gemm_splitk_finish_kernel<kEpi>, grid, dim3(256), 0, stream, 0, p, out, ldo, M, n_out, fuse) == cudaSuccess ? 0 : -5;
 }
 
 // kgroup > 0: stream-K with units of `kgroup` K blocks (needs the device's workspace; falls back to whole tiles without it).
@@ -1436,16 +1468,23 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
   // per-rank gate_up / down of 32B over 8 ranks: 25-53 us vs 32-62 us), where one pair tile covers all tokens and the
   // weights are read once.
   if (w_dynamic && (force_mode == 0 || force_mode == 2)) force_mode = 4;      // the only kernels that wait before reading W
-  // Two shapes where K split over otherwise idle SMs plus the reduce kernel wins (measured in CUDA-graph chains): a layer
-  // with few feature tiles and a very long K at 129..256 tokens (8B down_proj: 34 us vs 43), and a mid-sized gated MLP at
-  // 33..128 tokens (the per-rank gate_up of 32B over 8 ranks, 25 tiles: 20-22 us vs 25-36).
+  // K split over otherwise idle SMs plus the reduce kernel (measured in CUDA-graph chains, us with / without):
+  //  * 129..256 tokens on a large layer whose 256-feature pair tiles leave at least half of the SM pairs idle: 8B qkv 21.3 /
+  //    25.5 (3 ways), o_proj 18.5 / 21.1 (3), down_proj 32.6 / 43.3 (4), the per-rank 32B gate_up 26.3 / 29.1 (2);
+  //  * a mid-sized gated MLP at 33..128 tokens (the per-rank gate_up of 32B over 8 ranks, 25 tiles): 20-22 / 25-36.
   int defer_splits = 0;
   if (force_mode == 0 && push.size <= 1 && !wide && !w_dynamic) {
     const int max_pairs = sms / 2;
-    const int ptiles = (n_out + 255) / 256, stiles = (n_out + kBlockR - 1) / kBlockR;
-    if (epi == kEpiStore && M > 128 && M <= 256 && K >= 8192 && ptiles <= 18 && max_pairs / ptiles >= 2) {
-      force_mode = 5;
-      defer_splits = max_pairs / ptiles < 4 ? max_pairs / ptiles : 4;
+    const int stiles = (n_out + kBlockR - 1) / kBlockR;
+    const int ptiles = epi == kEpiSiluMul ? stiles : (n_out + 255) / 256;
+    if (M > 128 && M <= 256 && K >= 2048 && static_cast<long long>(w_rows) * K >= (12ll << 20)) {
+      int S = max_pairs / ptiles;
+      const int cap = K >= 8192 ? 4 : 3;
+      if (S > cap) S = cap;
+      if (S >= 2) {
+        force_mode = 5;
+        defer_splits = S;
+      }
     } else if (epi == kEpiSiluMul && M > 32 && M <= 128 && K >= 4096 && stiles >= 16 && stiles * 4 <= sms) {
       force_mode = 6;
       defer_splits = 4;
