@@ -65,6 +65,7 @@ struct GemmFuse {
   int add_residual;
   float* out_ssq;
   int out_parts;
+  int w_dynamic;      // weight-tile kernel only: W was written by the kernel launched just before, do not prefetch it early
 };
 
 __device__ __forceinline__ float fuse_row_scale(const GemmFuse& f, int row, int rows) {
@@ -1004,6 +1005,7 @@ gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       // Weights never depend on a predecessor kernel: start streaming them into every stage of the ring right
       // away, and wait for the predecessor only before the first activation tile is requested.
       const int first = min(my_kb, Cfg::kStages);
+      if (fuse_io.w_dynamic) pdl_wait();                 // ... unless they are a copy made by the preceding kernel
       for (int i = 0; i < first; ++i) {
         uint8_t* st = smem + i * Cfg::kStageBytes;
         const int kx = (kb0 + i) * kBlockK;
@@ -1313,6 +1315,7 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
                          int n_out, int K, unsigned* status, cudaStream_t stream, const TpPush& push, const GemmFuse& fuse,
                          const GemmSample& samp = GemmSample{}, int kgroup = 0, int w_dynamic = 0, int defer_splits = 0) {
   using Cfg = TokCfg<BLOCK_C, kEpi>;
+  w_dynamic |= fuse.w_dynamic;
   CUtensorMap tm_x, tm_w;
   if (forge_make_tmap_2d(&tm_x, x, M, K, ldx, kBlockR, 2) != 0) return -2;
   if (forge_make_tmap_2d(&tm_w, w, w_rows, K, ldw, BLOCK_C, 2) != 0) return -3;
@@ -1360,6 +1363,7 @@ static int launch_pair(const void* x, int ldx, const void* w, int w_rows, int ld
                        int K, unsigned* status, cudaStream_t stream, const TpPush& push, const GemmFuse& fuse, int kgroup,
                        int w_dynamic = 0, int defer_splits = 0) {
   using Cfg = PairCfg<kEpi>;
+  w_dynamic |= fuse.w_dynamic;
   CUtensorMap tm_x, tm_w;
   if (forge_make_tmap_2d(&tm_x, x, M, K, ldx, kBlockR, 2) != 0) return -2;
   if (forge_make_tmap_2d(&tm_w, w, w_rows, K, ldw, kBlockR, 2) != 0) return -3;
@@ -1448,9 +1452,11 @@ TpPush make_tp_push(int tp_size, int tp_rank, const long long* slot_ptrs, const 
 
 static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K, int epi,
                          int force_mode, int tune, unsigned* status, cudaStream_t stream, const TpPush& push,
-                         const GemmFuse& fuse = GemmFuse{}) {
+                         const GemmFuse& fuse_in = GemmFuse{}) {
   const int force_splits = tune & 0xff, force_deep = (tune >> 16) & 0xff;
-  const int w_dynamic = (tune >> 24) & 1;        // W is the output of the preceding kernel: only the many-token kernels take that
+  const int w_dynamic = (tune >> 24) & 1;        // W is the output of the preceding kernel: no kernel may prefetch it early
+  GemmFuse fuse = fuse_in;
+  fuse.w_dynamic = w_dynamic;
   int force_bc = (tune >> 8) & 0xff;
   if (M <= 0 || n_out <= 0 || K <= 0) return 0;
   if ((K & 7) || (ldx & 7) || (ldw & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
@@ -1467,7 +1473,6 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
   // 129..256 tokens of a decode step on a layer with at least ~20 tiles of 256 features (qkv and gate_up of 8B, the
   // per-rank gate_up / down of 32B over 8 ranks: 25-53 us vs 32-62 us), where one pair tile covers all tokens and the
   // weights are read once.
-  if (w_dynamic && (force_mode == 0 || force_mode == 2)) force_mode = 4;      // the only kernels that wait before reading W
   // K split over otherwise idle SMs plus the reduce kernel (measured in CUDA-graph chains, us with / without):
   //  * 129..256 tokens on a large layer whose 256-feature pair tiles leave at least half of the SM pairs idle: 8B qkv 21.3 /
   //    25.5 (3 ways), o_proj 18.5 / 21.1 (3), down_proj 32.6 / 43.3 (4), the per-rank 32B gate_up 26.3 / 29.1 (2);
@@ -1543,7 +1548,6 @@ static int gemm_dispatch(const void* x, int ldx, const void* w, int ldw, void* o
     if (epi == kEpiSiluMul) return launch_pair<kEpiSiluMul>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, force_splits, w_dynamic);
     return launch_pair<kEpiStore>(x, ldx, w, w_rows, ldw, o, ldo, M, n_out, K, status, stream, push, fuse, force_splits, w_dynamic);
   }
-  if (w_dynamic) return -8;
   const bool decode = force_mode == 2 || (force_mode == 0 && M <= 256 && !wide);
   if (decode) {
     if (M > 256) return -7;

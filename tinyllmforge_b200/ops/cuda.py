@@ -97,6 +97,7 @@ class CudaOps:
         self.sample_in_lm_head = os.environ.get("FORGE_LM_HEAD_SAMPLE", "1") != "0"
         self._flat_scratch = torch.empty(2 * self.num_sms * (2 * 4 * 130 + 2) + 64, dtype=torch.float32, device=self.device)
         _streamk_workspace(self.C, self.device, self.num_sms)
+        self.fp8_expand_max_weights = int(os.environ.get("FORGE_FP8_EXPAND_MAX_WEIGHTS", "0"))
         self._fp8_scratch = None                   # bf16 expansion of one fp8 weight (see _expand_fp8)
         self._fp8_retired = []
 
@@ -119,7 +120,7 @@ class CudaOps:
         """x @ w.T.  ``w`` must not be the output of the kernel launched just before this call: the decode
         kernel starts streaming weights before it waits for its predecessor (weights are static in the engine)."""
         if isinstance(w, Fp8BlockWeight):
-            if x.shape[0] <= FP8_EXPAND_MIN_ROWS:
+            if not self._expands_fp8(w, x.shape[0]):
                 return self.linear_fp8(x, w)
             w, force_deep = self._expand_fp8(w), force_deep | W_DYNAMIC
         out = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
@@ -130,7 +131,7 @@ class CudaOps:
     def linear_silu_mul(self, x: torch.Tensor, w_gate_up: torch.Tensor, force_mode: int = 0, force_splits: int = 0,
                         force_block_c: int = 0, force_deep: int = 0) -> torch.Tensor:
         if isinstance(w_gate_up, Fp8BlockWeight):
-            if x.shape[0] <= FP8_EXPAND_MIN_ROWS:
+            if not self._expands_fp8(w_gate_up, x.shape[0]):
                 return self.silu_mul(self.linear_fp8(x, w_gate_up))
             w_gate_up, force_deep = self._expand_fp8(w_gate_up), force_deep | W_DYNAMIC
         out = torch.empty(x.shape[0], w_gate_up.shape[0] // 2, dtype=x.dtype, device=x.device)
@@ -167,6 +168,12 @@ class CudaOps:
         [tokens, ceil(H / 128)]) receives the sums of squares of the new residual rows, one per 128 features."""
         self.C.gemm_fused(x, w, residual, 0, force_mode, tune, None, 0.0, True, ssq_out, self.status)
         self.launches += 1
+
+    def _expands_fp8(self, w: "Fp8BlockWeight", rows: int) -> bool:
+        """Many rows: the GEMM is bound by the tensor cores, the expansion costs a few per cent.  Few rows on a small matrix
+        (a shard of a large model over many ranks): the step is bound by its chain of launches, and the e4m3 path needs three
+        (quantise, multiply, add the K splits) where expansion + the fused bf16 kernel needs two and keeps its epilogues."""
+        return rows > FP8_EXPAND_MIN_ROWS or w.shape[0] * w.shape[1] <= self.fp8_expand_max_weights
 
     def _expand_fp8(self, w: "Fp8BlockWeight") -> torch.Tensor:
         """bf16 copy of a block-scaled e4m3 weight in a scratch buffer that the next expansion overwrites (stream-ordered:
@@ -396,20 +403,23 @@ class CudaOps:
         if self.fused is None or M > self.fused.max_tokens or H != self.fused.hidden:
             return self.add_rms_norm(tp.all_reduce(self.linear(x, layer.weight)), residual, norm_weight, eps)
         st = self.fused.sites[site]
-        if self.fused.use_tagged(M, H) and not isinstance(layer.weight, Fp8BlockWeight):
+        fp8 = isinstance(layer.weight, Fp8BlockWeight)
+        expand = fp8 and self._expands_fp8(layer.weight, M)
+        if self.fused.use_tagged(M, H) and (not fp8 or expand):
             # decode-sized: rows travel as tagged words from the GEMM epilogue to their owners and back normalised
             from ..parallel.symm import SITE_GATHER
             f, ag = self.fused, self.fused.sites[SITE_GATHER]
-            self.C.gemm_tp_tagged(x, layer.weight, 0, tp.rank, st.ll_ptrs, f.tagged_rows_per_rank, st.arrive, st.epoch, self.status)
+            w, tune = (self._expand_fp8(layer.weight), W_DYNAMIC << 16) if expand else (layer.weight, 0)
+            self.C.gemm_tp_tagged(x, w, tune, tp.rank, st.ll_ptrs, f.tagged_rows_per_rank, st.arrive, st.epoch, self.status)
             y = torch.empty(M, H, dtype=x.dtype, device=x.device)
             self.C.tp_tagged_reduce_norm(tp.rank, st.ll_local, f.tagged_rows_per_rank, st.epoch, ag.ll_ptrs, ag.arrive, ag.epoch,
                                          f.timeout_ns, f.local_only, residual, residual, norm_weight, y, eps, self.status)
             self.launches += 2
             return y, residual
-        if isinstance(layer.weight, Fp8BlockWeight) and M <= FP8_EXPAND_MIN_ROWS:
+        if fp8 and not expand:
             # the block-scaled GEMM has no signalling epilogue: publish its output with a copy kernel
             self.C.tp_rows_publish(self.linear_fp8(x, layer.weight), st.local_buf, tp.rank, st.signal_ptrs, st.arrive, st.epoch)
-        elif isinstance(layer.weight, Fp8BlockWeight):
+        elif fp8:
             self.C.gemm_tp(x, self._expand_fp8(layer.weight), st.local_buf, W_DYNAMIC << 16, tp.rank, st.signal_ptrs, st.arrive, st.epoch, self.status)
         else:
             self.C.gemm_tp(x, layer.weight, st.local_buf, 0, tp.rank, st.signal_ptrs, st.arrive, st.epoch, self.status)
