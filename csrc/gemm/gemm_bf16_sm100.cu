@@ -31,7 +31,7 @@ constexpr int kBlockK = 64;    // 64 bf16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
 constexpr int kGemmThreads = 192;
 
-enum GemmEpilogue { kEpiStore = 0, kEpiSiluMul = 1, kEpiSample = 2 };
+enum GemmEpilogue { kEpiStore = 0, kEpiSiluMul = 1, kEpiSample = 2, kEpiQkv = 3 };
 
 // Optional phase timeline of the decode kernel: when set (forge_gemm_set_trace), CTA b writes %globaltimer
 // (ns) at eight points into trace[b * 8 ..].  Null in normal operation.
@@ -91,6 +91,28 @@ struct GemmSample {
   float* part_v;             // [rows][n_tiles]
   int* part_i;
   int n_tiles;
+};
+
+// q/k-norm + rotary embedding + KV-cache store in the epilogue of the qkv projection (kEpiQkv; head_dim 128, tiles of 128
+// features = one head).  What the reference does in three steps after the GEMM (per-head RMSNorm of q and k:
+// tinyvllm/models/qwen3.py:74-96, rotation: tinyvllm/layers/rotary_embedding.py, cache write:
+// tinyvllm/layers/attention.py:9-44) happens on the accumulators: each epilogue thread owns one token row of one head,
+// rounds it to bf16 (what the GEMM would have stored), normalises (q and k heads), rotates with the token's position and
+// writes q rows to q_out and k / v rows into their cache slot (slot < 0: nothing is stored).  Same rounding steps as
+// qk_norm_rope_store128_kernel.
+struct GemmQkv {
+  const __nv_bfloat16* qw;      // [128] norm weights (nullptr: no norm)
+  const __nv_bfloat16* kw;
+  float eps;
+  const float* rope;            // [rope_rows][128]: cos of the 64 pairs, then sin
+  int rope_rows;
+  const int* positions;         // [tokens]
+  const int* slots;             // [tokens] flat cache slot (block * block_size + offset), < 0: do not store
+  __nv_bfloat16* q_out;         // [tokens][nq][128]
+  __nv_bfloat16* k_cache;       // [blocks][nkv][block_size][128]
+  __nv_bfloat16* v_cache;
+  int nq, nkv, block_size, do_rope;
+  long long num_slots;
 };
 
 constexpr int tmem_cols_for(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
@@ -366,7 +388,7 @@ template <int BLOCK_C, int kEpi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                    __nv_bfloat16* __restrict__ out, int ldo, int m_total, int n_total, int K, int dual_off, unsigned* status,
-                   const TpPush push, const GemmFuse fuse, const GemmSample samp, const GemmStreamK sk) {
+                   const TpPush push, const GemmFuse fuse, const GemmSample samp, const GemmStreamK sk, const GemmQkv qk) {
   using Cfg = TokCfg<BLOCK_C, kEpi>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -537,6 +559,107 @@ gemm_tokens_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             const size_t slot = static_cast<size_t>(r) * samp.n_tiles + nt;
             samp.part_v[slot] = best.v;
             samp.part_i[slot] = token;
+          }
+        }
+      } else if constexpr (kEpi == kEpiQkv) {
+        if (ok) {
+          const uint32_t tacc = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + buf * Cfg::kAccCols;
+          const int h = nt;                                             // one tile = one head
+          const bool live = r < m_total;
+          const bool is_q = h < qk.nq, is_k = !is_q && h < qk.nq + qk.nkv;
+          const float row_scale = fuse_row_scale(fuse, r, m_total);
+          __nv_bfloat16* dst = nullptr;
+          if (live) {
+            if (is_q) {
+              dst = qk.q_out + (static_cast<size_t>(r) * qk.nq + h) * 128;
+            } else {
+              const long long slot = qk.slots[r];
+              if (slot >= qk.num_slots) set_status(status, kStatusBadIndex);
+              if (slot >= 0 && slot < qk.num_slots) {
+                const int kvh = is_k ? h - qk.nq : h - qk.nq - qk.nkv;
+                const long long blk = slot / qk.block_size, off = slot % qk.block_size;
+                dst = (is_k ? qk.k_cache : qk.v_cache) + ((blk * qk.nkv + kvh) * qk.block_size + off) * 128;
+              }
+            }
+          }
+          const __nv_bfloat16* nw = is_q ? qk.qw : qk.kw;
+          const bool norm = (is_q || is_k) && nw != nullptr;            // uniform over the tile
+          const bool rot = (is_q || is_k) && qk.do_rope != 0;
+          float inv = 1.f;
+          if (norm) {
+            float ss = 0.f;
+#pragma unroll 1
+            for (int cc = 0; cc < 128; cc += 32) {
+              uint32_t v[32];
+              tmem_ld_x32(tacc + cc, v);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float x = bf16_round_g(__uint_as_float(v[j]) * row_scale);
+                ss += x * x;
+              }
+            }
+            inv = rsqrtf(ss / 128.f + qk.eps);
+          }
+          const float* cs = qk.rope;
+          if (rot) {
+            int pos = live ? qk.positions[r] : 0;
+            pos = pos < 0 ? 0 : (pos >= qk.rope_rows ? qk.rope_rows - 1 : pos);
+            cs = qk.rope + static_cast<size_t>(pos) * 128;
+          }
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {                                 // columns [32c, 32c + 32) and their partners 64 further
+            uint32_t va[32], vb[32];
+            tmem_ld_x32(tacc + 32 * c, va);
+            tmem_ld_x32(tacc + 64 + 32 * c, vb);
+            tmem_ld_wait();
+            float a[32], b[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              a[j] = bf16_round_g(__uint_as_float(va[j]) * row_scale);
+              b[j] = bf16_round_g(__uint_as_float(vb[j]) * row_scale);
+            }
+            if (norm) {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                const uint4 wa = *reinterpret_cast<const uint4*>(nw + 32 * c + 8 * q4);
+                const uint4 wb = *reinterpret_cast<const uint4*>(nw + 64 + 32 * c + 8 * q4);
+                const uint32_t ra[4] = {wa.x, wa.y, wa.z, wa.w}, rb[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int j = 8 * q4 + 2 * e;
+                  a[j] = bf16_round_g(bf16_round_g(a[j] * inv) * bf16_lo(ra[e]));
+                  a[j + 1] = bf16_round_g(bf16_round_g(a[j + 1] * inv) * bf16_hi(ra[e]));
+                  b[j] = bf16_round_g(bf16_round_g(b[j] * inv) * bf16_lo(rb[e]));
+                  b[j + 1] = bf16_round_g(bf16_round_g(b[j + 1] * inv) * bf16_hi(rb[e]));
+                }
+              }
+            }
+            if (rot) {
+#pragma unroll
+              for (int q4 = 0; q4 < 8; ++q4) {
+                const float4 cv = *reinterpret_cast<const float4*>(cs + 32 * c + 4 * q4);
+                const float4 sv = *reinterpret_cast<const float4*>(cs + 64 + 32 * c + 4 * q4);
+                const float cw[4] = {cv.x, cv.y, cv.z, cv.w}, sw[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const int j = 4 * q4 + e;
+                  const float x1 = a[j], x2 = b[j];
+                  a[j] = x1 * cw[e] - x2 * sw[e];
+                  b[j] = x2 * cw[e] + x1 * sw[e];
+                }
+              }
+            }
+            if (dst != nullptr) {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                const int j = 8 * q4;
+                *reinterpret_cast<uint4*>(dst + 32 * c + j) = make_uint4(pack_bf16x2(a[j], a[j + 1]), pack_bf16x2(a[j + 2], a[j + 3]),
+                                                                          pack_bf16x2(a[j + 4], a[j + 5]), pack_bf16x2(a[j + 6], a[j + 7]));
+                *reinterpret_cast<uint4*>(dst + 64 + 32 * c + j) = make_uint4(pack_bf16x2(b[j], b[j + 1]), pack_bf16x2(b[j + 2], b[j + 3]),
+                                                                               pack_bf16x2(b[j + 4], b[j + 5]), pack_bf16x2(b[j + 6], b[j + 7]));
+              }
+            }
           }
         }
       } else {
@@ -1313,7 +1436,8 @@ static int launch_finish(const GemmStreamK& sk, int tiles, int m_tiles, int n_ti
 template <int BLOCK_C, int kEpi>
 static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int ldw, __nv_bfloat16* out, int ldo, int M,
                          int n_out, int K, unsigned* status, cudaStream_t stream, const TpPush& push, const GemmFuse& fuse,
-                         const GemmSample& samp = GemmSample{}, int kgroup = 0, int w_dynamic = 0, int defer_splits = 0) {
+                         const GemmSample& samp = GemmSample{}, int kgroup = 0, int w_dynamic = 0, int defer_splits = 0,
+                         const GemmQkv& qk = GemmQkv{}) {
   using Cfg = TokCfg<BLOCK_C, kEpi>;
   w_dynamic |= fuse.w_dynamic;
   CUtensorMap tm_x, tm_w;
@@ -1328,7 +1452,7 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
   int ctas = tiles < num_sms ? tiles : num_sms;
   GemmStreamK sk = {nullptr, nullptr, 0, w_dynamic, 0};
   const StreamKWorkspace* wsp = streamk_workspace();
-  if constexpr (kEpi != kEpiSample && (BLOCK_C == 128 || BLOCK_C == 256)) {
+  if constexpr ((kEpi == kEpiStore || kEpi == kEpiSiluMul) && (BLOCK_C == 128 || BLOCK_C == 256)) {
     if (defer_splits > 1 && wsp != nullptr && push.size <= 1) {
       const int kg = (num_kb + defer_splits - 1) / defer_splits;
       const int num_kg = (num_kb + kg - 1) / kg;
@@ -1336,14 +1460,14 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
       if (num_kg > 1 && units <= num_sms && units <= wsp->ctas) {
         sk = GemmStreamK{wsp->ws, wsp->counters, kg, w_dynamic, 1};
         if (launch_kernel(kern, dim3(static_cast<unsigned>(units)), dim3(kGemmThreads), Cfg::kSmemBytes, stream, 0, tm_x, tm_w, out, ldo, M,
-                          n_out, K, n_out, status, push, fuse, samp, sk) != cudaSuccess)
+                          n_out, K, n_out, status, push, fuse, samp, sk, qk) != cudaSuccess)
           return -5;
         return launch_finish<kEpi>(sk, tiles, m_tiles, n_tiles, num_kg, static_cast<int>(units), 0, BLOCK_C, kRasterGroupTok, out, ldo, M,
                                    n_out, fuse, stream);
       }
     }
   }
-  if (kgroup > 0 && BLOCK_C >= 32 && kEpi != kEpiSample) {
+  if (kgroup > 0 && BLOCK_C >= 32 && (kEpi == kEpiStore || kEpi == kEpiSiluMul)) {
     if (kgroup > num_kb) kgroup = num_kb;
     const long long units = static_cast<long long>(tiles) * ((num_kb + kgroup - 1) / kgroup);
     const int want = units < num_sms ? static_cast<int>(units) : num_sms;
@@ -1353,7 +1477,7 @@ static int launch_tokens(const void* x, int ldx, const void* w, int w_rows, int 
     }
   }
   return launch_kernel(kern, dim3(ctas), dim3(kGemmThreads), Cfg::kSmemBytes, stream, 0, tm_x, tm_w, out, ldo, M, n_out, K, n_out,
-                       status, push, fuse, samp, sk) == cudaSuccess ? 0 : -5;
+                       status, push, fuse, samp, sk, qk) == cudaSuccess ? 0 : -5;
 }
 
 // CTA-pair kernel: grid = 2 x pairs, clusters of 2 along x.  kgroup > 0: stream-K over the pairs.  defer_splits > 1: K split
@@ -1644,6 +1768,30 @@ extern "C" int forge_gemm_bf16_sample(const void* x, int ldx, const void* w, int
 // The same with the neighbouring norm / residual add fused in (see GemmFuse).  in_ssq: fp32 [M][in_parts] partial sums of
 // squares of the rows of x (null: rows are not scaled).  add_residual: out += result in place and out_ssq (fp32
 // [M][ceil(n_out / 128)], may be null) receives the sums of squares of the new rows per 128 features.
+// qkv projection with q/k-norm + rotary embedding + KV-cache store in the epilogue (head_dim 128): x [M, K] times
+// w [(nq + 2 nkv) * 128, K]; q rows go to q_out, k / v rows into their cache slots; in_ssq as in forge_gemm_bf16_fused.
+extern "C" int forge_gemm_bf16_qkv(const void* x, int ldx, const void* w, int ldw, int M, int K, const float* in_ssq, int in_parts,
+                                   float in_eps, const void* qw, const void* kw, float eps, const float* rope, int rope_rows,
+                                   const int* positions, const int* slots, void* q_out, void* k_cache, void* v_cache, int nq, int nkv,
+                                   int block_size, long long num_slots, int do_rope, unsigned* status, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if ((K & 7) || (ldx & 7) || (ldw & 7) || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
+      (reinterpret_cast<uintptr_t>(q_out) & 15) || (reinterpret_cast<uintptr_t>(k_cache) & 15) || (reinterpret_cast<uintptr_t>(v_cache) & 15) ||
+      (reinterpret_cast<uintptr_t>(rope) & 15) || nq <= 0 || nkv <= 0 || block_size <= 0)
+    return -1;
+  GemmFuse fuse = {};
+  fuse.in_ssq = in_ssq;
+  fuse.in_parts = in_parts;
+  fuse.in_width_inv = 1.f / static_cast<float>(K);
+  fuse.eps = in_eps;
+  GemmQkv qk = {static_cast<const __nv_bfloat16*>(qw), static_cast<const __nv_bfloat16*>(kw), eps, rope, rope_rows, positions, slots,
+                static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache),
+                nq, nkv, block_size, do_rope, num_slots};
+  const int n_out = (nq + 2 * nkv) * 128;
+  TpPush none = {};
+  return launch_tokens<128, kEpiQkv>(x, ldx, w, n_out, ldw, nullptr, 0, M, n_out, K, status, stream, none, fuse, GemmSample{}, 0, 0, 0, qk);
+}
+
 extern "C" int forge_gemm_bf16_fused(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, int M, int n_out, int K,
                                      int epi, int force_mode, int tune, const float* in_ssq, int in_parts, float eps,
                                      int add_residual, float* out_ssq, unsigned* status, cudaStream_t stream) {

@@ -17,6 +17,10 @@ int forge_gemm_bf16_sample(const void* x, int ldx, const void* w, int ldw, int M
                            const int* header, float* part_v, int* part_i, int* out_i, float* out_v, unsigned* status,
                            cudaStream_t stream);
 int forge_gemm_set_trace(unsigned long long* buf);
+int forge_gemm_bf16_qkv(const void* x, int ldx, const void* w, int ldw, int M, int K, const float* in_ssq, int in_parts, float in_eps,
+                        const void* qw, const void* kw, float eps, const float* rope, int rope_rows, const int* positions,
+                        const int* slots, void* q_out, void* k_cache, void* v_cache, int nq, int nkv, int block_size,
+                        long long num_slots, int do_rope, unsigned* status, cudaStream_t stream);
 int forge_gemm_set_streamk_workspace(float* ws, int* counters, int ctas, int tiles);
 long long forge_gemm_streamk_workspace_floats(int ctas);
 int forge_quant_fp8_1x128(const void* x, void* xq, float* scale, int M, int K, int scale_ld, cudaStream_t stream);
@@ -234,6 +238,43 @@ void qk_norm_rope_store(const Tensor& qkv, const c10::optional<Tensor>& qw, cons
                                  static_cast<int>(bs), static_cast<long long>(k_cache.size(0)) * bs, do_rope ? 1 : 0,
                                  status_ptr(status), stream_of(qkv)),
         "forge_qk_norm_rope_store");
+}
+
+// qkv projection whose epilogue normalises q and k per head, rotates them and writes k / v into the cache (head_dim 128).
+void gemm_qkv_rope_store(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& in_ssq, double in_eps,
+                         const c10::optional<Tensor>& qw, const c10::optional<Tensor>& kw, double eps, const Tensor& rope,
+                         const Tensor& positions, const Tensor& slots, Tensor& q_out, Tensor& k_cache, Tensor& v_cache, int64_t nq,
+                         int64_t nkv, bool do_rope, const Tensor& status) {
+  CHECK_BF16(x); CHECK_BF16(w); CHECK_CUDA_CONTIG(q_out); CHECK_BF16(q_out);
+  CHECK_CUDA_CONTIG(k_cache); CHECK_CUDA_CONTIG(v_cache); CHECK_BF16(k_cache); CHECK_BF16(v_cache);
+  CHECK_CUDA_CONTIG(rope); CHECK_F32(rope); CHECK_CUDA_CONTIG(positions); CHECK_I32(positions);
+  CHECK_CUDA_CONTIG(slots); CHECK_I32(slots);
+  TORCH_CHECK(x.is_cuda() && w.is_cuda() && x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1, "gemm_qkv_rope_store: x [T, K], w [N, K]");
+  TORCH_CHECK(k_cache.dim() == 4 && v_cache.sizes() == k_cache.sizes() && k_cache.size(3) == 128, "caches must be [blocks, kv_heads, block_size, 128]");
+  const int64_t T = x.size(0), K = x.size(1), bs = k_cache.size(2);
+  TORCH_CHECK(w.size(1) == K && w.size(0) == (nq + 2 * nkv) * 128 && k_cache.size(1) == nkv, "gemm_qkv_rope_store: head layout mismatch");
+  TORCH_CHECK(positions.numel() >= T && slots.numel() >= T && q_out.numel() == T * nq * 128, "gemm_qkv_rope_store: length mismatch");
+  TORCH_CHECK(rope.dim() == 2 && rope.size(1) == 128, "rope table must be [positions, 128]");
+  const float* in_p = nullptr;
+  int in_parts = 0;
+  if (in_ssq.has_value()) {
+    CHECK_CUDA_CONTIG(*in_ssq); CHECK_F32(*in_ssq);
+    TORCH_CHECK(in_ssq->dim() == 2 && in_ssq->size(0) >= T && in_ssq->size(1) >= 1, "gemm_qkv_rope_store: in_ssq must be [>= T, parts]");
+    in_p = in_ssq->data_ptr<float>();
+    in_parts = static_cast<int>(in_ssq->size(1));
+  }
+  const void* qwp = nullptr;
+  const void* kwp = nullptr;
+  if (qw.has_value()) { CHECK_CUDA_CONTIG(*qw); CHECK_BF16(*qw); TORCH_CHECK(qw->numel() == 128); qwp = qw->data_ptr(); }
+  if (kw.has_value()) { CHECK_CUDA_CONTIG(*kw); CHECK_BF16(*kw); TORCH_CHECK(kw->numel() == 128); kwp = kw->data_ptr(); }
+  const c10::cuda::CUDAGuard guard(x.device());
+  check(forge_gemm_bf16_qkv(x.data_ptr(), static_cast<int>(x.stride(0)), w.data_ptr(), static_cast<int>(w.stride(0)), static_cast<int>(T),
+                            static_cast<int>(K), in_p, in_parts, static_cast<float>(in_eps), qwp, kwp, static_cast<float>(eps),
+                            rope.data_ptr<float>(), static_cast<int>(rope.size(0)), positions.data_ptr<int>(), slots.data_ptr<int>(),
+                            q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), static_cast<int>(nq), static_cast<int>(nkv),
+                            static_cast<int>(bs), static_cast<long long>(k_cache.size(0)) * bs, do_rope ? 1 : 0, status_ptr(status),
+                            stream_of(x)),
+        "forge_gemm_bf16_qkv");
 }
 
 void silu_mul(const Tensor& x, Tensor& out) {
@@ -652,6 +693,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tp_sample_pairs", &tp_sample_pairs);
   m.def("rms_norm", &rms_norm);
   m.def("qk_norm_rope_store", &qk_norm_rope_store);
+  m.def("gemm_qkv_rope_store", &gemm_qkv_rope_store);
   m.def("silu_mul", &silu_mul);
   m.def("embedding", &embedding);
   m.def("gather_rows", &gather_rows);

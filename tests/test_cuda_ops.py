@@ -343,6 +343,39 @@ def test_gemm_split_k_with_reduce_kernel_and_fused_epilogues(ops, M, N, K, S, mo
     ops.check_status()
 
 
+@pytest.mark.parametrize("T,K,nq,nkv,bs,folded", [(64, 1024, 16, 8, 256, True), (256, 1024, 16, 8, 256, False), (33, 4096, 32, 8, 16, True),
+                                                 (200, 512, 8, 1, 64, False), (1, 256, 4, 2, 256, True)])
+def test_qkv_gemm_with_norm_rope_and_cache_store_in_its_epilogue(ops, T, K, nq, nkv, bs, folded):
+    """The qkv projection whose epilogue normalises q and k per head, rotates them and writes k / v into the paged cache,
+    against the fp32 statement of the same chain (projection rounded to bf16, then q/k-norm + RoPE + store)."""
+    torch.manual_seed(T + K)
+    D, nblk = 128, 8 + T // bs
+    x = _rand(T, K)
+    w = _rand((nq + 2 * nkv) * D, K, scale=0.05)
+    qw, kw = _rand(D, scale=0.2) + 1, _rand(D, scale=0.2) + 1
+    table = ref.rope_table(4096, D, 1e6, "cuda")
+    pos = torch.randint(0, 4096, (T,), dtype=torch.int32, device="cuda")
+    slots = torch.randperm(nblk * bs, device="cuda")[:T].to(torch.int32)
+    if T > 2:
+        slots[1] = -1
+    kc, vc = torch.zeros(nblk, nkv, bs, D, dtype=BF, device="cuda"), torch.zeros(nblk, nkv, bs, D, dtype=BF, device="cuda")
+    kc2, vc2 = kc.clone(), vc.clone()
+    ssq = None
+    proj = x.float() @ w.float().t()
+    if folded:
+        parts = (K + 127) // 128
+        ssq = (x.float() ** 2).view(T, parts, -1).sum(-1).contiguous()
+        proj = proj * torch.rsqrt((x.float() ** 2).mean(-1, keepdim=True) + 1e-6)
+    q = ops.linear_qkv_rope_store(x, w, ssq, 1e-6, qw, kw, 1e-6, table, pos, slots, kc, vc, nq, nkv)
+    q_want = ref.qk_norm_rope_store(proj.to(BF), qw, kw, 1e-6, table, pos, slots, kc2, vc2, nq, nkv, D)
+    _close(q, q_want, 3e-2, 3e-2)
+    _close(kc, kc2, 3e-2, 3e-2)
+    _close(vc, vc2, 2e-2, 2e-2)
+    if T > 2:
+        assert torch.count_nonzero(kc) == torch.count_nonzero(kc2)          # the row with slot -1 was not stored
+    ops.check_status()
+
+
 def test_embedding_sum_of_squares(ops):
     V, H, T = 512, 1024, 37
     table = _rand(V, H)

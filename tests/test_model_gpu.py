@@ -62,12 +62,14 @@ def _check(ref, gpu, sb, what):
     return want, agree
 
 
-@pytest.mark.parametrize("fold", [True, False])
-def test_cuda_model_logits_match_the_fp32_model(fold):
+@pytest.mark.parametrize("fold,qkv_epilogue", [(True, False), (False, False), (True, True), (False, True)])
+def test_cuda_model_logits_match_the_fp32_model(fold, qkv_epilogue):
     from tinyllmforge_b200 import SamplingParams
     from tinyllmforge_b200.engine.request import Request
     from tinyllmforge_b200.engine.step_batch import build_decode, build_prefill
     cfg, ref, gpu, ops = _models(fold)
+    if qkv_epilogue:             # optional path: q/k-norm + RoPE + KV store in the qkv projection's epilogue, here for any decode step
+        ops.qkv_epilogue, ops.qkv_epilogue_min_rows = True, 1
     rng = np.random.default_rng(0)
     reqs, nblk = [], 0
     for n in (5, 300, 257, 700):

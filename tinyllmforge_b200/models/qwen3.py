@@ -133,15 +133,21 @@ class Qwen3ForCausalLM:
         ops, layers = self.ops, self.layers
         residual, ssq_a, ssq_b = ops.embedding_ssq(batch.input_ids, self.embed_tokens.weight, self.embed_tokens.vocab_start)
         fused_decode = (not batch.is_prefill and self.head_dim == 128 and batch.padded_seqs <= ops.fused_qkv_max_batch)
+        in_gemm = not batch.is_prefill and ops.qkv_rope_store_in_gemm(residual.shape[0], self.head_dim, layers[0].qkv_proj.weight)
         for i, l in enumerate(layers):
-            qkv = ops.linear_scaled(residual, l.qkv_proj.weight, ssq_a, self.eps)
             kc, vc = self.kv_cache[i, 0], self.kv_cache[i, 1]
-            if fused_decode:
-                a = ops.decode_attention_qkv(qkv, l.q_norm, l.k_norm, self.eps, self.rope, kc, vc, batch, self.num_heads, self.scale)
-            else:
-                q = ops.qk_norm_rope_store(qkv, l.q_norm, l.k_norm, self.eps, self.rope, batch.positions,
-                                           batch.slot_mapping, kc, vc, self.num_heads, self.num_kv_heads, self.head_dim)
+            if in_gemm:         # norm, rotation and cache write in the projection's epilogue: one launch less per block
+                q = ops.linear_qkv_rope_store(residual, l.qkv_proj.weight, ssq_a, self.eps, l.q_norm, l.k_norm, self.eps, self.rope,
+                                              batch.positions, batch.slot_mapping, kc, vc, self.num_heads, self.num_kv_heads)
                 a = ops.attention(q, kc, vc, batch, self.scale)
+            else:
+                qkv = ops.linear_scaled(residual, l.qkv_proj.weight, ssq_a, self.eps)
+                if fused_decode:
+                    a = ops.decode_attention_qkv(qkv, l.q_norm, l.k_norm, self.eps, self.rope, kc, vc, batch, self.num_heads, self.scale)
+                else:
+                    q = ops.qk_norm_rope_store(qkv, l.q_norm, l.k_norm, self.eps, self.rope, batch.positions,
+                                               batch.slot_mapping, kc, vc, self.num_heads, self.num_kv_heads, self.head_dim)
+                    a = ops.attention(q, kc, vc, batch, self.scale)
             ops.linear_residual(a, l.o_proj.weight, residual, ssq_b)
             g = ops.linear_scaled(residual, l.gate_up_proj.weight, ssq_b, self.eps, silu_mul=True)
             ops.linear_residual(g, l.down_proj.weight, residual, ssq_a)
@@ -164,9 +170,20 @@ class Qwen3ForCausalLM:
         # layer; at large batches the attention kernel is bandwidth-bound and the extra work per sequence costs more)
         fused_decode = (not batch.is_prefill and self.head_dim == 128 and hasattr(ops, "decode_attention_qkv")
                         and batch.padded_seqs <= ops.fused_qkv_max_batch)
+        in_gemm = (not batch.is_prefill and hasattr(ops, "qkv_rope_store_in_gemm") and getattr(layers[0].qkv_proj, "bias", None) is None
+                   and ops.qkv_rope_store_in_gemm(x.shape[0], self.head_dim, layers[0].qkv_proj.weight))
         for i, l in enumerate(layers):
-            qkv = l.qkv_proj.forward(ops, x)
             kc, vc = self.kv_cache[i, 0], self.kv_cache[i, 1]
+            if in_gemm:
+                q = ops.linear_qkv_rope_store(x, l.qkv_proj.weight, None, 0.0, l.q_norm, l.k_norm, self.eps, self.rope, batch.positions,
+                                              batch.slot_mapping, kc, vc, self.num_heads, self.num_kv_heads)
+                a = ops.attention(q, kc, vc, batch, self.scale)
+                x, residual = ops.row_linear_add_rms_norm(a, l.o_proj, residual, l.post_attention_layernorm, self.eps, SITE_O)
+                g = l.gate_up_proj.forward_silu_mul(ops, x)
+                next_norm = layers[i + 1].input_layernorm if i + 1 < len(layers) else self.norm
+                x, residual = ops.row_linear_add_rms_norm(g, l.down_proj, residual, next_norm, self.eps, SITE_DOWN)
+                continue
+            qkv = l.qkv_proj.forward(ops, x)
             if fused_decode:
                 a = ops.decode_attention_qkv(qkv, l.q_norm, l.k_norm, self.eps, self.rope, kc, vc, batch, self.num_heads, self.scale)
             else:

@@ -95,6 +95,11 @@ class CudaOps:
         self.decode_attention_mode = os.environ.get("FORGE_DECODE_ATTN", "auto")
         self.fused_qkv_max_batch = int(os.environ.get("FORGE_FUSED_QKV_MAX", "32"))   # see models/qwen3.py
         self.sample_in_lm_head = os.environ.get("FORGE_LM_HEAD_SAMPLE", "1") != "0"
+        # q/k-norm + RoPE + KV store in the qkv GEMM's epilogue (see qkv_rope_store_in_gemm): 174 instead of 201 launches per
+        # Qwen3-0.6B decode step, but measured slower (3.86 vs 3.76 ms mean step: head-sized tiles leave 32-64 CTAs for the
+        # projection, and each epilogue thread normalises and rotates a whole head) -> off unless asked for
+        self.qkv_epilogue = os.environ.get("FORGE_QKV_EPILOGUE", "0") != "0"
+        self.qkv_epilogue_min_rows = int(os.environ.get("FORGE_QKV_EPILOGUE_MIN_ROWS", "33"))
         self._flat_scratch = torch.empty(2 * self.num_sms * (2 * 4 * 130 + 2) + 64, dtype=torch.float32, device=self.device)
         _streamk_workspace(self.C, self.device, self.num_sms)
         self.fp8_expand_max_weights = int(os.environ.get("FORGE_FP8_EXPAND_MAX_WEIGHTS", "0"))
@@ -246,6 +251,23 @@ class CudaOps:
         q = torch.empty(T, num_heads, head_dim, dtype=qkv.dtype, device=qkv.device)
         self.C.qk_norm_rope_store(qkv, q_weight, k_weight, eps, table, positions, slot_mapping, q, k_cache, v_cache,
                                   num_heads, num_kv_heads, do_rope, self.status)
+        self.launches += 1
+        return q
+
+    def qkv_rope_store_in_gemm(self, rows: int, head_dim: int, weight) -> bool:
+        """Decode steps of 33..256 rows with head_dim 128 and a bf16 qkv weight: the projection's epilogue does the per-head
+        norm, the rotation and the cache write (tiles of 128 features = one head)."""
+        return (self.qkv_epilogue and head_dim == 128 and self.qkv_epilogue_min_rows <= rows <= 256
+                and not isinstance(weight, Fp8BlockWeight) and weight.dtype == torch.bfloat16)
+
+    def linear_qkv_rope_store(self, x, w, ssq_row, in_eps, q_weight, k_weight, eps, table, positions, slot_mapping, k_cache, v_cache,
+                              num_heads, num_kv_heads, do_rope=True):
+        """qkv projection (optionally with the folded input norm, see ``linear_scaled``) + q/k-norm + RoPE + KV store in
+        one kernel; returns q [T, heads, 128].  Replaces linear + qk_norm_rope_store for decode steps."""
+        T = x.shape[0]
+        q = torch.empty(T, num_heads, 128, dtype=x.dtype, device=x.device)
+        self.C.gemm_qkv_rope_store(x, w, ssq_row, in_eps, q_weight, k_weight, eps, table, positions, slot_mapping, q, k_cache, v_cache,
+                                   num_heads, num_kv_heads, do_rope, self.status)
         self.launches += 1
         return q
 
