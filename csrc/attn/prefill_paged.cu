@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(128) prefill_attn_kernel(
   const int qpos0 = past + m0 + warp * 16 + g;          // key positions visible to rows g and g + 8: <= qpos
   const int qpos1 = qpos0 + 8;
 
-  ok = __syncthreads_and(ok);                           // waits are bounded; keep the verdict uniform
+  ok = __syncthreads_and(ok);                           // waits are bounded; keep the outcome uniform
   for (int t = 0; t < n_tiles && ok; ++t) {
     if (threadIdx.x == 0 && t + 1 < n_tiles) issue_kv(t + 1);
     if (!mbar_wait(&bar_kv[t & 1], (t >> 1) & 1, status)) {

@@ -1069,7 +1069,7 @@ struct WgtCfg {
 // slots in rank order from its own shared memory (deterministic) and stores bf16 rows with 8-byte writes.
 // No global scratch, no atomics, no remote loads.
 // SiLU: one split -> combine gate and up on the way out of tensor memory.  Several splits -> the gate sum must
-// be complete before the nonlinearity: round 0 reduces the gate tile into gate_red, round 1 the up tile.
+// be complete before the nonlinearity: the first exchange reduces the gate tile into gate_red, the second the up tile.
 template <int BLOCK_C, int kEpi, bool kDeep>
 __global__ void __launch_bounds__(kGemmThreads, kDeep ? 1 : 2)
 gemm_weights_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
