@@ -5,7 +5,8 @@
 Cases: decode_attention (64 sequences x 2048 tokens, 16 / 8 heads), decode_attention_g4 (256 x 800, 32 / 8 heads: Qwen3-8B),
 decode_attention_g8 (64 x 2304, 64 / 8 heads: Qwen3-32B), prefill_attention, gemm_decode, gemm_decode_split, gemm_prefill,
 gemm_prefill_8b (8192 x 6144 x 4096), gemm_silu, gemm_fp8 (256 x 6144 x 4096, block-scaled e4m3 weights), gemm_residual (o_proj-like GEMM with the residual add + sums of squares
-epilogue), gemm_scaled (qkv-like GEMM with the folded-norm row scale), lm_head_sample (LM head + sampling in one kernel),
+epilogue), gemm_scaled (qkv-like GEMM with the folded-norm row scale), gemm_decode_8b_down (256 x 4096 x 12288 with the residual
+epilogue: K split over CTA pairs + the reduce kernel), lm_head_sample (LM head + sampling in one kernel),
 rms_norm, qk_norm_rope_store, sampler.
 ``--lib`` runs the library kernel the reference would use on the same case instead (cuBLAS through torch.matmul for the
 GEMMs, flash-attn 2 for the attention cases), for a same-box comparison.
@@ -95,9 +96,10 @@ def build(case: str, ops, lib: bool = False):
                 return torch.matmul(x, w.t())          # the library GEMM alone (the reference runs SiLU * mul as another kernel)
             return ops.linear_silu_mul(x, w) if case == "gemm_silu" else ops.linear(x, w)
         return run, (rows * K + M * K + M * N) * 2, 2 * M * rows * K
-    if case in ("gemm_residual", "gemm_scaled"):
-        M, N, K = (256, 1024, 2048) if case == "gemm_residual" else (256, 4096, 1024)
-        ws = [torch.randn(N, K, device="cuda", dtype=BF) * 0.02 for _ in range(28)]          # 28 weights in turn: each launch streams from HBM
+    if case in ("gemm_residual", "gemm_scaled", "gemm_decode_8b_down"):
+        M, N, K = {"gemm_residual": (256, 1024, 2048), "gemm_scaled": (256, 4096, 1024), "gemm_decode_8b_down": (256, 4096, 12288)}[case]
+        nw = 28 if N * K < (8 << 20) else 8
+        ws = [torch.randn(N, K, device="cuda", dtype=BF) * 0.02 for _ in range(nw)]           # several weights in turn: each launch streams from HBM
         x = torch.randn(M, K, device="cuda", dtype=BF)
         res = torch.randn(M, N, device="cuda", dtype=BF)
         ssq_out = torch.empty(M, (N + 127) // 128, dtype=torch.float32, device="cuda")
@@ -105,11 +107,11 @@ def build(case: str, ops, lib: bool = False):
         state = {"i": 0}
 
         def run():
-            w = ws[state["i"] % 28]
+            w = ws[state["i"] % nw]
             state["i"] += 1
             if lib:
                 return torch.matmul(x, w.t())
-            if case == "gemm_residual":
+            if case in ("gemm_residual", "gemm_decode_8b_down"):
                 return ops.linear_residual(x, w, res, ssq_out)
             return ops.linear_scaled(x, w, ssq_in, 1e-6)
         return run, (N * K + M * K + 2 * M * N) * 2, 2 * M * N * K
