@@ -456,8 +456,8 @@ def run_extras(args) -> dict:
     rank = int(os.environ.get("RANK", "0")) if n > 1 else 0
     if ref and rank != 0:
         return {}
-    per_pass = (6.5 if ref else 4.5)                       # seconds, the slowest N measured (N=1)
-    headline_s = (150.0 if ref else 75.0) + (args.steps + args.warmup + 1) * per_pass * 1.15
+    per_pass = (6.2 if ref else 4.5)                       # seconds, the slowest N measured (N=1)
+    headline_s = (100.0 if ref else 75.0) + (args.steps + args.warmup + 1) * per_pass * (1.10 if ref else 1.15)
     deadline = T_START + args.time_budget - headline_s
 
     def left() -> float:
