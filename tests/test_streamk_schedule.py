@@ -62,3 +62,41 @@ def test_every_k_block_once_and_reader_finds_the_writers():
         for t, w in writers.items():
             assert len(w) >= 2, "a partial tile has at least two contributors"
             assert [(c, s) for _, c, s in sorted(w)] == reader_view(t, G, tiles, num_kb, kg)
+
+
+def finish_kernel_writes(M, N, block_n, pair, raster_group):
+    """(row, column) pairs written by gemm_splitk_finish_kernel's grid, in the kernel's index arithmetic: grid
+    (blocks of 32 live rows, 128-column parts of a tile, tiles), block = 8 warps x 32 lanes; in the write phase warp w
+    handles rows 4w .. 4w + 3 of the block and lane l the four columns 4l .. 4l + 3 of the part."""
+    tile_rows = 256 if pair else 128
+    m_tiles, n_tiles = -(-M // tile_rows), -(-N // block_n)
+    live_rows = min(M, tile_rows)
+    out = []
+    for t in range(m_tiles * n_tiles):
+        per_group = raster_group * n_tiles
+        g = t // per_group
+        first = g * raster_group
+        gm = min(raster_group, m_tiles - first)
+        within = t - g * per_group
+        mt, nt = first + within % gm, within // gm
+        for bx in range(-(-live_rows // 32)):
+            row0 = mt * tile_rows + bx * 32
+            if row0 >= M:
+                continue
+            for by in range(-(-block_n // 128)):
+                c0 = nt * block_n + by * 128
+                for warp in range(8):
+                    for rr in range(4):
+                        r = row0 + warp * 4 + rr
+                        for lane in range(32):
+                            c = c0 + lane * 4
+                            if r < M and by * 128 + lane * 4 < block_n and c < N:
+                                out.extend((r, c + j) for j in range(4) if c + j < N)
+    return out
+
+
+def test_reduce_kernel_grid_covers_every_output_element_once():
+    for M, N, block_n, pair, grp in [(256, 4096, 256, 1, 8), (200, 1000, 256, 1, 8), (64, 6144, 256, 0, 16), (130, 3200, 128, 0, 16),
+                                     (300, 1100, 256, 1, 8), (7, 136, 128, 0, 16), (512, 640, 128, 1, 8)]:
+        w = finish_kernel_writes(M, N, block_n, pair, grp)
+        assert len(w) == len(set(w)) == M * N, (M, N, block_n, pair)
