@@ -1392,6 +1392,9 @@ extern "C" int forge_make_tmap_2d(CUtensorMap* tm, const void* base, uint64_t ro
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(r);
 }
 
+// Kernels of this library launched or captured so far (all source files share the counter of launch.cuh).
+extern "C" long long forge_launch_count() { return launch_counter().load(std::memory_order_relaxed); }
+
 extern "C" int forge_gemm_set_trace(unsigned long long* buf) {
   return cudaMemcpyToSymbol(g_gemm_trace, &buf, sizeof(buf)) == cudaSuccess ? 0 : -1;
 }

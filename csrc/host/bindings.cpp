@@ -17,6 +17,7 @@ int forge_gemm_bf16_sample(const void* x, int ldx, const void* w, int ldw, int M
                            const int* header, float* part_v, int* part_i, int* out_i, float* out_v, unsigned* status,
                            cudaStream_t stream);
 int forge_gemm_set_trace(unsigned long long* buf);
+long long forge_launch_count();
 int forge_gemm_bf16_qkv(const void* x, int ldx, const void* w, int ldw, int M, int K, const float* in_ssq, int in_parts, float in_eps,
                         const void* qw, const void* kw, float eps, const float* rope, int rope_rows, const int* positions,
                         const int* slots, void* q_out, void* k_cache, void* v_cache, int nq, int nkv, int block_size,
@@ -670,6 +671,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_fused", &gemm_fused);
   m.def("gemm_sample", &gemm_sample);
   m.def("gemm_set_trace", &gemm_set_trace);
+  m.def("launch_count", []() { return static_cast<int64_t>(forge_launch_count()); });
   m.def("quant_fp8", &quant_fp8);
   m.def("dequant_fp8_block", [](const Tensor& wq, const Tensor& scale, Tensor& out) {
     // e4m3 weights [N, K] with fp32 scales [ceil(N / 128), K / 128] -> bf16 [N, K]

@@ -12,6 +12,7 @@
 // the attribute off (kernels then see griddepcontrol.* as no-ops).
 #pragma once
 
+#include <atomic>
 #include <cuda_runtime.h>
 
 #include <cstdlib>
@@ -54,6 +55,13 @@ inline int device_sm_count() {
   return cached[dev];
 }
 
+// Kernels of this library launched (or captured into a CUDA graph) by this process so far: what the benchmark reports as
+// its launch count.  One counter for the whole shared object.
+inline std::atomic<long long>& launch_counter() {
+  static std::atomic<long long> n{0};
+  return n;
+}
+
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                  int cluster_y, Args... args) {
@@ -78,7 +86,9 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
   }
   cfg.attrs = attr;
   cfg.numAttrs = n;
-  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e == cudaSuccess) launch_counter().fetch_add(1, std::memory_order_relaxed);
+  return e;
 }
 
 // The same with clusters of `cluster_x` CTAs along x (CTA pairs of the cta_group::2 kernels: ranks 2i, 2i + 1 = blockIdx.x).
@@ -104,7 +114,9 @@ inline cudaError_t launch_kernel_cluster_x(void (*kernel)(KArgs...), dim3 grid, 
   }
   cfg.attrs = attr;
   cfg.numAttrs = n;
-  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+  if (e == cudaSuccess) launch_counter().fetch_add(1, std::memory_order_relaxed);
+  return e;
 }
 
 }  // namespace forge

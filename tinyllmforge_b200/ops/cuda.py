@@ -85,7 +85,7 @@ class CudaOps:
         self.tp = tp or TPGroup()
         self.max_model_len = config.max_model_len if config is not None else 4096
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
-        self.launches = 0                          # kernels of this library launched so far
+        self._launch_base = self.C.launch_count()
         self.fused = None                          # FusedTPComm once enable_fused_comm() ran
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         # "flat": all KV tiles of a decode step dealt out equally to two CTAs per SM; "chunked": one CTA per
@@ -105,6 +105,16 @@ class CudaOps:
         self.fp8_expand_max_weights = int(os.environ.get("FORGE_FP8_EXPAND_MAX_WEIGHTS", "0"))
         self._fp8_scratch = None                   # bf16 expansion of one fp8 weight (see _expand_fp8)
         self._fp8_retired = []
+
+    @property
+    def launches(self) -> int:
+        """Kernels of this library launched (or captured into a CUDA graph) since the counter was last set; counted where
+        they are launched, so GEMMs that run as two kernels (K split + reduce) count as two."""
+        return self.C.launch_count() - self._launch_base
+
+    @launches.setter
+    def launches(self, value: int) -> None:
+        self._launch_base = self.C.launch_count() - int(value)
 
     # ------------------------------------------------------------------ status word
     def check_status(self) -> None:
@@ -130,7 +140,6 @@ class CudaOps:
             w, force_deep = self._expand_fp8(w), force_deep | W_DYNAMIC
         out = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
         self.C.gemm(x, w, out, 0, force_mode, force_splits | (force_block_c << 8) | (force_deep << 16), self.status)
-        self.launches += 1
         return out
 
     def linear_silu_mul(self, x: torch.Tensor, w_gate_up: torch.Tensor, force_mode: int = 0, force_splits: int = 0,
@@ -141,7 +150,6 @@ class CudaOps:
             w_gate_up, force_deep = self._expand_fp8(w_gate_up), force_deep | W_DYNAMIC
         out = torch.empty(x.shape[0], w_gate_up.shape[0] // 2, dtype=x.dtype, device=x.device)
         self.C.gemm(x, w_gate_up, out, 1, force_mode, force_splits | (force_block_c << 8) | (force_deep << 16), self.status)
-        self.launches += 1
         return out
 
     # --- GEMMs with the neighbouring RMSNorm / residual add fused in (single GPU, bf16 weights; see models/qwen3.py)
@@ -153,7 +161,6 @@ class CudaOps:
         out = torch.empty(T, H, dtype=weight.dtype, device=weight.device)
         ssq = torch.empty(2, T, (H + 127) // 128, dtype=torch.float32, device=weight.device)
         self.C.embedding(ids, weight, out, vocab_start, ssq[0])
-        self.launches += 1
         return out, ssq[0], ssq[1]
 
     def linear_scaled(self, x: torch.Tensor, w: torch.Tensor, ssq_row: torch.Tensor, eps: float, silu_mul: bool = False,
@@ -164,7 +171,6 @@ class CudaOps:
         n_out = w.shape[0] // 2 if silu_mul else w.shape[0]
         out = torch.empty(x.shape[0], n_out, dtype=x.dtype, device=x.device)
         self.C.gemm_fused(x, w, out, 1 if silu_mul else 0, force_mode, tune, ssq_row, eps, False, None, self.status)
-        self.launches += 1
         return out
 
     def linear_residual(self, x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor, ssq_out: torch.Tensor,
@@ -172,7 +178,6 @@ class CudaOps:
         """residual += x @ w.T in place (rounded like a bf16 GEMM output followed by a bf16 add); ssq_out (fp32
         [tokens, ceil(H / 128)]) receives the sums of squares of the new residual rows, one per 128 features."""
         self.C.gemm_fused(x, w, residual, 0, force_mode, tune, None, 0.0, True, ssq_out, self.status)
-        self.launches += 1
 
     def _expands_fp8(self, w: "Fp8BlockWeight", rows: int) -> bool:
         """Many rows: the GEMM is bound by the tensor cores, the expansion costs a few per cent.  Few rows on a small matrix
@@ -192,7 +197,6 @@ class CudaOps:
             self._fp8_scratch = torch.empty(N * K, dtype=torch.bfloat16, device=self.device)
         out = self._fp8_scratch[:N * K].view(N, K)
         self.C.dequant_fp8_block(w.q.view(torch.uint8), w.scale, out)
-        self.launches += 1
         return out
 
     def linear_fp8(self, x: torch.Tensor, w: "Fp8BlockWeight") -> torch.Tensor:
@@ -207,20 +211,17 @@ class CudaOps:
         splits = self.C.gemm_fp8_splits(M, N, K)         # few tokens: K is split over CTAs, partials added by a second kernel
         partial = torch.empty(splits * M * N, dtype=torch.float32, device=x.device) if splits > 1 else None
         self.C.gemm_fp8_block(xq, xs, w.q.view(torch.uint8), w.scale, out, partial, self.status)
-        self.launches += 3 if splits > 1 else 2
         return out
 
     # ------------------------------------------------------------------ elementwise
     def rms_norm(self, x, weight, eps):
         y = torch.empty_like(x)
         self.C.rms_norm(x, None, weight, y, eps)
-        self.launches += 1
         return y
 
     def add_rms_norm(self, x, residual, weight, eps):
         """(normed, new_residual).  ``residual`` is updated in place and returned."""
         y = torch.empty_like(x)
-        self.launches += 1
         if residual is None:
             self.C.rms_norm(x, None, weight, y, eps)
             return y, x
@@ -230,19 +231,16 @@ class CudaOps:
     def silu_mul(self, x):
         out = torch.empty(x.shape[:-1] + (x.shape[-1] // 2,), dtype=x.dtype, device=x.device)
         self.C.silu_mul(x, out)
-        self.launches += 1
         return out
 
     def embedding(self, ids, weight, vocab_start=0):
         out = torch.empty(ids.shape[0], weight.shape[1], dtype=weight.dtype, device=weight.device)
         self.C.embedding(ids, weight, out, vocab_start, None)
-        self.launches += 1
         return out
 
     def select_rows(self, x, index):
         out = torch.empty(index.shape[0], x.shape[1], dtype=x.dtype, device=x.device)
         self.C.gather_rows(index, x, out)
-        self.launches += 1
         return out
 
     def qk_norm_rope_store(self, qkv, q_weight, k_weight, eps, table, positions, slot_mapping, k_cache, v_cache,
@@ -251,7 +249,6 @@ class CudaOps:
         q = torch.empty(T, num_heads, head_dim, dtype=qkv.dtype, device=qkv.device)
         self.C.qk_norm_rope_store(qkv, q_weight, k_weight, eps, table, positions, slot_mapping, q, k_cache, v_cache,
                                   num_heads, num_kv_heads, do_rope, self.status)
-        self.launches += 1
         return q
 
     def qkv_rope_store_in_gemm(self, rows: int, head_dim: int, weight) -> bool:
@@ -268,7 +265,6 @@ class CudaOps:
         q = torch.empty(T, num_heads, 128, dtype=x.dtype, device=x.device)
         self.C.gemm_qkv_rope_store(x, w, ssq_row, in_eps, q_weight, k_weight, eps, table, positions, slot_mapping, q, k_cache, v_cache,
                                    num_heads, num_kv_heads, do_rope, self.status)
-        self.launches += 1
         return q
 
     # ------------------------------------------------------------------ attention
@@ -278,7 +274,6 @@ class CudaOps:
         if batch.is_prefill:
             self.C.prefill_attention(q, k_cache, v_cache, batch.cu_seqlens_q, batch.context_lens, batch.block_tables, out,
                                      batch.num_seqs, batch.max_seqlen_q, scale, self.status)
-            self.launches += 1
             return out
         B = batch.padded_seqs
         if self.decode_attention_mode == "flat" or (self.decode_attention_mode == "auto" and 48 <= B <= 512):
@@ -286,7 +281,6 @@ class CudaOps:
             ctas = self._flat_ctas(H, k_cache, False)
             self.C.decode_attention_flat(q, k_cache, v_cache, batch.block_tables, batch.context_lens, out, self._flat_scratch,
                                          ctas, scale, self.status)
-            self.launches += 2
             return out
         # graph-safe sizing: the longest context the block table can describe
         max_len = batch.table_width * k_cache.shape[2]
@@ -297,7 +291,6 @@ class CudaOps:
             part_ml = torch.empty(B * H * max_chunks * 2, dtype=torch.float32, device=q.device)
         self.C.decode_attention(q, k_cache, v_cache, batch.block_tables, batch.context_lens, out, part_o, part_ml,
                                 chunk, max_chunks, scale, self.status)
-        self.launches += 2 if max_chunks > 1 else 1
         return out
 
     def _flat_ctas(self, num_heads, k_cache, from_raw_qkv: bool) -> int:
@@ -320,7 +313,6 @@ class CudaOps:
             ctas = self._flat_ctas(num_heads, k_cache, True)          # may grow the scratch: before it is passed on
             self.C.decode_attention_qkv(qkv, q_weight, k_weight, eps, rope, k_cache, v_cache, batch.block_tables, batch.context_lens,
                                         out, self._flat_scratch, ctas, None, None, 0, 0, num_heads, scale, self.status)
-            self.launches += 2
             return out
         max_len = batch.table_width * k_cache.shape[2]
         chunk, max_chunks = decode_chunking(B, k_cache.shape[1], k_cache.shape[2], max_len)
@@ -330,7 +322,6 @@ class CudaOps:
             part_ml = torch.empty(B * num_heads * max_chunks * 2, dtype=torch.float32, device=qkv.device)
         self.C.decode_attention_qkv(qkv, q_weight, k_weight, eps, rope, k_cache, v_cache, batch.block_tables, batch.context_lens,
                                     out, None, 0, part_o, part_ml, chunk, max_chunks, num_heads, scale, self.status)
-        self.launches += 2 if max_chunks > 1 else 1
         return out
 
     # ------------------------------------------------------------------ tensor-parallel exchange
@@ -350,7 +341,6 @@ class CudaOps:
         normalised rows; in the two-shot form they live in the broadcast buffer and ``residual_out`` holds only this
         rank's rows (rows r, r + tp, ...), which is all the next exchange of the same step reads."""
         f, tp = self.fused, self.tp
-        self.launches += 1
         if norm_weight is not None and f.two_shot(rows, H):
             from ..parallel.symm import SITE_GATHER
             ag = f.sites[SITE_GATHER]
@@ -378,7 +368,6 @@ class CudaOps:
         x = x.contiguous()
         out = torch.empty_like(x)
         self.C.tp_rows_publish(x, st.local_buf, tp.rank, st.signal_ptrs, st.arrive, st.epoch)
-        self.launches += 1
         self._reduce_norm(st, x.numel() // H, H, None, out, None, 0.0)
         return out
 
@@ -404,7 +393,6 @@ class CudaOps:
         y = torch.empty_like(residual)
         self.C.tp_reduce_rms_norm(tp.size, tp.rank, [], 0, st.local_buf, st.local_signal, st.epoch, f.timeout_ns, f.local_only,
                                   None, residual, norm_weight, y, eps, self.status)
-        self.launches += 2
         return y, residual
 
     def row_linear_add_rms_norm(self, x, layer, residual, norm_weight, eps, site):
@@ -436,7 +424,6 @@ class CudaOps:
             y = torch.empty(M, H, dtype=x.dtype, device=x.device)
             self.C.tp_tagged_reduce_norm(tp.rank, st.ll_local, f.tagged_rows_per_rank, st.epoch, ag.ll_ptrs, ag.arrive, ag.epoch,
                                          f.timeout_ns, f.local_only, residual, residual, norm_weight, y, eps, self.status)
-            self.launches += 2
             return y, residual
         if fp8 and not expand:
             # the block-scaled GEMM has no signalling epilogue: publish its output with a copy kernel
@@ -445,7 +432,6 @@ class CudaOps:
             self.C.gemm_tp(x, self._expand_fp8(layer.weight), st.local_buf, W_DYNAMIC << 16, tp.rank, st.signal_ptrs, st.arrive, st.epoch, self.status)
         else:
             self.C.gemm_tp(x, layer.weight, st.local_buf, 0, tp.rank, st.signal_ptrs, st.arrive, st.epoch, self.status)
-        self.launches += 1
         return self._reduce_norm(st, M, H, residual, residual, norm_weight, eps), residual
 
     # ------------------------------------------------------------------ sampling
@@ -458,7 +444,6 @@ class CudaOps:
         ids = torch.empty(rows, dtype=torch.int32, device=logits.device)
         best = torch.empty(rows, dtype=torch.float32, device=logits.device)
         self.C.sample(logits, vocab_start, temperatures, header, part_v, part_i, ids, best)
-        self.launches += 2
         return ids, best
 
     def can_sample_in_lm_head(self, rows: int, weight) -> bool:
@@ -477,7 +462,6 @@ class CudaOps:
         ids = torch.empty(rows, dtype=torch.int32, device=hidden.device)
         best = torch.empty(rows, dtype=torch.float32, device=hidden.device)
         self.C.gemm_sample(hidden, weight, vocab_start, temperatures, header, part_v, part_i, ids, best, self.status)
-        self.launches += 2
         return ids, best
 
     def sample(self, logits, batch, vocab_start, tp):
@@ -494,13 +478,11 @@ class CudaOps:
             out = torch.empty_like(ids)
             self.C.tp_sample_pairs(best, ids, tp.rank, st.slot_ptrs, st.signal_ptrs, st.arrive, st.epoch, st.local_buf,
                                    st.slot_stride, st.local_signal, self.fused.timeout_ns, self.fused.local_only, out, self.status)
-            self.launches += 2
             return out
         all_best = tp.all_gather_stack(best)
         all_ids = tp.all_gather_stack(ids)
         out = torch.empty_like(ids)
         self.C.sample_merge_ranks(all_best, all_ids, out)
-        self.launches += 1
         return out
 
     def close(self):
